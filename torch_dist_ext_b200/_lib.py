@@ -1,0 +1,53 @@
+"""Locates, (re)builds if necessary, and loads the native extension ``_C.so``.
+
+The reference loads ``lib<package>.so`` from the package's parent directory and prints the path
+on import (torch_dist_ext/__init__.py:8-12). Here the library sits inside the package, the
+import is silent, and a missing or unloadable library is an error - there is no Python
+fallback for the kernels.
+"""
+from __future__ import annotations
+
+import logging
+import os
+from pathlib import Path
+
+import torch
+
+log = logging.getLogger("torch_dist_ext_b200")
+
+_LIB = Path(__file__).resolve().parent / "_C.so"
+_loaded = False
+
+
+def lib_path() -> Path:
+    return _LIB
+
+
+def load() -> None:
+    """Load the extension once. Builds it first when it does not exist and nvcc is present."""
+    global _loaded
+    if _loaded:
+        return
+    if not _LIB.exists() or os.environ.get("TDX_REBUILD") == "1":
+        from . import _build
+
+        log.info("building native extension (first use)")
+        _build.build()
+    try:
+        torch.ops.load_library(str(_LIB))
+    except OSError as e:  # pragma: no cover - depends on the machine
+        raise ImportError(
+            f"torch_dist_ext_b200: could not load {_LIB}: {e}. Rebuild with "
+            f"`python -m torch_dist_ext_b200._build --force`.") from e
+    _loaded = True
+    log.debug("loaded %s", _LIB)
+
+
+def ops():
+    load()
+    return torch.ops.torch_dist_ext
+
+
+def classes():
+    load()
+    return torch.classes.torch_dist_ext

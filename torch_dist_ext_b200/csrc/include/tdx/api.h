@@ -1,0 +1,135 @@
+// Host-side C++ interface of the native runtime: launch planning for the fused all-reduce
+// kernels and the symmetric-workspace manager. Nothing here depends on PyTorch; the torch
+// bindings (register.cpp) and the standalone C++ test harness both sit on top of it.
+//
+// Reference counterparts: allreduce_fusion_kernel_launcher / allreduce_rms_fusion_impl
+// (src/common/all_reduce_fusion_impl.h:476-535) and class CommWorkspace
+// (src/ops/all_reduce_fusion.h:10-40, src/ops/all_reduce_fusion.cpp:63-174).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <string>
+#include <vector>
+#include "tdx/comm.h"
+
+namespace tdx {
+
+struct LaunchPlan {
+  int algo;      // Algo actually used
+  int n_tmpl;    // rank-count template argument (0 = runtime loop)
+  int vpt;       // 16-byte vectors per thread
+  int threads;
+  int grid;      // blocks per rank
+  int emu_ranks; // 0 for a real launch
+};
+
+// Crossover sizes (bytes of one rank's message) used by kAlgoAuto, per rank count.
+struct Policy {
+  uint64_t oneshot_max_bytes[kMaxRanks + 1];
+  uint64_t lamport_max_bytes[kMaxRanks + 1];   // above: flag-barrier two-shot
+  int prefer_nvls;                             // use NVLS paths when a multicast mapping exists
+  uint64_t nvls_min_bytes;
+};
+Policy& policy();
+
+// Validates shapes, alignment and capacity, resolves kAlgoAuto and sizes the launch.
+// Returns an empty string on success, else the reason.
+std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan);
+
+// Launches one rank's kernel on `stream` (real multi-GPU / multi-process use).
+std::string launch_allreduce(const ArParams& p, cudaStream_t stream, LaunchPlan* used = nullptr);
+
+// Launches ALL ranks as one cooperative kernel on the current device. `host_ranks` holds the
+// per-rank parameters, `dev_ranks` is a device copy of the same array.
+std::string launch_allreduce_emulated(const ArParams* host_ranks, const ArParams* dev_ranks,
+                                      int nranks, cudaStream_t stream, LaunchPlan* used = nullptr);
+
+// Per-dtype back ends (one translation unit per dtype, so that they compile in parallel).
+cudaError_t launch_ar_f32(const LaunchPlan&, int out_mode, const ArParams&, const ArParams* dev_ranks, cudaStream_t);
+cudaError_t launch_ar_f16(const LaunchPlan&, int out_mode, const ArParams&, const ArParams* dev_ranks, cudaStream_t);
+cudaError_t launch_ar_bf16(const LaunchPlan&, int out_mode, const ArParams&, const ArParams* dev_ranks, cudaStream_t);
+cudaError_t launch_ar_f32_emu(const LaunchPlan&, int out_mode, const ArParams&, const ArParams* dev_ranks, cudaStream_t);
+cudaError_t launch_ar_f16_emu(const LaunchPlan&, int out_mode, const ArParams&, const ArParams* dev_ranks, cudaStream_t);
+cudaError_t launch_ar_bf16_emu(const LaunchPlan&, int out_mode, const ArParams&, const ArParams* dev_ranks, cudaStream_t);
+// blocks of `plan.threads` threads that one SM holds for the kernel the plan selects
+int occupancy_ar_f32(const LaunchPlan&, int out_mode);
+int occupancy_ar_f16(const LaunchPlan&, int out_mode);
+int occupancy_ar_bf16(const LaunchPlan&, int out_mode);
+int occupancy_ar_f32_emu(const LaunchPlan&, int out_mode);
+int occupancy_ar_f16_emu(const LaunchPlan&, int out_mode);
+int occupancy_ar_bf16_emu(const LaunchPlan&, int out_mode);
+
+// ---- symmetric workspace -----------------------------------------------------------------
+
+constexpr int kHandleBytes = 128;  // opaque blob exchanged between ranks
+
+struct WorkspaceStats {
+  uint64_t total_bytes;
+  uint64_t lamport_bytes;
+  uint64_t stage_bytes;
+  uint32_t error_count;
+  uint32_t status[8];
+  uint32_t lamport_epoch;
+  uint32_t barrier_epoch;
+  int has_multicast;
+};
+
+class Workspace {
+ public:
+  // `device` < 0 keeps the current device. `max_message_bytes` bounds one rank's message on
+  // the flag-barrier path; `lamport_bytes` is the capacity of each of the three Lamport buffers
+  // (0 = default).
+  Workspace(int rank, int world_size, int nblocks, uint64_t max_message_bytes,
+            uint64_t lamport_bytes = 0, int device = -1);
+  ~Workspace();
+  Workspace(const Workspace&) = delete;
+  Workspace& operator=(const Workspace&) = delete;
+
+  // Cross-process registration: export this rank's handle, then open everyone's.
+  void export_handle(uint8_t out[kHandleBytes]) const;
+  void open_handles(const std::vector<const uint8_t*>& handles);
+  // Single-process registration (one process drives several GPUs, or emulated ranks on one
+  // GPU): peers are given directly. Enables peer access where the devices differ.
+  static void connect_local(const std::vector<Workspace*>& all);
+
+  // Device-resident table; valid after registration. Never re-uploaded.
+  const CommTable* device_table() const { return table_dev_; }
+  const CommTable& host_table() const { return table_host_; }
+  // Fills the communication part of a parameter block.
+  void fill_params(ArParams* p) const;
+
+  // Re-initialise flags, epochs, sentinels and the status record. Collective: all ranks must
+  // be idle and must call it between two host barriers.
+  void reset();
+  WorkspaceStats stats() const;       // synchronises the device
+  uint32_t errors_seen() const;       // non-blocking: reads the host-mapped status mirror
+  void set_timeout_ns(uint64_t t) { timeout_ns_ = t; }
+  uint64_t timeout_ns() const { return timeout_ns_; }
+  int rank() const { return rank_; }
+  int world_size() const { return world_; }
+  int device() const { return device_; }
+  bool registered() const { return registered_; }
+
+  // Looks up the workspace that owns a device table pointer (what the op receives).
+  static Workspace* from_table(const void* table_dev);
+
+ private:
+  void init_device_state();
+  int rank_, world_, device_, nblocks_;
+  Layout layout_;
+  void* base_ = nullptr;
+  void* peer_[kMaxRanks] = {};
+  bool opened_[kMaxRanks] = {};
+  CommTable table_host_{};
+  CommTable* table_dev_ = nullptr;
+  uint32_t* host_status_ = nullptr;   // pinned + mapped
+  uint32_t* host_status_dev_ = nullptr;
+  uint64_t timeout_ns_;
+  bool registered_ = false;
+};
+
+// Every (device, peer) pair of this process: check and enable peer access. Returns the number
+// of visible devices. Used by single-process multi-GPU harnesses.
+int enable_all_peer_access();
+
+}  // namespace tdx

@@ -1,0 +1,32 @@
+// Declarations shared by the PyTorch binding translation units.
+#pragma once
+#include <torch/custom_class.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+#include <memory>
+#include "tdx/api.h"
+
+namespace tdx_torch {
+
+// torch.classes.torch_dist_ext.CommWorkspace — same constructor and the same three methods as
+// the reference's class (src/ops/all_reduce_fusion.h:10-40), plus reset / timeout / status.
+class CommWorkspace : public torch::CustomClassHolder {
+ public:
+  CommWorkspace(int64_t rank, int64_t world_size, int64_t nblocks, int64_t size_in_bytes);
+  at::Tensor get_handle();
+  void open_handles(std::vector<at::Tensor> handles);
+  at::Tensor get_workspace(const at::Tensor& ref);
+  void reset();
+  void set_timeout_ms(int64_t ms);
+  int64_t errors_seen();
+  std::vector<int64_t> stats();
+  tdx::Workspace* impl() { return impl_.get(); }
+
+ private:
+  std::unique_ptr<tdx::Workspace> impl_;
+};
+
+// Registers the standalone ops, GEMMs and model kernels (defined in ops_register.cpp).
+void register_extra_ops(torch::Library& m);
+
+}  // namespace tdx_torch

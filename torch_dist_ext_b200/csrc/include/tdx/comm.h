@@ -1,0 +1,127 @@
+// Layout of the per-rank symmetric communication buffer, the device-resident pointer
+// table, kernel parameter blocks and status codes. Shared by host and device code.
+//
+// Counterpart of the reference's workspace layout and pointer table
+// (src/ops/all_reduce_fusion.cpp:63-96, :135-141, :159-169) and of its kernel argument
+// struct (src/common/all_reduce_fusion_impl.h:300-314). Differences by design:
+//  * one contiguous allocation per rank with fixed offsets, so a kernel needs only the
+//    peers' base pointers (passed by value, no dependent pointer-table load on the hot path);
+//  * phase state (epochs, dirty extents) lives in a control block at the start of the
+//    allocation and is advanced by the last block of every launch, so CUDA-graph replays
+//    need no host-side state;
+//  * every size is 64-bit and checked against the capacity before a launch.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace tdx {
+
+constexpr int kMaxRanks = 8;            // one NVSwitch domain (HGX B200 board)
+constexpr int kMaxBarrierBlocks = 1024; // barrier flag rows per rank
+constexpr uint32_t kSentinel = 0x80000000u;  // fp32 -0.0 / (bf16 -0.0, +0.0) pair
+
+// ---- region offsets inside one rank's symmetric allocation --------------------
+constexpr size_t kControlBytes = 4096;
+constexpr size_t kFlagBytes = size_t(kMaxBarrierBlocks) * kMaxRanks * sizeof(uint32_t);
+
+struct Layout {
+  uint64_t off_control;   // Control block (touched by the owning rank only)
+  uint64_t off_flags;     // uint32 flags[kMaxBarrierBlocks][kMaxRanks], written by peers
+  uint64_t off_lamport;   // 3 x lamport_bytes, sentinel-initialised
+  uint64_t lamport_bytes; // capacity of ONE of the three Lamport buffers
+  uint64_t off_stage;     // flag-synchronised staging (two-shot / NVLS paths)
+  uint64_t stage_bytes;
+  uint64_t total_bytes;
+};
+
+inline Layout make_layout(uint64_t max_message_bytes, uint64_t lamport_bytes) {
+  auto align_up = [](uint64_t v, uint64_t a) { return (v + a - 1) / a * a; };
+  Layout l{};
+  l.off_control = 0;
+  l.off_flags = kControlBytes;
+  l.off_lamport = align_up(l.off_flags + kFlagBytes, 1 << 16);
+  l.lamport_bytes = align_up(lamport_bytes, 1 << 16);
+  l.off_stage = l.off_lamport + 3 * l.lamport_bytes;
+  // gather area + result area + per-row trailers and row padding
+  l.stage_bytes = align_up(2 * max_message_bytes + max_message_bytes / 8 + (1 << 20), 1 << 16);
+  l.total_bytes = align_up(l.off_stage + l.stage_bytes, 1 << 21);
+  return l;
+}
+
+// Per-rank phase state. Only the owning rank reads or writes it.
+struct Control {
+  uint32_t lamport_epoch;      // Lamport calls completed; buffer in use = epoch % 3
+  uint32_t barrier_epoch;      // flag barriers completed
+  uint32_t arrive;             // blocks of the running launch that have finished
+  uint32_t error_count;        // waits that ran out since the last reset
+  uint64_t lamport_dirty[3];   // bytes (from buffer start) that hold non-sentinel data
+  uint32_t status[8];          // first error: {code, rank, peer, phase, block, row, 0, 0}
+};
+static_assert(sizeof(Control) <= kControlBytes, "control block overflow");
+
+// What the uint8 tensor returned by get_workspace() holds, in device memory.
+struct CommTable {
+  uint64_t magic;
+  int32_t rank;
+  int32_t nranks;
+  void* peer[kMaxRanks];  // base of every rank's symmetric allocation (own entry = local)
+  void* mc_base;          // NVSwitch multicast mapping of the same allocation, or null
+  Layout layout;
+  uint64_t reserved[8];
+};
+constexpr uint64_t kTableMagic = 0x7464785f62323030ull;  // "tdx_b200"
+
+// ---- status codes ------------------------------------------------------------
+enum Status : uint32_t {
+  kOk = 0,
+  kTimeoutLamportGather = 1,   // one-shot / two-shot: partial sums from a peer never arrived
+  kTimeoutLamportResult = 2,   // two-shot: reduced row from its owner never arrived
+  kTimeoutBarrier = 3,         // flag barrier: a peer never arrived
+  kTimeoutNvls = 4,
+  kTimeoutGemmPipeline = 5,    // an mbarrier of a GEMM pipeline never completed
+  kTimeoutTileFlag = 6,        // all-gather->GEMM: a peer tile never became ready
+};
+
+// ---- op description ------------------------------------------------------------
+enum DType : int32_t { kF32 = 0, kF16 = 1, kBF16 = 2 };
+enum OutMode : int32_t {
+  kOutSame = 0,        // norm_out has the input dtype (what the reference produces)
+  kOutFp8Token = 1,    // norm_out e4m3, one fp32 scale per token   [tokens, 1]
+  kOutFp8Block128 = 2, // norm_out e4m3, one fp32 scale per 128 cols [tokens, hidden/128]
+};
+enum Algo : int32_t {
+  kAlgoAuto = 0,
+  kAlgoLocal = 1,            // nranks == 1: residual + RMSNorm (+quant) only
+  kAlgoOneShotLamport = 2,   // push everything to everyone, sentinel polling, no barrier
+  kAlgoTwoShotLamport = 3,   // push-scatter -> owner reduce -> push-gather, sentinel polling
+  kAlgoTwoShotBarrier = 4,   // same data flow, flag barriers, any size up to the capacity
+  kAlgoNvlsOneShot = 5,      // multimem.ld_reduce of every row by every rank
+  kAlgoNvlsTwoShot = 6,      // multimem.ld_reduce own rows -> epilogue -> multimem.st
+};
+
+struct ArParams {
+  void* peer[kMaxRanks];
+  void* mc_base;
+  Layout layout;
+  int32_t rank;
+  int32_t nranks;
+  int32_t tokens;
+  int32_t hidden;
+  const void* in;           // [tokens, hidden] this rank's partial sums
+  const void* residual_in;  // [tokens, hidden] or null (treated as zeros)
+  const void* gamma;        // [hidden]
+  void* residual_out;       // [tokens, hidden] or null (not written)
+  void* norm_out;           // [tokens, hidden] input dtype or e4m3
+  float* scale_out;         // fp8 modes only
+  float eps;
+  int32_t dtype;
+  int32_t out_mode;
+  int32_t algo;
+  // Reduce-scatter variant: only the rows this rank owns (row % nranks == rank) are
+  // produced; outputs are then [ceil(tokens/nranks), hidden] and nothing is gathered.
+  int32_t scatter_only;
+  uint64_t timeout_ns;      // budget of every device-side wait
+  uint32_t* host_status;    // pinned, host-mapped mirror of Control::status (or null)
+};
+
+}  // namespace tdx

@@ -1,0 +1,150 @@
+// Warp/block reductions, bounded waits, error reporting, the cross-GPU flag barrier and
+// the end-of-launch phase update.
+//
+// Counterparts in the reference: block_utils::warp_reduce / block_reduce
+// (src/common/all_reduce_fusion_impl.h:32-57), comm::SyncComm (:63-93), comm::Barrier
+// (:95-164) and comm::LamportComm (:166-204). Differences by design:
+//  * every wait has a time budget; when it runs out the block records
+//    {code, rank, peer, phase, block, row} once, stops waiting and runs to a normal exit;
+//  * barrier flags carry a monotonically increasing epoch compared with a signed
+//    difference, so flag rows that an earlier, smaller launch never touched need no
+//    back-filling;
+//  * phase state is advanced by whichever block finishes LAST (arrival counter), not by
+//    block 0 spinning until every block has started.
+#pragma once
+#include "tdx/comm.h"
+#include "tdx/ptx.cuh"
+
+namespace tdx {
+
+// ---- reductions ------------------------------------------------------------------
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Reduction over aligned groups of `kLanes` lanes (power of two <= 32).
+template <int kLanes>
+__device__ __forceinline__ float group_max(float v) {
+#pragma unroll
+  for (int o = kLanes / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide all-reduce; every thread gets the result. `slot` is 32 floats of shared
+// memory; callers alternate between two slots so that no trailing barrier is needed.
+template <bool kMax>
+__device__ __forceinline__ float block_allreduce(float v, float* slot) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = kMax ? warp_max(v) : warp_sum(v);
+  if (nwarps == 1) return v;
+  if (lane == 0) slot[warp] = v;
+  __syncthreads();
+  float w = (lane < nwarps) ? slot[lane] : (kMax ? 0.f : 0.f);
+  return kMax ? warp_max(w) : warp_sum(w);
+}
+
+// ---- bounded waiting ---------------------------------------------------------------
+
+struct Waiter {
+  uint64_t budget_ns;
+  uint64_t deadline;   // 0 until the slow path is first entered
+  uint32_t spins;
+  bool failed;         // once a wait of this thread ran out, later waits give up at once
+
+  __device__ __forceinline__ explicit Waiter(uint64_t budget)
+      : budget_ns(budget), deadline(0), spins(0), failed(false) {}
+
+  // Call once per unsuccessful poll. Returns false when the caller must stop waiting.
+  __device__ __forceinline__ bool keep_waiting() {
+    if (failed) return false;
+    if ((++spins & 0xffu) != 0) return true;
+    const uint64_t now = ptx::globaltimer_ns();
+    if (deadline == 0) {
+      deadline = now + budget_ns;
+      return true;
+    }
+    if (now > deadline) {
+      failed = true;
+      return false;
+    }
+    return true;
+  }
+  __device__ __forceinline__ void begin() {
+    deadline = 0;
+    spins = 0;
+  }
+};
+
+__device__ __forceinline__ void report_error(Control* ctl, uint32_t* host_status, uint32_t code,
+                                             int rank, int peer, int phase, int row) {
+  const uint32_t prior = atomicAdd(&ctl->error_count, 1u);
+  if (prior == 0) {
+    const uint32_t rec[8] = {code, (uint32_t)rank, (uint32_t)peer, (uint32_t)phase,
+                             blockIdx.x, (uint32_t)row, 0u, 0u};
+#pragma unroll
+    for (int i = 7; i >= 0; --i) {
+      ctl->status[i] = rec[i];
+      if (host_status) reinterpret_cast<volatile uint32_t*>(host_status)[i] = rec[i];
+    }
+    __threadfence_system();
+  }
+}
+
+// ---- cross-GPU flag barrier ---------------------------------------------------------
+// flags[block][src_rank] on every rank. Thread t < nranks of block b publishes `target`
+// into rank t's flags[b][my_rank], then waits for its own flags[b][t] to reach `target`.
+// Block b only ever synchronises with block b of the peers.
+
+__device__ __forceinline__ uint32_t* flag_ptr(void* base, const Layout& l, int block, int src) {
+  return reinterpret_cast<uint32_t*>(static_cast<char*>(base) + l.off_flags) +
+         (size_t)block * kMaxRanks + src;
+}
+
+__device__ __forceinline__ void flag_barrier(const ArParams& p, Control* ctl, uint32_t target,
+                                             Waiter& w, int phase) {
+  __syncthreads();
+  if ((int)threadIdx.x < p.nranks) {
+    const int peer = threadIdx.x;
+    ptx::st_release_sys(flag_ptr(p.peer[peer], p.layout, blockIdx.x, p.rank), target);
+    const uint32_t* mine = flag_ptr(p.peer[p.rank], p.layout, blockIdx.x, peer);
+    w.begin();
+    while ((int32_t)(ptx::ld_acquire_sys(mine) - target) < 0) {
+      if (!w.keep_waiting()) {
+        report_error(ctl, p.host_status, kTimeoutBarrier, p.rank, peer, phase, -1);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// ---- end of launch -------------------------------------------------------------------
+// The last block to finish advances the epochs. Launches on one stream are ordered, so the
+// next launch reads the new values.
+__device__ __forceinline__ void finish_launch(Control* ctl, bool used_lamport, uint32_t epoch,
+                                              uint64_t dirty_bytes, uint32_t barriers_used) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(&ctl->arrive, 1u);
+    if (done == gridDim.x - 1) {
+      if (used_lamport) {
+        ctl->lamport_dirty[epoch % 3u] = dirty_bytes;
+        ctl->lamport_epoch = epoch + 1u;
+      }
+      if (barriers_used) ctl->barrier_epoch += barriers_used;
+      ctl->arrive = 0;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace tdx

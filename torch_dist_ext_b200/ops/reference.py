@@ -1,0 +1,100 @@
+"""Pure-PyTorch statement of the fused op: the oracle for every kernel test and the CPU/gloo
+path of the library.
+
+Math (identical to the reference's kernels, src/common/all_reduce_fusion_impl.h:280-298,
+:316-340, :381-393)::
+
+    s            = T( sum_r float(in_r) )            fp32, rank order, one rounding
+    residual_out = T( float(s) + float(residual_in) )
+    rstd         = rsqrt( mean_h float(residual_out)^2 + eps )
+    y            = float(residual_out) * rstd * float(gamma)
+    norm_out     = T(y)                               | e4m3(y / scale)
+
+fp8 (NVIDIA e4m3fn, max 448, saturating): per-token ``scale = max(amax_h |y|, 1e-10) / 448``
+with scales of shape ``[tokens, 1]``; 1x128 block scaling uses one such scale per 128
+consecutive columns, shape ``[tokens, hidden // 128]``. ``q = e4m3(y * (1 / scale))``.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+FP8_MAX = 448.0
+AMAX_FLOOR = 1e-10
+OUT_SAME, OUT_FP8_TOKEN, OUT_FP8_BLOCK128 = 0, 1, 2
+
+
+def _to_fp8(x: torch.Tensor) -> torch.Tensor:
+    return x.clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+
+
+def quantize_fp8(y: torch.Tensor, out_mode: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Quantise fp32 ``y`` [tokens, hidden] -> (e4m3 tensor, fp32 scales)."""
+    y = y.float()
+    tokens, hidden = y.shape
+    if out_mode == OUT_FP8_TOKEN:
+        amax = y.abs().amax(dim=-1, keepdim=True).clamp_min(AMAX_FLOOR)
+        scale = amax / FP8_MAX
+        return _to_fp8(y * (1.0 / scale)), scale
+    if out_mode == OUT_FP8_BLOCK128:
+        assert hidden % 128 == 0, "1x128 block scaling needs hidden % 128 == 0"
+        yb = y.view(tokens, hidden // 128, 128)
+        amax = yb.abs().amax(dim=-1, keepdim=True).clamp_min(AMAX_FLOOR)
+        scale = amax / FP8_MAX
+        return _to_fp8(yb * (1.0 / scale)).view(tokens, hidden), scale.squeeze(-1)
+    raise ValueError(f"not an fp8 output mode: {out_mode}")
+
+
+def dequantize_fp8(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    tokens, hidden = q.shape
+    if scale.numel() == tokens:
+        return q.float() * scale.view(tokens, 1)
+    return (q.float().view(tokens, -1, 128) * scale.view(tokens, -1, 1)).view(tokens, hidden)
+
+
+def residual_rmsnorm_reference(summed: torch.Tensor, residual: Optional[torch.Tensor], gamma: torch.Tensor,
+                               eps: float, out_mode: int = OUT_SAME):
+    """Everything after the all-reduce. ``summed`` is fp32 (the exact sum over ranks).
+
+    Returns ``(norm_out, residual_out, scales-or-None)``.
+    """
+    dtype = gamma.dtype
+    s = summed.float().to(dtype)
+    res_out = s if residual is None else (s.float() + residual.float()).to(dtype)
+    x = res_out.float()
+    rstd = torch.rsqrt(x.pow(2).sum(dim=-1, keepdim=True) / x.shape[-1] + eps)
+    y = x * rstd * gamma.float()
+    if out_mode == OUT_SAME:
+        return y.to(dtype), res_out, None
+    q, scale = quantize_fp8(y, out_mode)
+    return q, res_out, scale
+
+
+def fused_allreduce_rms_reference(inputs: Sequence[torch.Tensor], residual: Optional[torch.Tensor],
+                                  gamma: torch.Tensor, eps: float, out_mode: int = OUT_SAME):
+    """Single-process oracle: ``inputs[r]`` is rank r's partial sum."""
+    acc = torch.zeros_like(inputs[0], dtype=torch.float32)
+    for t in inputs:  # rank order, fp32
+        acc = acc + t.float()
+    return residual_rmsnorm_reference(acc, residual, gamma, eps, out_mode)
+
+
+def fused_allreduce_rms_distributed(allreduce_in: torch.Tensor, residual: Optional[torch.Tensor],
+                                    gamma: torch.Tensor, eps: float, out_mode: int = OUT_SAME,
+                                    group: Optional[dist.ProcessGroup] = None):
+    """Multi-process statement of the op over any torch.distributed backend (gloo on CPU).
+
+    The sum is formed in fp32 in rank order (all-gather + ordered add) so that every rank gets
+    bit-identical results, as the kernels guarantee.
+    """
+    world = dist.get_world_size(group)
+    parts: List[torch.Tensor] = [torch.empty_like(allreduce_in, dtype=torch.float32) for _ in range(world)]
+    dist.all_gather(parts, allreduce_in.float().contiguous(), group=group)
+    return fused_allreduce_rms_reference(parts, residual, gamma, eps, out_mode)
+
+
+def scatter_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rows owned by ``rank`` in the round-robin layout of the reduce-scatter variant."""
+    return t[rank::world].contiguous()
