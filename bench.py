@@ -1,0 +1,228 @@
+#!/usr/bin/env python
+"""Headline benchmark: latency of the fused all-reduce + residual add + RMSNorm step.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched through torchrun)
+    python bench.py --impl reference --gpus N ...              (the reference build, same loop)
+
+One step = one call of the fused op on a bf16 [128, 4096] message per rank (the TP decode-batch
+shape of a Llama-3-8B-sized layer). The timed region holds exactly K steps; every step is timed
+on the device with CUDA events, the L2 is flushed and the ranks are aligned (tiny NCCL
+all-reduce) before each step, and the reported time is the maximum over ranks. The same JSON
+line also carries an end-to-end figure through the public API that includes the pinned
+host->device copy of the step's inputs and the device->host read of its outputs, the clocks
+sampled under load, and (own arm, N > 1) the latency of every algorithm, of the fp8-quantising
+epilogues and of NCCL all-reduce + separate kernels on the same message.
+
+The reference publishes no number (its README has none), so ``vs_baseline`` is null; the ratio
+against ``--impl reference`` measured on the same box is the comparison.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from benchmarks import common  # noqa: E402
+
+TOKENS, HIDDEN, EPS = 128, 4096, 1e-6
+METRIC = "fused_allreduce_residual_rmsnorm_latency_us"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["own", "reference"], default="own")
+    ap.add_argument("--tokens", type=int, default=TOKENS)
+    ap.add_argument("--hidden", type=int, default=HIDDEN)
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-algorithm / baseline extras")
+    return ap.parse_args()
+
+
+def make_step_inputs(tokens, hidden, rank, n_sets):
+    """Seeded synthetic inputs: per-rank partial sums ~N(0,1) (seed = rank), a shared residual,
+    weight ~N(1, 0.1). `n_sets` rotating device copies so that consecutive steps touch
+    different memory."""
+    g = torch.Generator().manual_seed(1234 + rank)
+    gs = torch.Generator().manual_seed(99)
+    host_x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).pin_memory()
+    host_r = torch.randn(tokens, hidden, generator=gs).to(torch.bfloat16).pin_memory()
+    gamma = (1.0 + 0.1 * torch.randn(hidden, generator=gs)).to(torch.bfloat16).cuda()
+    xs = [host_x.cuda() for _ in range(n_sets)]
+    rs = [host_r.cuda() for _ in range(n_sets)]
+    return host_x, host_r, gamma, xs, rs
+
+
+def run(args):
+    rank, world, local = common.init_dist(args.gpus)
+    tokens, hidden, K, W = args.tokens, args.hidden, args.steps, max(args.warmup, 3)
+    out = {
+        "metric": METRIC, "unit": "us", "n_gpus": world, "steps": K, "warmup": W,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded N(0,1) partial sums per rank, shared residual, weight N(1,0.1); random-init, no dataset)",
+        "impl": args.impl,
+        "config": {"model": "fused allreduce+residual+RMSNorm op (Llama-3-8B-shaped TP message)",
+                   "global_batch": tokens, "seq_len": 1, "hidden": hidden, "parallelism": f"tp{world}",
+                   "l2": "256 MiB buffer written before every timed step", "eps": EPS},
+    }
+
+    if args.impl == "reference":
+        if world not in (2, 4, 8):
+            return {"impl": "reference", "unavailable": f"the reference supports 2, 4 or 8 ranks only (got {world}); "
+                    "its launcher asserts on any other rank count"}
+        ref, why = common.load_reference()
+        if ref is None:
+            return {"impl": "reference", "unavailable": why}
+        ref.setup_env(rank, world)
+        api = ref
+    else:
+        import torch_dist_ext_b200 as tdx
+
+        tdx.setup_env(rank, world, device=local)
+        api = tdx
+
+    host_x, host_r, gamma, xs, rs = make_step_inputs(tokens, hidden, rank, n_sets=4)
+    ws = api.get_workspace(xs[0])
+    timing = common.timing_utils()
+    flusher = timing.L2Flusher()
+    align = common.RankAligner(world)
+    state = {"i": 0, "out": None}
+
+    def step():
+        i = state["i"] = (state["i"] + 1) % len(xs)
+        state["out"] = api.allreduce_rms(rank, world, xs[i], rs[i], gamma, EPS, ws)
+
+    # correctness of what is being timed (also catches a launch that silently did nothing)
+    step()
+    torch.cuda.synchronize()
+    ok, err = _verify(state["out"], host_x, host_r, gamma, world, rank)
+    ok = bool(common.min_over_ranks(1.0 if ok else 0.0, world))
+    if not ok:
+        msg = f"outputs do not match the PyTorch statement of the op (max err {err})"
+        if args.impl == "reference":
+            return {"impl": "reference", "unavailable": "reference ran but " + msg}
+        raise SystemExit("bench: " + msg)
+
+    # ---- device-timed region: exactly K steps ------------------------------------------------
+    with timing.ClockSampler(local, period_s=0.05) as sampler:
+        common.barrier(world)
+        times = common.device_times_us(step, K, W, flusher, align)
+        common.barrier(world)
+        # a sustained burst of the same step so that the clock samples are taken under this load
+        t_end = common.now() + 0.6
+        while common.now() < t_end:
+            for _ in range(50):
+                step()
+            torch.cuda.synchronize()
+    mean_us = common.max_over_ranks(sum(times) / len(times), world)
+    med_us = common.max_over_ranks(common.summarize(times)["median"], world)
+
+    # ---- end to end through the public API: H2D inputs, op, D2H outputs, every step -----------
+    x_dev, r_dev = torch.empty_like(xs[0]), torch.empty_like(rs[0])
+    norm_host = torch.empty(tokens, hidden, dtype=torch.bfloat16).pin_memory()
+    res_host = torch.empty(tokens, hidden, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        x_dev.copy_(host_x, non_blocking=True)
+        r_dev.copy_(host_r, non_blocking=True)
+        norm, res = api.allreduce_rms(rank, world, x_dev, r_dev, gamma, EPS, ws)
+        norm_host.copy_(norm, non_blocking=True)
+        res_host.copy_(res, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        e2e_step()
+    common.barrier(world)
+    t0 = common.now()
+    for _ in range(K):
+        e2e_step()
+    common.barrier(world)
+    e2e_us = common.max_over_ranks((common.now() - t0) / K * 1e6, world)
+
+    out.update({
+        "value": round(mean_us, 3), "ms_per_step": round(mean_us / 1e3, 6), "median_us": round(med_us, 3),
+        "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": 2 * tokens * hidden * 2,
+                "d2h_bytes_per_step": 2 * tokens * hidden * 2},
+        "gpu_launches": K if args.impl == "own" else 0,
+        "clocks": sampler.summary(),
+    })
+    if args.impl == "own":
+        st = api.stats()
+        out["algorithm"] = st.get("algo_counts")
+        if not args.no_extras:
+            out["extras"] = _extras(api, rank, world, tokens, hidden, xs, rs, gamma, flusher, align, K, W)
+    return out if rank == 0 else None
+
+
+def _verify(outs, host_x, host_r, gamma, world, rank):
+    """norm_out against fp32 PyTorch math on the same seeded inputs."""
+    norm, res = outs
+    acc = torch.zeros(host_x.shape, dtype=torch.float32)
+    for r in range(world):
+        g = torch.Generator().manual_seed(1234 + r)
+        acc += torch.randn(host_x.shape, generator=g).to(torch.bfloat16).float()
+    s = acc.to(torch.bfloat16)
+    e_res = (s.float() + host_r.float()).to(torch.bfloat16)
+    x = e_res.float()
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + EPS) * gamma.cpu().float()
+    err = (norm.cpu().float() - y).abs().max().item()
+    res_ok = torch.equal(res.cpu(), e_res)
+    return (err <= 0.05 * max(1.0, y.abs().max().item())) and res_ok, err
+
+
+def _extras(tdx, rank, world, tokens, hidden, xs, rs, gamma, flusher, align, K, W):
+    """Own arm only: every algorithm, the fp8 epilogues, and NCCL + separate kernels."""
+    import torch.distributed as dist
+
+    from torch_dist_ext_b200.utils.config import OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME
+
+    K = min(K, 100)
+    res = {}
+
+    def timed(fn):
+        t = common.device_times_us(fn, K, W, flusher, align)
+        return round(common.max_over_ranks(common.summarize(t)["median"], world), 3)
+
+    x, r = xs[0], rs[0]
+    algos = ["auto"] if world == 1 else ["oneshot", "twoshot", "twoshot_barrier"]
+    for algo in algos:
+        a = None if algo == "auto" else algo
+        try:
+            res[f"{algo}_bf16_us"] = timed(lambda: tdx.fused_allreduce_rms(x, r, gamma, EPS, algo=a))
+        except RuntimeError as e:
+            res[f"{algo}_bf16_us"] = f"n/a: {str(e)[:80]}"
+    res["fp8_token_us"] = timed(lambda: tdx.fused_allreduce_rms(x, r, gamma, EPS, out_mode=OUT_FP8_TOKEN))
+    res["fp8_block128_us"] = timed(lambda: tdx.fused_allreduce_rms(x, r, gamma, EPS, out_mode=OUT_FP8_BLOCK128))
+    if world > 1:
+        from torch_dist_ext_b200.ops import norm as norm_ops
+
+        buf = torch.zeros_like(x)  # all-reduced in place every step; zeros stay zeros
+
+        def nccl_separate():
+            dist.all_reduce(buf)
+            norm_ops.fused_add_rmsnorm(buf, r, gamma, EPS)
+
+        try:
+            res["nccl_allreduce_plus_add_rmsnorm_kernel_us"] = timed(nccl_separate)
+        except Exception as e:  # pragma: no cover
+            res["nccl_allreduce_plus_add_rmsnorm_kernel_us"] = f"n/a: {type(e).__name__}"
+    return res
+
+
+def main():
+    args = parse()
+    result = run(args)
+    if result is not None and int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(result), flush=True)
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,68 @@
+"""Worker run by every rank of the multi-process tests (gloo on CPU, NCCL + real IPC on GPUs)."""
+from __future__ import annotations
+
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def make_case(world, tokens, hidden, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    ins = [torch.randn(tokens, hidden, generator=g).to(dtype) for _ in range(world)]
+    residual = torch.randn(tokens, hidden, generator=g).to(dtype)
+    gamma = (1.0 + 0.1 * torch.randn(hidden, generator=g)).to(dtype)
+    return ins, residual, gamma
+
+
+def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=None):
+    """Runs `cases` = [(tokens, hidden, dtype, algo, out_mode)] and asserts against the oracle."""
+    try:
+        import torch_dist_ext_b200 as tdx
+        from torch_dist_ext_b200.utils.config import OUT_SAME
+
+        cuda = backend == "nccl"
+        if cuda:
+            torch.cuda.set_device(rank)
+        dist.init_process_group(backend=backend, init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        tdx.setup_env(rank, world, max_size_in_bytes=32 << 20)
+        dev = torch.device("cuda", rank) if cuda else torch.device("cpu")
+        tol = {torch.float32: 2e-5, torch.float16: 4e-3, torch.bfloat16: 3.2e-2}
+        for i, (tokens, hidden, dtype, algo, out_mode) in enumerate(cases):
+            ins, residual, gamma = make_case(world, tokens, hidden, dtype, seed=i)
+            exp_norm, exp_res, exp_scale = tdx.reference.fused_allreduce_rms_reference(ins, residual, gamma, 1e-6, out_mode)
+            x, r, w = ins[rank].to(dev), residual.to(dev), gamma.to(dev)
+            if out_mode == OUT_SAME and algo is None:
+                ws = tdx.get_workspace(x)
+                norm, res = tdx.allreduce_rms(rank, world, x, r, w, 1e-6, ws)
+                scales = None
+            else:
+                norm, res, scales = tdx.fused_allreduce_rms(x, r, w, 1e-6, out_mode=out_mode, algo=algo)
+            if cuda:
+                torch.cuda.synchronize()
+                tdx.check_status()
+            assert torch.equal(res.cpu().float(), exp_res.float()), f"case {i}: residual_out mismatch on rank {rank}"
+            if out_mode == OUT_SAME:
+                err = (norm.cpu().float() - exp_norm.float()).abs().max().item()
+                assert err <= tol[dtype] * max(1.0, exp_norm.float().abs().max().item()), f"case {i}: norm err {err}"
+            else:
+                assert torch.allclose(scales.cpu(), exp_scale, rtol=1e-5), f"case {i}: scales mismatch"
+                got, want = norm.cpu().float(), exp_norm.float()
+                step = torch.maximum(got.abs(), want.abs()) * 0.125 + 2.0 ** -9
+                assert bool(((got - want).abs() <= step).all()), f"case {i}: fp8 codes differ by more than a step"
+        st = tdx.stats()
+        if cuda:
+            assert st["error_count"] == 0
+        dist.barrier()
+        tdx.teardown_env()
+        dist.destroy_process_group()
+        if result_queue is not None:
+            result_queue.put((rank, "ok", st.get("algo_counts")))
+    except Exception:
+        if result_queue is not None:
+            result_queue.put((rank, "error", traceback.format_exc()))
+        raise

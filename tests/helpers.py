@@ -23,7 +23,13 @@ def run_emulated(ws, ins, residual, gamma, eps, out_mode, algo, scatter_only=Fal
     tokens, hidden = ins[0].shape
     dev = ins[0].device
     rows = (tokens + n - 1) // n if scatter_only else tokens
-    res_in = [residual[r::n].contiguous() if scatter_only else residual for r in range(n)]
+    def shard(t, r):
+        part = t[r::n]
+        if part.shape[0] < rows:  # ragged tail: the last ranks own one row less; pad to the common shape
+            part = torch.cat([part, part.new_zeros(rows - part.shape[0], hidden)])
+        return part.contiguous()
+
+    res_in = [shard(residual, r) if scatter_only else residual for r in range(n)]
     res_out = [torch.full((rows, hidden), float("nan"), dtype=ins[0].dtype, device=dev) for _ in range(n)]
     if out_mode == OUT_SAME:
         norm = [torch.full((rows, hidden), float("nan"), dtype=ins[0].dtype, device=dev) for _ in range(n)]

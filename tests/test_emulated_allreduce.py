@@ -92,9 +92,6 @@ def test_reduce_scatter_variant(workspaces, algo, out_mode):
     ws = workspaces(4)
     for tokens in (64, 61, 2):
         ins, residual, gamma = make_inputs(4, tokens, 2048, torch.bfloat16, "cuda", seed=tokens)
-        if tokens % 4:
-            # ragged shards: pad the oracle's view by slicing, outputs have ceil(tokens/4) rows
-            pass
         _, norm, res, scales = run_emulated(ws, ins, residual, gamma, EPS, out_mode, algo, scatter_only=True)
         exp_norm, exp_res, exp_scale = tdx.reference.fused_allreduce_rms_reference(ins, residual, gamma, EPS, out_mode)
         for r in range(4):

@@ -1,0 +1,244 @@
+// Standalone memory-bound ops of a decoder layer, written as 16-byte-vector sm_100a kernels:
+// fp8 e4m3 quantisation (per-token and 1x128 block scales), SiLU(gate) * up (optionally
+// quantising its output for an fp8 GEMM), and rotary position embedding (rotate-half layout).
+//
+// The reference contains none of these (its only device code is the fused all-reduce,
+// src/common/all_reduce_fusion_impl.h); they are the remaining hot ops of the Llama-shaped
+// tensor-parallel layers built on top of it.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include "tdx/ops.h"
+#include "tdx/ptx.cuh"
+#include "tdx/sync.cuh"
+#include "tdx/vec.cuh"
+
+namespace tdx {
+namespace {
+
+constexpr float kFp8MaxQ = 448.f;
+constexpr float kAmaxFloorQ = 1e-10f;
+
+template <int kVec>
+__device__ __forceinline__ void store_fp8_vec(void* dst, const float (&q)[kVec]) {
+  if constexpr (kVec == 8) {
+    uint2 o;
+    o.x = ptx::cvt_e4m3x4(q[0], q[1], q[2], q[3]);
+    o.y = ptx::cvt_e4m3x4(q[4], q[5], q[6], q[7]);
+    *reinterpret_cast<uint2*>(dst) = o;
+  } else {
+    *reinterpret_cast<uint32_t*>(dst) = ptx::cvt_e4m3x4(q[0], q[1], q[2], q[3]);
+  }
+}
+
+// ---- fp8 quantisation ---------------------------------------------------------------------
+// One CTA per row (grid-stride). kBlock: one scale per 128 columns; else one scale per row,
+// found in a first pass over the row (the second pass re-reads it from L1/L2).
+template <typename T, bool kBlock>
+__global__ void __launch_bounds__(512) quant_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q,
+                                                        float* __restrict__ scales, int rows, int cols) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  __shared__ float red[32];
+  const int nvec = cols / kVec;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const char* src = reinterpret_cast<const char*>(x + (size_t)row * cols);
+    uint8_t* dst = q + (size_t)row * cols;
+    if constexpr (kBlock) {
+      constexpr int kLanes = 128 / kVec;
+      // nvec is a multiple of kLanes, so whole lane groups are active or inactive together
+      for (int base = 0; base < nvec; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        float f[kVec];
+        float amax = 0.f;
+        if (i < nvec) {
+          unpack<T>(ptx::ld_stream_v4(src + (size_t)i * 16), f);
+#pragma unroll
+          for (int k = 0; k < kVec; ++k) amax = fmaxf(amax, fabsf(f[k]));
+        }
+        amax = group_max<kLanes>(amax);
+        const float scale = fmaxf(amax, kAmaxFloorQ) / kFp8MaxQ;
+        const float inv = 1.f / scale;
+        if (i < nvec) {
+#pragma unroll
+          for (int k = 0; k < kVec; ++k) f[k] *= inv;
+          store_fp8_vec<kVec>(dst + (size_t)i * kVec, f);
+          if ((threadIdx.x & (kLanes - 1)) == 0) scales[(size_t)row * (cols / 128) + (size_t)i * kVec / 128] = scale;
+        }
+      }
+    } else {
+      float amax = 0.f;
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        float f[kVec];
+        unpack<T>(ptx::ld_v4(src + (size_t)i * 16), f);
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) amax = fmaxf(amax, fabsf(f[k]));
+      }
+      amax = block_allreduce<true>(amax, red);
+      const float scale = fmaxf(amax, kAmaxFloorQ) / kFp8MaxQ;
+      const float inv = 1.f / scale;
+      if (threadIdx.x == 0) scales[row] = scale;
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        float f[kVec];
+        unpack<T>(ptx::ld_v4(src + (size_t)i * 16), f);
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) f[k] *= inv;
+        store_fp8_vec<kVec>(dst + (size_t)i * kVec, f);
+      }
+      __syncthreads();  // `red` is reused by the next row
+    }
+  }
+}
+
+// ---- SiLU(gate) * up --------------------------------------------------------------------------
+// in: [rows, 2*inter] with the gate in the first half of each row; out: [rows, inter].
+// kQuant: out is e4m3 with 1x128 block scales (input of an fp8 block-scaled down projection).
+template <typename T, bool kQuant>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ in, void* __restrict__ out,
+                                                       float* __restrict__ scales, int rows, int inter) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  const int nvec = inter / kVec;
+  const size_t total = (size_t)rows * nvec;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  // Warp-uniform trip count: the quantising variant shuffles inside the loop.
+  for (size_t base = (size_t)blockIdx.x * blockDim.x + (threadIdx.x & ~31u); base < total; base += stride) {
+    const size_t idx = base + (threadIdx.x & 31u);
+    const bool live = idx < total;
+    const size_t row = live ? idx / nvec : 0;
+    const int i = live ? int(idx % nvec) : 0;
+    float g[kVec], u[kVec], y[kVec];
+    if (live) {
+      const char* base = reinterpret_cast<const char*>(in + row * 2 * (size_t)inter);
+      unpack<T>(ptx::ld_stream_v4(base + (size_t)i * 16), g);
+      unpack<T>(ptx::ld_stream_v4(base + (size_t)inter * sizeof(T) + (size_t)i * 16), u);
+#pragma unroll
+      for (int k = 0; k < kVec; ++k) y[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < kVec; ++k) y[k] = 0.f;
+    }
+    if constexpr (kQuant) {
+      constexpr int kLanes = 128 / kVec;
+      round_through<T>(y);  // quantise what a separate kernel would have stored in T
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < kVec; ++k) amax = fmaxf(amax, fabsf(y[k]));
+      // lanes of one 128-column block are adjacent: nvec % kLanes == 0 and idx is linear in i
+      amax = group_max<kLanes>(amax);
+      const float scale = fmaxf(amax, kAmaxFloorQ) / kFp8MaxQ;
+      const float inv = 1.f / scale;
+      if (live) {
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) y[k] *= inv;
+        store_fp8_vec<kVec>(static_cast<uint8_t*>(out) + row * inter + (size_t)i * kVec, y);
+        if ((i & (kLanes - 1)) == 0) scales[row * (inter / 128) + (size_t)i * kVec / 128] = scale;
+      }
+    } else {
+      if (live) ptx::st_stream_v4(static_cast<char*>(out) + (row * inter + (size_t)i * kVec) * sizeof(T), pack<T>(y));
+    }
+  }
+}
+
+// ---- rotary embedding (rotate-half / "neox" layout), in place ------------------------------------
+// x: [tokens, heads, dim]; cache: [max_pos, dim] fp32 = {cos[0..dim/2), sin[0..dim/2)} per position.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ q, T* __restrict__ k,
+                                                   const int64_t* __restrict__ positions,
+                                                   const float* __restrict__ cache, int tokens, int q_heads,
+                                                   int k_heads, int dim, int64_t q_stride, int64_t k_stride) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  const int half = dim / 2;
+  const int per_head = half / kVec;
+  const int items = (q_heads + k_heads) * per_head;
+  for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
+    const float* cs = cache + positions[t] * dim;
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+      const int head = it / per_head;
+      const int off = (it % per_head) * kVec;
+      T* base = head < q_heads ? q + (size_t)t * q_stride + (size_t)head * dim
+                               : k + (size_t)t * k_stride + (size_t)(head - q_heads) * dim;
+      float a[kVec], b[kVec];
+      unpack<T>(ptx::ld_v4(base + off), a);
+      unpack<T>(ptx::ld_v4(base + half + off), b);
+      float ra[kVec], rb[kVec];
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        const float c = cs[off + i], s = cs[half + off + i];
+        ra[i] = a[i] * c - b[i] * s;
+        rb[i] = b[i] * c + a[i] * s;
+      }
+      *reinterpret_cast<uint4*>(base + off) = pack<T>(ra);
+      *reinterpret_cast<uint4*>(base + half + off) = pack<T>(rb);
+    }
+  }
+}
+
+int grid_for(size_t work_items, int threads, int max_blocks = 148 * 8) {
+  size_t b = (work_items + threads - 1) / threads;
+  if (b > (size_t)max_blocks) b = max_blocks;
+  return b == 0 ? 1 : int(b);
+}
+
+}  // namespace
+
+#define TDX_DISPATCH_DTYPE(dtype, ...)                                    \
+  switch (dtype) {                                                        \
+    case kF32: { using T = float; __VA_ARGS__; break; }                   \
+    case kF16: { using T = __half; __VA_ARGS__; break; }                  \
+    case kBF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }          \
+    default: return "unsupported dtype";                                  \
+  }
+
+std::string quant_fp8(const void* x, void* q, float* scales, int rows, int cols, int dtype, bool block128,
+                      cudaStream_t stream) {
+  const int vec = dtype == kF32 ? 4 : 8;
+  if (cols % vec) return "columns must be a multiple of 16 bytes";
+  if (block128 && cols % 128) return "1x128 block scaling needs columns % 128 == 0";
+  if (rows == 0) return "";
+  const int nvec = cols / vec;
+  int threads = (nvec + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  TDX_DISPATCH_DTYPE(dtype, {
+    if (block128)
+      quant_fp8_kernel<T, true><<<grid, threads, 0, stream>>>(static_cast<const T*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
+    else
+      quant_fp8_kernel<T, false><<<grid, threads, 0, stream>>>(static_cast<const T*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
+  });
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : cudaGetErrorString(e);
+}
+
+std::string silu_mul(const void* in, void* out, float* scales, int rows, int inter, int dtype, bool quant_block128,
+                     cudaStream_t stream) {
+  const int vec = dtype == kF32 ? 4 : 8;
+  if (inter % vec) return "intermediate size must be a multiple of 16 bytes";
+  if (quant_block128 && inter % 128) return "1x128 block scaling needs intermediate size % 128 == 0";
+  if (rows == 0) return "";
+  const size_t total = (size_t)rows * (inter / vec);
+  const int grid = grid_for(total, 256);
+  TDX_DISPATCH_DTYPE(dtype, {
+    if (quant_block128)
+      silu_mul_kernel<T, true><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), out, scales, rows, inter);
+    else
+      silu_mul_kernel<T, false><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), out, scales, rows, inter);
+  });
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : cudaGetErrorString(e);
+}
+
+std::string rope_inplace(void* q, void* k, const int64_t* positions, const float* cos_sin_cache, int tokens,
+                         int q_heads, int k_heads, int dim, int64_t q_stride, int64_t k_stride, int dtype,
+                         cudaStream_t stream) {
+  const int vec = dtype == kF32 ? 4 : 8;
+  if (dim % (2 * vec)) return "head dimension must be a multiple of 2 x 16 bytes";
+  if (tokens == 0) return "";
+  const int grid = tokens < 148 * 8 ? tokens : 148 * 8;
+  TDX_DISPATCH_DTYPE(dtype, {
+    rope_kernel<T><<<grid, 256, 0, stream>>>(static_cast<T*>(q), static_cast<T*>(k), positions, cos_sin_cache, tokens,
+                                             q_heads, k_heads, dim, q_stride, k_stride);
+  });
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : cudaGetErrorString(e);
+}
+
+}  // namespace tdx

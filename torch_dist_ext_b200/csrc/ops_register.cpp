@@ -1,9 +1,105 @@
 // Registration of the standalone ops (normalisation, quantisation, RoPE, activation), the
 // tcgen05 GEMMs, the fused GEMM+collective ops and the decode-attention kernel.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include "tdx/bindings.h"
+#include "tdx/ops.h"
 
 namespace tdx_torch {
 
-void register_extra_ops(torch::Library& m) { (void)m; }
+using at::Tensor;
+
+static int dtype_code(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return tdx::kF32;
+    case at::kHalf: return tdx::kF16;
+    case at::kBFloat16: return tdx::kBF16;
+    default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+  }
+  return -1;
+}
+
+static cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// residual add + RMSNorm (+ fp8 quant) without communication: the single-rank form of the fused op.
+int64_t fused_add_rmsnorm(const Tensor& x, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
+                          c10::optional<Tensor> residual_out, Tensor norm_out, c10::optional<Tensor> scale_out,
+                          double eps, int64_t out_mode) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "x must be a contiguous CUDA tensor");
+  const c10::cuda::CUDAGuard guard(x.device());
+  tdx::ArParams p{};
+  p.rank = 0;
+  p.nranks = 1;
+  p.hidden = (int32_t)x.size(-1);
+  p.tokens = (int32_t)(x.numel() / std::max<int64_t>(1, x.size(-1)));
+  p.in = x.data_ptr();
+  p.residual_in = residual_in.has_value() && residual_in->defined() ? residual_in->data_ptr() : nullptr;
+  p.residual_out = residual_out.has_value() && residual_out->defined() ? residual_out->data_ptr() : nullptr;
+  p.gamma = gamma.data_ptr();
+  p.norm_out = norm_out.data_ptr();
+  p.scale_out = scale_out.has_value() && scale_out->defined() ? scale_out->data_ptr<float>() : nullptr;
+  p.eps = (float)eps;
+  p.dtype = dtype_code(x);
+  p.out_mode = (int32_t)out_mode;
+  p.algo = tdx::kAlgoLocal;
+  TORCH_CHECK(gamma.numel() == p.hidden && gamma.scalar_type() == x.scalar_type(), "gamma must be [hidden] in x's dtype");
+  TORCH_CHECK(norm_out.numel() == x.numel(), "norm_out has the wrong size");
+  tdx::LaunchPlan used{};
+  const std::string err = tdx::launch_allreduce(p, cur_stream(), &used);
+  TORCH_CHECK(err.empty(), "fused_add_rmsnorm: ", err);
+  return used.grid;
+}
+
+void quant_fp8(const Tensor& x, Tensor q, Tensor scales, bool block128) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && q.is_contiguous() && scales.is_contiguous(), "contiguous CUDA tensors expected");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t cols = x.size(-1), rows = x.numel() / std::max<int64_t>(1, cols);
+  TORCH_CHECK(q.numel() == x.numel() && q.element_size() == 1, "q must be a 1-byte tensor of x's shape");
+  TORCH_CHECK(scales.scalar_type() == at::kFloat && scales.numel() == (block128 ? rows * (cols / 128) : rows), "scales has the wrong size");
+  const std::string err = tdx::quant_fp8(x.data_ptr(), q.data_ptr(), scales.data_ptr<float>(), (int)rows, (int)cols,
+                                         dtype_code(x), block128, cur_stream());
+  TORCH_CHECK(err.empty(), "quant_fp8: ", err);
+}
+
+void silu_mul(const Tensor& gate_up, Tensor out, c10::optional<Tensor> scales) {
+  TORCH_CHECK(gate_up.is_cuda() && gate_up.is_contiguous() && out.is_contiguous(), "contiguous CUDA tensors expected");
+  const c10::cuda::CUDAGuard guard(gate_up.device());
+  const int64_t inter = gate_up.size(-1) / 2, rows = gate_up.numel() / std::max<int64_t>(1, gate_up.size(-1));
+  const bool quant = scales.has_value() && scales->defined();
+  TORCH_CHECK(out.numel() == rows * inter, "out must be [rows, inter]");
+  if (quant) {
+    TORCH_CHECK(out.element_size() == 1 && scales->scalar_type() == at::kFloat && scales->numel() == rows * (inter / 128),
+                "fp8 output needs [rows, inter/128] fp32 scales");
+  } else {
+    TORCH_CHECK(out.scalar_type() == gate_up.scalar_type(), "out must have the input dtype");
+  }
+  const std::string err = tdx::silu_mul(gate_up.data_ptr(), out.data_ptr(), quant ? scales->data_ptr<float>() : nullptr,
+                                        (int)rows, (int)inter, dtype_code(gate_up), quant, cur_stream());
+  TORCH_CHECK(err.empty(), "silu_mul: ", err);
+}
+
+void rope_(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin_cache) {
+  TORCH_CHECK(q.is_cuda() && k.is_cuda() && q.dim() == 3 && k.dim() == 3, "q and k must be [tokens, heads, dim] CUDA tensors");
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && q.stride(1) == q.size(2) && k.stride(1) == k.size(2), "heads must be densely packed");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_cuda() && positions.numel() == q.size(0), "positions must be int64 [tokens]");
+  TORCH_CHECK(cos_sin_cache.scalar_type() == at::kFloat && cos_sin_cache.is_contiguous() && cos_sin_cache.size(-1) == q.size(2), "cos_sin_cache must be fp32 [max_pos, dim]");
+  TORCH_CHECK(q.scalar_type() == k.scalar_type() && q.size(2) == k.size(2) && q.size(0) == k.size(0), "q and k must agree in dtype, tokens and dim");
+  const int64_t esz = q.element_size();
+  TORCH_CHECK((q.stride(0) * esz) % 16 == 0 && (k.stride(0) * esz) % 16 == 0 && (uintptr_t)q.data_ptr() % 16 == 0 && (uintptr_t)k.data_ptr() % 16 == 0,
+              "q and k rows must be 16-byte aligned");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const std::string err = tdx::rope_inplace(q.data_ptr(), k.data_ptr(), positions.data_ptr<int64_t>(), cos_sin_cache.data_ptr<float>(),
+                                            (int)q.size(0), (int)q.size(1), (int)k.size(1), (int)q.size(2), q.stride(0),
+                                            k.stride(0), dtype_code(q), cur_stream());
+  TORCH_CHECK(err.empty(), "rope: ", err);
+}
+
+void register_extra_ops(torch::Library& m) {
+  m.def("fused_add_rmsnorm(Tensor x, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
+        "Tensor(c!)? scale_out, float eps, int out_mode) -> int", &fused_add_rmsnorm);
+  m.def("quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) scales, bool block128) -> ()", &quant_fp8);
+  m.def("silu_mul(Tensor gate_up, Tensor(a!) out, Tensor(b!)? scales) -> ()", &silu_mul);
+  m.def("rope_(Tensor(a!) q, Tensor(b!) k, Tensor positions, Tensor cos_sin_cache) -> ()", &rope_);
+}
 
 }  // namespace tdx_torch
