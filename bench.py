@@ -214,8 +214,20 @@ def _extras(tdx, rank, world, tokens, hidden, xs, rs, gamma, flusher, align, K, 
     return res
 
 
+def _reexec_with_reference_on_library_path():
+    """The reference's op library needs its companion device library, which it locates through
+    the dynamic loader's search path; that path is read at process start."""
+    cur = os.environ.get("LD_LIBRARY_PATH", "")
+    if common.REF_DIR in cur.split(":"):
+        return
+    os.environ["LD_LIBRARY_PATH"] = common.REF_DIR + (":" + cur if cur else "")
+    os.execve(sys.executable, [sys.executable] + sys.argv, os.environ)
+
+
 def main():
     args = parse()
+    if args.impl == "reference" and os.path.isdir(common.REF_DIR):
+        _reexec_with_reference_on_library_path()
     result = run(args)
     if result is not None and int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(result), flush=True)

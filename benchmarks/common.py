@@ -3,7 +3,6 @@ timing with rank alignment and L2 flushing, max-over-ranks reduction, and loadin
 reference build for the comparison arm."""
 from __future__ import annotations
 
-import ctypes
 import os
 import statistics
 import sys
@@ -63,10 +62,15 @@ class RankAligner:
             dist.all_reduce(self.t)
 
 
+HEAD_START_CYCLES = 400_000   # ~0.2 ms of device-side delay
+
+
 def device_times_us(fn: Callable[[], None], steps: int, warmup: int, flush: Optional[Callable[[], None]],
                     align: Callable[[], None]) -> List[float]:
     """Per-step device time in microseconds: CUDA events around `fn` only; before every step the
-    L2 is flushed (if given) and the ranks are aligned on the device."""
+    L2 is flushed (if given) and the ranks are aligned on the device. A short device-side delay
+    precedes the first event so that the host has queued the whole step before the GPU reaches
+    it: the interval then holds device work only, not Python launch latency."""
     for _ in range(warmup):
         if flush:
             flush()
@@ -78,6 +82,7 @@ def device_times_us(fn: Callable[[], None], steps: int, warmup: int, flush: Opti
         if flush:
             flush()
         align()
+        torch.cuda._sleep(HEAD_START_CYCLES)
         a = torch.cuda.Event(enable_timing=True)
         b = torch.cuda.Event(enable_timing=True)
         a.record()
@@ -121,7 +126,6 @@ def load_reference():
     if "torch_dist_ext_b200" in sys.modules:
         return None, "the reference registers the same op namespace as this library; use a separate process"
     try:
-        ctypes.CDLL(dev, mode=ctypes.RTLD_GLOBAL)
         sys.path.insert(0, REF_DIR)
         import io
         from contextlib import redirect_stdout

@@ -1,0 +1,202 @@
+// Standalone C++ harness for the fused all-reduce kernels: no PyTorch, one host process.
+//
+// With N >= 2 visible GPUs every rank runs on its own device (peer access enabled in-process,
+// one launch per device, like the reference's harness test/unit_test.cpp:219-315). With one GPU
+// the same N ranks run as ONE cooperative launch on that device (separate launches that wait on
+// each other must never share a GPU). Shapes: the reference's sweep tokens {513,1257,127,778,
+// 10024,3} x hidden {1024,508,124} in fp32 (test/unit_test.cpp:322-323) for every algorithm,
+// plus bf16 cases. The oracle accumulates in double on the CPU; fp32 results must be within
+// 1e-4 absolute (the reference's criterion, test/unit_test.cpp:219), bf16 within bf16 rounding.
+// Unlike the reference's harness, a failed case makes the process exit non-zero.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <memory>
+#include <random>
+#include <string>
+#include <vector>
+#include "tdx/api.h"
+
+#define CK(expr)                                                                      \
+  do {                                                                                \
+    cudaError_t e__ = (expr);                                                         \
+    if (e__ != cudaSuccess) {                                                         \
+      std::fprintf(stderr, "%s failed: %s\n", #expr, cudaGetErrorString(e__));       \
+      std::exit(2);                                                                   \
+    }                                                                                 \
+  } while (0)
+
+using tdx::ArParams;
+
+static float bf16_round(float f) { return __bfloat162float(__float2bfloat16(f)); }
+
+struct Case {
+  int tokens, hidden, dtype, algo;
+};
+
+template <typename T>
+static T from_float(float f);
+template <>
+float from_float<float>(float f) { return f; }
+template <>
+__nv_bfloat16 from_float<__nv_bfloat16>(float f) { return __float2bfloat16(f); }
+static float to_float(float f) { return f; }
+static float to_float(__nv_bfloat16 f) { return __bfloat162float(f); }
+
+template <typename T>
+static bool run_case(const Case& c, int nranks, bool multi_gpu, std::vector<std::unique_ptr<tdx::Workspace>>& ws) {
+  const size_t n = (size_t)c.tokens * c.hidden;
+  std::mt19937 rng(c.tokens * 131 + c.hidden);
+  std::uniform_real_distribution<float> dist(0.f, 0.5f);
+  std::vector<std::vector<T>> h_in(nranks, std::vector<T>(n));
+  std::vector<T> h_res(n), h_gamma(c.hidden);
+  for (auto& v : h_in)
+    for (auto& x : v) x = from_float<T>(dist(rng));
+  for (auto& x : h_res) x = from_float<T>(dist(rng));
+  for (auto& x : h_gamma) x = from_float<T>(dist(rng));
+
+  std::vector<T*> d_in(nranks), d_res(nranks), d_gamma(nranks), d_res_out(nranks), d_norm(nranks);
+  std::vector<ArParams> params(nranks);
+  for (int r = 0; r < nranks; ++r) {
+    CK(cudaSetDevice(multi_gpu ? r : 0));
+    CK(cudaMalloc(&d_in[r], n * sizeof(T)));
+    CK(cudaMalloc(&d_res[r], n * sizeof(T)));
+    CK(cudaMalloc(&d_gamma[r], c.hidden * sizeof(T)));
+    CK(cudaMalloc(&d_res_out[r], n * sizeof(T)));
+    CK(cudaMalloc(&d_norm[r], n * sizeof(T)));
+    CK(cudaMemcpy(d_in[r], h_in[r].data(), n * sizeof(T), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(d_res[r], h_res.data(), n * sizeof(T), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(d_gamma[r], h_gamma.data(), c.hidden * sizeof(T), cudaMemcpyHostToDevice));
+    CK(cudaMemset(d_norm[r], 0xff, n * sizeof(T)));
+    ArParams& p = params[r];
+    p = ArParams{};
+    ws[r]->fill_params(&p);
+    p.tokens = c.tokens;
+    p.hidden = c.hidden;
+    p.in = d_in[r];
+    p.residual_in = d_res[r];
+    p.gamma = d_gamma[r];
+    p.residual_out = d_res_out[r];
+    p.norm_out = d_norm[r];
+    p.eps = 1e-6f;
+    p.dtype = c.dtype;
+    p.out_mode = tdx::kOutSame;
+    p.algo = c.algo;
+  }
+  std::string err;
+  if (multi_gpu) {
+    // one launch per device from one host thread: each kernel waits (bounded) for the later ones
+    for (int r = 0; r < nranks && err.empty(); ++r) {
+      CK(cudaSetDevice(r));
+      err = tdx::launch_allreduce(params[r], 0);
+    }
+    for (int r = 0; r < nranks; ++r) {
+      CK(cudaSetDevice(r));
+      CK(cudaDeviceSynchronize());
+    }
+  } else {
+    CK(cudaSetDevice(0));
+    ArParams* dev = nullptr;
+    CK(cudaMalloc(&dev, nranks * sizeof(ArParams)));
+    CK(cudaMemcpy(dev, params.data(), nranks * sizeof(ArParams), cudaMemcpyHostToDevice));
+    err = tdx::launch_allreduce_emulated(params.data(), dev, nranks, 0);
+    CK(cudaDeviceSynchronize());
+    CK(cudaFree(dev));
+  }
+  bool ok = err.empty();
+  if (!ok) std::fprintf(stderr, "launch error: %s\n", err.c_str());
+
+  // oracle (double accumulation; intermediate roundings of T as the kernels do)
+  std::vector<float> e_res(n), e_norm(n);
+  for (int t = 0; t < c.tokens; ++t) {
+    double ss = 0;
+    for (int h = 0; h < c.hidden; ++h) {
+      const size_t i = (size_t)t * c.hidden + h;
+      float s = 0.f;
+      for (int r = 0; r < nranks; ++r) s += to_float(h_in[r][i]);
+      if (sizeof(T) == 2) s = bf16_round(s);
+      float x = s + to_float(h_res[i]);
+      if (sizeof(T) == 2) x = bf16_round(x);
+      e_res[i] = x;
+      ss += (double)x * x;
+    }
+    const double rstd = 1.0 / std::sqrt(ss / c.hidden + 1e-6);
+    for (int h = 0; h < c.hidden; ++h) {
+      const size_t i = (size_t)t * c.hidden + h;
+      e_norm[i] = (float)(e_res[i] * rstd * to_float(h_gamma[h]));
+    }
+  }
+  const double atol = sizeof(T) == 4 ? 1e-4 : 2e-2;
+  double worst = 0;
+  std::vector<T> got(n);
+  for (int r = 0; r < nranks && ok; ++r) {
+    CK(cudaSetDevice(multi_gpu ? r : 0));
+    CK(cudaMemcpy(got.data(), d_norm[r], n * sizeof(T), cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < n; ++i) {
+      const double d = std::fabs((double)to_float(got[i]) - e_norm[i]);
+      if (!(d <= atol)) { ok = false; worst = d; break; }   // also catches NaN
+      if (d > worst) worst = d;
+    }
+    CK(cudaMemcpy(got.data(), d_res_out[r], n * sizeof(T), cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < n && ok; ++i)
+      if (!(std::fabs((double)to_float(got[i]) - e_res[i]) <= (sizeof(T) == 4 ? 1e-5 : 1e-2))) ok = false;
+  }
+  for (int r = 0; r < nranks; ++r) {
+    CK(cudaSetDevice(multi_gpu ? r : 0));
+    if (ws[r]->errors_seen() != 0) ok = false;
+    cudaFree(d_in[r]); cudaFree(d_res[r]); cudaFree(d_gamma[r]); cudaFree(d_res_out[r]); cudaFree(d_norm[r]);
+  }
+  std::printf("tokens:%d hidden:%d dtype:%s algo:%d ranks:%d max_abs_err:%.3g validation:%d\n", c.tokens, c.hidden,
+              c.dtype == tdx::kF32 ? "f32" : "bf16", c.algo, nranks, worst, ok ? 1 : 0);
+  return ok;
+}
+
+int main(int argc, char** argv) {
+  int ndev = 0;
+  CK(cudaGetDeviceCount(&ndev));
+  int nranks = argc > 1 ? std::atoi(argv[1]) : (ndev >= 2 ? ndev : 4);
+  if (nranks > tdx::kMaxRanks) nranks = tdx::kMaxRanks;
+  const bool multi_gpu = ndev >= nranks && nranks >= 2 && !(argc > 2 && std::string(argv[2]) == "emulate");
+  std::printf("devices:%d ranks:%d mode:%s\n", ndev, nranks, multi_gpu ? "one-gpu-per-rank" : "emulated-on-gpu0");
+  if (multi_gpu) tdx::enable_all_peer_access();
+
+  std::vector<std::unique_ptr<tdx::Workspace>> ws;
+  std::vector<tdx::Workspace*> raw;
+  for (int r = 0; r < nranks; ++r) {
+    CK(cudaSetDevice(multi_gpu ? r : 0));
+    ws.emplace_back(new tdx::Workspace(r, nranks, 256, 64ull << 20, 64ull << 20, multi_gpu ? r : 0, /*multicast=*/0));
+    ws.back()->set_timeout_ns(2000000000ull);
+    raw.push_back(ws.back().get());
+  }
+  if (nranks > 1) tdx::Workspace::connect_local(raw);
+
+  const int tokens[] = {513, 1257, 127, 778, 10024, 3};
+  const int hiddens[] = {1024, 508, 124};
+  const int algos[] = {tdx::kAlgoAuto, tdx::kAlgoOneShotLamport, tdx::kAlgoTwoShotLamport, tdx::kAlgoTwoShotBarrier};
+  bool all_ok = true;
+  int ran = 0;
+  for (int algo : algos)
+    for (int t : tokens)
+      for (int h : hiddens) {
+        if (nranks == 1 && algo != tdx::kAlgoAuto) continue;
+        // skip what exceeds this harness's buffer sizes for the chosen algorithm
+        const uint64_t msg = (uint64_t)t * h * 4;
+        if (algo == tdx::kAlgoOneShotLamport && msg * nranks > (64ull << 20)) continue;
+        if (algo == tdx::kAlgoTwoShotLamport && 2 * msg + 16ull * t + (uint64_t)nranks * h * 4 > (64ull << 20)) continue;
+        all_ok &= run_case<float>({t, h, tdx::kF32, algo}, nranks, multi_gpu, ws);
+        ++ran;
+      }
+  for (int algo : algos)
+    for (int t : {1, 128, 129, 2048})
+      for (int h : {4096, 8192}) {
+        if (nranks == 1 && algo != tdx::kAlgoAuto) continue;
+        const uint64_t msg = (uint64_t)t * h * 2;
+        if (algo == tdx::kAlgoOneShotLamport && msg * nranks > (64ull << 20)) continue;
+        all_ok &= run_case<__nv_bfloat16>({t, h, tdx::kBF16, algo}, nranks, multi_gpu, ws);
+        ++ran;
+      }
+  std::printf("cases:%d result:%s\n", ran, all_ok ? "PASS" : "FAIL");
+  return all_ok ? 0 : 1;
+}

@@ -24,6 +24,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 BUILD_DIR = PKG_DIR.parent / "build" / "tdx"
 LIB_PATH = PKG_DIR / "_C.so"
+UNIT_TEST_SRC = PKG_DIR.parent / "tests" / "cpp" / "unit_test.cu"
+UNIT_TEST_BIN = PKG_DIR.parent / "tests" / "cpp" / "unit_test.bin"
 
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = NVCC_ARCH + [
@@ -120,7 +122,19 @@ def write_ninja() -> Path:
         f"-L{cuda}/lib64", "-lcudart", "-ldl", "-lpthread",
         f"-Wl,-rpath,{torch_lib}", "-Wl,--no-as-needed",
     ]
-    lines += [f"build {LIB_PATH}: link {' '.join(objs)}", f"  ldflags = {' '.join(ld)}", f"default {LIB_PATH}", ""]
+    lines += [f"build {LIB_PATH}: link {' '.join(objs)}", f"  ldflags = {' '.join(ld)}"]
+    # Standalone C++ harness (no PyTorch): the kernels, the launcher and the workspace manager only.
+    core = [o for o in objs if o.startswith("ar_inst_") or o in ("workspace.o", "ar_fusion_launch.host.o")]
+    lines += [
+        "rule nvlink_exe",
+        "  command = $nvcc $nvflags -o $out $in -lcudart",
+        "  description = NVCC-LINK $out",
+        f"build unit_test.o: nvcc {UNIT_TEST_SRC}",
+        "  defs = ",
+        f"build {UNIT_TEST_BIN}: nvlink_exe unit_test.o {' '.join(core)}",
+        f"default {LIB_PATH} {UNIT_TEST_BIN}",
+        "",
+    ]
     path = BUILD_DIR / "build.ninja"
     text = "\n".join(lines)
     if not path.exists() or path.read_text() != text:

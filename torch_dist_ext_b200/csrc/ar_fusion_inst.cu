@@ -66,6 +66,12 @@ const void* select(const LaunchPlan& plan, int out) {
     case kAlgoOneShotLamport: return by_n<kAlgoOneShotLamport>(plan.n_tmpl, plan.vpt, out);
     case kAlgoTwoShotLamport: return by_n<kAlgoTwoShotLamport>(plan.n_tmpl, plan.vpt, out);
     case kAlgoTwoShotBarrier: return by_n<kAlgoTwoShotBarrier>(plan.n_tmpl, plan.vpt, out);
+    case kAlgoNvlsOneShot:
+      if constexpr (!kEmu) return by_n<kAlgoNvlsOneShot>(plan.n_tmpl, plan.vpt, out);
+      break;
+    case kAlgoNvlsTwoShot:
+      if constexpr (!kEmu) return by_n<kAlgoNvlsTwoShot>(plan.n_tmpl, plan.vpt, out);
+      break;
   }
   return nullptr;
 }

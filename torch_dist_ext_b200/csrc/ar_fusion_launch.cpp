@@ -25,7 +25,7 @@ Policy& policy() {
       q.lamport_max_bytes[n] = 8u << 20;
     }
     q.prefer_nvls = 1;
-    q.nvls_min_bytes = 1u << 20;
+    q.nvls_min_bytes = 4u << 20;
     return q;
   }();
   return pol;
@@ -126,7 +126,12 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
     if (algo == kAlgoLocal) return "the local algorithm needs nranks == 1";
     if (algo == kAlgoAuto) {
       const Policy& pol = policy();
-      if (!p.scatter_only && msg_bytes <= pol.oneshot_max_bytes[n] && need_oneshot <= p.layout.lamport_bytes)
+      const bool nvls_ok = p.mc_base != nullptr && pol.prefer_nvls && emu_ranks == 0 &&
+                           msg_bytes <= p.layout.nvls_in_bytes &&
+                           uint64_t(p.tokens) * (row_bytes + 16) + 2 * p.layout.nvls_in_bytes <= p.layout.nvls_bytes;
+      if (nvls_ok && msg_bytes >= pol.nvls_min_bytes)
+        algo = kAlgoNvlsTwoShot;
+      else if (!p.scatter_only && msg_bytes <= pol.oneshot_max_bytes[n] && need_oneshot <= p.layout.lamport_bytes)
         algo = kAlgoOneShotLamport;
       else if (msg_bytes <= pol.lamport_max_bytes[n] && need_ts_lamport <= p.layout.lamport_bytes)
         algo = kAlgoTwoShotLamport;
@@ -144,7 +149,13 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
       if (need_ts_barrier > p.layout.stage_bytes)
         return fmt("message of %lld bytes exceeds the workspace capacity (needs %lld of %lld staging bytes)", msg_bytes, need_ts_barrier, p.layout.stage_bytes);
     } else if (algo == kAlgoNvlsOneShot || algo == kAlgoNvlsTwoShot) {
-      return "NVLS algorithms are not available in this build";
+      if (p.mc_base == nullptr || p.layout.nvls_in_bytes == 0)
+        return "NVLS algorithms need a workspace with an NVSwitch multicast mapping (not available here)";
+      if (emu_ranks > 0) return "NVLS algorithms cannot be emulated on one device";
+      if (algo == kAlgoNvlsOneShot && p.scatter_only) return "the one-shot algorithm cannot produce scattered output";
+      const uint64_t result_cap = p.layout.nvls_bytes - 2 * p.layout.nvls_in_bytes;
+      if (msg_bytes > p.layout.nvls_in_bytes || uint64_t(p.tokens) * (row_bytes + 16) > result_cap)
+        return fmt("message of %lld bytes exceeds the NVLS staging capacity of %lld bytes", msg_bytes, p.layout.nvls_in_bytes);
     } else {
       return fmt("unknown algorithm %lld", algo);
     }
@@ -153,7 +164,8 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
   pl.n_tmpl = (n == 1) ? 1 : (n == 2 || n == 4 || n == 8) ? n : 0;
 
   // grid: one block per row (or row group), capped by what is co-resident
-  const uint64_t work = (algo == kAlgoLocal || algo == kAlgoOneShotLamport) ? uint64_t(p.tokens) : groups;
+  const uint64_t work =
+      (algo == kAlgoLocal || algo == kAlgoOneShotLamport || algo == kAlgoNvlsOneShot) ? uint64_t(p.tokens) : groups;
   int dev = 0, ndev = 0;
   int sms = 148, per_sm = 1;  // planning without a device (dry runs) assumes one block per B200 SM
   if (cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0) {
@@ -166,7 +178,8 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
   }
   uint64_t cap = uint64_t(per_sm) * sms;
   if (emu_ranks > 0) cap /= emu_ranks;
-  if (algo == kAlgoTwoShotBarrier && cap > uint64_t(kMaxBarrierBlocks)) cap = kMaxBarrierBlocks;
+  const bool uses_flags = algo == kAlgoTwoShotBarrier || algo == kAlgoNvlsOneShot || algo == kAlgoNvlsTwoShot;
+  if (uses_flags && cap > uint64_t(kMaxBarrierBlocks)) cap = kMaxBarrierBlocks;
   if (cap == 0) return "too many emulated ranks for one cooperative launch";
   uint64_t grid = work < cap ? work : cap;
   if (grid == 0) grid = 1;

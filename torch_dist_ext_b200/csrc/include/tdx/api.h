@@ -78,9 +78,12 @@ class Workspace {
  public:
   // `device` < 0 keeps the current device. `max_message_bytes` bounds one rank's message on
   // the flag-barrier path; `lamport_bytes` is the capacity of each of the three Lamport buffers
-  // (0 = default).
+  // (0 = default). `multicast`: 1 = allocate through the virtual-memory API, share by POSIX file
+  // descriptor and bind to an NVSwitch multicast object (needed by the NVLS kernels; falls back
+  // to plain cudaIpc sharing when the device or the container does not allow it), 0 = cudaMalloc
+  // + cudaIpc, -1 = decide from the TDX_NVLS environment variable (default on) and world size.
   Workspace(int rank, int world_size, int nblocks, uint64_t max_message_bytes,
-            uint64_t lamport_bytes = 0, int device = -1);
+            uint64_t lamport_bytes = 0, int device = -1, int multicast = -1);
   ~Workspace();
   Workspace(const Workspace&) = delete;
   Workspace& operator=(const Workspace&) = delete;
@@ -103,6 +106,11 @@ class Workspace {
   void reset();
   WorkspaceStats stats() const;       // synchronises the device
   uint32_t errors_seen() const;       // non-blocking: reads the host-mapped status mirror
+  // Drop the multicast mapping from the table (all ranks must agree; used when some rank could
+  // not join the multicast object). The NVLS algorithms are then refused by the planner.
+  void disable_multicast();
+  bool has_multicast() const { return table_host_.mc_base != nullptr; }
+  const std::string& multicast_note() const { return mc_note_; }
   void set_timeout_ns(uint64_t t) { timeout_ns_ = t; }
   uint64_t timeout_ns() const { return timeout_ns_; }
   int rank() const { return rank_; }
@@ -126,6 +134,11 @@ class Workspace {
   uint32_t* host_status_dev_ = nullptr;
   uint64_t timeout_ns_;
   bool registered_ = false;
+  struct Vmm;                // virtual-memory / multicast state (workspace.cu)
+  Vmm* vmm_ = nullptr;
+  std::string mc_note_;      // why multicast is off, when it is
+  void release_vmm();
+  void upload_table();
 };
 
 // Every (device, peer) pair of this process: check and enable peer access. Returns the number

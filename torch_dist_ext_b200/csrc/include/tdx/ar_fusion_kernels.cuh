@@ -601,6 +601,155 @@ __device__ __forceinline__ void twoshot_barrier_body(const ArParams& p) {
   finish_launch(ctl, false, 0, 0, 2);
 }
 
+// ---- NVLS (NVSwitch multicast) ---------------------------------------------------------------
+// Every rank's symmetric allocation is bound to one multicast object; `mc_base` addresses all
+// copies at once. multimem.ld_reduce returns the sum over ranks computed inside the switch
+// (fp32 accumulation for 16-bit types, one rounding to T; the order of the additions is the
+// switch's). The input is first copied into the NVLS staging buffer selected by the parity of the
+// barrier epoch, so that a rank that runs ahead never overwrites data a peer is still reducing.
+
+template <typename T>
+__device__ __forceinline__ uint4 mc_ld_reduce(const void* mc_addr) {
+  if constexpr (sizeof(T) == 4) return ptx::multimem_ld_reduce_f32x4(mc_addr);
+  else if constexpr (VecTraits<T>::kDType == kF16) return ptx::multimem_ld_reduce_f16x8(mc_addr);
+  else return ptx::multimem_ld_reduce_bf16x8(mc_addr);
+}
+
+__device__ __forceinline__ size_t nvls_in_offset(const Layout& l, uint32_t bepoch) {
+  return l.off_nvls + (size_t)(bepoch & 1u) * l.nvls_in_bytes;
+}
+
+template <typename T, int kVpt>
+__device__ __forceinline__ void nvls_copy_in_row(const ArParams& p, const RowView<T, kVpt>& rv, char* dst_base, int row) {
+  const char* in = static_cast<const char*>(p.in);
+#pragma unroll
+  for (int v = 0; v < kVpt; ++v) {
+    if (!rv.active(v)) continue;
+    const size_t off = (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16;
+    ptx::st_v4(dst_base + off, ptx::ld_stream_v4(in + off));
+  }
+}
+
+template <typename T, int kN, int kVpt, int kOut>
+__device__ __forceinline__ void nvls_oneshot_body(const ArParams& p) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  __shared__ float red[4][32];
+  const RowView<T, kVpt> rv(p.hidden);
+  char* self = static_cast<char*>(p.peer[p.rank]);
+  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
+  const uint32_t bepoch = ctl->barrier_epoch;
+  const size_t in_off = nvls_in_offset(p.layout, bepoch);
+  Waiter w(p.timeout_ns);
+
+  for (int row = blockIdx.x; row < p.tokens; row += gridDim.x) nvls_copy_in_row<T, kVpt>(p, rv, self + in_off, row);
+  flag_barrier(p, ctl, bepoch + 1u, w, 1);
+
+  uint4 gamma[kVpt];
+  load_gamma<T, kVpt>(p, rv, gamma);
+  const char* mc_in = static_cast<const char*>(p.mc_base) + in_off;
+  int parity = 0;
+  for (int row = blockIdx.x; row < p.tokens; row += gridDim.x, parity ^= 1) {
+    float x[kVpt][kVec];
+#pragma unroll
+    for (int v = 0; v < kVpt; ++v) {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
+      if (!rv.active(v)) continue;
+      const size_t off = (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16;
+      unpack<T>(mc_ld_reduce<T>(mc_in + off), x[v]);
+      add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) + off : nullptr);
+      if (p.residual_out) ptx::st_stream_v4(static_cast<char*>(p.residual_out) + off, pack<T>(x[v]));
+    }
+    float rstd, sc;
+    finish_row<T, kVpt, kOut>(p, rv, row, x, gamma, red, parity, rstd, sc);
+  }
+  finish_launch(ctl, false, 0, 0, 1);
+}
+
+template <typename T, int kN, int kVpt, int kOut>
+__device__ __forceinline__ void nvls_twoshot_body(const ArParams& p) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  __shared__ float red[4][32];
+  const int nranks = kN > 0 ? kN : p.nranks;
+  const RowView<T, kVpt> rv(p.hidden);
+  char* self = static_cast<char*>(p.peer[p.rank]);
+  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
+  const uint32_t bepoch = ctl->barrier_epoch;
+  const size_t in_off = nvls_in_offset(p.layout, bepoch);
+  const size_t result_off = p.layout.off_nvls + 2 * p.layout.nvls_in_bytes;
+  const size_t trailer_off = (size_t)p.tokens * rv.row_bytes;
+  const int groups = (p.tokens + nranks - 1) / nranks;
+  const bool gather_back = p.scatter_only == 0;
+  Waiter w(p.timeout_ns);
+
+  for (int j = blockIdx.x; j < groups; j += gridDim.x)
+    for (int r = 0; r < nranks; ++r)
+      if (j * nranks + r < p.tokens) nvls_copy_in_row<T, kVpt>(p, rv, self + in_off, j * nranks + r);
+  flag_barrier(p, ctl, bepoch + 1u, w, 1);
+
+  uint4 gamma[kVpt];
+  load_gamma<T, kVpt>(p, rv, gamma);
+  const char* mc_in = static_cast<const char*>(p.mc_base) + in_off;
+  char* mc_result = static_cast<char*>(p.mc_base) + result_off;
+  int parity = 0;
+  for (int j = blockIdx.x; j < groups; j += gridDim.x) {
+    const int row = j * nranks + p.rank;
+    if (row >= p.tokens) continue;
+    const int64_t out_row = gather_back ? row : j;
+    float x[kVpt][kVec];
+#pragma unroll
+    for (int v = 0; v < kVpt; ++v) {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
+      if (!rv.active(v)) continue;
+      const size_t voff = (size_t)rv.vec_index(v) * 16;
+      unpack<T>(mc_ld_reduce<T>(mc_in + (size_t)row * rv.row_bytes + voff), x[v]);
+      add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) +
+                                                (size_t)out_row * rv.row_bytes + voff
+                                          : nullptr);
+      const uint4 packed = pack<T>(x[v]);
+      if (p.residual_out)
+        ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)out_row * rv.row_bytes + voff, packed);
+      // one store, replicated by the switch into every rank's result area (this rank's included)
+      if (gather_back) ptx::multimem_st_v4(mc_result + (size_t)row * rv.row_bytes + voff, packed);
+    }
+    float rstd, sc;
+    finish_row<T, kVpt, kOut>(p, rv, out_row, x, gamma, red, parity, rstd, sc);
+    parity ^= 1;
+    if (gather_back && threadIdx.x == 0)
+      ptx::multimem_st_v4(mc_result + trailer_off + (size_t)row * 16,
+                          make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u));
+  }
+  if (gather_back) {
+    flag_barrier(p, ctl, bepoch + 2u, w, 2);
+    const char* result = self + result_off;
+    for (int j = blockIdx.x; j < groups; j += gridDim.x) {
+      for (int r = 0; r < nranks; ++r) {
+        const int row = j * nranks + r;
+        if (r == p.rank || row >= p.tokens) continue;
+        const uint4 trailer = ptx::ld_volatile_v4(result + trailer_off + (size_t)row * 16);
+        const float rstd = __uint_as_float(trailer.x);
+        const float sc = __uint_as_float(trailer.y);
+        float x[kVpt][kVec];
+#pragma unroll
+        for (int v = 0; v < kVpt; ++v) {
+#pragma unroll
+          for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
+          if (!rv.active(v)) continue;
+          const size_t voff = (size_t)rv.vec_index(v) * 16;
+          const uint4 val = ptx::ld_volatile_v4(result + (size_t)row * rv.row_bytes + voff);
+          unpack<T>(val, x[v]);
+          if (p.residual_out)
+            ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)row * rv.row_bytes + voff, val);
+        }
+        if (kOut == kOutFp8Token && threadIdx.x == 0) p.scale_out[row] = sc;
+        store_norm<T, kVpt, kOut>(p, rv, row, x, gamma, rstd, sc);
+      }
+    }
+  }
+  finish_launch(ctl, false, 0, 0, gather_back ? 2 : 1);
+}
+
 // ---- kernel wrappers ---------------------------------------------------------------------
 
 template <typename T, int kAlgo, int kN, int kVpt, int kOut>
@@ -609,6 +758,8 @@ __device__ __forceinline__ void ar_dispatch_body(const ArParams& p) {
   else if constexpr (kAlgo == kAlgoOneShotLamport) oneshot_lamport_body<T, kN, kVpt, kOut>(p);
   else if constexpr (kAlgo == kAlgoTwoShotLamport) twoshot_lamport_body<T, kN, kVpt, kOut>(p);
   else if constexpr (kAlgo == kAlgoTwoShotBarrier) twoshot_barrier_body<T, kN, kVpt, kOut>(p);
+  else if constexpr (kAlgo == kAlgoNvlsOneShot) nvls_oneshot_body<T, kN, kVpt, kOut>(p);
+  else if constexpr (kAlgo == kAlgoNvlsTwoShot) nvls_twoshot_body<T, kN, kVpt, kOut>(p);
 }
 
 // kVpt == 1 kernels may run with up to 1024 threads (64 registers); wider rows use at most

@@ -13,10 +13,15 @@ namespace tdx_torch {
 class CommWorkspace : public torch::CustomClassHolder {
  public:
   CommWorkspace(int64_t rank, int64_t world_size, int64_t nblocks, int64_t size_in_bytes);
+  CommWorkspace(int64_t rank, int64_t world_size, int64_t nblocks, int64_t size_in_bytes, int64_t lamport_bytes,
+                int64_t device, int64_t multicast);
   at::Tensor get_handle();
   void open_handles(std::vector<at::Tensor> handles);
   at::Tensor get_workspace(const at::Tensor& ref);
   void reset();
+  bool has_multicast();
+  void disable_multicast();
+  std::string multicast_note();
   void set_timeout_ms(int64_t ms);
   int64_t errors_seen();
   std::vector<int64_t> stats();

@@ -29,12 +29,15 @@ struct Layout {
   uint64_t off_flags;     // uint32 flags[kMaxBarrierBlocks][kMaxRanks], written by peers
   uint64_t off_lamport;   // 3 x lamport_bytes, sentinel-initialised
   uint64_t lamport_bytes; // capacity of ONE of the three Lamport buffers
-  uint64_t off_stage;     // flag-synchronised staging (two-shot / NVLS paths)
+  uint64_t off_stage;     // flag-synchronised staging of the peer-to-peer two-shot path
   uint64_t stage_bytes;
+  uint64_t off_nvls;      // NVLS: two input staging buffers (by barrier-epoch parity) + result area
+  uint64_t nvls_in_bytes; // capacity of one NVLS input buffer (0: no NVLS region)
+  uint64_t nvls_bytes;
   uint64_t total_bytes;
 };
 
-inline Layout make_layout(uint64_t max_message_bytes, uint64_t lamport_bytes) {
+inline Layout make_layout(uint64_t max_message_bytes, uint64_t lamport_bytes, bool with_nvls = false) {
   auto align_up = [](uint64_t v, uint64_t a) { return (v + a - 1) / a * a; };
   Layout l{};
   l.off_control = 0;
@@ -44,7 +47,10 @@ inline Layout make_layout(uint64_t max_message_bytes, uint64_t lamport_bytes) {
   l.off_stage = l.off_lamport + 3 * l.lamport_bytes;
   // gather area + result area + per-row trailers and row padding
   l.stage_bytes = align_up(2 * max_message_bytes + max_message_bytes / 8 + (1 << 20), 1 << 16);
-  l.total_bytes = align_up(l.off_stage + l.stage_bytes, 1 << 21);
+  l.off_nvls = l.off_stage + l.stage_bytes;
+  l.nvls_in_bytes = with_nvls ? align_up(max_message_bytes, 1 << 16) : 0;
+  l.nvls_bytes = with_nvls ? 2 * l.nvls_in_bytes + align_up(max_message_bytes + max_message_bytes / 8 + (1 << 20), 1 << 16) : 0;
+  l.total_bytes = align_up(l.off_nvls + l.nvls_bytes, 1 << 21);
   return l;
 }
 

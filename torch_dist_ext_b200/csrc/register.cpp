@@ -29,12 +29,23 @@ int dtype_code(at::ScalarType t) {
 
 namespace tdx_torch {
 
-CommWorkspace::CommWorkspace(int64_t rank, int64_t world_size, int64_t nblocks, int64_t size_in_bytes) {
+CommWorkspace::CommWorkspace(int64_t rank, int64_t world_size, int64_t nblocks, int64_t size_in_bytes)
+    : CommWorkspace(rank, world_size, nblocks, size_in_bytes, 0, -1, -1) {}
+
+CommWorkspace::CommWorkspace(int64_t rank, int64_t world_size, int64_t nblocks, int64_t size_in_bytes,
+                             int64_t lamport_bytes, int64_t device, int64_t multicast) {
   try {
-    impl_ = std::make_unique<tdx::Workspace>((int)rank, (int)world_size, (int)nblocks, (uint64_t)size_in_bytes);
+    impl_ = std::make_unique<tdx::Workspace>((int)rank, (int)world_size, (int)nblocks, (uint64_t)size_in_bytes,
+                                             (uint64_t)lamport_bytes, (int)device, (int)multicast);
   } catch (const std::exception& e) {
     TORCH_CHECK(false, "CommWorkspace: ", e.what());
   }
+}
+
+c10::intrusive_ptr<CommWorkspace> create_workspace(int64_t rank, int64_t world_size, int64_t nblocks,
+                                                   int64_t size_in_bytes, int64_t lamport_bytes, int64_t device,
+                                                   int64_t multicast) {
+  return c10::make_intrusive<CommWorkspace>(rank, world_size, nblocks, size_in_bytes, lamport_bytes, device, multicast);
 }
 
 Tensor CommWorkspace::get_handle() {
@@ -72,6 +83,9 @@ Tensor CommWorkspace::get_workspace(const Tensor& ref) {
 }
 
 void CommWorkspace::reset() { impl_->reset(); }
+bool CommWorkspace::has_multicast() { return impl_->has_multicast(); }
+void CommWorkspace::disable_multicast() { impl_->disable_multicast(); }
+std::string CommWorkspace::multicast_note() { return impl_->multicast_note(); }
 void CommWorkspace::set_timeout_ms(int64_t ms) { impl_->set_timeout_ns((uint64_t)ms * 1000000ull); }
 int64_t CommWorkspace::errors_seen() { return impl_->errors_seen(); }
 
@@ -258,7 +272,13 @@ TORCH_LIBRARY(torch_dist_ext, m) {
       .def("reset", &CommWorkspace::reset)
       .def("set_timeout_ms", &CommWorkspace::set_timeout_ms)
       .def("errors_seen", &CommWorkspace::errors_seen)
-      .def("stats", &CommWorkspace::stats);
+      .def("stats", &CommWorkspace::stats)
+      .def("has_multicast", &CommWorkspace::has_multicast)
+      .def("disable_multicast", &CommWorkspace::disable_multicast)
+      .def("multicast_note", &CommWorkspace::multicast_note);
+  m.def("create_workspace(int rank, int world_size, int nblocks, int size_in_bytes, int lamport_bytes, int device, "
+        "int multicast) -> __torch__.torch.classes.torch_dist_ext.CommWorkspace", &tdx_torch::create_workspace);
+  m.def("table_nbytes() -> int", []() -> int64_t { return (int64_t)sizeof(tdx::CommTable); });
   m.def("connect_local(__torch__.torch.classes.torch_dist_ext.CommWorkspace[] workspaces) -> ()", &tdx_torch::connect_local);
   m.def(
       "allreduce_rms_fusion(SymInt rank, SymInt nranks, Tensor allreduce_in, Tensor residual_in, Tensor rms_gamma, "

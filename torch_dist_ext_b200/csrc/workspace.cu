@@ -1,20 +1,35 @@
-// Symmetric-workspace manager: allocates one peer-mappable buffer per rank, exports and
-// opens cudaIpc handles, keeps the pointer table resident on the device, initialises flags
-// and sentinels with a kernel, mirrors the error record into host-mapped memory and closes
-// what it opened.
+// Symmetric-workspace manager: allocates one peer-mappable buffer per rank, shares it with the
+// peers, keeps the pointer table resident on the device, initialises flags and sentinels with a
+// kernel, mirrors the error record into host-mapped memory and releases what it mapped.
 //
 // Reference counterpart: class CommWorkspace (src/ops/all_reduce_fusion.cpp:63-174) and
 // enable_p2p (src/common/collectives.h:5-19). Differences by design: the table is uploaded
 // once at registration (the reference rebuilds and copies it on every get_workspace call,
 // :159-173); flags are zeroed and sentinels written by a device kernel at construction and by
 // reset() (the reference never zeroes its barrier flags and re-fills sentinels with a blocking
-// host copy whenever the dtype changes, :143-158); IPC mappings are closed in the destructor;
+// host copy whenever the dtype changes, :143-158); mappings are released in the destructor;
 // sizes are 64-bit; the CUDA device is explicit instead of being equal to the rank.
+//
+// Two sharing tiers:
+//  A  cudaMalloc + cudaIpcGetMemHandle / cudaIpcOpenMemHandle (what the reference does).
+//  B  cuMemCreate with a POSIX-fd shareable handle; fds travel between processes over an abstract
+//     Unix-domain socket (SCM_RIGHTS) served by a small thread of the exporting rank; every rank
+//     binds its allocation to ONE multicast object created by rank 0, which gives the NVLS kernels
+//     an address whose loads reduce, and whose stores replicate, inside the NVSwitch.
+// Tier B falls back to tier A when any step is refused (no multicast support, no fd export).
+#include <cuda.h>
+#include <poll.h>
+#include <sys/socket.h>
+#include <sys/un.h>
 #include <unistd.h>
+#include <atomic>
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
 #include <stdexcept>
+#include <thread>
 #include "tdx/api.h"
 #include "tdx/ptx.cuh"
 #include "tdx/vec.cuh"
@@ -37,8 +52,13 @@ struct HandleBlob {
   int64_t pid;
   uint64_t total_bytes;
   uint64_t local_ptr;  // for same-process registration
-  cudaIpcMemHandle_t ipc;
-  uint8_t pad[kHandleBytes - 8 - 4 - 4 - 8 - 8 - 8 - sizeof(cudaIpcMemHandle_t)];
+  union {
+    cudaIpcMemHandle_t ipc;   // tier A
+    char socket_name[64];     // tier B: abstract Unix socket that serves this rank's fds
+  };
+  int32_t tier;               // 0 = cudaIpc, 1 = VMM allocation shared by POSIX fd
+  int32_t has_multicast;      // rank 0 only: a multicast object exists and its fd is served
+  uint8_t pad[kHandleBytes - 8 - 4 - 4 - 8 - 8 - 8 - 64 - 4 - 4];
 };
 static_assert(sizeof(HandleBlob) == kHandleBytes, "handle blob size");
 
@@ -74,10 +94,154 @@ struct DeviceGuard {
   }
 };
 
+// ---- driver entry points (resolved at run time: the library does not link libcuda) -----------
+struct Driver {
+  decltype(&cuMemCreate) MemCreate = nullptr;
+  decltype(&cuMemRelease) MemRelease = nullptr;
+  decltype(&cuMemAddressReserve) MemAddressReserve = nullptr;
+  decltype(&cuMemAddressFree) MemAddressFree = nullptr;
+  decltype(&cuMemMap) MemMap = nullptr;
+  decltype(&cuMemUnmap) MemUnmap = nullptr;
+  decltype(&cuMemSetAccess) MemSetAccess = nullptr;
+  decltype(&cuMemGetAllocationGranularity) MemGetAllocationGranularity = nullptr;
+  decltype(&cuMemExportToShareableHandle) MemExportToShareableHandle = nullptr;
+  decltype(&cuMemImportFromShareableHandle) MemImportFromShareableHandle = nullptr;
+  decltype(&cuMulticastCreate) MulticastCreate = nullptr;
+  decltype(&cuMulticastAddDevice) MulticastAddDevice = nullptr;
+  decltype(&cuMulticastBindMem) MulticastBindMem = nullptr;
+  decltype(&cuMulticastUnbind) MulticastUnbind = nullptr;
+  decltype(&cuMulticastGetGranularity) MulticastGetGranularity = nullptr;
+  decltype(&cuDeviceGetAttribute) DeviceGetAttribute = nullptr;
+  decltype(&cuDeviceGet) DeviceGet = nullptr;
+  bool ok = false;
+
+  template <typename F>
+  bool get(const char* name, F& fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    fn = reinterpret_cast<F>(p);
+    return true;
+  }
+  Driver() {
+    ok = get("cuMemCreate", MemCreate) && get("cuMemRelease", MemRelease) &&
+         get("cuMemAddressReserve", MemAddressReserve) && get("cuMemAddressFree", MemAddressFree) &&
+         get("cuMemMap", MemMap) && get("cuMemUnmap", MemUnmap) && get("cuMemSetAccess", MemSetAccess) &&
+         get("cuMemGetAllocationGranularity", MemGetAllocationGranularity) &&
+         get("cuMemExportToShareableHandle", MemExportToShareableHandle) &&
+         get("cuMemImportFromShareableHandle", MemImportFromShareableHandle) &&
+         get("cuMulticastCreate", MulticastCreate) && get("cuMulticastAddDevice", MulticastAddDevice) &&
+         get("cuMulticastBindMem", MulticastBindMem) && get("cuMulticastUnbind", MulticastUnbind) &&
+         get("cuMulticastGetGranularity", MulticastGetGranularity) &&
+         get("cuDeviceGetAttribute", DeviceGetAttribute) && get("cuDeviceGet", DeviceGet);
+  }
+};
+Driver& driver() {
+  static Driver d;
+  return d;
+}
+
+// ---- fd passing over an abstract Unix-domain socket ------------------------------------------
+socklen_t abstract_addr(sockaddr_un* addr, const char* name) {
+  std::memset(addr, 0, sizeof(*addr));
+  addr->sun_family = AF_UNIX;
+  const size_t n = std::strlen(name);
+  std::memcpy(addr->sun_path + 1, name, n);  // sun_path[0] == 0: abstract namespace
+  return (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
+}
+
+bool send_fd(int sock, int fd) {
+  char byte = 'f';
+  iovec iov{&byte, 1};
+  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int))] = {};
+  msghdr msg{};
+  msg.msg_iov = &iov;
+  msg.msg_iovlen = 1;
+  msg.msg_control = ctrl;
+  msg.msg_controllen = sizeof(ctrl);
+  cmsghdr* c = CMSG_FIRSTHDR(&msg);
+  c->cmsg_level = SOL_SOCKET;
+  c->cmsg_type = SCM_RIGHTS;
+  c->cmsg_len = CMSG_LEN(sizeof(int));
+  std::memcpy(CMSG_DATA(c), &fd, sizeof(int));
+  return sendmsg(sock, &msg, 0) == 1;
+}
+
+int recv_fd(int sock) {
+  char byte = 0;
+  iovec iov{&byte, 1};
+  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int))] = {};
+  msghdr msg{};
+  msg.msg_iov = &iov;
+  msg.msg_iovlen = 1;
+  msg.msg_control = ctrl;
+  msg.msg_controllen = sizeof(ctrl);
+  if (recvmsg(sock, &msg, 0) != 1) return -1;
+  cmsghdr* c = CMSG_FIRSTHDR(&msg);
+  if (c == nullptr || c->cmsg_level != SOL_SOCKET || c->cmsg_type != SCM_RIGHTS) return -1;
+  int fd = -1;
+  std::memcpy(&fd, CMSG_DATA(c), sizeof(int));
+  return fd;
+}
+
+// Ask the rank that listens on `name` for its memory fd ('m') or the multicast fd ('c').
+int request_fd(const char* name, char what) {
+  sockaddr_un addr;
+  const socklen_t len = abstract_addr(&addr, name);
+  for (int attempt = 0; attempt < 200; ++attempt) {
+    int s = socket(AF_UNIX, SOCK_STREAM, 0);
+    if (s < 0) return -1;
+    if (connect(s, reinterpret_cast<sockaddr*>(&addr), len) == 0) {
+      int fd = -1;
+      if (write(s, &what, 1) == 1) fd = recv_fd(s);
+      close(s);
+      return fd;
+    }
+    close(s);
+    std::this_thread::sleep_for(std::chrono::milliseconds(25));
+  }
+  return -1;
+}
+
 }  // namespace
 
+struct Workspace::Vmm {
+  size_t size = 0;                 // mapped bytes (total_bytes rounded up to the granularity)
+  CUmemGenericAllocationHandle mem = 0;
+  int mem_fd = -1;
+  CUmemGenericAllocationHandle mc = 0;
+  bool mc_created = false, mc_bound = false;
+  int mc_fd = -1;
+  CUdeviceptr mc_va = 0;
+  CUmemGenericAllocationHandle peer_mem[kMaxRanks] = {};
+  CUdeviceptr peer_va[kMaxRanks] = {};
+  char socket_name[64] = {};
+  int listen_fd = -1;
+  std::thread server;
+  std::atomic<bool> stop{false};
+
+  void serve() {
+    while (!stop.load()) {
+      pollfd p{listen_fd, POLLIN, 0};
+      if (poll(&p, 1, 100) <= 0) continue;
+      int c = accept(listen_fd, nullptr, nullptr);
+      if (c < 0) continue;
+      char what = 0;
+      if (read(c, &what, 1) == 1) {
+        const int fd = what == 'c' ? mc_fd : mem_fd;
+        if (fd >= 0) send_fd(c, fd);
+      }
+      close(c);
+    }
+  }
+};
+
 Workspace::Workspace(int rank, int world_size, int nblocks, uint64_t max_message_bytes,
-                     uint64_t lamport_bytes, int device)
+                     uint64_t lamport_bytes, int device, int multicast)
     : rank_(rank), world_(world_size), device_(device), nblocks_(nblocks), timeout_ns_(5000000000ull) {
   if (world_size < 1 || world_size > kMaxRanks)
     throw std::invalid_argument("world_size must be between 1 and 8");
@@ -85,8 +249,93 @@ Workspace::Workspace(int rank, int world_size, int nblocks, uint64_t max_message
   if (device_ < 0) TDX_CUDA_CHECK(cudaGetDevice(&device_));
   DeviceGuard guard(device_);
   if (lamport_bytes == 0) lamport_bytes = 32ull << 20;
-  layout_ = make_layout(max_message_bytes, lamport_bytes);
-  TDX_CUDA_CHECK(cudaMalloc(&base_, layout_.total_bytes));
+  if (multicast < 0) {
+    const char* env = std::getenv("TDX_NVLS");
+    multicast = (env == nullptr || (std::strcmp(env, "0") != 0 && std::strcmp(env, "off") != 0 &&
+                                    std::strcmp(env, "false") != 0)) ? 1 : 0;
+  }
+  if (world_size == 1) multicast = 0;
+  // The layout (and with it every offset the peers use) depends only on the request, never on
+  // whether this rank's multicast set-up succeeds, so that all ranks agree.
+  layout_ = make_layout(max_message_bytes, lamport_bytes, multicast != 0);
+
+  if (multicast) {
+    Driver& d = driver();
+    int mc_ok = 0, fd_ok = 0;
+    CUdevice cudev = 0;
+    if (!d.ok) {
+      mc_note_ = "driver entry points for virtual memory / multicast are not available";
+    } else if (d.DeviceGet(&cudev, device_) != CUDA_SUCCESS ||
+               d.DeviceGetAttribute(&mc_ok, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, cudev) != CUDA_SUCCESS ||
+               d.DeviceGetAttribute(&fd_ok, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED, cudev) != CUDA_SUCCESS ||
+               !mc_ok || !fd_ok) {
+      mc_note_ = "device does not support multicast objects or POSIX-fd memory handles";
+    } else {
+      vmm_ = new Vmm();
+      CUmemAllocationProp prop{};
+      prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+      prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+      prop.location.id = device_;
+      prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+      size_t gran = 0, mc_gran = 0;
+      CUmulticastObjectProp mprop{};
+      mprop.numDevices = (unsigned)world_;
+      mprop.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+      mprop.size = layout_.total_bytes;
+      CUresult r = d.MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED);
+      if (r == CUDA_SUCCESS) r = d.MulticastGetGranularity(&mc_gran, &mprop, CU_MULTICAST_GRANULARITY_RECOMMENDED);
+      if (r == CUDA_SUCCESS) {
+        if (mc_gran > gran) gran = mc_gran;
+        vmm_->size = (layout_.total_bytes + gran - 1) / gran * gran;
+        r = d.MemCreate(&vmm_->mem, vmm_->size, &prop, 0);
+      }
+      CUdeviceptr va = 0;
+      if (r == CUDA_SUCCESS) r = d.MemAddressReserve(&va, vmm_->size, gran, 0, 0);
+      if (r == CUDA_SUCCESS) r = d.MemMap(va, vmm_->size, 0, vmm_->mem, 0);
+      CUmemAccessDesc acc{};
+      acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+      acc.location.id = device_;
+      acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+      if (r == CUDA_SUCCESS) r = d.MemSetAccess(va, vmm_->size, &acc, 1);
+      if (r == CUDA_SUCCESS)
+        r = d.MemExportToShareableHandle(&vmm_->mem_fd, vmm_->mem, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+      if (r != CUDA_SUCCESS) {
+        mc_note_ = "virtual-memory allocation or fd export failed (CUresult " + std::to_string((int)r) + ")";
+        if (va) {
+          d.MemUnmap(va, vmm_->size);
+          d.MemAddressFree(va, vmm_->size);
+        }
+        if (vmm_->mem) d.MemRelease(vmm_->mem);
+        delete vmm_;
+        vmm_ = nullptr;
+      } else {
+        base_ = reinterpret_cast<void*>(va);
+        if (rank_ == 0) {
+          mprop.size = vmm_->size;
+          CUresult m = d.MulticastCreate(&vmm_->mc, &mprop);
+          if (m == CUDA_SUCCESS) {
+            vmm_->mc_created = true;
+            m = d.MemExportToShareableHandle(&vmm_->mc_fd, vmm_->mc, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+          }
+          if (m != CUDA_SUCCESS) {
+            mc_note_ = "multicast object could not be created or exported (CUresult " + std::to_string((int)m) + ")";
+            vmm_->mc_fd = -1;
+          }
+        }
+        // listener that hands this rank's fds to the peers
+        std::snprintf(vmm_->socket_name, sizeof(vmm_->socket_name), "tdx-b200-%d-%d-%llx", (int)getpid(), rank_,
+                      (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count());
+        vmm_->listen_fd = socket(AF_UNIX, SOCK_STREAM, 0);
+        sockaddr_un addr;
+        const socklen_t len = abstract_addr(&addr, vmm_->socket_name);
+        if (vmm_->listen_fd < 0 || bind(vmm_->listen_fd, reinterpret_cast<sockaddr*>(&addr), len) != 0 ||
+            listen(vmm_->listen_fd, 32) != 0)
+          throw std::runtime_error("could not open the Unix-domain socket that shares the workspace with the peers");
+        vmm_->server = std::thread([v = vmm_] { v->serve(); });
+      }
+    }
+  }
+  if (vmm_ == nullptr) TDX_CUDA_CHECK(cudaMalloc(&base_, layout_.total_bytes));
   TDX_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&host_status_), 64, cudaHostAllocMapped));
   std::memset(host_status_, 0, 64);
   TDX_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&host_status_dev_), host_status_, 0));
@@ -107,6 +356,41 @@ void Workspace::init_device_state() {
   std::memset(host_status_, 0, 64);
 }
 
+void Workspace::release_vmm() {
+  if (vmm_ == nullptr) return;
+  Driver& d = driver();
+  vmm_->stop.store(true);
+  if (vmm_->server.joinable()) vmm_->server.join();
+  if (vmm_->listen_fd >= 0) close(vmm_->listen_fd);
+  if (vmm_->mc_va) {
+    d.MemUnmap(vmm_->mc_va, vmm_->size);
+    d.MemAddressFree(vmm_->mc_va, vmm_->size);
+  }
+  if (vmm_->mc_bound) {
+    CUdevice cudev = 0;
+    d.DeviceGet(&cudev, device_);
+    d.MulticastUnbind(vmm_->mc, cudev, 0, vmm_->size);
+  }
+  if (vmm_->mc) d.MemRelease(vmm_->mc);
+  for (int r = 0; r < world_; ++r) {
+    if (vmm_->peer_va[r]) {
+      d.MemUnmap(vmm_->peer_va[r], vmm_->size);
+      d.MemAddressFree(vmm_->peer_va[r], vmm_->size);
+    }
+    if (vmm_->peer_mem[r]) d.MemRelease(vmm_->peer_mem[r]);
+  }
+  if (base_) {
+    d.MemUnmap(reinterpret_cast<CUdeviceptr>(base_), vmm_->size);
+    d.MemAddressFree(reinterpret_cast<CUdeviceptr>(base_), vmm_->size);
+    base_ = nullptr;
+  }
+  if (vmm_->mem) d.MemRelease(vmm_->mem);
+  if (vmm_->mem_fd >= 0) close(vmm_->mem_fd);
+  if (vmm_->mc_fd >= 0) close(vmm_->mc_fd);
+  delete vmm_;
+  vmm_ = nullptr;
+}
+
 Workspace::~Workspace() {
   {
     std::lock_guard<std::mutex> lock(g_registry_mu);
@@ -119,7 +403,8 @@ Workspace::~Workspace() {
   for (int r = 0; r < world_; ++r)
     if (opened_[r] && peer_[r]) cudaIpcCloseMemHandle(peer_[r]);
   if (table_dev_) cudaFree(table_dev_);
-  if (base_) cudaFree(base_);
+  if (vmm_) release_vmm();
+  else if (base_) cudaFree(base_);
   if (host_status_) cudaFreeHost(host_status_);
   if (prev >= 0) cudaSetDevice(prev);
 }
@@ -133,7 +418,14 @@ void Workspace::export_handle(uint8_t out[kHandleBytes]) const {
   h.pid = (int64_t)getpid();
   h.total_bytes = layout_.total_bytes;
   h.local_ptr = reinterpret_cast<uint64_t>(base_);
-  TDX_CUDA_CHECK(cudaIpcGetMemHandle(&h.ipc, base_));
+  if (vmm_) {
+    h.tier = 1;
+    std::memcpy(h.socket_name, vmm_->socket_name, sizeof(h.socket_name));
+    h.has_multicast = vmm_->mc_fd >= 0 ? 1 : 0;
+  } else {
+    h.tier = 0;
+    TDX_CUDA_CHECK(cudaIpcGetMemHandle(&h.ipc, base_));
+  }
   std::memcpy(out, &h, sizeof(h));
 }
 
@@ -143,21 +435,30 @@ void Workspace::open_handles(const std::vector<const uint8_t*>& handles) {
                                 "), got " + std::to_string(handles.size()));
   if (registered_) throw std::runtime_error("workspace is already registered");
   DeviceGuard guard(device_);
+  Driver& d = driver();
+  std::vector<HandleBlob> blobs(world_);
   for (int r = 0; r < world_; ++r) {
     if (handles[r] == nullptr) throw std::invalid_argument("missing handle for rank " + std::to_string(r));
-    HandleBlob h;
+    HandleBlob& h = blobs[r];
     std::memcpy(&h, handles[r], sizeof(h));
     if (h.magic != kTableMagic) throw std::invalid_argument("handle " + std::to_string(r) + " is not a workspace handle");
     if (h.rank != r) throw std::invalid_argument("handle at position " + std::to_string(r) + " belongs to rank " + std::to_string(h.rank));
     if (h.total_bytes != layout_.total_bytes)
-      throw std::invalid_argument("rank " + std::to_string(r) + " allocated a workspace of a different size");
+      throw std::invalid_argument("rank " + std::to_string(r) + " allocated a workspace of a different size "
+                                  "(all ranks must pass the same sizes and the same TDX_NVLS setting)");
+    if (h.tier != (vmm_ ? 1 : 0))
+      throw std::invalid_argument("rank " + std::to_string(r) + " shares its workspace differently (cudaIpc versus "
+                                  "file descriptor); set TDX_NVLS=0 on all ranks");
+  }
+  for (int r = 0; r < world_; ++r) {
+    const HandleBlob& h = blobs[r];
     if (r == rank_) {
       peer_[r] = base_;
-    } else if (h.pid == (int64_t)getpid()) {
+    } else if (h.pid == (int64_t)getpid() && (!vmm_ || h.device == device_)) {
       // Same process (several ranks driven by one host process): the pointer is already valid
       // here; an IPC handle cannot be opened by the process that exported it.
-      int can = 0;
       if (h.device != device_) {
+        int can = 0;
         TDX_CUDA_CHECK(cudaDeviceCanAccessPeer(&can, device_, h.device));
         if (!can) throw std::runtime_error("no peer access between devices " + std::to_string(device_) + " and " + std::to_string(h.device));
         cudaError_t e = cudaDeviceEnablePeerAccess(h.device, 0);
@@ -165,9 +466,65 @@ void Workspace::open_handles(const std::vector<const uint8_t*>& handles) {
         cudaGetLastError();
       }
       peer_[r] = reinterpret_cast<void*>(h.local_ptr);
+    } else if (vmm_) {
+      const int fd = request_fd(h.socket_name, 'm');
+      if (fd < 0) throw std::runtime_error("could not obtain the memory handle of rank " + std::to_string(r));
+      CUresult rc = d.MemImportFromShareableHandle(&vmm_->peer_mem[r], reinterpret_cast<void*>((uintptr_t)fd),
+                                                   CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+      close(fd);
+      CUdeviceptr va = 0;
+      if (rc == CUDA_SUCCESS) rc = d.MemAddressReserve(&va, vmm_->size, 0, 0, 0);
+      if (rc == CUDA_SUCCESS) rc = d.MemMap(va, vmm_->size, 0, vmm_->peer_mem[r], 0);
+      CUmemAccessDesc acc{};
+      acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+      acc.location.id = device_;
+      acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+      if (rc == CUDA_SUCCESS) rc = d.MemSetAccess(va, vmm_->size, &acc, 1);
+      if (rc != CUDA_SUCCESS)
+        throw std::runtime_error("mapping the workspace of rank " + std::to_string(r) + " failed (CUresult " + std::to_string((int)rc) + ")");
+      vmm_->peer_va[r] = va;
+      peer_[r] = reinterpret_cast<void*>(va);
     } else {
       TDX_CUDA_CHECK(cudaIpcOpenMemHandle(&peer_[r], h.ipc, cudaIpcMemLazyEnablePeerAccess));
       opened_[r] = true;
+    }
+  }
+  // multicast: import rank 0's object, join it, bind this rank's memory, map it
+  void* mc_base = nullptr;
+  if (vmm_ && world_ > 1) {
+    if (!blobs[0].has_multicast) {
+      if (mc_note_.empty()) mc_note_ = "rank 0 could not create the multicast object";
+    } else {
+      CUresult rc = CUDA_SUCCESS;
+      if (rank_ != 0) {
+        const int fd = request_fd(blobs[0].socket_name, 'c');
+        if (fd < 0) rc = CUDA_ERROR_UNKNOWN;
+        else {
+          rc = d.MemImportFromShareableHandle(&vmm_->mc, reinterpret_cast<void*>((uintptr_t)fd),
+                                              CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+          close(fd);
+        }
+      }
+      CUdevice cudev = 0;
+      if (rc == CUDA_SUCCESS) rc = d.DeviceGet(&cudev, device_);
+      if (rc == CUDA_SUCCESS) rc = d.MulticastAddDevice(vmm_->mc, cudev);
+      // blocks until every rank has added its device
+      if (rc == CUDA_SUCCESS) rc = d.MulticastBindMem(vmm_->mc, 0, vmm_->mem, 0, vmm_->size, 0);
+      if (rc == CUDA_SUCCESS) vmm_->mc_bound = true;
+      CUdeviceptr va = 0;
+      if (rc == CUDA_SUCCESS) rc = d.MemAddressReserve(&va, vmm_->size, 0, 0, 0);
+      if (rc == CUDA_SUCCESS) rc = d.MemMap(va, vmm_->size, 0, vmm_->mc, 0);
+      CUmemAccessDesc acc{};
+      acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+      acc.location.id = device_;
+      acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+      if (rc == CUDA_SUCCESS) rc = d.MemSetAccess(va, vmm_->size, &acc, 1);
+      if (rc == CUDA_SUCCESS) {
+        vmm_->mc_va = va;
+        mc_base = reinterpret_cast<void*>(va);
+      } else {
+        mc_note_ = "joining the multicast object failed (CUresult " + std::to_string((int)rc) + ")";
+      }
     }
   }
   table_host_ = CommTable{};
@@ -175,12 +532,24 @@ void Workspace::open_handles(const std::vector<const uint8_t*>& handles) {
   table_host_.rank = rank_;
   table_host_.nranks = world_;
   for (int r = 0; r < world_; ++r) table_host_.peer[r] = peer_[r];
-  table_host_.mc_base = nullptr;
+  table_host_.mc_base = mc_base;
   table_host_.layout = layout_;
-  TDX_CUDA_CHECK(cudaMemcpy(table_dev_, &table_host_, sizeof(CommTable), cudaMemcpyHostToDevice));
+  upload_table();
   registered_ = true;
   std::lock_guard<std::mutex> lock(g_registry_mu);
   registry()[table_dev_] = this;
+}
+
+void Workspace::upload_table() {
+  DeviceGuard guard(device_);
+  TDX_CUDA_CHECK(cudaMemcpy(table_dev_, &table_host_, sizeof(CommTable), cudaMemcpyHostToDevice));
+}
+
+void Workspace::disable_multicast() {
+  if (table_host_.mc_base == nullptr) return;
+  table_host_.mc_base = nullptr;
+  if (mc_note_.empty()) mc_note_ = "disabled because not every rank could join the multicast object";
+  upload_table();
 }
 
 void Workspace::connect_local(const std::vector<Workspace*>& all) {

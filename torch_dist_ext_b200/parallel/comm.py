@@ -10,6 +10,7 @@ same interface so that the plumbing is testable without GPUs; ``teardown_env`` e
 """
 from __future__ import annotations
 
+import atexit
 import logging
 from typing import List, Optional
 
@@ -48,7 +49,8 @@ class CommProcess:
                 device = torch.cuda.current_device()
         torch.cuda.set_device(device)
         self.device = torch.device("cuda", device)
-        self.comm = _lib.classes().CommWorkspace(rank, world_size, NBLOCKS, size_in_bytes)
+        self.comm = _lib.ops().create_workspace(rank, world_size, NBLOCKS, size_in_bytes, config.lamport_mb << 20,
+                                                device, 1 if (config.nvls and world_size > 1) else 0)
         self.comm.set_timeout_ms(config.timeout_ms)
         if world_size > 1:
             handle = self.comm.get_handle()
@@ -58,6 +60,13 @@ class CommProcess:
             dist.barrier(group=group)
             self.comm.open_handles(handle_list)
             torch.cuda.synchronize(device)
+            # NVLS is used only if EVERY rank joined the multicast object
+            flags: List[Optional[bool]] = [None] * world_size
+            dist.all_gather_object(flags, bool(self.comm.has_multicast()), group=group)
+            if not all(flags) and self.comm.has_multicast():
+                self.comm.disable_multicast()
+            if not all(flags):
+                log.info("NVLS disabled: %s", self.comm.multicast_note() or "a peer could not join the multicast object")
             dist.barrier(group=group)
         for n, (a, b) in config.policy.items():
             _lib.ops().set_policy(n, a, b)
@@ -110,7 +119,7 @@ class CommProcess:
 
 def table_nbytes() -> int:
     """Size of the tensor returned by ``get_workspace`` (the device-resident pointer table)."""
-    return 8 + 4 + 4 + 8 * 8 + 8 + 7 * 8 + 8 * 8
+    return int(_lib.ops().table_nbytes())
 
 
 _comm: Optional[CommProcess] = None
@@ -129,13 +138,23 @@ def setup_env(rank: int, world_size: int, max_size_in_bytes: int = DEFAULT_MAX_B
 
 
 def teardown_env() -> None:
+    """Collective: wait for the device, agree with the peers that nobody is still using the
+    buffers, then unmap and free them (multicast bindings included)."""
     global _comm, _world_size
     if _comm is not None and _comm.is_cuda:
         torch.cuda.synchronize(_comm.device)
         if _comm.world_size > 1 and dist.is_initialized():
-            dist.barrier(group=_comm.group)
+            try:
+                dist.barrier(group=_comm.group)
+            except Exception:  # the group may already be gone at interpreter exit
+                pass
+        _comm.comm = None
+        _comm._table = None
     _comm = None
     _world_size = None
+
+
+atexit.register(teardown_env)
 
 
 def get_comm() -> CommProcess:
@@ -151,8 +170,9 @@ def world_size() -> Optional[int]:
 def local_workspaces(world_size: int, size_in_bytes: int = 16 << 20, timeout_ms: Optional[int] = None):
     """``world_size`` workspaces on the CURRENT device, registered with each other inside this
     process. For the single-GPU emulation of the multi-rank kernels."""
-    cls = _lib.classes().CommWorkspace
-    ws = [cls(r, world_size, NBLOCKS, size_in_bytes) for r in range(world_size)]
+    # multicast off: every emulated rank lives on the same device, which can join a multicast
+    # object only once
+    ws = [_lib.ops().create_workspace(r, world_size, NBLOCKS, size_in_bytes, 0, -1, 0) for r in range(world_size)]
     if world_size > 1:
         _lib.ops().connect_local(ws)
     for w in ws:
