@@ -70,7 +70,8 @@ def device_times_us(fn: Callable[[], None], steps: int, warmup: int, flush: Opti
     """Per-step device time in microseconds: CUDA events around `fn` only; before every step the
     L2 is flushed (if given) and the ranks are aligned on the device. A short device-side delay
     precedes the first event so that the host has queued the whole step before the GPU reaches
-    it: the interval then holds device work only, not Python launch latency."""
+    it: the interval then holds device work only, not Python launch latency. The alignment comes
+    last, so that differing clocks during the delay do not skew the ranks."""
     for _ in range(warmup):
         if flush:
             flush()
@@ -81,8 +82,8 @@ def device_times_us(fn: Callable[[], None], steps: int, warmup: int, flush: Opti
     for _ in range(steps):
         if flush:
             flush()
-        align()
         torch.cuda._sleep(HEAD_START_CYCLES)
+        align()
         a = torch.cuda.Event(enable_timing=True)
         b = torch.cuda.Event(enable_timing=True)
         a.record()
@@ -91,6 +92,35 @@ def device_times_us(fn: Callable[[], None], steps: int, warmup: int, flush: Opti
         pairs.append((a, b))
     torch.cuda.synchronize()
     return [a.elapsed_time(b) * 1e3 for a, b in pairs]
+
+
+def region_time_us(fn: Callable[[], None], steps: int, warmup: int, align: Callable[[], None]) -> float:
+    """Device time per step of `steps` back-to-back calls of `fn`, timed as ONE region with two CUDA
+    events. `fn` must rotate over inputs that together exceed the L2. The stream is first held
+    back by a device-side delay sized from the measured host cost of a call, so that the whole
+    region is queued before the GPU starts it and no host launch latency is inside the interval;
+    the ranks are aligned after the delay."""
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    probe = min(steps, 20)
+    for _ in range(probe):
+        fn()
+    host_s = (time.perf_counter() - t0) / probe      # host-side cost of one call (GPU keeps up or not)
+    torch.cuda.synchronize()
+    clock_hz = 2.0e9
+    cycles = int(min(max(1.5 * host_s * steps, 2e-4), 0.25) * clock_hz)
+    torch.cuda._sleep(cycles)
+    align()
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / steps
 
 
 def pipelined_us(fn: Callable[[], None], calls: int, warmup: int, align: Callable[[], None]) -> float:

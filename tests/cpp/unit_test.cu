@@ -184,7 +184,8 @@ int main(int argc, char** argv) {
         // skip what exceeds this harness's buffer sizes for the chosen algorithm
         const uint64_t msg = (uint64_t)t * h * 4;
         if (algo == tdx::kAlgoOneShotLamport && msg * nranks > (64ull << 20)) continue;
-        if (algo == tdx::kAlgoTwoShotLamport && 2 * msg + 16ull * t + (uint64_t)nranks * h * 4 > (64ull << 20)) continue;
+        const uint64_t groups = ((uint64_t)t + nranks - 1) / nranks;
+        if (algo == tdx::kAlgoTwoShotLamport && groups * nranks * h * 4 + (uint64_t)t * (h * 4 + 16) > (64ull << 20)) continue;
         all_ok &= run_case<float>({t, h, tdx::kF32, algo}, nranks, multi_gpu, ws);
         ++ran;
       }
@@ -194,6 +195,8 @@ int main(int argc, char** argv) {
         if (nranks == 1 && algo != tdx::kAlgoAuto) continue;
         const uint64_t msg = (uint64_t)t * h * 2;
         if (algo == tdx::kAlgoOneShotLamport && msg * nranks > (64ull << 20)) continue;
+        const uint64_t groups = ((uint64_t)t + nranks - 1) / nranks;
+        if (algo == tdx::kAlgoTwoShotLamport && groups * nranks * h * 2 + (uint64_t)t * (h * 2 + 16) > (64ull << 20)) continue;
         all_ok &= run_case<__nv_bfloat16>({t, h, tdx::kBF16, algo}, nranks, multi_gpu, ws);
         ++ran;
       }

@@ -37,6 +37,8 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
             nvls = isinstance(algo, str) and algo.startswith("nvls")
             if nvls and not has_mc:
                 continue
+            # the automatic choice moves large messages onto the NVLS path when there is one
+            nvls = nvls or (algo is None and has_mc and tokens * hidden * torch.finfo(dtype).bits // 8 >= (4 << 20))
             ins, residual, gamma = make_case(world, tokens, hidden, dtype, seed=i)
             exp_norm, exp_res, exp_scale = tdx.reference.fused_allreduce_rms_reference(ins, residual, gamma, 1e-6, out_mode)
             x, r, w = ins[rank].to(dev), residual.to(dev), gamma.to(dev)
@@ -50,13 +52,20 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
                 torch.cuda.synchronize()
                 tdx.check_status()
             if nvls:
-                # the switch adds in its own order: equal up to one rounding step of the dtype
+                # The switch accumulates in fp32 but rounds the sum to the element type in its own way
+                # (results one step below round-to-nearest were observed), so the sum s may differ by one
+                # step of ITS magnitude; that error then passes unchanged through the residual add.
+                step = {torch.float32: 2.0 ** -22, torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}[dtype]
+                sabs = sum(t.float().abs() for t in ins)
                 d = (res.cpu().float() - exp_res.float()).abs()
-                lim = exp_res.float().abs() * {torch.float32: 2e-6, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype] + 1e-6
+                lim = (sabs + exp_res.float().abs()) * step + 1e-6
                 assert bool((d <= lim).all()), f"case {i}: NVLS residual_out off by {d.max().item()} on rank {rank}"
             else:
                 assert torch.equal(res.cpu().float(), exp_res.float()), f"case {i}: residual_out mismatch on rank {rank}"
-            if nvls and out_mode != OUT_SAME:
+            if nvls and out_mode == OUT_SAME:
+                err = (norm.cpu().float() - exp_norm.float()).abs().max().item()
+                assert err <= 4 * tol[dtype] * max(1.0, exp_norm.float().abs().max().item()), f"case {i}: NVLS norm err {err}"
+            elif nvls:
                 back = tdx.reference.dequantize_fp8(norm.cpu(), scales.cpu())
                 want = tdx.reference.dequantize_fp8(exp_norm, exp_scale)
                 assert (back - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -3, f"case {i}: NVLS fp8"

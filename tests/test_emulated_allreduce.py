@@ -96,6 +96,8 @@ def test_reduce_scatter_variant(workspaces, algo, out_mode):
         exp_norm, exp_res, exp_scale = tdx.reference.fused_allreduce_rms_reference(ins, residual, gamma, EPS, out_mode)
         for r in range(4):
             k = exp_res[r::4].shape[0]
+            if k == 0:      # fewer tokens than ranks: this rank owns no row
+                continue
             assert torch.equal(res[r][:k].float(), exp_res[r::4].float())
             if out_mode == OUT_SAME:
                 assert (norm[r][:k].float() - exp_norm[r::4].float()).abs().max().item() <= 3.2e-2 * 4
