@@ -1,0 +1,426 @@
+// tcgen05 / TMEM GEMM for sm_100a:  D[x, y] = sum_k X[x, k] * Y[y, k]   (both operands K-major).
+//
+// One CTA computes a 128 x kBN tile of D. Warp 0 streams operand tiles with TMA into a ring of
+// 128-byte-swizzled shared-memory stages; warp 1 owns the tensor memory and issues tcgen05.mma
+// (one elected thread) into an fp32 accumulator in TMEM; warps 2-5 read the accumulator back with
+// tcgen05.ld and write the output. "X" and "Y" are roles, not matrices: a linear layer
+// out[M, N] = a[M, K] * w[N, K]^T runs either as (X = a, Y = w) for large M, or as (X = w, Y = a)
+// for decode-sized M, so that the weights fill the 128-row dimension of the instruction and the
+// few tokens sit on the narrow N side; the output strides (sx, sy) place D either way round.
+// K can be split over gridDim.z; partial tiles are then reduced in an fp32 workspace with
+// red.global.add and finished by whichever CTA arrives last at the tile.
+//
+// fp8 (e4m3) operands use kind::f8f6f4. With block scales (1x128 on one operand, 128x128 on the
+// other, fp32) each 128-wide K block is multiplied into its own TMEM buffer and promoted by the
+// epilogue warps: acc += partial * x_scale * y_scale, with two TMEM buffers so that the next
+// block's MMAs overlap the promotion.
+//
+// Every mbarrier wait is bounded; a wait that runs out records a status word, raises the CTA's
+// abort flag, lets copies in flight land, frees the tensor memory and returns.
+//
+// The reference (xytpai/torch_dist_ext) has no GEMM; this kernel exists for the tensor-parallel
+// decoder layers around its fused all-reduce.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <mutex>
+#include "tdx/comm.h"
+#include "tdx/gemm.h"
+#include "tdx/tc.cuh"
+
+namespace tdx {
+namespace {
+
+constexpr int kBM = 128;          // tile rows (tcgen05.mma M)
+constexpr int kSwizzleBytes = 128; // one K block = 128 bytes per row (64 bf16 / 128 fp8)
+constexpr int kThreads = 192;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+struct GemmArgs {
+  int x_rows, y_rows;
+  int kblocks;             // K / (128 / elem_size)
+  int kblocks_per_split;
+  void* out;
+  int64_t sx, sy;          // D[x, y] -> out[x * sx + y * sy]
+  int out_dtype;           // kF32 / kF16 / kBF16
+  uint32_t idesc;
+  float* ws;               // split-K: fp32 [x_tiles*128, ws_ld], zero on entry and on exit
+  int ws_ld;
+  uint32_t* counters;      // split-K: one per output tile, zero on entry and on exit
+  uint32_t* status;        // device word: non-zero after a wait ran out
+  // block scales (scaled kernels only); *_per_row: one scale per row and K block, else per 128 rows
+  const float* x_scale;
+  const float* y_scale;
+  int x_scale_per_row, y_scale_per_row;
+  int scale_kb;            // K blocks per scale row (= total K / 128)
+};
+
+template <int kBN, int kStages>
+struct SmemLayout {
+  static constexpr int kXBytes = kBM * kSwizzleBytes;
+  static constexpr int kYBytes = kBN * kSwizzleBytes;
+  static constexpr int kStageBytes = kXBytes + kYBytes;
+  static constexpr int kBarrierOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarrierOffset + 1024 /*barriers + scratch*/ + 1024 /*alignment slack*/;
+};
+
+__device__ __forceinline__ void store_out(const GemmArgs& a, int64_t idx, float v) {
+  if (a.out_dtype == kBF16) static_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16(v);
+  else if (a.out_dtype == kF16) static_cast<__half*>(a.out)[idx] = __float2half(v);
+  else static_cast<float*>(a.out)[idx] = v;
+}
+
+// Writes 16 consecutive y columns of row x (values already final).
+__device__ __forceinline__ void store_chunk(const GemmArgs& a, int x, int y0, const float (&v)[16]) {
+  if (x >= a.x_rows) return;
+  if (a.sy == 1 && a.out_dtype != kF32 && y0 + 16 <= a.y_rows && ((a.sx * 2) % 16 == 0) && (y0 % 8 == 0) &&
+      (reinterpret_cast<uintptr_t>(a.out) % 16 == 0)) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (a.out_dtype == kBF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(a.out) + ((int64_t)x * a.sx + y0) * 2);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (y0 + i < a.y_rows) store_out(a, (int64_t)x * a.sx + (int64_t)(y0 + i) * a.sy, v[i]);
+  }
+}
+
+template <int kBN, int kStages, bool kFp8, bool kScaled>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmArgs a) {
+  using L = SmemLayout<kBN, kStages>;
+  constexpr int kElemsPerBlock = kFp8 ? 128 : 64;   // K elements per 128-byte block
+  constexpr uint32_t kTmemCols = kScaled ? (2 * kBN < 32 ? 32 : 2 * kBN) : (kBN < 32 ? 32 : kBN);
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
+  uint64_t* empty = full + kStages;
+  uint64_t* acc_full = empty + kStages;    // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint32_t* last_flag = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_x = blockIdx.x, tile_y = blockIdx.y;
+  const int kb0 = blockIdx.z * a.kblocks_per_split;
+  const int kb1 = min(a.kblocks, kb0 + a.kblocks_per_split);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&full[s], 1);
+      tc::mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&acc_full[i], 1);
+      tc::mbar_init(&acc_empty[i], 128);
+    }
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_x);
+    tc::tma_prefetch_desc(&map_y);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer -------------------------------------------------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % kStages;
+        if (i >= kStages && !tc::mbar_wait(&empty[s], ((i / kStages) - 1) & 1, kWaitLimit, abort_flag)) {
+          *abort_flag = 1;
+          if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
+          break;
+        }
+        uint8_t* sx = smem + s * L::kStageBytes;
+        tc::mbar_arrive_expect_tx(&full[s], L::kStageBytes);
+        tc::tma_load_2d(sx, &map_x, &full[s], (kb0 + i) * kElemsPerBlock, tile_x * kBM);
+        tc::tma_load_2d(sx + L::kXBytes, &map_y, &full[s], (kb0 + i) * kElemsPerBlock, tile_y * kBN);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -----------------------------------------------------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % kStages;
+        if (!tc::mbar_wait(&full[s], (i / kStages) & 1, kWaitLimit, abort_flag)) {
+          *abort_flag = 1;
+          if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
+          break;
+        }
+        uint32_t acc_col = 0;
+        if constexpr (kScaled) {
+          const int buf = i & 1;
+          if (i >= 2 && !tc::mbar_wait(&acc_empty[buf], ((i >> 1) - 1) & 1, kWaitLimit, abort_flag)) {
+            *abort_flag = 1;
+            if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
+            break;
+          }
+          acc_col = buf * kBN;
+        }
+        tc::fence_after_thread_sync();
+        const uint32_t xa = tc::smem_u32(smem + s * L::kStageBytes);
+        const uint64_t dx = tc::make_smem_desc_sw128(xa);
+        const uint64_t dy = tc::make_smem_desc_sw128(xa + L::kXBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // one instruction covers 32 bytes of K; step the start address inside the swizzle span
+          const uint32_t accumulate = kScaled ? (k > 0) : (i > 0 || k > 0);
+          tc::umma<kFp8>(tmem_base + acc_col, dx + (uint64_t)(k * 2), dy + (uint64_t)(k * 2), a.idesc, accumulate);
+        }
+        tc::umma_commit(&empty[s]);                       // stage reusable once these MMAs have read it
+        if constexpr (kScaled) tc::umma_commit(&acc_full[i & 1]);
+      }
+      if constexpr (!kScaled) tc::umma_commit(&acc_full[0]);
+    }
+  } else {
+    // ---- epilogue (warps 2..5): TMEM lane quarter = warp % 4 -----------------------------------------
+    const int q = warp & 3;
+    const int x = tile_x * kBM + q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int y_base = tile_y * kBN;
+    bool ok = true;
+    float acc[kScaled ? kBN : 1];
+    if constexpr (kScaled) {
+#pragma unroll
+      for (int i = 0; i < kBN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int buf = i & 1;
+        ok = tc::mbar_wait(&acc_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        const int kb = kb0 + i;
+        const float xs = a.x_scale[(size_t)(a.x_scale_per_row ? min(x, a.x_rows - 1) : (x < a.x_rows ? x / 128 : 0)) * a.scale_kb + kb];
+#pragma unroll
+        for (int c = 0; c < kBN; c += 16) {
+          float v[16];
+          tc::tmem_ld_16(lane_addr + buf * kBN + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int y = min(y_base + c + j, a.y_rows - 1);
+            const float ys = a.y_scale[(size_t)(a.y_scale_per_row ? y : y / 128) * a.scale_kb + kb];
+            acc[c + j] = fmaf(v[j], xs * ys, acc[c + j]);
+          }
+        }
+        tc::fence_before_thread_sync();
+        tc::mbar_arrive(&acc_empty[buf]);
+      }
+    } else {
+      ok = nkb <= 0 || tc::mbar_wait(&acc_full[0], 0, kWaitLimit, abort_flag);
+      tc::fence_after_thread_sync();
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
+    }
+    const bool split = gridDim.z > 1;
+    if (ok && nkb > 0) {
+#pragma unroll
+      for (int c = 0; c < kBN; c += 16) {
+        float v[16];
+        if constexpr (kScaled) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
+        } else {
+          tc::tmem_ld_16(lane_addr + c, v);
+        }
+        if (!split) {
+          store_chunk(a, x, y_base + c, v);
+        } else {
+          float* dst = a.ws + (size_t)(tile_x * kBM + q * 32 + lane) * a.ws_ld + y_base + c;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) atomicAdd(dst + j, v[j]);
+        }
+      }
+    }
+    if (split) {
+      // the CTA that arrives last at this tile turns the fp32 sums into the output and re-zeroes them
+      __threadfence();
+      tc::named_barrier_sync(1, 128);
+      if (threadIdx.x == 64) {
+        const uint32_t prev = atomicAdd(&a.counters[tile_y * gridDim.x + tile_x], 1u);
+        *last_flag = (prev == gridDim.z - 1) ? 1u : 0u;
+      }
+      tc::named_barrier_sync(1, 128);
+      if (*last_flag) {
+        __threadfence();
+        float* src = a.ws + (size_t)(tile_x * kBM + q * 32 + lane) * a.ws_ld + y_base;
+#pragma unroll
+        for (int c = 0; c < kBN; c += 16) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            v[j] = __ldcg(src + c + j);
+            __stcg(src + c + j, 0.f);
+          }
+          store_chunk(a, x, y_base + c, v);
+        }
+        if (threadIdx.x == 64) a.counters[tile_y * gridDim.x + tile_x] = 0;
+      }
+    }
+  }
+
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // let TMA copies that were already issued land before the CTA's shared memory goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc::fence_after_thread_sync();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major [rows, k] matrix with row pitch ld (elements); box = 128 bytes of K x box_rows rows.
+std::string make_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t ld, int elem_size, int elem_kind,
+                     int box_rows) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
+  if (reinterpret_cast<uintptr_t>(ptr) % 16) return "GEMM operands must be 16-byte aligned";
+  if ((ld * elem_size) % 16) return "GEMM operand row pitch must be a multiple of 16 bytes";
+  const CUtensorMapDataType dt = elem_size == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : elem_kind == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)(ld * elem_size)};
+  const cuuint32_t box[2] = {(cuuint32_t)(kSwizzleBytes / elem_size), (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled failed (CUresult " + std::to_string((int)r) + ")";
+  return "";
+}
+
+template <int kBN, int kStages, bool kFp8, bool kScaled>
+std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
+  using L = SmemLayout<kBN, kStages>;
+  auto kern = gemm_tn_kernel<kBN, kStages, kFp8, kScaled>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal); });
+  // the attribute is per device; set it again cheaply when several devices are used by one process
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    last_dev = dev;
+  }
+  if (attr_err != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(attr_err);
+  kern<<<grid, kThreads, L::kTotal, stream>>>(mx, my, a);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
+}
+
+template <bool kFp8, bool kScaled>
+std::string launch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs& a, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch<16, 10, kFp8, kScaled>(mx, my, a, grid, s);
+    case 32: return launch<32, 8, kFp8, kScaled>(mx, my, a, grid, s);
+    case 64: return launch<64, 8, kFp8, kScaled>(mx, my, a, grid, s);
+    case 128:
+      if constexpr (!kScaled) return launch<128, 6, kFp8, kScaled>(mx, my, a, grid, s);
+      break;
+    case 256:
+      if constexpr (!kScaled) return launch<256, 4, kFp8, kScaled>(mx, my, a, grid, s);
+      break;
+  }
+  return "unsupported tile width";
+}
+
+}  // namespace
+
+int gemm_pick_block_n(int y_rows, bool scaled) {
+  const int cap = scaled ? 64 : 256;   // the promoting epilogue keeps one fp32 accumulator per column in registers
+  for (int bn : {16, 32, 64, 128, 256})
+    if (bn <= cap && y_rows <= bn) return bn;
+  return cap;
+}
+
+std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
+  const bool fp8 = g.elem_size == 1;
+  const bool scaled = g.x_scale != nullptr || g.y_scale != nullptr;
+  if (scaled && !(fp8 && g.x_scale && g.y_scale)) return "block scales need fp8 operands and scales for both of them";
+  const int epb = kSwizzleBytes / g.elem_size;
+  if (g.k <= 0 || g.k % epb) return "K must be a positive multiple of " + std::to_string(epb);
+  if (g.x_rows <= 0 || g.y_rows <= 0) return "";
+  const int bn = g.block_n > 0 ? g.block_n : gemm_pick_block_n(g.y_rows, scaled);
+  GemmArgs a{};
+  a.x_rows = g.x_rows;
+  a.y_rows = g.y_rows;
+  a.kblocks = g.k / epb;
+  int splits = g.splits < 1 ? 1 : g.splits;
+  if (splits > a.kblocks) splits = a.kblocks;
+  a.kblocks_per_split = (a.kblocks + splits - 1) / splits;
+  splits = (a.kblocks + a.kblocks_per_split - 1) / a.kblocks_per_split;
+  a.out = g.out;
+  a.sx = g.sx;
+  a.sy = g.sy;
+  a.out_dtype = g.out_dtype;
+  a.idesc = fp8 ? tc::make_idesc(kBM, bn, 0, 0) : tc::make_idesc(kBM, bn, g.elem_kind == kBF16 ? 1 : 0, g.elem_kind == kBF16 ? 1 : 0);
+  a.status = g.status;
+  const dim3 grid((g.x_rows + kBM - 1) / kBM, (g.y_rows + bn - 1) / bn, splits);
+  if (splits > 1) {
+    if (!g.ws || !g.counters) return "split-K needs a workspace";
+    a.ws_ld = grid.y * bn;
+    if ((size_t)grid.x * kBM * a.ws_ld * sizeof(float) > g.ws_bytes || (size_t)grid.x * grid.y > g.counter_count)
+      return "split-K workspace is too small for this problem";
+    a.ws = g.ws;
+    a.counters = g.counters;
+  }
+  a.x_scale = g.x_scale;
+  a.y_scale = g.y_scale;
+  a.x_scale_per_row = g.x_scale_per_row;
+  a.y_scale_per_row = g.y_scale_per_row;
+  a.scale_kb = a.kblocks;
+  CUtensorMap mx, my;
+  std::string err = make_map(&mx, g.x, g.x_rows, g.k, g.ldx, g.elem_size, g.elem_kind, kBM);
+  if (!err.empty()) return err;
+  err = make_map(&my, g.y, g.y_rows, g.k, g.ldy, g.elem_size, g.elem_kind, bn);
+  if (!err.empty()) return err;
+  if (fp8) return scaled ? launch_bn<true, true>(bn, mx, my, a, grid, stream) : launch_bn<true, false>(bn, mx, my, a, grid, stream);
+  return launch_bn<false, false>(bn, mx, my, a, grid, stream);
+}
+
+}  // namespace tdx

@@ -3,6 +3,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include "tdx/bindings.h"
+#include "tdx/gemm.h"
 #include "tdx/ops.h"
 
 namespace tdx_torch {
@@ -94,7 +95,62 @@ void rope_(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin_ca
   TORCH_CHECK(err.empty(), "rope: ", err);
 }
 
+// D[x, y] = sum_k X[x, k] * Y[y, k] written to out.flatten()[x * sx + y * sy] (tcgen05 GEMM).
+void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, int64_t block_n, int64_t splits,
+             const c10::optional<Tensor>& ws, const c10::optional<Tensor>& counters, const c10::optional<Tensor>& status,
+             const c10::optional<Tensor>& x_scale, const c10::optional<Tensor>& y_scale, bool x_scale_per_row,
+             bool y_scale_per_row) {
+  TORCH_CHECK(x.is_cuda() && y.is_cuda() && out.is_cuda() && x.dim() == 2 && y.dim() == 2, "gemm_tn: 2-D CUDA operands expected");
+  TORCH_CHECK(x.stride(1) == 1 && y.stride(1) == 1, "gemm_tn: operands must be K-major (unit stride along K)");
+  TORCH_CHECK(x.size(1) == y.size(1) && x.scalar_type() == y.scalar_type(), "gemm_tn: operands disagree in K or dtype");
+  const c10::cuda::CUDAGuard guard(x.device());
+  tdx::GemmProblem g{};
+  g.x = x.data_ptr();
+  g.y = y.data_ptr();
+  g.x_rows = (int)x.size(0);
+  g.y_rows = (int)y.size(0);
+  g.k = (int)x.size(1);
+  g.ldx = x.stride(0);
+  g.ldy = y.stride(0);
+  g.elem_size = (int)x.element_size();
+  TORCH_CHECK(g.elem_size == 1 || x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf,
+              "gemm_tn: operands must be bfloat16, float16 or float8_e4m3fn");
+  g.elem_kind = x.scalar_type() == at::kHalf ? tdx::kF16 : tdx::kBF16;
+  g.out = out.data_ptr();
+  g.sx = sx;
+  g.sy = sy;
+  g.out_dtype = dtype_code(out);
+  const int64_t max_idx = (g.x_rows - 1) * sx + (g.y_rows - 1) * sy;
+  TORCH_CHECK(g.x_rows == 0 || g.y_rows == 0 || (max_idx < out.numel() && sx >= 1 && sy >= 1), "gemm_tn: output strides exceed the output tensor");
+  g.block_n = (int)block_n;
+  g.splits = (int)splits;
+  if (ws.has_value() && ws->defined()) {
+    TORCH_CHECK(ws->scalar_type() == at::kFloat && counters.has_value() && counters->scalar_type() == at::kInt, "gemm_tn: workspace dtypes");
+    g.ws = ws->data_ptr<float>();
+    g.ws_bytes = (size_t)ws->numel() * 4;
+    g.counters = reinterpret_cast<uint32_t*>(counters->data_ptr<int>());
+    g.counter_count = (size_t)counters->numel();
+  }
+  if (status.has_value() && status->defined()) g.status = reinterpret_cast<uint32_t*>(status->data_ptr<int>());
+  if (x_scale.has_value() && x_scale->defined()) {
+    TORCH_CHECK(y_scale.has_value() && y_scale->defined(), "gemm_tn: both operands need scales");
+    TORCH_CHECK(x_scale->scalar_type() == at::kFloat && y_scale->scalar_type() == at::kFloat && x_scale->is_contiguous() && y_scale->is_contiguous(), "gemm_tn: scales must be contiguous float32");
+    const int64_t kb = g.k / 128;
+    TORCH_CHECK(x_scale->numel() == (x_scale_per_row ? g.x_rows : (g.x_rows + 127) / 128) * kb, "gemm_tn: x_scale has the wrong size");
+    TORCH_CHECK(y_scale->numel() == (y_scale_per_row ? g.y_rows : (g.y_rows + 127) / 128) * kb, "gemm_tn: y_scale has the wrong size");
+    g.x_scale = x_scale->data_ptr<float>();
+    g.y_scale = y_scale->data_ptr<float>();
+    g.x_scale_per_row = x_scale_per_row;
+    g.y_scale_per_row = y_scale_per_row;
+  }
+  const std::string err = tdx::gemm_tn(g, cur_stream());
+  TORCH_CHECK(err.empty(), "gemm_tn: ", err);
+}
+
 void register_extra_ops(torch::Library& m) {
+  m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
+        "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
+        "bool y_scale_per_row) -> ()", &gemm_tn);
   m.def("fused_add_rmsnorm(Tensor x, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
         "Tensor(c!)? scale_out, float eps, int out_mode) -> int", &fused_add_rmsnorm);
   m.def("quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) scales, bool block128) -> ()", &quant_fp8);

@@ -1,2 +1,2 @@
 """Operators: the fused all-reduce family, standalone hot ops, GEMMs and attention."""
-from . import activation, norm, quant, reference, rope  # noqa: F401
+from . import activation, gemm, norm, quant, reference, rope  # noqa: F401

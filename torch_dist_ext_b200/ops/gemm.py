@@ -1,0 +1,108 @@
+"""Linear layers on the 5th-generation tensor cores (tcgen05 / TMEM), bf16 / fp16 / fp8.
+
+``linear(a, w)`` computes ``a @ w.T`` for ``a [M, K]`` and ``w [N, K]`` (the ``nn.Linear`` weight
+layout). Small ``M`` (decode) runs "swapped": the weight rows fill the 128-row side of the MMA
+tile and the tokens its narrow side, so a decode step streams the weights once at full tile
+efficiency; K is split over CTAs until the grid covers the 148 SMs.
+
+``linear_fp8_blockscaled`` multiplies e4m3 activations with 1x128 scales by e4m3 weights with
+128x128 scales (fp32 scales), promoting every 128-wide K block in fp32.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+_SM_COUNT = 148
+_ws = {}
+
+
+def _workspace(device: torch.device):
+    """Per-device split-K scratch: zeroed once; every kernel leaves it zeroed again."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _ws:
+        _ws[key] = (torch.zeros(8 << 20, dtype=torch.float32, device=device),      # 32 MiB
+                    torch.zeros(4096, dtype=torch.int32, device=device),
+                    torch.zeros(1, dtype=torch.int32, device=device))
+    return _ws[key]
+
+
+def pipeline_status(device=None) -> int:
+    """Non-zero if a GEMM pipeline wait ever ran out on this device (reads the device word)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    return int(_workspace(dev)[2].item())
+
+
+def _pick_bn(rows: int, cap: int) -> int:
+    for bn in (16, 32, 64, 128, 256):
+        if bn <= cap and rows <= bn:
+            return bn
+    return cap
+
+
+def plan(m: int, n: int, k: int, elem_size: int = 2, scaled: bool = False) -> Tuple[bool, int, int]:
+    """(swap, block_n, splits) for ``[m, k] x [n, k]^T``."""
+    cap = 64 if scaled else 256
+    swap = m <= 128 if not scaled else True
+    x_rows, y_rows = (n, m) if swap else (m, n)
+    bn = _pick_bn(y_rows, cap)
+    if not swap and n >= 256:
+        bn = 256 if (m // 128) * (n // 256) >= _SM_COUNT else 128
+    tiles = ((x_rows + 127) // 128) * ((y_rows + bn - 1) // bn)
+    kblocks = k // (128 // elem_size)
+    splits = 1
+    if tiles < _SM_COUNT:
+        splits = max(1, min(kblocks // 2 if kblocks >= 2 else 1, _SM_COUNT // tiles))
+    return swap, bn, splits
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *, out_dtype=None,
+           swap: Optional[bool] = None, block_n: int = 0, splits: Optional[int] = None) -> torch.Tensor:
+    """``a [M, K] @ w [N, K]^T -> [M, N]`` (bf16 / fp16 / e4m3 operands, fp32 accumulation)."""
+    assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "linear: a [M, K], w [N, K]"
+    m, k = a.shape
+    n = w.shape[0]
+    p_swap, p_bn, p_splits = plan(m, n, k, a.element_size())
+    swap = p_swap if swap is None else swap
+    if block_n == 0:
+        block_n = p_bn if swap == p_swap else _pick_bn(m if swap else n, 256)
+    splits = p_splits if splits is None else splits
+    if out is None:
+        dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
+        out = torch.empty(m, n, dtype=dt, device=a.device)
+    ws, counters, status = _workspace(a.device)
+    if swap:
+        _lib.ops().gemm_tn(w, a, out, 1, n, block_n, splits, ws, counters, status, None, None, False, False)
+    else:
+        _lib.ops().gemm_tn(a, w, out, n, 1, block_n, splits, ws, counters, status, None, None, False, False)
+    return out
+
+
+def linear_fp8_blockscaled(a_q: torch.Tensor, a_scale: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor,
+                           out: Optional[torch.Tensor] = None, *, out_dtype=torch.bfloat16,
+                           splits: Optional[int] = None) -> torch.Tensor:
+    """``(a_q * a_scale) @ (w_q * w_scale)^T`` with ``a_scale [M, K/128]`` and ``w_scale [N/128, K/128]``."""
+    m, k = a_q.shape
+    n = w_q.shape[0]
+    _, bn, p_splits = plan(m, n, k, 1, scaled=True)
+    splits = p_splits if splits is None else splits
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a_q.device)
+    ws, counters, status = _workspace(a_q.device)
+    _lib.ops().gemm_tn(w_q, a_q, out, 1, n, bn, splits, ws, counters, status, w_scale.contiguous(),
+                       a_scale.contiguous(), False, True)
+    return out
+
+
+def quantize_weight_block128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """e4m3 weights with one fp32 scale per 128x128 block (PyTorch; done once at load time)."""
+    n, k = w.shape
+    assert n % 128 == 0 and k % 128 == 0
+    blocks = w.float().view(n // 128, 128, k // 128, 128)
+    amax = blocks.abs().amax(dim=(1, 3), keepdim=True).clamp_min(1e-10)
+    scale = amax / 448.0
+    q = (blocks / scale).clamp(-448, 448).to(torch.float8_e4m3fn).view(n, k)
+    return q, scale.view(n // 128, k // 128).contiguous()
