@@ -1,0 +1,73 @@
+"""GEMM fused with its collective, single rank (world_size 1): the kernels run their full flow -
+tcgen05 GEMM, tile push into the Lamport gather slots, reduce + residual + RMSNorm tail, and the
+all-gather staging with its arrival flag - with this rank as its own only peer."""
+import pytest
+import torch
+
+import torch_dist_ext_b200 as tdx
+from torch_dist_ext_b200.ops import fused_gemm, gemm
+from torch_dist_ext_b200.ops import reference as ref
+from torch_dist_ext_b200.utils.config import OUT_FP8_BLOCK128, OUT_SAME
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def env():
+    tdx.setup_env(0, 1, max_size_in_bytes=16 << 20)
+    yield
+    tdx.teardown_env()
+
+
+def oracle(a, w, residual, gamma, eps, out_mode=OUT_SAME):
+    y = (a.float() @ w.float().t()).to(torch.bfloat16)       # each rank's GEMM output is rounded to bf16
+    return ref.residual_rmsnorm_reference(y.float(), residual, gamma, eps, out_mode)
+
+
+@pytest.mark.parametrize("tokens,hidden,k", [(1, 4096, 512), (16, 4096, 1792), (64, 8192, 1024), (33, 1024, 256), (100, 2048, 128)])
+def test_gemm_allreduce_rms_world1(tokens, hidden, k):
+    a = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(hidden, k, device="cuda") * 0.05).to(torch.bfloat16)
+    r = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(hidden, device="cuda")).to(torch.bfloat16)
+    for _ in range(3):   # repeated calls walk through the three Lamport buffers
+        norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6)
+    e_norm, e_res, _ = oracle(a, w, r, g, 1e-6)
+    assert (res.float() - e_res.float()).abs().max().item() <= 0.07
+    assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07
+    tdx.check_status()
+    assert gemm.pipeline_status() == 0
+
+
+def test_gemm_allreduce_rms_fp8_output_world1():
+    tokens, hidden, k = 16, 4096, 512
+    a = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(hidden, k, device="cuda") * 0.05).to(torch.bfloat16)
+    r = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    g = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+    q, res, scales = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6, out_mode=OUT_FP8_BLOCK128)
+    e_norm, _, _ = oracle(a, w, r, g, 1e-6)
+    back = ref.dequantize_fp8(q, scales)
+    assert (back - e_norm.float()).abs().max().item() <= e_norm.float().abs().max().item() * 2.0 ** -3
+
+
+@pytest.mark.parametrize("tokens,n_out,k", [(1, 768, 4096), (16, 3584, 4096), (64, 1280, 8192), (40, 256, 128)])
+def test_allgather_gemm_world1(tokens, n_out, k):
+    x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(n_out, k, device="cuda") * 0.05).to(torch.bfloat16)
+    for _ in range(3):   # both staging buffers and the epoch flags
+        out = fused_gemm.allgather_gemm(x, w, tokens)
+    want = x.float() @ w.float().t()
+    assert (out.float() - want).abs().max().item() <= 8e-3 * want.abs().max().item() + 1e-3
+    tdx.check_status()
+    assert gemm.pipeline_status() == 0
+
+
+def test_large_token_counts_take_the_unfused_route():
+    a = torch.randn(4096, 256, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(1024, 256, device="cuda") * 0.05).to(torch.bfloat16)
+    r = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)
+    g = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6)
+    e_norm, e_res, _ = oracle(a, w, r, g, 1e-6)
+    assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07

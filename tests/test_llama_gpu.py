@@ -1,0 +1,102 @@
+"""Llama-shaped decoder, single rank: every decode step through the library's kernels against a
+plain PyTorch fp32 forward pass over the same (dequantised) weights and the same KV cache."""
+import math
+
+import pytest
+import torch
+
+import torch_dist_ext_b200 as tdx
+from torch_dist_ext_b200.models.llama import LlamaConfig, TPLlama
+from torch_dist_ext_b200.ops import rope
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def env():
+    tdx.setup_env(0, 1, max_size_in_bytes=8 << 20)
+    yield
+    tdx.teardown_env()
+
+
+def rms(x, g, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * g
+
+
+def reference_step(model, tokens, positions, k_cache, v_cache):
+    cfg, w = model.cfg, model.weights_for_reference()
+    d, hq, hkv = cfg.head_dim, model.hq, model.hkv
+    res = w["embed"][tokens]
+    b = tokens.shape[0]
+    x = rms(res, w["layers"][0]["ln1"], cfg.eps)
+    for i, L in enumerate(w["layers"]):
+        qkv = x @ L["wqkv"].t()
+        q = qkv[:, : hq * d].view(b, hq, d)
+        k = qkv[:, hq * d: (hq + hkv) * d].view(b, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].view(b, hkv, d)
+        q = rope.rope_reference(q, positions, model.cos_sin).float()
+        k = rope.rope_reference(k, positions, model.cos_sin).float()
+        outs = []
+        for s in range(b):
+            n = int(positions[s])
+            kk = torch.cat([k_cache[i][s, :n].float(), k[s:s + 1]]).repeat_interleave(hq // hkv, dim=1)
+            vv = torch.cat([v_cache[i][s, :n].float(), v[s:s + 1]]).repeat_interleave(hq // hkv, dim=1)
+            sc = torch.einsum("hd,nhd->hn", q[s], kk) / math.sqrt(d)
+            outs.append(torch.einsum("hn,nhd->hd", torch.softmax(sc, -1), vv))
+        attn = torch.stack(outs).reshape(b, hq * d)
+        res = res + attn @ L["wo"].t()
+        x = rms(res, L["ln2"], cfg.eps)
+        gu = x @ L["wgu"].t()
+        act = torch.nn.functional.silu(gu[:, : model.ffn_r]) * gu[:, model.ffn_r:]
+        res = res + act @ L["wd"].t()
+        g = w["layers"][i + 1]["ln1"] if i + 1 < cfg.n_layers else w["final_norm"]
+        x = rms(res, g, cfg.eps)
+    return x
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("batch", [1, 5])
+def test_decode_step_matches_pytorch(fp8, batch):
+    cfg = LlamaConfig.tiny(fp8=fp8)
+    model = TPLlama(cfg, max_batch=8, max_seq=64)
+    model.fill_cache_random(batch, 20)
+    k0 = [k.clone() for k in model.k_cache]
+    v0 = [v.clone() for v in model.v_cache]
+    tokens = torch.randint(0, cfg.vocab, (batch,), device="cuda")
+    positions = torch.randint(5, 20, (batch,), device="cuda")
+    want = reference_step(model, tokens, positions, k0, v0)
+    nxt = model.decode_step(tokens, positions, max_len=21)
+    got = model.last_hidden.float()
+    tol = 0.25 if fp8 else 0.08      # the final norm output has unit scale; fp8 adds ~3 % per quantised GEMM input
+    assert (got - want).abs().max().item() <= tol, (got - want).abs().max().item()
+    assert torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0).item() > (0.99 if fp8 else 0.999)
+    assert nxt.shape == (batch,)
+    tdx.check_status()
+
+
+def test_cuda_graph_replay_equals_eager():
+    cfg = LlamaConfig.tiny()
+    model = TPLlama(cfg, max_batch=4, max_seq=64)
+    model.fill_cache_random(4, 10)
+    tokens = torch.randint(0, cfg.vocab, (4,), device="cuda")
+    positions = torch.full((4,), 10, device="cuda", dtype=torch.long)
+    eager = model.decode_step(tokens, positions, max_len=32).clone()
+    hidden = model.last_hidden.clone()
+    model.capture_decode(4, max_len=32)
+    for _ in range(3):      # replays walk the Lamport buffers with device-resident epochs
+        out = model.decode(tokens, positions)
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    assert torch.equal(model.last_hidden, hidden)
+    tdx.check_status()
+
+
+def test_prefill_then_decode_runs():
+    cfg = LlamaConfig.tiny()
+    model = TPLlama(cfg, max_batch=2, max_seq=128)
+    prompt = torch.randint(0, cfg.vocab, (48,), device="cuda")
+    first = model.prefill(prompt, seq_index=0)
+    assert first.shape == (1,)
+    nxt = model.decode_step(first, torch.tensor([48], device="cuda"), max_len=49)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(model.last_hidden.float()).all()) and nxt.shape == (1,)

@@ -37,3 +37,14 @@ def test_fused_op_across_processes(world):
     results = run_world(world, "nccl", cases())
     counts = results[0][2]
     assert counts, "no algorithm statistics recorded"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gemm_fused_with_collectives_across_processes(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from dist_worker_gemm import worker as gemm_worker
+
+    cases = [(1, 4096, 4096, False), (16, 4096, 4096, False), (64, 8192, 8192, False), (33, 2048, 1024, False),
+             (16, 4096, 4096, True), (61, 2048, 2048, True)]
+    run_world(world, "nccl", cases, target=gemm_worker)

@@ -24,11 +24,11 @@ def free_port():
         return s.getsockname()[1]
 
 
-def run_world(world, backend, cases):
+def run_world(world, backend, cases, target=worker):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=worker, args=(r, world, port, backend, cases, q)) for r in range(world)]
+    procs = [ctx.Process(target=target, args=(r, world, port, backend, cases, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = []

@@ -44,8 +44,10 @@ def _device_units():
         for emu in (0, 1):
             units.append(("ar_fusion_inst.cu", f"ar_inst_{name}{'_emu' if emu else ''}",
                           [f"-DTDX_INST_DTYPE={code}", f"-DTDX_INST_EMU={emu}"]))
+    for n in (0, 2, 4, 8):
+        units.append(("gemm_fused.cu", f"gemm_fused_n{n}", [f"-DTDX_FUSED_N={n}"]))
     for src in sorted(CSRC.glob("*.cu")):
-        if src.name == "ar_fusion_inst.cu":
+        if src.name in ("ar_fusion_inst.cu", "gemm_fused.cu"):
             continue
         units.append((src.name, src.stem, []))
     return units

@@ -1,0 +1,414 @@
+// GEMMs fused with their collectives over peer memory (NVLink / NVSwitch), one kernel each:
+//
+//  gemm_ar_rmsnorm   row-parallel linear (o_proj / down_proj of a tensor-parallel layer):
+//                    every rank multiplies its K shard on the tensor cores (tcgen05, accumulator in
+//                    TMEM); the epilogue pushes each finished 128-column x tokens tile straight into
+//                    the gather slots of the rows' OWNER ranks (reduce-scatter by peer stores, tile
+//                    by tile, while other CTAs are still multiplying); the same CTAs then turn into
+//                    the reducers of the two-shot Lamport flow: sum the N partial rows, add the
+//                    residual, RMS-normalise (optionally quantise to e4m3 with 1x128 scales), and
+//                    either keep the scattered rows (sequence-parallel) or push them back to all
+//                    peers (replicated output).
+//  ag_gemm           column-parallel linear on sequence-parallel input: every rank pushes its row
+//                    shard of the activations into all peers' staging buffers and raises a flag; the
+//                    TMA producer prefetches the first ring of weight tiles, waits (bounded) for the
+//                    N flags, then streams the gathered activations from LOCAL memory. No TMA load
+//                    ever reads a peer's memory, and none uses cluster multicast.
+//
+// Both need all CTAs of the grid to be resident at once (CTAs wait for data produced by others), so
+// the host refuses grids larger than the SM count.
+//
+// The reference has neither (its only kernel is the standalone all-reduce+RMSNorm,
+// src/common/all_reduce_fusion_impl.h:342-474); these are the two paths that a tensor-parallel
+// decoder layer built on that op needs next to it.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <mutex>
+#include <set>
+#include <utility>
+#include "tdx/ar_fusion_kernels.cuh"
+#include "tdx/gemm.h"
+#include "tdx/gemm_core.cuh"
+#include "tdx/tc.cuh"
+
+#ifndef TDX_FUSED_N
+#define TDX_FUSED_N 0
+#endif
+
+namespace tdx {
+namespace {
+
+using gemm_core::kBM;
+using gemm_core::SmemLayout;
+using T = __nv_bfloat16;
+constexpr int kThreads = 256;
+constexpr int kElemsPerBlock = 64;
+
+struct FusedArgs {
+  ArParams ar;        // communication state and the description of the reduce/normalise tail
+  int kblocks;
+  uint32_t idesc;
+  uint32_t* status;
+};
+
+// D tile (TMEM) -> bf16 rows in shared memory -> 16-byte pushes into the owners' gather slots.
+template <int kBN>
+__device__ __forceinline__ void push_tile_to_owners(const ArParams& p, uint8_t* stage, uint32_t tmem_base, int tile_x,
+                                                    int tile_y, size_t buf_off, int groups) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = warp & 3;
+  const int te = threadIdx.x - 64;                 // 0..127 among the epilogue threads
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+  __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
+#pragma unroll
+  for (int c = 0; c < kBN; c += 16) {
+    float v[16];
+    tc::tmem_ld_16(lane_addr + c, v);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) st[(c + j) * kBM + q * 32 + lane] = __float2bfloat16(v[j]);
+  }
+  tc::named_barrier_sync(1, 128);
+  const int y_base = tile_y * kBN;
+  const int valid = min(kBN, p.tokens - y_base);
+  const size_t row_bytes = (size_t)p.hidden * sizeof(T);
+  for (int i = te; i < valid * 16; i += 128) {
+    const int tl = i >> 4, part = i & 15;
+    const int t = y_base + tl;
+    const int owner = t % p.nranks, j = t / p.nranks;
+    const uint4 val = scrub(*reinterpret_cast<const uint4*>(stage + (size_t)tl * (kBM * 2) + part * 16));
+    char* dst = static_cast<char*>(p.peer[owner]) + buf_off + ((size_t)p.rank * groups + j) * row_bytes +
+                ((size_t)tile_x * kBM + part * 8) * sizeof(T);
+    ptx::st_v4(dst, val);
+  }
+}
+
+template <int kBN, int kStages, int kN, int kVpt, int kOut>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const FusedArgs f) {
+  constexpr uint32_t kTmemCols = kBN < 32 ? 32 : kBN;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ float red[4][32];
+  gemm_core::Pipeline<kBN, kStages> pipe;
+  pipe.init(smem_raw, kTmemCols, &map_w, &map_a);
+  const ArParams& p = f.ar;
+  char* self = static_cast<char*>(p.peer[p.rank]);
+  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
+  const uint32_t epoch = ctl->lamport_epoch;
+  const uint64_t dirty_prev = ctl->lamport_dirty[(epoch + 2u) % 3u];
+  const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
+  const int groups = (p.tokens + p.nranks - 1) / p.nranks;
+  const int cta = blockIdx.x + gridDim.x * blockIdx.y, nctas = gridDim.x * gridDim.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (warp == 0) {
+    if (lane == 0)
+      pipe.template produce<kElemsPerBlock>(&map_w, &map_a, blockIdx.x * kBM, blockIdx.y * kBN, 0, f.kblocks, f.status,
+                                            [] { return true; });
+  } else if (warp == 1) {
+    if (lane == 0) pipe.template issue<false, false>(f.kblocks, f.idesc, f.status);
+  } else if (warp < 6) {
+    const bool ok = tc::mbar_wait(&pipe.acc_full[0], 0, gemm_core::kWaitLimit, pipe.abort_flag);
+    tc::fence_after_thread_sync();
+    if (!ok) pipe.fail(f.status);
+    // every MMA has completed, so the operand ring is free: stage the tile there
+    if (ok) push_tile_to_owners<kBN>(p, pipe.smem, pipe.tmem_base, blockIdx.x, blockIdx.y, buf_off, groups);
+  }
+  __syncthreads();
+  clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev, cta, nctas);
+  const uint64_t dirty = twoshot_lamport_tail<T, kN, kVpt, kOut, true>(p, cta, nctas, epoch, red);
+  finish_launch(ctl, true, epoch, dirty, 0, nctas);
+  pipe.finish(kTmemCols);
+}
+
+// ---- all-gather -> GEMM --------------------------------------------------------------------------
+
+struct AgArgs {
+  void* peer[kMaxRanks];
+  Layout layout;
+  int rank, nranks;
+  int tokens, k;            // gathered activation matrix [tokens, k]
+  const void* x_shard;      // this rank's rows (token t with t % nranks == rank, in order), [ceil, k]
+  int out_rows;             // weight rows of this rank (output columns)
+  void* out;                // [tokens, out_rows] row-major
+  int64_t ldo;
+  int kblocks;
+  uint32_t idesc;
+  uint32_t* status;
+  uint64_t timeout_ns;
+  uint32_t* host_status;
+};
+
+__device__ __forceinline__ uint32_t* ag_flag(void* base, const Layout& l, int src) {
+  return reinterpret_cast<uint32_t*>(static_cast<char*>(base) + l.off_ag_flags) + src;
+}
+
+template <int kBN, int kStages>
+__global__ void __launch_bounds__(kThreads, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_g0,
+               const __grid_constant__ CUtensorMap map_g1, const AgArgs a) {
+  constexpr uint32_t kTmemCols = kBN < 32 ? 32 : kBN;
+  extern __shared__ uint8_t smem_raw[];
+  gemm_core::Pipeline<kBN, kStages> pipe;
+  pipe.init(smem_raw, kTmemCols, &map_w, &map_g0);
+  char* self = static_cast<char*>(a.peer[a.rank]);
+  Control* ctl = reinterpret_cast<Control*>(self + a.layout.off_control);
+  const uint32_t epoch = ctl->ag_epoch;
+  const uint32_t target = epoch + 1u;
+  const size_t gbuf_off = a.layout.off_ag + (size_t)(epoch & 1u) * a.layout.ag_buf_bytes;
+  const CUtensorMap* map_g = (epoch & 1u) ? &map_g1 : &map_g0;
+  const int cta = blockIdx.x + gridDim.x * blockIdx.y, nctas = gridDim.x * gridDim.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t row_bytes = (size_t)a.k * sizeof(T);
+  const int my_rows = (a.tokens - a.rank + a.nranks - 1) / a.nranks;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      auto gate = [&]() -> bool {
+        // all N shards must have landed in THIS rank's staging buffer
+        Waiter w(a.timeout_ns);
+        for (int r = 0; r < a.nranks; ++r) {
+          const uint32_t* fl = ag_flag(self, a.layout, r);
+          w.begin();
+          while ((int32_t)(ptx::ld_acquire_sys(fl) - target) < 0) {
+            if (!w.keep_waiting()) {
+              report_error(ctl, a.host_status, kTimeoutTileFlag, a.rank, r, 1, -1);
+              return false;
+            }
+          }
+        }
+        // the rows were written through the generic proxy (peer stores); TMA reads through the async proxy
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        return true;
+      };
+      pipe.template produce<kElemsPerBlock>(&map_w, map_g, blockIdx.x * kBM, blockIdx.y * kBN, 0, a.kblocks, a.status, gate);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) pipe.template issue<false, false>(a.kblocks, a.idesc, a.status);
+  } else {
+    // warps 2..7: destination `d` of the all-gather is served by CTA d % nctas
+    const int tp = threadIdx.x - 64;   // 0..191
+    for (int d = cta; d < a.nranks; d += nctas) {
+      char* dst_base = static_cast<char*>(a.peer[d]) + gbuf_off;
+      const size_t vec_per_row = row_bytes / 16;
+      const size_t total = (size_t)my_rows * vec_per_row;
+      for (size_t i = tp; i < total; i += 192) {
+        const size_t j = i / vec_per_row, part = i % vec_per_row;
+        const uint4 val = ptx::ld_stream_v4(static_cast<const char*>(a.x_shard) + j * row_bytes + part * 16);
+        ptx::st_v4(dst_base + (j * a.nranks + a.rank) * row_bytes + part * 16, val);
+      }
+      tc::named_barrier_sync(2, 192);
+      if (tp == 0) ptx::st_release_sys(ag_flag(a.peer[d], a.layout, a.rank), target);
+    }
+    if (warp < 6) {
+      // epilogue: D[x = weight row, y = token] -> out[token, weight row]
+      const int q = warp & 3;
+      const bool ok = tc::mbar_wait(&pipe.acc_full[0], 0, gemm_core::kWaitLimit, pipe.abort_flag);
+      tc::fence_after_thread_sync();
+      if (!ok) pipe.fail(a.status);
+      const int x = blockIdx.x * kBM + q * 32 + lane;
+      const uint32_t lane_addr = pipe.tmem_base + ((uint32_t)(q * 32) << 16);
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < kBN; c += 16) {
+          float v[16];
+          tc::tmem_ld_16(lane_addr + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = blockIdx.y * kBN + c + j;
+            if (t < a.tokens && x < a.out_rows) static_cast<T*>(a.out)[(int64_t)t * a.ldo + x] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(&ctl->arrive, 1u);
+    if (done == (uint32_t)nctas - 1) {
+      ctl->ag_epoch = target;
+      ctl->arrive = 0;
+      __threadfence();
+    }
+  }
+  pipe.finish(kTmemCols);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encoder() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+std::string bf16_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t ld, int box_rows) {
+  EncodeFn enc = encoder();
+  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
+  if (reinterpret_cast<uintptr_t>(ptr) % 16 || (ld * 2) % 16) return "GEMM operands must be 16-byte aligned with a 16-byte row pitch";
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)(ld * 2)};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? "" : "cuTensorMapEncodeTiled failed (CUresult " + std::to_string((int)r) + ")";
+}
+
+// Opt in to the large dynamic shared-memory size once per kernel and device.
+template <typename Kern>
+std::string prepare(Kern kern, int smem) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const auto key = std::make_pair(reinterpret_cast<const void*>(kern), dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count(key)) return "";
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
+  done.insert(key);
+  return "";
+}
+
+int sm_count() {
+  int dev = 0, n = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+template <int kBN, int kStages, int kVpt, int kOut>
+std::string launch_ar(const CUtensorMap& mw, const CUtensorMap& ma, const FusedArgs& f, dim3 grid, cudaStream_t s) {
+  auto kern = gemm_ar_rmsnorm_kernel<kBN, kStages, TDX_FUSED_N, kVpt, kOut>;
+  std::string err = prepare(kern, SmemLayout<kBN, kStages>::kTotal);
+  if (!err.empty()) return err;
+  kern<<<grid, kThreads, SmemLayout<kBN, kStages>::kTotal, s>>>(mw, ma, f);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : std::string("fused GEMM launch failed: ") + cudaGetErrorString(e);
+}
+
+template <int kBN, int kStages>
+std::string launch_ar_vpt(int vpt, int out_mode, const CUtensorMap& mw, const CUtensorMap& ma, const FusedArgs& f, dim3 grid,
+                          cudaStream_t s) {
+  const bool q = out_mode == kOutFp8Block128;
+  switch (vpt) {
+    case 1: return q ? launch_ar<kBN, kStages, 1, kOutFp8Block128>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 1, kOutSame>(mw, ma, f, grid, s);
+    case 2: return q ? launch_ar<kBN, kStages, 2, kOutFp8Block128>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 2, kOutSame>(mw, ma, f, grid, s);
+    case 4: return q ? launch_ar<kBN, kStages, 4, kOutFp8Block128>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 4, kOutSame>(mw, ma, f, grid, s);
+  }
+  return "unsupported hidden size for the fused GEMM";
+}
+
+}  // namespace
+
+#define TDX_CAT2(a, b) a##b
+#define TDX_CAT(a, b) TDX_CAT2(a, b)
+
+// Row-parallel linear + reduce(-scatter) + residual + RMSNorm; one function per rank-count
+// specialisation (0 = any rank count, runtime loop).
+std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, cudaStream_t stream) {
+  const ArParams& p = g.ar;
+  if (p.dtype != kBF16) return "the fused GEMM paths take bfloat16 operands";
+  if (p.hidden % 128) return "hidden must be a multiple of 128";
+  if (g.k <= 0 || g.k % 64) return "K must be a positive multiple of 64";
+  if (p.out_mode != kOutSame && p.out_mode != kOutFp8Block128) return "fused GEMM output is bf16 or e4m3 with 1x128 scales";
+  if (p.tokens <= 0) return "";
+  const int bn = p.tokens <= 16 ? 16 : 64;
+  const dim3 grid(p.hidden / 128, (p.tokens + bn - 1) / bn, 1);
+  if ((int)(grid.x * grid.y) > sm_count())
+    return "too many tokens for the fused GEMM (all CTAs must be resident): use the GEMM followed by the all-reduce op";
+  const int nvec = p.hidden / 8;
+  const int vpt = nvec <= kThreads ? 1 : nvec <= 2 * kThreads ? 2 : nvec <= 4 * kThreads ? 4 : 0;
+  const uint64_t row_bytes = (uint64_t)p.hidden * 2;
+  const uint64_t groups = ((uint64_t)p.tokens + p.nranks - 1) / p.nranks;
+  const uint64_t need = (uint64_t)p.nranks * groups * row_bytes + (p.scatter_only ? 0 : (uint64_t)p.tokens * (row_bytes + 16));
+  if (need > p.layout.lamport_bytes) return "message exceeds the Lamport buffer capacity";
+  for (int r = 0; r < p.nranks; ++r)
+    if (p.peer[r] == nullptr) return "workspace is not registered with all peers";
+  FusedArgs f{};
+  f.ar = p;
+  f.kblocks = g.k / 64;
+  f.idesc = tc::make_idesc(kBM, bn, 1, 1);
+  f.status = g.status;
+  CUtensorMap mw, ma;
+  std::string err = bf16_map(&mw, g.w, p.hidden, g.k, g.ldw, kBM);
+  if (!err.empty()) return err;
+  err = bf16_map(&ma, g.a, p.tokens, g.k, g.lda, bn);
+  if (!err.empty()) return err;
+  return bn == 16 ? launch_ar_vpt<16, 10>(vpt, p.out_mode, mw, ma, f, grid, stream)
+                  : launch_ar_vpt<64, 8>(vpt, p.out_mode, mw, ma, f, grid, stream);
+}
+
+#if TDX_FUSED_N == 0
+std::string ag_gemm(const AgGemmProblem& g, cudaStream_t stream) {
+  if (g.k <= 0 || g.k % 64) return "K must be a positive multiple of 64";
+  if (g.tokens <= 0 || g.out_rows <= 0) return "";
+  if ((uint64_t)g.tokens * g.k * 2 > g.layout.ag_buf_bytes) return "gathered activations exceed the staging buffer";
+  for (int r = 0; r < g.nranks; ++r)
+    if (g.peer[r] == nullptr) return "workspace is not registered with all peers";
+  const int bn = g.tokens <= 16 ? 16 : 64;
+  const dim3 grid((g.out_rows + kBM - 1) / kBM, (g.tokens + bn - 1) / bn, 1);
+  if ((int)(grid.x * grid.y) > sm_count())
+    return "too many tiles for the fused all-gather GEMM (all CTAs must be resident)";
+  AgArgs a{};
+  for (int r = 0; r < kMaxRanks; ++r) a.peer[r] = g.peer[r];
+  a.layout = g.layout;
+  a.rank = g.rank;
+  a.nranks = g.nranks;
+  a.tokens = g.tokens;
+  a.k = g.k;
+  a.x_shard = g.x_shard;
+  a.out_rows = g.out_rows;
+  a.out = g.out;
+  a.ldo = g.ldo;
+  a.kblocks = g.k / 64;
+  a.idesc = tc::make_idesc(kBM, bn, 1, 1);
+  a.status = g.status;
+  a.timeout_ns = g.timeout_ns;
+  a.host_status = g.host_status;
+  CUtensorMap mw, m0, m1;
+  std::string err = bf16_map(&mw, g.w, g.out_rows, g.k, g.ldw, kBM);
+  if (!err.empty()) return err;
+  char* own = static_cast<char*>(g.peer[g.rank]) + g.layout.off_ag;
+  err = bf16_map(&m0, own, g.tokens, g.k, g.k, bn);
+  if (!err.empty()) return err;
+  err = bf16_map(&m1, own + g.layout.ag_buf_bytes, g.tokens, g.k, g.k, bn);
+  if (!err.empty()) return err;
+  if (bn == 16) {
+    auto kern = ag_gemm_kernel<16, 10>;
+    err = prepare(kern, SmemLayout<16, 10>::kTotal);
+    if (!err.empty()) return err;
+    kern<<<grid, kThreads, SmemLayout<16, 10>::kTotal, stream>>>(mw, m0, m1, a);
+  } else {
+    auto kern = ag_gemm_kernel<64, 8>;
+    err = prepare(kern, SmemLayout<64, 8>::kTotal);
+    if (!err.empty()) return err;
+    kern<<<grid, kThreads, SmemLayout<64, 8>::kTotal, stream>>>(mw, m0, m1, a);
+  }
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : std::string("all-gather GEMM launch failed: ") + cudaGetErrorString(e);
+}
+
+std::string gemm_ar_rmsnorm(const FusedGemmProblem& g, cudaStream_t stream) {
+  switch (g.ar.nranks) {
+    case 2: return gemm_ar_rmsnorm_n2(g, stream);
+    case 4: return gemm_ar_rmsnorm_n4(g, stream);
+    case 8: return gemm_ar_rmsnorm_n8(g, stream);
+    default: return gemm_ar_rmsnorm_n0(g, stream);
+  }
+}
+#endif
+
+}  // namespace tdx

@@ -27,15 +27,17 @@
 #include <mutex>
 #include "tdx/comm.h"
 #include "tdx/gemm.h"
+#include "tdx/gemm_core.cuh"
 #include "tdx/tc.cuh"
 
 namespace tdx {
 namespace {
 
-constexpr int kBM = 128;          // tile rows (tcgen05.mma M)
-constexpr int kSwizzleBytes = 128; // one K block = 128 bytes per row (64 bf16 / 128 fp8)
+using gemm_core::kBM;
+using gemm_core::kSwizzleBytes;
+using gemm_core::kWaitLimit;
+using gemm_core::SmemLayout;
 constexpr int kThreads = 192;
-constexpr uint32_t kWaitLimit = 1u << 22;
 
 struct GemmArgs {
   int x_rows, y_rows;
@@ -54,15 +56,6 @@ struct GemmArgs {
   const float* y_scale;
   int x_scale_per_row, y_scale_per_row;
   int scale_kb;            // K blocks per scale row (= total K / 128)
-};
-
-template <int kBN, int kStages>
-struct SmemLayout {
-  static constexpr int kXBytes = kBM * kSwizzleBytes;
-  static constexpr int kYBytes = kBN * kSwizzleBytes;
-  static constexpr int kStageBytes = kXBytes + kYBytes;
-  static constexpr int kBarrierOffset = kStages * kStageBytes;
-  static constexpr int kTotal = kBarrierOffset + 1024 /*barriers + scratch*/ + 1024 /*alignment slack*/;
 };
 
 __device__ __forceinline__ void store_out(const GemmArgs& a, int64_t idx, float v) {
@@ -106,14 +99,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two");
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
-  uint64_t* empty = full + kStages;
-  uint64_t* acc_full = empty + kStages;    // [2]
-  uint64_t* acc_empty = acc_full + 2;      // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
-  uint32_t* last_flag = tmem_slot + 2;
+  gemm_core::Pipeline<kBN, kStages> pipe;
+  pipe.init(smem_raw, kTmemCols, &map_x, &map_y);
+  uint64_t* acc_full = pipe.acc_full;
+  uint64_t* acc_empty = pipe.acc_empty;
+  volatile uint32_t* abort_flag = pipe.abort_flag;
+  uint32_t* last_flag = pipe.scratch;
+  const uint32_t tmem_base = pipe.tmem_base;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_x = blockIdx.x, tile_y = blockIdx.y;
@@ -121,80 +113,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int kb1 = min(a.kblocks, kb0 + a.kblocks_per_split);
   const int nkb = kb1 - kb0;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      tc::mbar_init(&full[s], 1);
-      tc::mbar_init(&empty[s], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&acc_full[i], 1);
-      tc::mbar_init(&acc_empty[i], 128);
-    }
-    *abort_flag = 0;
-    tc::fence_barrier_init();
-    tc::tma_prefetch_desc(&map_x);
-    tc::tma_prefetch_desc(&map_y);
-  }
-  if (warp == 1) {
-    tc::tmem_alloc(tmem_slot, kTmemCols);
-    tc::tmem_relinquish();
-  }
-  tc::fence_before_thread_sync();
-  __syncthreads();
-  tc::fence_after_thread_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
   if (warp == 0) {
-    // ---- TMA producer -------------------------------------------------------------------------
-    if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % kStages;
-        if (i >= kStages && !tc::mbar_wait(&empty[s], ((i / kStages) - 1) & 1, kWaitLimit, abort_flag)) {
-          *abort_flag = 1;
-          if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
-          break;
-        }
-        uint8_t* sx = smem + s * L::kStageBytes;
-        tc::mbar_arrive_expect_tx(&full[s], L::kStageBytes);
-        tc::tma_load_2d(sx, &map_x, &full[s], (kb0 + i) * kElemsPerBlock, tile_x * kBM);
-        tc::tma_load_2d(sx + L::kXBytes, &map_y, &full[s], (kb0 + i) * kElemsPerBlock, tile_y * kBN);
-      }
-    }
+    if (lane == 0)
+      pipe.template produce<kElemsPerBlock>(&map_x, &map_y, tile_x * kBM, tile_y * kBN, kb0, nkb, a.status, [] { return true; });
   } else if (warp == 1) {
-    // ---- MMA issuer -----------------------------------------------------------------------------
-    if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % kStages;
-        if (!tc::mbar_wait(&full[s], (i / kStages) & 1, kWaitLimit, abort_flag)) {
-          *abort_flag = 1;
-          if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
-          break;
-        }
-        uint32_t acc_col = 0;
-        if constexpr (kScaled) {
-          const int buf = i & 1;
-          if (i >= 2 && !tc::mbar_wait(&acc_empty[buf], ((i >> 1) - 1) & 1, kWaitLimit, abort_flag)) {
-            *abort_flag = 1;
-            if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
-            break;
-          }
-          acc_col = buf * kBN;
-        }
-        tc::fence_after_thread_sync();
-        const uint32_t xa = tc::smem_u32(smem + s * L::kStageBytes);
-        const uint64_t dx = tc::make_smem_desc_sw128(xa);
-        const uint64_t dy = tc::make_smem_desc_sw128(xa + L::kXBytes);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          // one instruction covers 32 bytes of K; step the start address inside the swizzle span
-          const uint32_t accumulate = kScaled ? (k > 0) : (i > 0 || k > 0);
-          tc::umma<kFp8>(tmem_base + acc_col, dx + (uint64_t)(k * 2), dy + (uint64_t)(k * 2), a.idesc, accumulate);
-        }
-        tc::umma_commit(&empty[s]);                       // stage reusable once these MMAs have read it
-        if constexpr (kScaled) tc::umma_commit(&acc_full[i & 1]);
-      }
-      if constexpr (!kScaled) tc::umma_commit(&acc_full[0]);
-    }
+    if (lane == 0) pipe.template issue<kFp8, kScaled>(nkb, a.idesc, a.status);
   } else {
     // ---- epilogue (warps 2..5): TMEM lane quarter = warp % 4 -----------------------------------------
     const int q = warp & 3;
@@ -282,16 +205,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   }
 
-  tc::fence_before_thread_sync();
-  __syncthreads();
-  if (*abort_flag) {
-    // let TMA copies that were already issued land before the CTA's shared memory goes away
-    for (int i = 0; i < 64; ++i) __nanosleep(1000);
-  }
-  if (warp == 1) {
-    tc::fence_after_thread_sync();
-    tc::tmem_dealloc(tmem_base, kTmemCols);
-  }
+  pipe.finish(kTmemCols);
 }
 
 // ---- host side -------------------------------------------------------------------------------------

@@ -100,6 +100,9 @@ class Workspace {
   const CommTable& host_table() const { return table_host_; }
   // Fills the communication part of a parameter block.
   void fill_params(ArParams* p) const;
+  uint32_t* host_status_device_ptr() const { return host_status_dev_; }
+  const Layout& layout() const { return layout_; }
+  void* peer_base(int r) const { return peer_[r]; }
 
   // Re-initialise flags, epochs, sentinels and the status record. Collective: all ranks must
   // be idle and must call it between two host barriers.

@@ -186,12 +186,14 @@ __device__ __forceinline__ char* lamport_buf(void* base, const Layout& l, uint32
 }
 
 // All blocks of this rank cooperatively re-fill the buffer that the previous Lamport call used.
-__device__ __forceinline__ void clear_previous(char* buf, uint64_t dirty_bytes) {
+__device__ __forceinline__ void clear_previous(char* buf, uint64_t dirty_bytes, int cta, int nctas) {
   const uint4 s = sentinel_vec();
-  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 16;
-  for (uint64_t off = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 16; off < dirty_bytes;
-       off += stride)
+  const uint64_t stride = (uint64_t)nctas * blockDim.x * 16;
+  for (uint64_t off = ((uint64_t)cta * blockDim.x + threadIdx.x) * 16; off < dirty_bytes; off += stride)
     ptx::st_v4(buf + off, s);
+}
+__device__ __forceinline__ void clear_previous(char* buf, uint64_t dirty_bytes) {
+  clear_previous(buf, dirty_bytes, blockIdx.x, gridDim.x);
 }
 
 // Poll one 16-byte vector until every 32-bit lane has been overwritten by its producer.
@@ -375,24 +377,23 @@ __device__ __forceinline__ void twoshot_scatter(const ArParams& p, const RowView
 
 // ---- two-shot Lamport -------------------------------------------------------------------
 
-template <typename T, int kN, int kVpt, int kOut>
-__device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
+// Owner and receive phases of the two-shot Lamport flow for the row groups cta, cta + nctas, ...
+// kOwnFromBuffer: this rank's own partial row is polled from its gather slot like the peers'
+// (used when the partial rows are produced by a GEMM epilogue instead of being an input tensor).
+// Returns the number of bytes of the Lamport buffer that hold data after this call.
+template <typename T, int kN, int kVpt, int kOut, bool kOwnFromBuffer>
+__device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int cta, int nctas, uint32_t epoch,
+                                                         float (*red)[32]) {
   constexpr int kVec = VecTraits<T>::kVec;
-  __shared__ float red[4][32];
   const int nranks = kN > 0 ? kN : p.nranks;
   const RowView<T, kVpt> rv(p.hidden);
   char* self = static_cast<char*>(p.peer[p.rank]);
   Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
-  const uint32_t epoch = ctl->lamport_epoch;
-  const uint64_t dirty_prev = ctl->lamport_dirty[(epoch + 2u) % 3u];
   const TwoShotGeometry g = twoshot_geometry<T, kVpt>(p, rv, nranks, true);
   const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
   const size_t result_off = buf_off + g.gather_bytes;
   const char* in = static_cast<const char*>(p.in);
   const bool gather_back = p.scatter_only == 0;
-
-  twoshot_scatter<T, kN, kVpt, true>(p, rv, g, nranks, buf_off);
-  clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev);
 
   uint4 gamma[kVpt];
   load_gamma<T, kVpt>(p, rv, gamma);
@@ -400,7 +401,7 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
   int parity = 0;
 
   // owner phase: rows j*N + rank
-  for (int j = blockIdx.x; j < g.groups; j += gridDim.x) {
+  for (int j = cta; j < g.groups; j += nctas) {
     const int row = j * nranks + p.rank;
     if (row >= p.tokens) continue;
     const int64_t out_row = gather_back ? row : j;
@@ -419,11 +420,11 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
         uint4 vals[kN];
 #pragma unroll
         for (int r = 0; r < kN; ++r)
-          vals[r] = (r == p.rank) ? ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff)
-                                  : ptx::ld_volatile_v4(slot0 + r * slot_stride);
+          vals[r] = (!kOwnFromBuffer && r == p.rank) ? ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff)
+                                                     : ptx::ld_volatile_v4(slot0 + r * slot_stride);
 #pragma unroll
         for (int r = 0; r < kN; ++r)
-          if (r != p.rank && !all_arrived(vals[r]))
+          if ((kOwnFromBuffer || r != p.rank) && !all_arrived(vals[r]))
             vals[r] = poll_vec(slot0 + r * slot_stride, w, p, ctl, kTimeoutLamportGather, r, 1, row);
 #pragma unroll
         for (int r = 0; r < kN; ++r) {
@@ -434,7 +435,7 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
         }
       } else {
         for (int r = 0; r < nranks; ++r) {
-          const uint4 val = (r == p.rank)
+          const uint4 val = (!kOwnFromBuffer && r == p.rank)
                                 ? ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff)
                                 : poll_vec(slot0 + r * slot_stride, w, p, ctl, kTimeoutLamportGather, r, 1, row);
           float f[kVec];
@@ -469,7 +470,7 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
 
   // receive phase: rows owned by the peers
   if (gather_back) {
-    for (int j = blockIdx.x; j < g.groups; j += gridDim.x) {
+    for (int j = cta; j < g.groups; j += nctas) {
       for (int r = 0; r < nranks; ++r) {
         const int row = j * nranks + r;
         if (r == p.rank || row >= p.tokens) continue;
@@ -494,7 +495,24 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
       }
     }
   }
-  const uint64_t dirty = g.gather_bytes + (gather_back ? (uint64_t)p.tokens * g.result_stride : 0);
+  return g.gather_bytes + (gather_back ? (uint64_t)p.tokens * g.result_stride : 0);
+}
+
+template <typename T, int kN, int kVpt, int kOut>
+__device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
+  __shared__ float red[4][32];
+  const int nranks = kN > 0 ? kN : p.nranks;
+  const RowView<T, kVpt> rv(p.hidden);
+  char* self = static_cast<char*>(p.peer[p.rank]);
+  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
+  const uint32_t epoch = ctl->lamport_epoch;
+  const uint64_t dirty_prev = ctl->lamport_dirty[(epoch + 2u) % 3u];
+  const TwoShotGeometry g = twoshot_geometry<T, kVpt>(p, rv, nranks, true);
+  const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
+
+  twoshot_scatter<T, kN, kVpt, true>(p, rv, g, nranks, buf_off);
+  clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev);
+  const uint64_t dirty = twoshot_lamport_tail<T, kN, kVpt, kOut, false>(p, blockIdx.x, gridDim.x, epoch, red);
   finish_launch(ctl, true, epoch, dirty, 0);
 }
 

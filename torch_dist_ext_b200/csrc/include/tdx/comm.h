@@ -23,6 +23,7 @@ constexpr uint32_t kSentinel = 0x80000000u;  // fp32 -0.0 / (bf16 -0.0, +0.0) pa
 // ---- region offsets inside one rank's symmetric allocation --------------------
 constexpr size_t kControlBytes = 4096;
 constexpr size_t kFlagBytes = size_t(kMaxBarrierBlocks) * kMaxRanks * sizeof(uint32_t);
+constexpr size_t kAgFlagBytes = 256;    // all-gather->GEMM: one arrival word per source rank
 
 struct Layout {
   uint64_t off_control;   // Control block (touched by the owning rank only)
@@ -31,6 +32,9 @@ struct Layout {
   uint64_t lamport_bytes; // capacity of ONE of the three Lamport buffers
   uint64_t off_stage;     // flag-synchronised staging of the peer-to-peer two-shot path
   uint64_t stage_bytes;
+  uint64_t off_ag_flags;  // uint32 ag_flags[kMaxRanks], written by peers (all-gather->GEMM)
+  uint64_t off_ag;        // all-gather->GEMM: two gathered-activation buffers (by epoch parity)
+  uint64_t ag_buf_bytes;  // capacity of one of them
   uint64_t off_nvls;      // NVLS: two input staging buffers (by barrier-epoch parity) + result area
   uint64_t nvls_in_bytes; // capacity of one NVLS input buffer (0: no NVLS region)
   uint64_t nvls_bytes;
@@ -42,12 +46,15 @@ inline Layout make_layout(uint64_t max_message_bytes, uint64_t lamport_bytes, bo
   Layout l{};
   l.off_control = 0;
   l.off_flags = kControlBytes;
-  l.off_lamport = align_up(l.off_flags + kFlagBytes, 1 << 16);
+  l.off_ag_flags = l.off_flags + kFlagBytes;
+  l.off_lamport = align_up(l.off_ag_flags + kAgFlagBytes, 1 << 16);
   l.lamport_bytes = align_up(lamport_bytes, 1 << 16);
   l.off_stage = l.off_lamport + 3 * l.lamport_bytes;
   // gather area + result area + per-row trailers and row padding
   l.stage_bytes = align_up(2 * max_message_bytes + max_message_bytes / 8 + (1 << 20), 1 << 16);
-  l.off_nvls = l.off_stage + l.stage_bytes;
+  l.off_ag = l.off_stage + l.stage_bytes;
+  l.ag_buf_bytes = align_up(max_message_bytes < (32ull << 20) ? max_message_bytes : (32ull << 20), 1 << 16);
+  l.off_nvls = l.off_ag + 2 * l.ag_buf_bytes;
   l.nvls_in_bytes = with_nvls ? align_up(max_message_bytes, 1 << 16) : 0;
   l.nvls_bytes = with_nvls ? 2 * l.nvls_in_bytes + align_up(max_message_bytes + max_message_bytes / 8 + (1 << 20), 1 << 16) : 0;
   l.total_bytes = align_up(l.off_nvls + l.nvls_bytes, 1 << 21);
@@ -60,6 +67,8 @@ struct Control {
   uint32_t barrier_epoch;      // flag barriers completed
   uint32_t arrive;             // blocks of the running launch that have finished
   uint32_t error_count;        // waits that ran out since the last reset
+  uint32_t ag_epoch;           // all-gather->GEMM calls completed; buffer in use = epoch & 1
+  uint32_t reserved0;
   uint64_t lamport_dirty[3];   // bytes (from buffer start) that hold non-sentinel data
   uint32_t status[8];          // first error: {code, rank, peer, phase, block, row, 0, 0}
 };
@@ -73,7 +82,7 @@ struct CommTable {
   void* peer[kMaxRanks];  // base of every rank's symmetric allocation (own entry = local)
   void* mc_base;          // NVSwitch multicast mapping of the same allocation, or null
   Layout layout;
-  uint64_t reserved[8];
+  uint64_t reserved[5];
 };
 constexpr uint64_t kTableMagic = 0x7464785f62323030ull;  // "tdx_b200"
 

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <string>
+#include "tdx/comm.h"
 
 namespace tdx {
 
@@ -31,6 +32,42 @@ struct GemmProblem {
 };
 
 std::string gemm_tn(const GemmProblem& g, cudaStream_t stream);
+
+// Row-parallel linear fused with reduce(-scatter) + residual + RMSNorm (gemm_fused.cu).
+// `ar` carries the communication state (Workspace::fill_params) and describes the tail: tokens,
+// hidden, residual_in, gamma, residual_out, norm_out, scale_out, eps, out_mode (bf16 or e4m3 with
+// 1x128 scales), scatter_only. `ar.in` is unused: the partial rows come from the GEMM.
+struct FusedGemmProblem {
+  ArParams ar;
+  const void* a;      // [tokens, k] bf16, this rank's K shard of the activations
+  const void* w;      // [hidden, k] bf16, this rank's K shard of the weight
+  int k;
+  int64_t lda, ldw;
+  uint32_t* status;
+};
+std::string gemm_ar_rmsnorm(const FusedGemmProblem& g, cudaStream_t stream);
+std::string gemm_ar_rmsnorm_n0(const FusedGemmProblem& g, cudaStream_t stream);
+std::string gemm_ar_rmsnorm_n2(const FusedGemmProblem& g, cudaStream_t stream);
+std::string gemm_ar_rmsnorm_n4(const FusedGemmProblem& g, cudaStream_t stream);
+std::string gemm_ar_rmsnorm_n8(const FusedGemmProblem& g, cudaStream_t stream);
+
+// All-gather of sequence-parallel activations fused with a column-parallel linear (gemm_fused.cu).
+struct AgGemmProblem {
+  void* peer[kMaxRanks];
+  Layout layout;
+  int rank, nranks;
+  int tokens, k;
+  const void* x_shard;   // [ceil((tokens - rank) / nranks), k] bf16: rows rank, rank + nranks, ...
+  const void* w;         // [out_rows, k] bf16
+  int64_t ldw;
+  int out_rows;
+  void* out;             // [tokens, out_rows] bf16
+  int64_t ldo;
+  uint32_t* status;
+  uint64_t timeout_ns;
+  uint32_t* host_status;
+};
+std::string ag_gemm(const AgGemmProblem& g, cudaStream_t stream);
 int gemm_pick_block_n(int y_rows, bool scaled);
 
 }  // namespace tdx

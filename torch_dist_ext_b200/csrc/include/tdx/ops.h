@@ -23,4 +23,12 @@ std::string rope_inplace(void* q, void* k, const int64_t* positions, const float
                          int q_heads, int k_heads, int dim, int64_t q_stride, int64_t k_stride, int dtype,
                          cudaStream_t stream);
 
+// Decode attention over a contiguous bf16 KV cache [B, S_max, Hkv, 128] for one new token per
+// sequence: q [B, Hq, 128] -> out [B, Hq, 128]. `partial` is fp32 scratch of at least
+// B * Hq * nsplit * 130 floats. Strides are in elements.
+std::string attention_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
+                             float* partial, size_t partial_floats, void* out, int B, int Hq, int Hkv, int D, int S_max,
+                             int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,
+                             cudaStream_t stream);
+
 }  // namespace tdx

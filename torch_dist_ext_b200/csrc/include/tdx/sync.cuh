@@ -130,12 +130,14 @@ __device__ __forceinline__ void flag_barrier(const ArParams& p, Control* ctl, ui
 // The last block to finish advances the epochs. Launches on one stream are ordered, so the
 // next launch reads the new values.
 __device__ __forceinline__ void finish_launch(Control* ctl, bool used_lamport, uint32_t epoch,
-                                              uint64_t dirty_bytes, uint32_t barriers_used) {
+                                              uint64_t dirty_bytes, uint32_t barriers_used,
+                                              uint32_t nctas = 0) {
+  if (nctas == 0) nctas = gridDim.x;   // blocks of THIS rank (an emulated launch holds several ranks)
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     const uint32_t done = atomicAdd(&ctl->arrive, 1u);
-    if (done == gridDim.x - 1) {
+    if (done == nctas - 1) {
       if (used_lamport) {
         ctl->lamport_dirty[epoch % 3u] = dirty_bytes;
         ctl->lamport_epoch = epoch + 1u;

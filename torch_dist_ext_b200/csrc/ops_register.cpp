@@ -147,7 +147,114 @@ void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t s
   TORCH_CHECK(err.empty(), "gemm_tn: ", err);
 }
 
+void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor out,
+                      Tensor partial, int64_t nsplit, double scale) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 3 && k_cache.dim() == 4 && v_cache.dim() == 4, "attention_decode: q [B, Hq, D], caches [B, S, Hkv, D]");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k_cache.scalar_type() == at::kBFloat16 && v_cache.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "attention_decode: bfloat16 tensors");
+  TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == q.size(2) && out.is_contiguous(), "attention_decode: q heads densely packed, out contiguous");
+  TORCH_CHECK(k_cache.stride(3) == 1 && k_cache.stride(2) == k_cache.size(3) && k_cache.strides() == v_cache.strides() && k_cache.sizes() == v_cache.sizes(), "attention_decode: cache layout [B, S, Hkv, D] with dense heads");
+  TORCH_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.is_cuda() && seq_lens.numel() == q.size(0), "attention_decode: seq_lens int32 [B]");
+  TORCH_CHECK(partial.scalar_type() == at::kFloat && partial.is_contiguous(), "attention_decode: partial must be contiguous fp32");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const std::string err = tdx::attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), seq_lens.data_ptr<int>(),
+                                                partial.data_ptr<float>(), (size_t)partial.numel(), out.data_ptr(), (int)q.size(0),
+                                                (int)q.size(1), (int)k_cache.size(2), (int)q.size(2), (int)k_cache.size(1),
+                                                q.stride(0), k_cache.stride(0), k_cache.stride(1), (int)nsplit, (float)scale, cur_stream());
+  TORCH_CHECK(err.empty(), "attention_decode: ", err);
+}
+
+static tdx::Workspace* workspace_of(const Tensor& table) {
+  TORCH_CHECK(table.is_cuda(), "workspace must be the CUDA tensor returned by get_workspace");
+  tdx::Workspace* ws = tdx::Workspace::from_table(table.data_ptr());
+  TORCH_CHECK(ws != nullptr, "workspace tensor does not belong to a registered CommWorkspace");
+  return ws;
+}
+
+// Row-parallel linear + all-reduce (or reduce-scatter) + residual + RMSNorm in one kernel.
+void gemm_ar_rmsnorm(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
+                     c10::optional<Tensor> residual_out, Tensor norm_out, c10::optional<Tensor> scale_out, double eps,
+                     const Tensor& workspace, int64_t out_mode, bool scatter_only, const c10::optional<Tensor>& status) {
+  tdx::Workspace* ws = workspace_of(workspace);
+  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1), "gemm_ar_rmsnorm: a [tokens, k], w [hidden, k]");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && gamma.scalar_type() == at::kBFloat16, "gemm_ar_rmsnorm: bfloat16 operands");
+  TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1 && gamma.is_contiguous() && norm_out.is_contiguous(), "gemm_ar_rmsnorm: K-major operands, contiguous outputs");
+  const c10::cuda::CUDAGuard guard(a.device());
+  tdx::FusedGemmProblem g{};
+  ws->fill_params(&g.ar);
+  const int64_t tokens = a.size(0), hidden = w.size(0);
+  const int64_t rows = scatter_only ? (tokens + g.ar.nranks - 1) / g.ar.nranks : tokens;
+  g.ar.tokens = (int)tokens;
+  g.ar.hidden = (int)hidden;
+  g.ar.in = nullptr;
+  auto opt_ptr = [&](const c10::optional<Tensor>& t, const char* name) -> void* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_contiguous() && t->numel() == rows * hidden && t->scalar_type() == at::kBFloat16, name, " must be contiguous bf16 [", rows, ", ", hidden, "]");
+    return t->data_ptr();
+  };
+  g.ar.residual_in = opt_ptr(residual_in, "residual_in");
+  g.ar.residual_out = opt_ptr(residual_out, "residual_out");
+  g.ar.gamma = gamma.data_ptr();
+  TORCH_CHECK(gamma.numel() == hidden && norm_out.numel() == rows * hidden, "gemm_ar_rmsnorm: gamma / norm_out sizes");
+  g.ar.norm_out = norm_out.data_ptr();
+  g.ar.scale_out = nullptr;
+  if (out_mode != tdx::kOutSame) {
+    TORCH_CHECK(scale_out.has_value() && scale_out->scalar_type() == at::kFloat && scale_out->numel() == rows * (hidden / 128) && norm_out.element_size() == 1,
+                "gemm_ar_rmsnorm: fp8 output needs 1-byte norm_out and [rows, hidden/128] fp32 scales");
+    g.ar.scale_out = scale_out->data_ptr<float>();
+  } else {
+    TORCH_CHECK(norm_out.scalar_type() == at::kBFloat16, "gemm_ar_rmsnorm: norm_out must be bf16");
+  }
+  g.ar.eps = (float)eps;
+  g.ar.dtype = tdx::kBF16;
+  g.ar.out_mode = (int)out_mode;
+  g.ar.scatter_only = scatter_only ? 1 : 0;
+  g.a = a.data_ptr();
+  g.w = w.data_ptr();
+  g.k = (int)a.size(1);
+  g.lda = a.stride(0);
+  g.ldw = w.stride(0);
+  g.status = status.has_value() && status->defined() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+  const std::string err = tdx::gemm_ar_rmsnorm(g, cur_stream());
+  TORCH_CHECK(err.empty(), "gemm_ar_rmsnorm: ", err);
+}
+
+// All-gather of the sequence-parallel activation shards fused with a column-parallel linear.
+void ag_gemm(const Tensor& x_shard, const Tensor& w, Tensor out, int64_t tokens, const Tensor& workspace,
+             const c10::optional<Tensor>& status) {
+  tdx::Workspace* ws = workspace_of(workspace);
+  TORCH_CHECK(x_shard.is_cuda() && x_shard.is_contiguous() && w.is_cuda() && w.stride(1) == 1 && out.is_contiguous(), "ag_gemm: contiguous CUDA tensors");
+  TORCH_CHECK(x_shard.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "ag_gemm: bfloat16 tensors");
+  const c10::cuda::CUDAGuard guard(x_shard.device());
+  tdx::AgGemmProblem g{};
+  g.rank = ws->rank();
+  g.nranks = ws->world_size();
+  for (int r = 0; r < g.nranks; ++r) g.peer[r] = ws->peer_base(r);
+  g.layout = ws->layout();
+  g.tokens = (int)tokens;
+  g.k = (int)w.size(1);
+  const int64_t my_rows = (tokens - g.rank + g.nranks - 1) / g.nranks;
+  TORCH_CHECK(x_shard.dim() == 2 && x_shard.size(1) == g.k && x_shard.size(0) >= my_rows, "ag_gemm: x_shard must hold this rank's rows [", my_rows, ", ", g.k, "]");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == tokens && out.size(1) == w.size(0), "ag_gemm: out must be [tokens, weight rows]");
+  g.x_shard = x_shard.data_ptr();
+  g.w = w.data_ptr();
+  g.ldw = w.stride(0);
+  g.out_rows = (int)w.size(0);
+  g.out = out.data_ptr();
+  g.ldo = out.stride(0);
+  g.status = status.has_value() && status->defined() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+  g.timeout_ns = ws->timeout_ns();
+  g.host_status = ws->host_status_device_ptr();
+  const std::string err = tdx::ag_gemm(g, cur_stream());
+  TORCH_CHECK(err.empty(), "ag_gemm: ", err);
+}
+
 void register_extra_ops(torch::Library& m) {
+  m.def("gemm_ar_rmsnorm(Tensor a, Tensor w, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
+        "Tensor(c!)? scale_out, float eps, Tensor workspace, int out_mode, bool scatter_only, Tensor(d!)? status) -> ()",
+        &gemm_ar_rmsnorm);
+  m.def("attention_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor seq_lens, Tensor(a!) out, Tensor(b!) partial, "
+        "int nsplit, float scale) -> ()", &attention_decode);
+  m.def("ag_gemm(Tensor x_shard, Tensor w, Tensor(a!) out, int tokens, Tensor workspace, Tensor(b!)? status) -> ()", &ag_gemm);
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
         "bool y_scale_per_row) -> ()", &gemm_tn);

@@ -1,0 +1,51 @@
+"""Decode attention (one new token per sequence) over a contiguous bf16 KV cache, grouped-query heads."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+_scratch = {}
+
+
+def _partial(device, floats: int) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _scratch or _scratch[key].numel() < floats:
+        _scratch[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+    return _scratch[key]
+
+
+def pick_splits(batch: int, kv_heads: int, max_len: int, sms: int = 148) -> int:
+    want = max(1, (2 * sms + batch * kv_heads - 1) // (batch * kv_heads))
+    return max(1, min(want, (max_len + 255) // 256))
+
+
+def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: torch.Tensor,
+                     max_len: int, out: Optional[torch.Tensor] = None, nsplit: Optional[int] = None) -> torch.Tensor:
+    """``q [B, Hq, 128]``, caches ``[B, S_max, Hkv, 128]``, ``seq_lens`` int32 ``[B]`` -> ``[B, Hq, 128]``.
+
+    ``max_len`` (a host integer >= every sequence length) only sizes the KV split."""
+    b, hq, d = q.shape
+    hkv = k_cache.shape[2]
+    nsplit = pick_splits(b, hkv, max_len) if nsplit is None else nsplit
+    out = torch.empty(b, hq, d, dtype=q.dtype, device=q.device) if out is None else out
+    part = _partial(q.device, b * hq * nsplit * (d + 2))
+    _lib.ops().attention_decode(q, k_cache, v_cache, seq_lens, out, part, nsplit, 1.0 / math.sqrt(d))
+    return out
+
+
+def decode_attention_reference(q, k_cache, v_cache, seq_lens):
+    b, hq, d = q.shape
+    hkv = k_cache.shape[2]
+    g = hq // hkv
+    outs = []
+    for i in range(b):
+        n = int(seq_lens[i])
+        k = k_cache[i, :n].float().repeat_interleave(g, dim=1)   # [n, hq, d]
+        v = v_cache[i, :n].float().repeat_interleave(g, dim=1)
+        s = torch.einsum("hd,nhd->hn", q[i].float(), k) / math.sqrt(d)
+        outs.append(torch.einsum("hn,nhd->hd", torch.softmax(s, dim=-1), v))
+    return torch.stack(outs).to(q.dtype)

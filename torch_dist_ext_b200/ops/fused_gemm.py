@@ -1,0 +1,80 @@
+"""GEMMs fused with their collectives (one kernel each, data moved by peer loads/stores).
+
+``gemm_allreduce_rms``  row-parallel linear + all-reduce (or reduce-scatter) + residual + RMSNorm:
+                        the o_proj / down_proj step of a tensor-parallel decoder layer.
+``allgather_gemm``      all-gather of sequence-parallel rows + column-parallel linear:
+                        the qkv / gate-up step that follows a reduce-scattered norm.
+
+Both are decode-sized paths (all CTAs must be resident at once); for more tokens the functions
+fall back to the tcgen05 GEMM followed / preceded by the fused all-reduce op.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+from ..parallel import comm as _comm
+from ..utils.config import OUT_FP8_BLOCK128, OUT_SAME
+from . import gemm as _gemm
+from .fused_allreduce import fused_allreduce_rms
+
+_SM_COUNT = 148
+
+
+def _fits(tokens: int, rows: int) -> bool:
+    bn = 16 if tokens <= 16 else 64
+    return ((rows + 127) // 128) * ((tokens + bn - 1) // bn) <= _SM_COUNT
+
+
+def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor], gamma: torch.Tensor,
+                       eps: float, *, out_mode: int = OUT_SAME, scatter_only: bool = False,
+                       want_residual: bool = True, force_unfused: bool = False,
+                       ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """``y = all_reduce(a @ w.T); res = y + residual; norm = rmsnorm(res) * gamma``.
+
+    ``a [tokens, K_shard]``, ``w [hidden, K_shard]`` (bf16). Returns ``(norm, res, scales)``; with
+    ``scatter_only`` only the rows ``rank::world`` (and ``residual`` is that row shard).
+    """
+    c = _comm.get_comm()
+    tokens, hidden = a.shape[0], w.shape[0]
+    if force_unfused or not _fits(tokens, hidden) or hidden % 128 or out_mode not in (OUT_SAME, OUT_FP8_BLOCK128):
+        y = _gemm.linear(a, w)
+        return fused_allreduce_rms(y, residual, gamma, eps, out_mode=out_mode, scatter_only=scatter_only,
+                                   want_residual=want_residual)
+    n = c.world_size
+    rows = (tokens + n - 1) // n if scatter_only else tokens
+    res_out = torch.empty(rows, hidden, dtype=a.dtype, device=a.device) if want_residual else None
+    if out_mode == OUT_SAME:
+        norm, scales = torch.empty(rows, hidden, dtype=a.dtype, device=a.device), None
+    else:
+        norm = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=a.device)
+        scales = torch.empty(rows, hidden // 128, dtype=torch.float32, device=a.device)
+    status = _gemm._workspace(a.device)[2]
+    _lib.ops().gemm_ar_rmsnorm(a, w, residual, gamma, res_out, norm, scales, eps, c.get_workspace(a), out_mode,
+                               scatter_only, status)
+    return norm, res_out, scales
+
+
+def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, tokens: int, *, force_unfused: bool = False) -> torch.Tensor:
+    """``gather(x_shard) @ w.T`` where rank r holds the rows ``r::world`` of the ``[tokens, K]`` input."""
+    c = _comm.get_comm()
+    n = c.world_size
+    if force_unfused or not _fits(tokens, w.shape[0]) or tokens * w.shape[1] * 2 > (32 << 20):
+        import torch.distributed as dist
+
+        rows = (tokens + n - 1) // n
+        pad = torch.zeros(rows, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        pad[: x_shard.shape[0]] = x_shard
+        parts = [torch.empty_like(pad) for _ in range(n)]
+        if n > 1:
+            dist.all_gather(parts, pad, group=c.group)
+        else:
+            parts = [pad]
+        full = torch.stack(parts, dim=1).reshape(rows * n, -1)[:tokens].contiguous()
+        return _gemm.linear(full, w)
+    out = torch.empty(tokens, w.shape[0], dtype=x_shard.dtype, device=x_shard.device)
+    status = _gemm._workspace(x_shard.device)[2]
+    _lib.ops().ag_gemm(x_shard.contiguous(), w, out, tokens, c.get_workspace(x_shard), status)
+    return out
