@@ -1,0 +1,6 @@
+"""Drop-in name for code written against the reference package: ``import torch_dist_ext`` gives
+the same ``setup_env`` / ``get_workspace`` / ``allreduce_rms`` / ``CommProcess`` / ``CommWorkspace``
+names (reference: torch_dist_ext/__init__.py:15-84), backed by torch_dist_ext_b200."""
+from torch_dist_ext_b200 import *  # noqa: F401,F403
+from torch_dist_ext_b200 import (CommProcess, CommWorkspace, allreduce_rms, allreduce_rms_fusion_impl,  # noqa: F401
+                                 get_workspace, setup_env)
