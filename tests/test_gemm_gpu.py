@@ -43,7 +43,8 @@ def test_split_k_and_orientation_agree(splits, swap):
     check(out, a, w, 8e-3)
     # the workspace must be left zeroed: a second call gives the same result
     out2 = gemm.linear(a, w, swap=swap, splits=splits)
-    assert torch.equal(out, out2) or (out.float() - out2.float()).abs().max().item() < 1e-2
+    # (fp32 atomics add in varying order: the two results may differ by a bf16 rounding step)
+    assert (out.float() - out2.float()).abs().max().item() <= 8e-3 * out.float().abs().max().item()
 
 
 def test_fp32_output_and_strided_operands():

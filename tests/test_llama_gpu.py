@@ -80,9 +80,9 @@ def test_cuda_graph_replay_equals_eager():
     model.fill_cache_random(4, 10)
     tokens = torch.randint(0, cfg.vocab, (4,), device="cuda")
     positions = torch.full((4,), 10, device="cuda", dtype=torch.long)
+    model.capture_decode(4, max_len=32)      # its warm-up steps write position 0 of the cache
     model.decode_step(tokens, positions, max_len=32)
     hidden = model.last_hidden.float().clone()
-    model.capture_decode(4, max_len=32)
     for _ in range(4):      # replays walk the Lamport buffers with device-resident epochs
         out = model.decode(tokens, positions)
         torch.cuda.synchronize()

@@ -1,21 +1,26 @@
 // Split-KV decode attention for grouped-query heads (head dimension 128, bf16 KV cache).
 //
 // One CTA handles one (sequence, KV head, KV split) and all G query heads that share the KV head,
-// so every K/V byte is read from HBM exactly once per step. Per chunk of 128 cache positions:
-//   A  each thread takes ONE position and forms its G scores (q is broadcast from shared memory,
-//      the K row is read with 16-byte loads) - no cross-lane reduction per position;
-//   B  chunk maximum and sum per head (one block reduction per chunk), online-softmax rescale;
-//   C  threads re-map to (position group, 8-column slice) and accumulate P*V from shared-memory
-//      probabilities, V rows read coalesced.
+// so every K/V byte is read from HBM exactly once per step. K and V chunks of 64 cache positions are
+// brought into a 3-stage shared-memory ring by TMA (tiled 4-D tensor maps over the cache, 128-byte
+// swizzle, no multicast), so the copies of later chunks overlap the arithmetic. Per chunk:
+//   A  half a cache row per lane: G partial scores, the two halves joined by one shuffle per head;
+//   B  chunk maximum and sum per head, online-softmax rescale;
+//   C  16 lanes cover one V row (8 columns each) and accumulate P*V from shared-memory probabilities.
 // Splits write (max, sum, unnormalised output) to a scratch buffer; a second small kernel merges
 // them. Decode attention is bandwidth-bound (G FLOP per byte), so this path uses the SIMT pipes;
 // the tensor cores are kept for the GEMMs.
 //
 // Not part of the reference (it has no attention); needed by the Llama-shaped decoder layers.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <cfloat>
+#include <mutex>
+#include <set>
+#include "tdx/comm.h"
 #include "tdx/ops.h"
+#include "tdx/tc.cuh"
 #include "tdx/ptx.cuh"
 #include "tdx/sync.cuh"
 #include "tdx/vec.cuh"
@@ -24,42 +29,92 @@ namespace tdx {
 namespace {
 
 constexpr int kD = 128;
-constexpr int kChunk = 128;
+constexpr int kChunk = 64;            // cache positions per pipeline stage
+constexpr int kStagesKV = 3;
 constexpr int kAttnThreads = 128;
 constexpr int kMaxG = 8;
+constexpr int kHalfBytes = kChunk * 128;          // one 64-column half of a K or V chunk
+constexpr int kStageBytesKV = 4 * kHalfBytes;     // K lo, K hi, V lo, V hi
+constexpr int kAttnSmem = kStagesKV * kStageBytesKV + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr uint32_t kAttnWaitLimit = 1u << 22;
 
 struct AttnArgs {
   const __nv_bfloat16* q;      // [B, Hq, D]
-  const __nv_bfloat16* k;      // [B, S_max, Hkv, D]
-  const __nv_bfloat16* v;
   const int32_t* seq_lens;     // [B] valid positions per sequence
   float* partial;              // [B, Hq, nsplit, D + 2]
   __nv_bfloat16* out;          // [B, Hq, D]
   int B, Hq, Hkv, S_max, nsplit;
-  int64_t q_stride_b, kv_stride_b, kv_stride_s;   // elements
+  int64_t q_stride_b;          // elements
   float scale;
+  uint32_t* status;
 };
 
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(tc::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// 16 bytes (8 bf16) of row `r`, logical 16-byte chunk `c` (0..7) of a 128-byte-swizzled half tile.
+__device__ __forceinline__ uint4 ld_swizzled(const uint8_t* half_tile, int r, int c) {
+  return *reinterpret_cast<const uint4*>(half_tile + r * 128 + ((c ^ (r & 7)) << 4));
+}
+
+// K and V chunks arrive by TMA (tiled 4-D maps over the cache, 128-byte swizzle) in a 3-stage ring,
+// so the loads of later chunks overlap the arithmetic on the current one and no thread issues a
+// global load for the cache. Thread mapping per 64-row chunk:
+//   scores   lane l of warp w takes row 16*w + (l & 15) and the column half (l >> 4); the two halves
+//            are added with one shuffle per query head;
+//   P * V    16 lanes cover one V row (8 columns each), a warp takes two rows per step.
 template <int kG>
-__global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                         const __grid_constant__ CUtensorMap map_v,
+                                                                         const AttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
   __shared__ float q_s[kG][kD];
   __shared__ float p_s[kG][kChunk];
-  __shared__ float acc_s[4][kG][kD];      // per-warp partial outputs, merged at the end
+  __shared__ float wred[2][kG][4];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + kStagesKV * kStageBytesKV);
+  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(full + kStagesKV);
+
   const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int len = a.seq_lens[b];
   const int per = (len + a.nsplit - 1) / a.nsplit;
   const int s0 = split * per, s1 = min(len, s0 + per);
+  const int nchunks = s1 > s0 ? (s1 - s0 + kChunk - 1) / kChunk : 0;
 
+  auto issue = [&](int i) {
+    const int st = i % kStagesKV;
+    uint8_t* base = ring + st * kStageBytesKV;
+    tc::mbar_arrive_expect_tx(&full[st], kStageBytesKV);
+    const int pos0 = s0 + i * kChunk;
+    tma_load_4d(base, &map_k, &full[st], 0, hkv, pos0, b);
+    tma_load_4d(base + kHalfBytes, &map_k, &full[st], 64, hkv, pos0, b);
+    tma_load_4d(base + 2 * kHalfBytes, &map_v, &full[st], 0, hkv, pos0, b);
+    tma_load_4d(base + 3 * kHalfBytes, &map_v, &full[st], 64, hkv, pos0, b);
+  };
+  if (tid == 0) {
+    for (int st = 0; st < kStagesKV; ++st) tc::mbar_init(&full[st], 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_k);
+    tc::tma_prefetch_desc(&map_v);
+  }
   for (int i = tid; i < kG * kD; i += kAttnThreads) {
     const int g = i / kD, d = i % kD;
     q_s[g][d] = __bfloat162float(a.q[(int64_t)b * a.q_stride_b + (int64_t)(hkv * kG + g) * kD + d]) * a.scale;
   }
   __syncthreads();
+  if (tid == 0)
+    for (int i = 0; i < nchunks && i < kStagesKV; ++i) issue(i);
 
   float m_run[kG], l_run[kG];
-  // phase C mapping: 16 threads cover one V row (8 columns each); a warp handles 2 rows per step
-  const int vslice = (lane & 15) * 8;
+  const int arow = warp * 16 + (lane & 15);   // score phase: row inside the chunk
+  const int ahalf = lane >> 4;                // score phase: column half
+  const int vslice = lane & 15;               // P*V phase: 8-column slice of the row
   const int vsub = lane >> 4;
   float acc[kG][8];
 #pragma unroll
@@ -69,89 +124,92 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const A
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[g][i] = 0.f;
   }
-  const __nv_bfloat16* kbase = a.k + (int64_t)b * a.kv_stride_b + (int64_t)hkv * kD;
-  const __nv_bfloat16* vbase = a.v + (int64_t)b * a.kv_stride_b + (int64_t)hkv * kD;
 
-  for (int c0 = s0; c0 < s1; c0 += kChunk) {
-    const int pos = c0 + tid;
-    // ---- A: one position per thread ----
+  for (int i = 0; i < nchunks; ++i) {
+    const int st = i % kStagesKV;
+    const uint8_t* base = ring + st * kStageBytesKV;
+    if (!tc::mbar_wait(&full[st], (i / kStagesKV) & 1, kAttnWaitLimit, abort_flag)) {
+      *abort_flag = 1;
+      if (a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
+      break;
+    }
+    const int c0 = s0 + i * kChunk;
+    const bool live = c0 + arow < s1;
+    // ---- scores: half a row per lane ----
     float s[kG];
 #pragma unroll
     for (int g = 0; g < kG; ++g) s[g] = 0.f;
-    if (pos < s1) {
-      const char* krow = reinterpret_cast<const char*>(kbase + (int64_t)pos * a.kv_stride_s);
-#pragma unroll 4
-      for (int d = 0; d < kD; d += 8) {
-        float kf[8];
-        unpack<__nv_bfloat16>(ptx::ld_v4(krow + d * 2), kf);
+    const uint8_t* khalf = base + ahalf * kHalfBytes;
 #pragma unroll
-        for (int g = 0; g < kG; ++g)
+    for (int c = 0; c < 8; ++c) {
+      float kf[8];
+      unpack<__nv_bfloat16>(ld_swizzled(khalf, arow, c), kf);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) s[g] = fmaf(q_s[g][d + i], kf[i], s[g]);
-      }
-    } else {
+      for (int g = 0; g < kG; ++g)
 #pragma unroll
-      for (int g = 0; g < kG; ++g) s[g] = -FLT_MAX;
+        for (int j = 0; j < 8; ++j) s[g] = fmaf(q_s[g][ahalf * 64 + c * 8 + j], kf[j], s[g]);
     }
-    // ---- B: chunk statistics, rescale ----
-    // chunk maximum per head (scores can be negative: the identity is -FLT_MAX)
-    float cmaxv[kG];
 #pragma unroll
     for (int g = 0; g < kG; ++g) {
+      s[g] += __shfl_xor_sync(0xffffffffu, s[g], 16);
+      if (!live) s[g] = -FLT_MAX;
       float v = s[g];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-      if (lane == 0) acc_s[0][g][warp] = v;   // scratch use before the final merge
+      for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+      if (lane == 0) wred[0][g][warp] = v;
     }
     __syncthreads();
-#pragma unroll
-    for (int g = 0; g < kG; ++g)
-      cmaxv[g] = fmaxf(fmaxf(acc_s[0][g][0], acc_s[0][g][1]), fmaxf(acc_s[0][g][2], acc_s[0][g][3]));
     float corr[kG];
 #pragma unroll
     for (int g = 0; g < kG; ++g) {
-      const float m_new = fmaxf(m_run[g], cmaxv[g]);
+      const float cmax = fmaxf(fmaxf(wred[0][g][0], wred[0][g][1]), fmaxf(wred[0][g][2], wred[0][g][3]));
+      const float m_new = fmaxf(m_run[g], cmax);
       corr[g] = __expf(m_run[g] - m_new);
-      const float p = (pos < s1) ? __expf(s[g] - m_new) : 0.f;
-      p_s[g][tid] = p;
-      float ps = p;
+      const float p = live ? __expf(s[g] - m_new) : 0.f;
+      if (ahalf == 0) p_s[g][arow] = p;
+      float ps = ahalf == 0 ? p : 0.f;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-      if (lane == 0) acc_s[1][g][warp] = ps;
+      for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      if (lane == 0) wred[1][g][warp] = ps;
       m_run[g] = m_new;
     }
     __syncthreads();
 #pragma unroll
     for (int g = 0; g < kG; ++g) {
-      const float csum = acc_s[1][g][0] + acc_s[1][g][1] + acc_s[1][g][2] + acc_s[1][g][3];
+      const float csum = wred[1][g][0] + wred[1][g][1] + wred[1][g][2] + wred[1][g][3];
       l_run[g] = l_run[g] * corr[g] + csum;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[g][i] *= corr[g];
+      for (int j = 0; j < 8; ++j) acc[g][j] *= corr[g];
     }
-    // ---- C: P * V; warp w covers chunk rows w*32 .. w*32+31, two rows per step ----
-    const int rows = min(kChunk, s1 - c0);
-    for (int r = warp * 32 + vsub; r < min(rows, warp * 32 + 32); r += 2) {
+    // ---- P * V: warp w covers rows 16w .. 16w+15 of the chunk, two rows per step ----
+    const uint8_t* vhalf = base + (2 + (vslice >> 3)) * kHalfBytes;
+#pragma unroll
+    for (int step = 0; step < 8; ++step) {
+      const int r = warp * 16 + step * 2 + vsub;
       float vf[8];
-      unpack<__nv_bfloat16>(ptx::ld_v4(reinterpret_cast<const char*>(vbase + (int64_t)(c0 + r) * a.kv_stride_s) + vslice * 2), vf);
+      unpack<__nv_bfloat16>(ld_swizzled(vhalf, r, vslice & 7), vf);
 #pragma unroll
       for (int g = 0; g < kG; ++g) {
-        const float p = p_s[g][r];
+        const float p = p_s[g][r];       // zero for rows beyond the sequence
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i]);
+        for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(p, vf[j], acc[g][j]);
       }
     }
-    __syncthreads();   // p_s / scratch reused by the next chunk
+    __syncthreads();   // every thread is done with this stage, p_s and wred
+    if (tid == 0 && i + kStagesKV < nchunks) issue(i + kStagesKV);
   }
   // merge the two half-warps, then the four warps
 #pragma unroll
   for (int g = 0; g < kG; ++g)
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[g][i] += __shfl_xor_sync(0xffffffffu, acc[g][i], 16);
+    for (int j = 0; j < 8; ++j) acc[g][j] += __shfl_xor_sync(0xffffffffu, acc[g][j], 16);
+  // all chunks have been consumed, so the ring is free: use it for the per-warp partial outputs
+  float (*acc_s)[kG][kD] = reinterpret_cast<float (*)[kG][kD]>(ring);
   if (vsub == 0) {
 #pragma unroll
     for (int g = 0; g < kG; ++g)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc_s[warp][g][vslice + i] = acc[g][i];
+      for (int j = 0; j < 8; ++j) acc_s[warp][g][vslice * 8 + j] = acc[g][j];
   }
   __syncthreads();
   for (int i = tid; i < kG * kD; i += kAttnThreads) {
@@ -163,6 +221,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const A
       dst[kD] = m_run[g];      // identical in every thread
       dst[kD + 1] = l_run[g];
     }
+  }
+  if (*abort_flag) {
+    // let copies that were already requested land before the shared memory goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
 }
 
@@ -183,10 +245,62 @@ __global__ void __launch_bounds__(kD) attn_combine_kernel(const AttnArgs a) {
 
 }  // namespace
 
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn attn_encoder() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// cache [B, S, Hkv, 128] bf16 -> 4-D map (128, Hkv, S, B); one box = 64 columns x 64 positions of one head
+std::string cache_map(CUtensorMap* map, const void* ptr, int B, int S, int Hkv, int64_t stride_b, int64_t stride_s) {
+  EncodeFn enc = attn_encoder();
+  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
+  const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)Hkv, (cuuint64_t)S, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)stride_s * 2, (cuuint64_t)stride_b * 2};
+  const cuuint32_t box[4] = {64, 1, (cuuint32_t)kChunk, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? "" : "cuTensorMapEncodeTiled failed for the KV cache (CUresult " + std::to_string((int)r) + ")";
+}
+
+template <int kG>
+std::string launch_attn(const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, dim3 grid, cudaStream_t stream) {
+  auto kern = attn_decode_split_kernel<kG>;
+  static std::mutex mu;
+  static std::set<int> done;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done.count(dev)) {
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+      if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
+      done.insert(dev);
+    }
+  }
+  kern<<<grid, kAttnThreads, kAttnSmem, stream>>>(mk, mv, a);
+  return "";
+}
+
+}  // namespace
+
 std::string attention_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
                              float* partial, size_t partial_floats, void* out, int B, int Hq, int Hkv, int D, int S_max,
                              int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, uint32_t* status) {
   if (D != kD) return "decode attention supports head dimension 128";
   if (Hkv <= 0 || Hq % Hkv) return "query heads must be a multiple of KV heads";
   const int G = Hq / Hkv;
@@ -199,21 +313,26 @@ std::string attention_decode(const void* q, const void* k_cache, const void* v_c
   if (B == 0) return "";
   AttnArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q);
-  a.k = static_cast<const __nv_bfloat16*>(k_cache);
-  a.v = static_cast<const __nv_bfloat16*>(v_cache);
   a.seq_lens = seq_lens;
   a.partial = partial;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.S_max = S_max; a.nsplit = nsplit;
-  a.q_stride_b = q_stride_b; a.kv_stride_b = kv_stride_b; a.kv_stride_s = kv_stride_s;
+  a.q_stride_b = q_stride_b;
   a.scale = scale;
+  a.status = status;
+  CUtensorMap mk, mv;
+  std::string err = cache_map(&mk, k_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s);
+  if (!err.empty()) return err;
+  err = cache_map(&mv, v_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s);
+  if (!err.empty()) return err;
   const dim3 grid(B, Hkv, nsplit);
   switch (G) {
-    case 1: attn_decode_split_kernel<1><<<grid, kAttnThreads, 0, stream>>>(a); break;
-    case 2: attn_decode_split_kernel<2><<<grid, kAttnThreads, 0, stream>>>(a); break;
-    case 4: attn_decode_split_kernel<4><<<grid, kAttnThreads, 0, stream>>>(a); break;
-    case 8: attn_decode_split_kernel<8><<<grid, kAttnThreads, 0, stream>>>(a); break;
+    case 1: err = launch_attn<1>(mk, mv, a, grid, stream); break;
+    case 2: err = launch_attn<2>(mk, mv, a, grid, stream); break;
+    case 4: err = launch_attn<4>(mk, mv, a, grid, stream); break;
+    case 8: err = launch_attn<8>(mk, mv, a, grid, stream); break;
   }
+  if (!err.empty()) return err;
   attn_combine_kernel<<<dim3(B, Hq), kD, 0, stream>>>(a);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);

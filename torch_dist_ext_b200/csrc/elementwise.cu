@@ -144,13 +144,25 @@ template <typename T>
 __global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ q, T* __restrict__ k,
                                                    const int64_t* __restrict__ positions,
                                                    const float* __restrict__ cache, int tokens, int q_heads,
-                                                   int k_heads, int dim, int64_t q_stride, int64_t k_stride) {
+                                                   int k_heads, int dim, int64_t q_stride, int64_t k_stride,
+                                                   const T* __restrict__ v, int64_t v_stride, T* __restrict__ k_cache,
+                                                   T* __restrict__ v_cache, int64_t cache_stride_b,
+                                                   int64_t cache_stride_s) {
   constexpr int kVec = VecTraits<T>::kVec;
   const int half = dim / 2;
   const int per_head = half / kVec;
   const int items = (q_heads + k_heads) * per_head;
   for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
-    const float* cs = cache + positions[t] * dim;
+    const int64_t pos = positions[t];
+    const float* cs = cache + pos * dim;
+    // decode: sequence t appends its new key/value row at position pos of its cache
+    T* kc = k_cache ? k_cache + t * cache_stride_b + pos * cache_stride_s : nullptr;
+    if (v_cache) {
+      T* vc = v_cache + t * cache_stride_b + pos * cache_stride_s;
+      const T* vsrc = v + (size_t)t * v_stride;
+      for (int it = threadIdx.x; it < k_heads * dim / kVec; it += blockDim.x)
+        *reinterpret_cast<uint4*>(vc + it * kVec) = ptx::ld_v4(vsrc + it * kVec);
+    }
     for (int it = threadIdx.x; it < items; it += blockDim.x) {
       const int head = it / per_head;
       const int off = (it % per_head) * kVec;
@@ -168,6 +180,11 @@ __global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ q, T* __restr
       }
       *reinterpret_cast<uint4*>(base + off) = pack<T>(ra);
       *reinterpret_cast<uint4*>(base + half + off) = pack<T>(rb);
+      if (kc && head >= q_heads) {
+        T* dst = kc + (size_t)(head - q_heads) * dim;
+        *reinterpret_cast<uint4*>(dst + off) = pack<T>(ra);
+        *reinterpret_cast<uint4*>(dst + half + off) = pack<T>(rb);
+      }
     }
   }
 }
@@ -228,14 +245,17 @@ std::string silu_mul(const void* in, void* out, float* scales, int rows, int int
 
 std::string rope_inplace(void* q, void* k, const int64_t* positions, const float* cos_sin_cache, int tokens,
                          int q_heads, int k_heads, int dim, int64_t q_stride, int64_t k_stride, int dtype,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const void* v, int64_t v_stride, void* k_cache, void* v_cache,
+                         int64_t cache_stride_b, int64_t cache_stride_s) {
   const int vec = dtype == kF32 ? 4 : 8;
   if (dim % (2 * vec)) return "head dimension must be a multiple of 2 x 16 bytes";
   if (tokens == 0) return "";
   const int grid = tokens < 148 * 8 ? tokens : 148 * 8;
   TDX_DISPATCH_DTYPE(dtype, {
     rope_kernel<T><<<grid, 256, 0, stream>>>(static_cast<T*>(q), static_cast<T*>(k), positions, cos_sin_cache, tokens,
-                                             q_heads, k_heads, dim, q_stride, k_stride);
+                                             q_heads, k_heads, dim, q_stride, k_stride, static_cast<const T*>(v), v_stride,
+                                             static_cast<T*>(k_cache), static_cast<T*>(v_cache), cache_stride_b,
+                                             cache_stride_s);
   });
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);

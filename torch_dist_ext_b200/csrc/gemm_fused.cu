@@ -48,26 +48,65 @@ constexpr int kElemsPerBlock = 64;
 struct FusedArgs {
   ArParams ar;        // communication state and the description of the reduce/normalise tail
   int kblocks;
+  int kblocks_per_split;
   uint32_t idesc;
   uint32_t* status;
+  float* ws;          // split-K scratch, zero on entry and on exit
+  uint32_t* counters;
 };
 
 // D tile (TMEM) -> bf16 rows in shared memory -> 16-byte pushes into the owners' gather slots.
+// With K split over gridDim.z the partial tiles are first summed in an fp32 scratch tile with
+// red.global.add; the CTA that arrives last at the tile converts and pushes it (and leaves the
+// scratch tile and its counter zeroed for the next call).
 template <int kBN>
-__device__ __forceinline__ void push_tile_to_owners(const ArParams& p, uint8_t* stage, uint32_t tmem_base, int tile_x,
-                                                    int tile_y, size_t buf_off, int groups) {
+__device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const FusedArgs& f, uint8_t* stage,
+                                                    uint32_t* shared_flag, uint32_t tmem_base, int tile_x, int tile_y,
+                                                    size_t buf_off, int groups) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = warp & 3;
   const int te = threadIdx.x - 64;                 // 0..127 among the epilogue threads
+  const int xl = q * 32 + lane;                    // column of this thread inside the tile
   const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
   __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
+  bool push = true;
+  if (gridDim.z > 1) {
+    // column-major scratch tile: a warp's 32 lanes add to one 128-byte line per instruction
+    float* tile = f.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + xl;
 #pragma unroll
-  for (int c = 0; c < kBN; c += 16) {
-    float v[16];
-    tc::tmem_ld_16(lane_addr + c, v);
+    for (int c = 0; c < kBN; c += 16) {
+      float v[16];
+      tc::tmem_ld_16(lane_addr + c, v);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) st[(c + j) * kBM + q * 32 + lane] = __float2bfloat16(v[j]);
+      for (int j = 0; j < 16; ++j) atomicAdd(tile + (size_t)(c + j) * kBM, v[j]);
+    }
+    __threadfence();
+    tc::named_barrier_sync(1, 128);
+    if (te == 0) {
+      const uint32_t prev = atomicAdd(&f.counters[tile_y * gridDim.x + tile_x], 1u);
+      *shared_flag = (prev == gridDim.z - 1) ? 1u : 0u;
+    }
+    tc::named_barrier_sync(1, 128);
+    push = *shared_flag != 0;
+    if (push) {
+      __threadfence();
+#pragma unroll
+      for (int c = 0; c < kBN; ++c) {
+        st[c * kBM + xl] = __float2bfloat16(__ldcg(tile + (size_t)c * kBM));
+        __stcg(tile + (size_t)c * kBM, 0.f);
+      }
+      if (te == 0) f.counters[tile_y * gridDim.x + tile_x] = 0;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < kBN; c += 16) {
+      float v[16];
+      tc::tmem_ld_16(lane_addr + c, v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) st[(c + j) * kBM + xl] = __float2bfloat16(v[j]);
+    }
   }
+  if (!push) return;
   tc::named_barrier_sync(1, 128);
   const int y_base = tile_y * kBN;
   const int valid = min(kBN, p.tokens - y_base);
@@ -98,21 +137,25 @@ gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   const uint64_t dirty_prev = ctl->lamport_dirty[(epoch + 2u) % 3u];
   const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
   const int groups = (p.tokens + p.nranks - 1) / p.nranks;
-  const int cta = blockIdx.x + gridDim.x * blockIdx.y, nctas = gridDim.x * gridDim.y;
+  const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const int nctas = gridDim.x * gridDim.y * gridDim.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb0 = blockIdx.z * f.kblocks_per_split;
+  const int nkb = min(f.kblocks, kb0 + f.kblocks_per_split) - kb0;
 
   if (warp == 0) {
     if (lane == 0)
-      pipe.template produce<kElemsPerBlock>(&map_w, &map_a, blockIdx.x * kBM, blockIdx.y * kBN, 0, f.kblocks, f.status,
+      pipe.template produce<kElemsPerBlock>(&map_w, &map_a, blockIdx.x * kBM, blockIdx.y * kBN, kb0, nkb, f.status,
                                             [] { return true; });
   } else if (warp == 1) {
-    if (lane == 0) pipe.template issue<false, false>(f.kblocks, f.idesc, f.status);
+    if (lane == 0) pipe.template issue<false, false>(nkb, f.idesc, f.status);
   } else if (warp < 6) {
     const bool ok = tc::mbar_wait(&pipe.acc_full[0], 0, gemm_core::kWaitLimit, pipe.abort_flag);
     tc::fence_after_thread_sync();
     if (!ok) pipe.fail(f.status);
     // every MMA has completed, so the operand ring is free: stage the tile there
-    if (ok) push_tile_to_owners<kBN>(p, pipe.smem, pipe.tmem_base, blockIdx.x, blockIdx.y, buf_off, groups);
+    if (ok)
+      push_tile_to_owners<kBN>(p, f, pipe.smem, pipe.scratch, pipe.tmem_base, blockIdx.x, blockIdx.y, buf_off, groups);
   }
   __syncthreads();
   clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev, cta, nctas);
@@ -326,9 +369,21 @@ std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, c
   if (p.out_mode != kOutSame && p.out_mode != kOutFp8Block128) return "fused GEMM output is bf16 or e4m3 with 1x128 scales";
   if (p.tokens <= 0) return "";
   const int bn = p.tokens <= 16 ? 16 : 64;
-  const dim3 grid(p.hidden / 128, (p.tokens + bn - 1) / bn, 1);
-  if ((int)(grid.x * grid.y) > sm_count())
+  dim3 grid(p.hidden / 128, (p.tokens + bn - 1) / bn, 1);
+  const int sms = sm_count();
+  if ((int)(grid.x * grid.y) > sms)
     return "too many tokens for the fused GEMM (all CTAs must be resident): use the GEMM followed by the all-reduce op";
+  // split K until the grid covers the SMs (every CTA must stay resident, so never beyond them)
+  const int kblocks = g.k / 64;
+  int splits = g.splits > 0 ? g.splits : sms / (int)(grid.x * grid.y);
+  if (splits > kblocks / 2) splits = kblocks / 2;
+  if (splits < 1 || g.ws == nullptr || g.counters == nullptr) splits = 1;
+  while (splits > 1 && (int)(grid.x * grid.y) * splits > sms) --splits;
+  int per_split = (kblocks + splits - 1) / splits;
+  splits = (kblocks + per_split - 1) / per_split;
+  if (splits > 1 && ((size_t)grid.x * grid.y * kBM * bn * sizeof(float) > g.ws_bytes || (size_t)grid.x * grid.y > g.counter_count))
+    return "split-K workspace is too small";
+  grid.z = splits;
   const int nvec = p.hidden / 8;
   const int vpt = nvec <= kThreads ? 1 : nvec <= 2 * kThreads ? 2 : nvec <= 4 * kThreads ? 4 : 0;
   const uint64_t row_bytes = (uint64_t)p.hidden * 2;
@@ -339,9 +394,12 @@ std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, c
     if (p.peer[r] == nullptr) return "workspace is not registered with all peers";
   FusedArgs f{};
   f.ar = p;
-  f.kblocks = g.k / 64;
+  f.kblocks = kblocks;
+  f.kblocks_per_split = per_split;
   f.idesc = tc::make_idesc(kBM, bn, 1, 1);
   f.status = g.status;
+  f.ws = g.ws;
+  f.counters = g.counters;
   CUtensorMap mw, ma;
   std::string err = bf16_map(&mw, g.w, p.hidden, g.k, g.ldw, kBM);
   if (!err.empty()) return err;

@@ -47,7 +47,7 @@ struct GemmArgs {
   int64_t sx, sy;          // D[x, y] -> out[x * sx + y * sy]
   int out_dtype;           // kF32 / kF16 / kBF16
   uint32_t idesc;
-  float* ws;               // split-K: fp32 [x_tiles*128, ws_ld], zero on entry and on exit
+  float* ws;               // split-K: fp32 tiles [tile][column][128 rows], zero on entry and on exit
   int ws_ld;
   uint32_t* counters;      // split-K: one per output tile, zero on entry and on exit
   uint32_t* status;        // device word: non-zero after a wait ran out
@@ -172,9 +172,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (!split) {
           store_chunk(a, x, y_base + c, v);
         } else {
-          float* dst = a.ws + (size_t)(tile_x * kBM + q * 32 + lane) * a.ws_ld + y_base + c;
+          // scratch tile is column-major ([column][128 rows]): the lanes of a warp add to 32
+          // consecutive floats, one 128-byte line per instruction
+          float* dst = a.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + (size_t)c * kBM + q * 32 + lane;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) atomicAdd(dst + j, v[j]);
+          for (int j = 0; j < 16; ++j) atomicAdd(dst + j * kBM, v[j]);
         }
       }
     }
@@ -189,14 +191,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       tc::named_barrier_sync(1, 128);
       if (*last_flag) {
         __threadfence();
-        float* src = a.ws + (size_t)(tile_x * kBM + q * 32 + lane) * a.ws_ld + y_base;
+        float* src = a.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + q * 32 + lane;
 #pragma unroll
         for (int c = 0; c < kBN; c += 16) {
           float v[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            v[j] = __ldcg(src + c + j);
-            __stcg(src + c + j, 0.f);
+            v[j] = __ldcg(src + (size_t)(c + j) * kBM);
+            __stcg(src + (size_t)(c + j) * kBM, 0.f);
           }
           store_chunk(a, x, y_base + c, v);
         }
@@ -318,7 +320,7 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
   if (splits > 1) {
     if (!g.ws || !g.counters) return "split-K needs a workspace";
     a.ws_ld = grid.y * bn;
-    if ((size_t)grid.x * kBM * a.ws_ld * sizeof(float) > g.ws_bytes || (size_t)grid.x * grid.y > g.counter_count)
+    if ((size_t)grid.x * grid.y * kBM * bn * sizeof(float) > g.ws_bytes || (size_t)grid.x * grid.y > g.counter_count)
       return "split-K workspace is too small for this problem";
     a.ws = g.ws;
     a.counters = g.counters;

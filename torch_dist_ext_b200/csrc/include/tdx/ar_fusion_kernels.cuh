@@ -203,9 +203,13 @@ __device__ __forceinline__ uint4 poll_vec(const char* addr, Waiter& w, const ArP
   uint4 v = ptx::ld_volatile_v4(addr);
   if (all_arrived(v)) return v;
   w.begin();
+  uint32_t backoff = 20;
   while (true) {
     v = ptx::ld_volatile_v4(addr);
     if (all_arrived(v)) return v;
+    // back off between polls so that waiting blocks do not crowd the L2 that the producers need
+    __nanosleep(backoff);
+    if (backoff < 320) backoff <<= 1;
     if (!w.keep_waiting()) {
       report_error(ctl, p.host_status, code, p.rank, peer, phase, row);
       return v;

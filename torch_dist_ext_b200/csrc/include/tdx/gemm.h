@@ -44,6 +44,11 @@ struct FusedGemmProblem {
   int k;
   int64_t lda, ldw;
   uint32_t* status;
+  int splits;          // K splits (0 = fill the SMs); > 1 needs the scratch below
+  float* ws;           // zero-initialised fp32 scratch, left zeroed by the kernel
+  size_t ws_bytes;
+  uint32_t* counters;  // zero-initialised, one per output tile
+  size_t counter_count;
 };
 std::string gemm_ar_rmsnorm(const FusedGemmProblem& g, cudaStream_t stream);
 std::string gemm_ar_rmsnorm_n0(const FusedGemmProblem& g, cudaStream_t stream);

@@ -19,9 +19,12 @@ std::string silu_mul(const void* in, void* out, float* scales, int rows, int int
 
 // Rotary embedding in place on q [tokens, q_heads, dim] and k [tokens, k_heads, dim] (row strides in
 // elements), rotate-half layout; cos_sin_cache [max_pos, dim] fp32 = {cos | sin}.
+// With caches given (decode: token t is the new token of sequence t) the rotated key row and the
+// value row are also written to k_cache / v_cache [B, S, k_heads, dim] at [t, positions[t]].
 std::string rope_inplace(void* q, void* k, const int64_t* positions, const float* cos_sin_cache, int tokens,
                          int q_heads, int k_heads, int dim, int64_t q_stride, int64_t k_stride, int dtype,
-                         cudaStream_t stream);
+                         cudaStream_t stream, const void* v = nullptr, int64_t v_stride = 0, void* k_cache = nullptr,
+                         void* v_cache = nullptr, int64_t cache_stride_b = 0, int64_t cache_stride_s = 0);
 
 // Decode attention over a contiguous bf16 KV cache [B, S_max, Hkv, 128] for one new token per
 // sequence: q [B, Hq, 128] -> out [B, Hq, 128]. `partial` is fp32 scratch of at least
@@ -29,6 +32,6 @@ std::string rope_inplace(void* q, void* k, const int64_t* positions, const float
 std::string attention_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
                              float* partial, size_t partial_floats, void* out, int B, int Hq, int Hkv, int D, int S_max,
                              int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,
-                             cudaStream_t stream);
+                             cudaStream_t stream, uint32_t* status = nullptr);
 
 }  // namespace tdx

@@ -79,7 +79,21 @@ void silu_mul(const Tensor& gate_up, Tensor out, c10::optional<Tensor> scales) {
   TORCH_CHECK(err.empty(), "silu_mul: ", err);
 }
 
+void rope_impl(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin_cache, const c10::optional<Tensor>& v,
+               c10::optional<Tensor> k_cache, c10::optional<Tensor> v_cache);
+
 void rope_(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin_cache) {
+  rope_impl(q, k, positions, cos_sin_cache, c10::nullopt, c10::nullopt, c10::nullopt);
+}
+
+// rope on q and k, and append of the rotated k row and the v row to the decode KV cache, in one kernel
+void rope_append_kv_(Tensor q, Tensor k, const Tensor& v, const Tensor& positions, const Tensor& cos_sin_cache, Tensor k_cache,
+                     Tensor v_cache) {
+  rope_impl(q, k, positions, cos_sin_cache, v, k_cache, v_cache);
+}
+
+void rope_impl(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin_cache, const c10::optional<Tensor>& v,
+               c10::optional<Tensor> k_cache, c10::optional<Tensor> v_cache) {
   TORCH_CHECK(q.is_cuda() && k.is_cuda() && q.dim() == 3 && k.dim() == 3, "q and k must be [tokens, heads, dim] CUDA tensors");
   TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && q.stride(1) == q.size(2) && k.stride(1) == k.size(2), "heads must be densely packed");
   TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_cuda() && positions.numel() == q.size(0), "positions must be int64 [tokens]");
@@ -89,9 +103,25 @@ void rope_(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin_ca
   TORCH_CHECK((q.stride(0) * esz) % 16 == 0 && (k.stride(0) * esz) % 16 == 0 && (uintptr_t)q.data_ptr() % 16 == 0 && (uintptr_t)k.data_ptr() % 16 == 0,
               "q and k rows must be 16-byte aligned");
   const c10::cuda::CUDAGuard guard(q.device());
+  const void* vp = nullptr;
+  void *kc = nullptr, *vc = nullptr;
+  int64_t vs = 0, cb = 0, cs = 0;
+  if (k_cache.has_value() && k_cache->defined()) {
+    TORCH_CHECK(v.has_value() && v_cache.has_value(), "rope_append_kv_: v and both caches are needed");
+    TORCH_CHECK(k_cache->dim() == 4 && k_cache->sizes() == v_cache->sizes() && k_cache->strides() == v_cache->strides() &&
+                    k_cache->size(2) == k.size(1) && k_cache->size(3) == k.size(2) && k_cache->size(0) >= q.size(0) &&
+                    k_cache->stride(3) == 1 && k_cache->stride(2) == k.size(2) && k_cache->scalar_type() == k.scalar_type(),
+                "rope_append_kv_: caches must be [B >= tokens, S, k_heads, dim] with dense heads, in k's dtype");
+    TORCH_CHECK(v->dim() == 3 && v->sizes() == k.sizes() && v->stride(2) == 1 && v->stride(1) == v->size(2) &&
+                    (v->stride(0) * esz) % 16 == 0 && (uintptr_t)v->data_ptr() % 16 == 0, "rope_append_kv_: v must look like k");
+    TORCH_CHECK((k_cache->stride(1) * esz) % 16 == 0 && (k_cache->stride(0) * esz) % 16 == 0, "rope_append_kv_: cache rows must be 16-byte aligned");
+    vp = v->data_ptr(); vs = v->stride(0);
+    kc = k_cache->data_ptr(); vc = v_cache->data_ptr();
+    cb = k_cache->stride(0); cs = k_cache->stride(1);
+  }
   const std::string err = tdx::rope_inplace(q.data_ptr(), k.data_ptr(), positions.data_ptr<int64_t>(), cos_sin_cache.data_ptr<float>(),
                                             (int)q.size(0), (int)q.size(1), (int)k.size(1), (int)q.size(2), q.stride(0),
-                                            k.stride(0), dtype_code(q), cur_stream());
+                                            k.stride(0), dtype_code(q), cur_stream(), vp, vs, kc, vc, cb, cs);
   TORCH_CHECK(err.empty(), "rope: ", err);
 }
 
@@ -148,7 +178,7 @@ void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t s
 }
 
 void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor out,
-                      Tensor partial, int64_t nsplit, double scale) {
+                      Tensor partial, int64_t nsplit, double scale, const c10::optional<Tensor>& status) {
   TORCH_CHECK(q.is_cuda() && q.dim() == 3 && k_cache.dim() == 4 && v_cache.dim() == 4, "attention_decode: q [B, Hq, D], caches [B, S, Hkv, D]");
   TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k_cache.scalar_type() == at::kBFloat16 && v_cache.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "attention_decode: bfloat16 tensors");
   TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == q.size(2) && out.is_contiguous(), "attention_decode: q heads densely packed, out contiguous");
@@ -159,7 +189,8 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   const std::string err = tdx::attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), seq_lens.data_ptr<int>(),
                                                 partial.data_ptr<float>(), (size_t)partial.numel(), out.data_ptr(), (int)q.size(0),
                                                 (int)q.size(1), (int)k_cache.size(2), (int)q.size(2), (int)k_cache.size(1),
-                                                q.stride(0), k_cache.stride(0), k_cache.stride(1), (int)nsplit, (float)scale, cur_stream());
+                                                q.stride(0), k_cache.stride(0), k_cache.stride(1), (int)nsplit, (float)scale, cur_stream(),
+                                                status.has_value() && status->defined() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr);
   TORCH_CHECK(err.empty(), "attention_decode: ", err);
 }
 
@@ -173,7 +204,8 @@ static tdx::Workspace* workspace_of(const Tensor& table) {
 // Row-parallel linear + all-reduce (or reduce-scatter) + residual + RMSNorm in one kernel.
 void gemm_ar_rmsnorm(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
                      c10::optional<Tensor> residual_out, Tensor norm_out, c10::optional<Tensor> scale_out, double eps,
-                     const Tensor& workspace, int64_t out_mode, bool scatter_only, const c10::optional<Tensor>& status) {
+                     const Tensor& workspace, int64_t out_mode, bool scatter_only, const c10::optional<Tensor>& status,
+                     int64_t splits, const c10::optional<Tensor>& splitk_ws, const c10::optional<Tensor>& splitk_counters) {
   tdx::Workspace* ws = workspace_of(workspace);
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1), "gemm_ar_rmsnorm: a [tokens, k], w [hidden, k]");
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && gamma.scalar_type() == at::kBFloat16, "gemm_ar_rmsnorm: bfloat16 operands");
@@ -214,6 +246,14 @@ void gemm_ar_rmsnorm(const Tensor& a, const Tensor& w, const c10::optional<Tenso
   g.lda = a.stride(0);
   g.ldw = w.stride(0);
   g.status = status.has_value() && status->defined() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr;
+  g.splits = (int)splits;
+  if (splitk_ws.has_value() && splitk_ws->defined() && splitk_counters.has_value() && splitk_counters->defined()) {
+    TORCH_CHECK(splitk_ws->scalar_type() == at::kFloat && splitk_counters->scalar_type() == at::kInt, "gemm_ar_rmsnorm: split-K scratch dtypes");
+    g.ws = splitk_ws->data_ptr<float>();
+    g.ws_bytes = (size_t)splitk_ws->numel() * 4;
+    g.counters = reinterpret_cast<uint32_t*>(splitk_counters->data_ptr<int>());
+    g.counter_count = (size_t)splitk_counters->numel();
+  }
   const std::string err = tdx::gemm_ar_rmsnorm(g, cur_stream());
   TORCH_CHECK(err.empty(), "gemm_ar_rmsnorm: ", err);
 }
@@ -250,10 +290,11 @@ void ag_gemm(const Tensor& x_shard, const Tensor& w, Tensor out, int64_t tokens,
 
 void register_extra_ops(torch::Library& m) {
   m.def("gemm_ar_rmsnorm(Tensor a, Tensor w, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
-        "Tensor(c!)? scale_out, float eps, Tensor workspace, int out_mode, bool scatter_only, Tensor(d!)? status) -> ()",
+        "Tensor(c!)? scale_out, float eps, Tensor workspace, int out_mode, bool scatter_only, Tensor(d!)? status, "
+        "int splits, Tensor(e!)? splitk_ws, Tensor(f!)? splitk_counters) -> ()",
         &gemm_ar_rmsnorm);
   m.def("attention_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor seq_lens, Tensor(a!) out, Tensor(b!) partial, "
-        "int nsplit, float scale) -> ()", &attention_decode);
+        "int nsplit, float scale, Tensor(c!)? status) -> ()", &attention_decode);
   m.def("ag_gemm(Tensor x_shard, Tensor w, Tensor(a!) out, int tokens, Tensor workspace, Tensor(b!)? status) -> ()", &ag_gemm);
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
@@ -263,6 +304,8 @@ void register_extra_ops(torch::Library& m) {
   m.def("quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) scales, bool block128) -> ()", &quant_fp8);
   m.def("silu_mul(Tensor gate_up, Tensor(a!) out, Tensor(b!)? scales) -> ()", &silu_mul);
   m.def("rope_(Tensor(a!) q, Tensor(b!) k, Tensor positions, Tensor cos_sin_cache) -> ()", &rope_);
+  m.def("rope_append_kv_(Tensor(a!) q, Tensor(b!) k, Tensor v, Tensor positions, Tensor cos_sin_cache, Tensor(c!) k_cache, "
+        "Tensor(d!) v_cache) -> ()", &rope_append_kv_);
 }
 
 }  // namespace tdx_torch

@@ -164,9 +164,7 @@ class TPLlama:
         q = qkv[:, : self.hq * d].view(tokens, self.hq, d)
         k = qkv[:, self.hq * d: (self.hq + self.hkv) * d].view(tokens, self.hkv, d)
         v = qkv[:, (self.hq + self.hkv) * d:].view(tokens, self.hkv, d)
-        rope.rope_(q, k, positions, self.cos_sin)
-        self.k_cache[i][batch_idx, positions] = k
-        self.v_cache[i][batch_idx, positions] = v
+        rope.rope_append_kv_(q, k, v, positions, self.cos_sin, self.k_cache[i], self.v_cache[i])
         attn = attention.decode_attention(q, self.k_cache[i][:tokens], self.v_cache[i][:tokens], self.seq_lens[:tokens], max_len)
         x, x_scale, res = self._row_parallel(attn.view(tokens, self.hq * d), L["wo"], res, L["ln2"])
         gu = self._col_parallel(x, L["wgu"], tokens, x_scale)
@@ -236,9 +234,7 @@ class TPLlama:
         q = qkv[:, : self.hq * d].view(tokens, self.hq, d)
         k = qkv[:, self.hq * d: (self.hq + self.hkv) * d].view(tokens, self.hkv, d)
         v = qkv[:, (self.hq + self.hkv) * d:].view(tokens, self.hkv, d)
-        rope.rope_(q, k, positions, self.cos_sin)
-        self.k_cache[i][batch_idx, positions] = k
-        self.v_cache[i][batch_idx, positions] = v
+        rope.rope_append_kv_(q, k, v, positions, self.cos_sin, self.k_cache[i], self.v_cache[i])
         attn = attention.decode_attention(q, self.k_cache[i][:tokens], self.v_cache[i][:tokens], self.seq_lens[:tokens], max_len)
         x, x_scale, res = self._row_parallel(attn.view(tokens, self.hq * d), L["wo"], res, L["ln2"])
         gu = self._col_parallel(x, L["wgu"], tokens, x_scale)

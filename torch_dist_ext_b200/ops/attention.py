@@ -19,8 +19,9 @@ def _partial(device, floats: int) -> torch.Tensor:
 
 
 def pick_splits(batch: int, kv_heads: int, max_len: int, sms: int = 148) -> int:
+    """Two CTAs fit on an SM; split the cache until the grid fills them, but keep >= 128 positions per split."""
     want = max(1, (2 * sms + batch * kv_heads - 1) // (batch * kv_heads))
-    return max(1, min(want, (max_len + 255) // 256))
+    return max(1, min(want, (max_len + 127) // 128))
 
 
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: torch.Tensor,
@@ -33,7 +34,10 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     nsplit = pick_splits(b, hkv, max_len) if nsplit is None else nsplit
     out = torch.empty(b, hq, d, dtype=q.dtype, device=q.device) if out is None else out
     part = _partial(q.device, b * hq * nsplit * (d + 2))
-    _lib.ops().attention_decode(q, k_cache, v_cache, seq_lens, out, part, nsplit, 1.0 / math.sqrt(d))
+    from . import gemm as _gemm
+
+    _lib.ops().attention_decode(q, k_cache, v_cache, seq_lens, out, part, nsplit, 1.0 / math.sqrt(d),
+                                _gemm._workspace(q.device)[2])
     return out
 
 

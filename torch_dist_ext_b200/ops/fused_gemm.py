@@ -30,7 +30,7 @@ def _fits(tokens: int, rows: int) -> bool:
 
 def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor], gamma: torch.Tensor,
                        eps: float, *, out_mode: int = OUT_SAME, scatter_only: bool = False,
-                       want_residual: bool = True, force_unfused: bool = False,
+                       want_residual: bool = True, force_unfused: bool = False, splits: int = 0,
                        ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """``y = all_reduce(a @ w.T); res = y + residual; norm = rmsnorm(res) * gamma``.
 
@@ -51,9 +51,9 @@ def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torc
     else:
         norm = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=a.device)
         scales = torch.empty(rows, hidden // 128, dtype=torch.float32, device=a.device)
-    status = _gemm._workspace(a.device)[2]
+    ws, counters, status = _gemm._workspace(a.device)
     _lib.ops().gemm_ar_rmsnorm(a, w, residual, gamma, res_out, norm, scales, eps, c.get_workspace(a), out_mode,
-                               scatter_only, status)
+                               scatter_only, status, splits, ws, counters)
     return norm, res_out, scales
 
 

@@ -18,6 +18,12 @@ def rope_(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin_cac
     _lib.ops().rope_(q, k, positions, cos_sin_cache)
 
 
+def rope_append_kv_(q, k, v, positions, cos_sin_cache, k_cache, v_cache) -> None:
+    """Decode step: rotate ``q``/``k`` in place and append the rotated key row and the value row of
+    token ``t`` to ``k_cache``/``v_cache`` ``[B, S, k_heads, dim]`` at ``[t, positions[t]]`` - one kernel."""
+    _lib.ops().rope_append_kv_(q, k, v, positions, cos_sin_cache, k_cache, v_cache)
+
+
 def rope_reference(x: torch.Tensor, positions: torch.Tensor, cos_sin_cache: torch.Tensor) -> torch.Tensor:
     half = x.shape[-1] // 2
     cs = cos_sin_cache[positions].float()
