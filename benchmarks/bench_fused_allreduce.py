@@ -36,6 +36,9 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--steps", type=int, default=60)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--tokens", default=None, help="comma-separated token counts (default: the full sweep)")
+    ap.add_argument("--hidden", default=None, help="comma-separated hidden sizes for the bf16 part")
+    ap.add_argument("--no-fp8", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         cur = os.environ.get("LD_LIBRARY_PATH", "")
@@ -49,6 +52,12 @@ def main():
     fp8_hidden = [5120, 7168]
     if args.quick:
         tokens_list, fp8_hidden = [1, 128, 2048], [7168]
+    if args.tokens:
+        tokens_list = [int(t) for t in args.tokens.split(",")]
+    if args.hidden:
+        hidden_list = [int(t) for t in args.hidden.split(",")]
+    if args.no_fp8:
+        fp8_hidden = []
 
     if args.impl == "reference":
         api, why = common.load_reference()
@@ -105,7 +114,19 @@ def main():
                 else:
                     out = api.allreduce_rms(rank, world, xs[0], rs[0], gamma, EPS, ws)
                     torch.cuda.synchronize()
-                    row["reference_us"] = timed(lambda: api.allreduce_rms(rank, world, *rot(), gamma, EPS, ws), steps)
+                    # The reference ignores the result of its cooperative launch; a launch that cannot be
+                    # resident leaves the outputs unwritten and "runs" in no time. Check against NCCL + PyTorch.
+                    ref_sum = xs[0].float().clone()
+                    dist.all_reduce(ref_sum)
+                    e_res = (ref_sum.to(torch.bfloat16).float() + rs[0].float()).to(torch.bfloat16).float()
+                    e_norm = e_res * torch.rsqrt(e_res.pow(2).mean(-1, keepdim=True) + EPS) * gamma.float()
+                    ok = bool(torch.isfinite(out[0].float()).all()) and \
+                        (out[0].float() - e_norm).abs().max().item() <= 0.06 * max(1.0, e_norm.abs().max().item())
+                    ok = bool(common.min_over_ranks(1.0 if ok else 0.0, world))
+                    if ok:
+                        row["reference_us"] = timed(lambda: api.allreduce_rms(rank, world, *rot(), gamma, EPS, ws), steps)
+                    else:
+                        row["reference_us"] = "n/a: outputs wrong or unwritten (its cooperative launch failed and the error is ignored)"
                 rows.append(row)
                 continue
             if hidden in hidden_list:

@@ -27,6 +27,7 @@ def test_algorithm_selection_by_bytes_not_tokens():
     # 128 tokens x 8192 bf16 = 2 MiB at 8 ranks: the reference would push 8 x 2 MiB one-shot
     assert plan(8, 128, 8192)[0] == ALGO_CODES["twoshot"]
     assert plan(8, 8, 4096)[0] == ALGO_CODES["oneshot"]
+    assert plan(8, 32, 8192)[0] == ALGO_CODES["oneshot"]       # 512 KiB: measured crossover at 8 ranks
     assert plan(2, 128, 4096)[0] == ALGO_CODES["oneshot"]
     assert plan(8, 8192, 8192)[0] == ALGO_CODES["twoshot_barrier"]      # 128 MiB
     assert plan(1, 77, 4096)[0] == ALGO_CODES["local"]

@@ -19,12 +19,12 @@ def cases():
             out.append((tokens, 1024, dtype, None, OUT_SAME))
     for algo in ("oneshot", "twoshot", "twoshot_barrier"):
         out.append((64, 8192, torch.bfloat16, algo, OUT_SAME))
-        out.append((513, 4096, torch.bfloat16, algo, OUT_FP8_TOKEN))
+        out.append((257, 4096, torch.bfloat16, algo, OUT_FP8_TOKEN))
         out.append((37, 5120, torch.bfloat16, algo, OUT_FP8_BLOCK128))
     for algo in ("nvls_oneshot", "nvls_twoshot"):           # skipped by the worker without multicast
         out.append((64, 8192, torch.bfloat16, algo, OUT_SAME))
         out.append((1, 4096, torch.float32, algo, OUT_SAME))
-        out.append((513, 4096, torch.bfloat16, algo, OUT_FP8_TOKEN))
+        out.append((257, 4096, torch.bfloat16, algo, OUT_FP8_TOKEN))
         out.append((300, 1024, torch.float16, algo, OUT_SAME))
     out.append((4096, 4096, torch.bfloat16, None, OUT_SAME))   # 32 MiB: NVLS two-shot or flag-barrier path
     return out

@@ -21,11 +21,12 @@ Policy& policy() {
     Policy q{};
     for (int n = 0; n <= kMaxRanks; ++n) {
       // Egress of the one-shot push grows with (n-1) x message, so its range shrinks with n.
-      q.oneshot_max_bytes[n] = n <= 2 ? (1u << 20) : n <= 4 ? (512u << 10) : (256u << 10);
-      q.lamport_max_bytes[n] = 8u << 20;
+      // measured on 8 x B200 (benchmarks/bench_fused_allreduce.py); 4 ranks interpolated
+      q.oneshot_max_bytes[n] = n <= 2 ? (4u << 20) : n <= 4 ? (1u << 20) : (512u << 10);
+      q.lamport_max_bytes[n] = 12u << 20;
     }
     q.prefer_nvls = 1;
-    q.nvls_min_bytes = 4u << 20;
+    q.nvls_min_bytes = 12u << 20;
     return q;
   }();
   return pol;
@@ -164,8 +165,9 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
   pl.n_tmpl = (n == 1) ? 1 : (n == 2 || n == 4 || n == 8) ? n : 0;
 
   // grid: one block per row (or row group), capped by what is co-resident
-  const uint64_t work =
-      (algo == kAlgoLocal || algo == kAlgoOneShotLamport || algo == kAlgoNvlsOneShot) ? uint64_t(p.tokens) : groups;
+  // Work items that set the grid: rows, except on the flag-synchronised two-shot paths where block b
+  // of every rank must handle the same row groups.
+  const uint64_t work = (algo == kAlgoTwoShotBarrier || algo == kAlgoNvlsTwoShot) ? groups : uint64_t(p.tokens);
   int dev = 0, ndev = 0;
   int sms = 148, per_sm = 1;  // planning without a device (dry runs) assumes one block per B200 SM
   if (cudaGetDeviceCount(&ndev) == cudaSuccess && ndev > 0) {

@@ -379,6 +379,26 @@ __device__ __forceinline__ void twoshot_scatter(const ArParams& p, const RowView
   }
 }
 
+// Same push, but work is split by ROW over all blocks: with sentinel-validated data any block may
+// push any row (no block-to-block pairing as on the flag-barrier path), so mid-sized messages use
+// tokens blocks instead of tokens / N.
+template <typename T, int kVpt>
+__device__ __forceinline__ void twoshot_scatter_rows(const ArParams& p, const RowView<T, kVpt>& rv,
+                                                     const TwoShotGeometry& g, int nranks, size_t area_off) {
+  const char* in = static_cast<const char*>(p.in);
+  for (int row = blockIdx.x; row < p.tokens; row += gridDim.x) {
+    const int r = row % nranks, j = row / nranks;
+    if (r == p.rank) continue;
+    char* dst = static_cast<char*>(p.peer[r]) + area_off + ((size_t)p.rank * g.groups + j) * rv.row_bytes;
+#pragma unroll
+    for (int v = 0; v < kVpt; ++v) {
+      if (!rv.active(v)) continue;
+      const uint4 val = scrub(ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16));
+      ptx::st_v4(dst + (size_t)rv.vec_index(v) * 16, val);
+    }
+  }
+}
+
 // ---- two-shot Lamport -------------------------------------------------------------------
 
 // Owner and receive phases of the two-shot Lamport flow for the row groups cta, cta + nctas, ...
@@ -472,12 +492,12 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
     }
   }
 
-  // receive phase: rows owned by the peers
+  // receive phase: rows owned by the peers, split by row over all blocks
   if (gather_back) {
-    for (int j = cta; j < g.groups; j += nctas) {
-      for (int r = 0; r < nranks; ++r) {
-        const int row = j * nranks + r;
-        if (r == p.rank || row >= p.tokens) continue;
+    for (int row = cta; row < p.tokens; row += nctas) {
+      const int r = row % nranks;
+      if (r == p.rank) continue;
+      {
         const char* src = self + result_off + (size_t)row * g.result_stride;
         const uint4 trailer = poll_vec(src + rv.row_bytes, w, p, ctl, kTimeoutLamportResult, r, 2, row);
         const float rstd = __uint_as_float(trailer.x);
@@ -514,7 +534,7 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
   const TwoShotGeometry g = twoshot_geometry<T, kVpt>(p, rv, nranks, true);
   const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
 
-  twoshot_scatter<T, kN, kVpt, true>(p, rv, g, nranks, buf_off);
+  twoshot_scatter_rows<T, kVpt>(p, rv, g, nranks, buf_off);
   clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev);
   const uint64_t dirty = twoshot_lamport_tail<T, kN, kVpt, kOut, false>(p, blockIdx.x, gridDim.x, epoch, red);
   finish_launch(ctl, true, epoch, dirty, 0);
