@@ -24,9 +24,10 @@ Policy& policy() {
       // measured on 8 x B200 (benchmarks/bench_fused_allreduce.py); 4 ranks interpolated
       q.oneshot_max_bytes[n] = n <= 2 ? (4u << 20) : n <= 4 ? (1u << 20) : (512u << 10);
       q.lamport_max_bytes[n] = 12u << 20;
+      // in-switch reduction pays off once N-1 peers' worth of traffic is saved: never at 2 ranks
+      q.nvls_min_bytes[n] = n <= 2 ? ~0ull : n <= 4 ? (32ull << 20) : (12ull << 20);
     }
     q.prefer_nvls = 1;
-    q.nvls_min_bytes = 12u << 20;
     return q;
   }();
   return pol;
@@ -130,7 +131,7 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
       const bool nvls_ok = p.mc_base != nullptr && pol.prefer_nvls && emu_ranks == 0 &&
                            msg_bytes <= p.layout.nvls_in_bytes &&
                            uint64_t(p.tokens) * (row_bytes + 16) + 2 * p.layout.nvls_in_bytes <= p.layout.nvls_bytes;
-      if (nvls_ok && msg_bytes >= pol.nvls_min_bytes)
+      if (nvls_ok && msg_bytes >= pol.nvls_min_bytes[n])
         algo = kAlgoNvlsTwoShot;
       else if (!p.scatter_only && msg_bytes <= pol.oneshot_max_bytes[n] && need_oneshot <= p.layout.lamport_bytes)
         algo = kAlgoOneShotLamport;

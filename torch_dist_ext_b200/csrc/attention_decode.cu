@@ -38,9 +38,12 @@ constexpr int kStageBytesKV = 4 * kHalfBytes;     // K lo, K hi, V lo, V hi
 constexpr int kAttnSmem = kStagesKV * kStageBytesKV + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr uint32_t kAttnWaitLimit = 1u << 22;
 
+constexpr int kAttnCounters = 4096;   // words at the start of the scratch buffer: one arrival counter per (b, kv head)
+
 struct AttnArgs {
   const __nv_bfloat16* q;      // [B, Hq, D]
   const int32_t* seq_lens;     // [B] valid positions per sequence
+  uint32_t* counters;          // [B * Hkv] zero on entry, left zero on exit (null: a separate kernel merges)
   float* partial;              // [B, Hq, nsplit, D + 2]
   __nv_bfloat16* out;          // [B, Hq, D]
   int B, Hq, Hkv, S_max, nsplit;
@@ -212,14 +215,52 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const _
       for (int j = 0; j < 8; ++j) acc_s[warp][g][vslice * 8 + j] = acc[g][j];
   }
   __syncthreads();
-  for (int i = tid; i < kG * kD; i += kAttnThreads) {
-    const int g = i / kD, d = i % kD;
-    const float o = acc_s[0][g][d] + acc_s[1][g][d] + acc_s[2][g][d] + acc_s[3][g][d];
-    float* dst = a.partial + (((int64_t)b * a.Hq + hkv * kG + g) * a.nsplit + split) * (kD + 2);
-    dst[d] = o;
-    if (d == 0) {
-      dst[kD] = m_run[g];      // identical in every thread
-      dst[kD + 1] = l_run[g];
+  if (a.nsplit == 1) {
+    // a single split: normalise and write the output directly
+    for (int i = tid; i < kG * kD; i += kAttnThreads) {
+      const int g = i / kD, d = i % kD;
+      const float o = acc_s[0][g][d] + acc_s[1][g][d] + acc_s[2][g][d] + acc_s[3][g][d];
+      a.out[((int64_t)b * a.Hq + hkv * kG + g) * kD + d] = __float2bfloat16(l_run[g] > 0.f ? o / l_run[g] : 0.f);
+    }
+  } else {
+    for (int i = tid; i < kG * kD; i += kAttnThreads) {
+      const int g = i / kD, d = i % kD;
+      const float o = acc_s[0][g][d] + acc_s[1][g][d] + acc_s[2][g][d] + acc_s[3][g][d];
+      float* dst = a.partial + (((int64_t)b * a.Hq + hkv * kG + g) * a.nsplit + split) * (kD + 2);
+      dst[d] = o;
+      if (d == 0) {
+        dst[kD] = m_run[g];      // identical in every thread
+        dst[kD + 1] = l_run[g];
+      }
+    }
+    if (a.counters != nullptr) {
+      // the split that arrives last merges all of them (saves a launch per layer)
+      __shared__ uint32_t s_last;
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const uint32_t prev = atomicAdd(&a.counters[b * a.Hkv + hkv], 1u);
+        s_last = (prev == (uint32_t)a.nsplit - 1u) ? 1u : 0u;
+        if (s_last) a.counters[b * a.Hkv + hkv] = 0;
+      }
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        const int d = tid;   // kAttnThreads == kD
+#pragma unroll
+        for (int g = 0; g < kG; ++g) {
+          const float* src = a.partial + ((int64_t)b * a.Hq + hkv * kG + g) * a.nsplit * (kD + 2);
+          float m = -FLT_MAX;
+          for (int sp = 0; sp < a.nsplit; ++sp) m = fmaxf(m, __ldcg(src + sp * (kD + 2) + kD));
+          float num = 0.f, den = 0.f;
+          for (int sp = 0; sp < a.nsplit; ++sp) {
+            const float wgt = __expf(__ldcg(src + sp * (kD + 2) + kD) - m);
+            num = fmaf(wgt, __ldcg(src + sp * (kD + 2) + d), num);
+            den = fmaf(wgt, __ldcg(src + sp * (kD + 2) + kD + 1), den);
+          }
+          a.out[((int64_t)b * a.Hq + hkv * kG + g) * kD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+        }
+      }
     }
   }
   if (*abort_flag) {
@@ -306,7 +347,10 @@ std::string attention_decode(const void* q, const void* k_cache, const void* v_c
   const int G = Hq / Hkv;
   if (G > kMaxG || (G & (G - 1))) return "query heads per KV head must be 1, 2, 4 or 8";
   if (nsplit < 1) nsplit = 1;
-  if ((size_t)B * Hq * nsplit * (kD + 2) > partial_floats) return "attention scratch buffer is too small";
+  // scratch layout: kAttnCounters arrival counters (zero on entry, zeroed again by the kernel), then the partials
+  const bool in_kernel_merge = (size_t)B * Hkv <= (size_t)kAttnCounters && partial_floats > (size_t)kAttnCounters;
+  const size_t head = in_kernel_merge ? (size_t)kAttnCounters : 0;
+  if (head + (size_t)B * Hq * nsplit * (kD + 2) > partial_floats) return "attention scratch buffer is too small";
   if ((kv_stride_s * 2) % 16 || (kv_stride_b * 2) % 16 || reinterpret_cast<uintptr_t>(k_cache) % 16 ||
       reinterpret_cast<uintptr_t>(v_cache) % 16)
     return "KV cache rows must be 16-byte aligned";
@@ -314,7 +358,8 @@ std::string attention_decode(const void* q, const void* k_cache, const void* v_c
   AttnArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.seq_lens = seq_lens;
-  a.partial = partial;
+  a.counters = in_kernel_merge ? reinterpret_cast<uint32_t*>(partial) : nullptr;
+  a.partial = partial + head;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.S_max = S_max; a.nsplit = nsplit;
   a.q_stride_b = q_stride_b;
@@ -333,7 +378,7 @@ std::string attention_decode(const void* q, const void* k_cache, const void* v_c
     case 8: err = launch_attn<8>(mk, mv, a, grid, stream); break;
   }
   if (!err.empty()) return err;
-  attn_combine_kernel<<<dim3(B, Hq), kD, 0, stream>>>(a);
+  if (nsplit > 1 && !in_kernel_merge) attn_combine_kernel<<<dim3(B, Hq), kD, 0, stream>>>(a);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }

@@ -28,7 +28,7 @@ struct Policy {
   uint64_t oneshot_max_bytes[kMaxRanks + 1];
   uint64_t lamport_max_bytes[kMaxRanks + 1];   // above: flag-barrier two-shot
   int prefer_nvls;                             // use NVLS paths when a multicast mapping exists
-  uint64_t nvls_min_bytes;
+  uint64_t nvls_min_bytes[kMaxRanks + 1];      // per rank count; NVLS two-shot at or above this size
 };
 Policy& policy();
 

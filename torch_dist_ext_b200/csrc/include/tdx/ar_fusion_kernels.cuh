@@ -540,115 +540,21 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
   finish_launch(ctl, true, epoch, dirty, 0);
 }
 
-// ---- two-shot with flag barriers -----------------------------------------------------------
-
-template <typename T, int kN, int kVpt, int kOut>
-__device__ __forceinline__ void twoshot_barrier_body(const ArParams& p) {
-  constexpr int kVec = VecTraits<T>::kVec;
-  __shared__ float red[4][32];
-  const int nranks = kN > 0 ? kN : p.nranks;
-  const RowView<T, kVpt> rv(p.hidden);
-  char* self = static_cast<char*>(p.peer[p.rank]);
-  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
-  const uint32_t bepoch = ctl->barrier_epoch;
-  const TwoShotGeometry g = twoshot_geometry<T, kVpt>(p, rv, nranks, false);
-  const size_t gather_off = p.layout.off_stage;
-  const size_t result_off = gather_off + g.gather_bytes;
-  const char* in = static_cast<const char*>(p.in);
-  const bool gather_back = p.scatter_only == 0;
-  Waiter w(p.timeout_ns);
-
-  twoshot_scatter<T, kN, kVpt, false>(p, rv, g, nranks, gather_off);
-  flag_barrier(p, ctl, bepoch + 1u, w, 1);
-
-  uint4 gamma[kVpt];
-  load_gamma<T, kVpt>(p, rv, gamma);
-  int parity = 0;
-  for (int j = blockIdx.x; j < g.groups; j += gridDim.x) {
-    const int row = j * nranks + p.rank;
-    if (row >= p.tokens) continue;
-    const int64_t out_row = gather_back ? row : j;
-    float x[kVpt][kVec];
-#pragma unroll
-    for (int v = 0; v < kVpt; ++v) {
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
-      if (!rv.active(v)) continue;
-      const size_t voff = (size_t)rv.vec_index(v) * 16;
-      const char* slot0 = self + gather_off + (size_t)j * rv.row_bytes + voff;
-      const size_t slot_stride = (size_t)g.groups * rv.row_bytes;
-#pragma unroll
-      for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
-        if (r >= nranks) continue;
-        const uint4 val = (r == p.rank) ? ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff)
-                                        : ptx::ld_volatile_v4(slot0 + r * slot_stride);
-        float f[kVec];
-        unpack<T>(val, f);
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
-      }
-      add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) +
-                                                (size_t)out_row * rv.row_bytes + voff
-                                          : nullptr);
-      const uint4 packed = pack<T>(x[v]);
-      if (p.residual_out)
-        ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)out_row * rv.row_bytes + voff, packed);
-      if (gather_back) {
-#pragma unroll
-        for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
-          if (r >= nranks || r == p.rank) continue;
-          ptx::st_v4(static_cast<char*>(p.peer[r]) + result_off + (size_t)row * rv.row_bytes + voff, packed);
-        }
-      }
-    }
-    float rstd, sc;
-    finish_row<T, kVpt, kOut>(p, rv, out_row, x, gamma, red, parity, rstd, sc);
-    parity ^= 1;
-    if (gather_back && threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
-      const uint4 trailer = make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u);
-      ptx::st_v4(static_cast<char*>(p.peer[threadIdx.x]) + result_off + g.trailer_off + (size_t)row * 16, trailer);
-    }
-  }
-
-  // The second barrier both publishes the result rows and keeps a fast rank's next scatter
-  // from overwriting gather slots that a slow rank is still reading.
-  flag_barrier(p, ctl, bepoch + 2u, w, 2);
-
-  if (gather_back) {
-    for (int j = blockIdx.x; j < g.groups; j += gridDim.x) {
-      for (int r = 0; r < nranks; ++r) {
-        const int row = j * nranks + r;
-        if (r == p.rank || row >= p.tokens) continue;
-        const char* src = self + result_off + (size_t)row * rv.row_bytes;
-        const uint4 trailer = ptx::ld_volatile_v4(self + result_off + g.trailer_off + (size_t)row * 16);
-        const float rstd = __uint_as_float(trailer.x);
-        const float sc = __uint_as_float(trailer.y);
-        float x[kVpt][kVec];
-#pragma unroll
-        for (int v = 0; v < kVpt; ++v) {
-#pragma unroll
-          for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
-          if (!rv.active(v)) continue;
-          const size_t voff = (size_t)rv.vec_index(v) * 16;
-          const uint4 val = ptx::ld_volatile_v4(src + voff);
-          unpack<T>(val, x[v]);
-          if (p.residual_out)
-            ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)row * rv.row_bytes + voff, val);
-        }
-        if (kOut == kOutFp8Token && threadIdx.x == 0) p.scale_out[row] = sc;
-        store_norm<T, kVpt, kOut>(p, rv, row, x, gamma, rstd, sc);
-      }
-    }
-  }
-  finish_launch(ctl, false, 0, 0, 2);
-}
-
-// ---- NVLS (NVSwitch multicast) ---------------------------------------------------------------
-// Every rank's symmetric allocation is bound to one multicast object; `mc_base` addresses all
-// copies at once. multimem.ld_reduce returns the sum over ranks computed inside the switch
-// (fp32 accumulation for 16-bit types, one rounding to T; the order of the additions is the
-// switch's). The input is first copied into the NVLS staging buffer selected by the parity of the
-// barrier epoch, so that a rank that runs ahead never overwrites data a peer is still reducing.
+// ---- two-shot with flag barriers (peer-to-peer staging or NVLS), pipelined in waves -------------
+// Block b of every rank handles the row groups b, b + gridDim, ... . They can be processed in up to
+// kMaxWaves waves (ArParams::waves, default 1) so that the three phases of different waves overlap in
+// time: while one wave's finished rows are normalised locally, the next wave's partial rows already
+// cross the links. Measured at 2 ranks every extra wave costs more in flag round trips (two per wave)
+// than the overlap returns, so one wave is the default. Per wave w (flag values are epoch + w + 1; plane 0 = "gathered", plane 1 = "results"):
+//     stage(w+1), signal(plane 0)   |  wait(plane 0, w)  reduce(w) + publish, signal(plane 1)
+//                                   |  wait(plane 1, w)  epilogue(w)
+// kNvls = false: stage = push my rows to their owners' gather slots; reduce reads them locally;
+//                publish = peer stores into every rank's result area.
+// kNvls = true : stage = copy my rows into my multicast-bound input buffer; reduce =
+//                multimem.ld_reduce (the switch adds); publish = multimem.st (the switch replicates).
+// The last wave's plane-1 wait also keeps a fast rank's next call from overwriting slots that a
+// slow rank is still reading.
+constexpr int kMaxWaves = 4;
 
 template <typename T>
 __device__ __forceinline__ uint4 mc_ld_reduce(const void* mc_addr) {
@@ -660,6 +566,174 @@ __device__ __forceinline__ uint4 mc_ld_reduce(const void* mc_addr) {
 __device__ __forceinline__ size_t nvls_in_offset(const Layout& l, uint32_t bepoch) {
   return l.off_nvls + (size_t)(bepoch & 1u) * l.nvls_in_bytes;
 }
+
+template <typename T, int kN, int kVpt, int kOut, bool kNvls>
+__device__ __forceinline__ void twoshot_flag_body(const ArParams& p) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  __shared__ float red[4][32];
+  const int nranks = kN > 0 ? kN : p.nranks;
+  const RowView<T, kVpt> rv(p.hidden);
+  char* self = static_cast<char*>(p.peer[p.rank]);
+  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
+  const uint32_t bepoch = ctl->barrier_epoch;
+  const TwoShotGeometry g = twoshot_geometry<T, kVpt>(p, rv, nranks, false);
+  // staging: gather slots [src][group][hidden] (peer-to-peer) or my rows in natural order (NVLS)
+  const size_t stage_off = kNvls ? nvls_in_offset(p.layout, bepoch) : p.layout.off_stage;
+  const size_t result_off = kNvls ? p.layout.off_nvls + 2 * p.layout.nvls_in_bytes : p.layout.off_stage + g.gather_bytes;
+  const char* in = static_cast<const char*>(p.in);
+  const bool gather_back = p.scatter_only == 0;
+  Waiter w(p.timeout_ns);
+
+  // waves: the same count on every block and rank (derived from the largest per-block group count)
+  const int per_block = (g.groups + gridDim.x - 1) / gridDim.x;
+  const int want = p.waves < 1 ? 1 : (p.waves > kMaxWaves ? kMaxWaves : p.waves);
+  const int waves = per_block < want ? (per_block > 0 ? per_block : 1) : want;
+  const int wave_len = (per_block + waves - 1) / waves;
+
+  auto stage_wave = [&](int wv) {
+    for (int k = wv * wave_len; k < (wv + 1) * wave_len && k < per_block; ++k) {
+      const int j = blockIdx.x + k * gridDim.x;
+      if (j >= g.groups) break;
+#pragma unroll
+      for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
+        const int row = j * nranks + r;
+        if (r >= nranks || row >= p.tokens) continue;
+        if (!kNvls && r == p.rank) continue;
+        char* dst = kNvls ? self + stage_off + (size_t)row * rv.row_bytes
+                          : static_cast<char*>(p.peer[r]) + stage_off + ((size_t)p.rank * g.groups + j) * rv.row_bytes;
+#pragma unroll
+        for (int v = 0; v < kVpt; ++v) {
+          if (!rv.active(v)) continue;
+          const size_t voff = (size_t)rv.vec_index(v) * 16;
+          ptx::st_v4(dst + voff, ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff));
+        }
+      }
+    }
+  };
+
+  uint4 gamma[kVpt];
+  load_gamma<T, kVpt>(p, rv, gamma);
+  int parity = 0;
+
+  stage_wave(0);
+  flag_signal(p, 0, bepoch + 1u);
+  for (int wv = 0; wv < waves; ++wv) {
+    if (wv + 1 < waves) {
+      stage_wave(wv + 1);
+      flag_signal(p, 0, bepoch + (uint32_t)wv + 2u);
+    }
+    flag_wait(p, ctl, 0, bepoch + (uint32_t)wv + 1u, w, 1);
+
+    // ---- reduce + publish the rows this rank owns in this wave ----
+    for (int k = wv * wave_len; k < (wv + 1) * wave_len && k < per_block; ++k) {
+      const int j = blockIdx.x + k * gridDim.x;
+      if (j >= g.groups) break;
+      const int row = j * nranks + p.rank;
+      if (row >= p.tokens) continue;
+      const int64_t out_row = gather_back ? row : j;
+      float x[kVpt][kVec];
+#pragma unroll
+      for (int v = 0; v < kVpt; ++v) {
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
+        if (!rv.active(v)) continue;
+        const size_t voff = (size_t)rv.vec_index(v) * 16;
+        if constexpr (kNvls) {
+          unpack<T>(mc_ld_reduce<T>(static_cast<const char*>(p.mc_base) + stage_off + (size_t)row * rv.row_bytes + voff), x[v]);
+        } else {
+          const char* slot0 = self + stage_off + (size_t)j * rv.row_bytes + voff;
+          const size_t slot_stride = (size_t)g.groups * rv.row_bytes;
+#pragma unroll
+          for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
+            if (r >= nranks) continue;
+            const uint4 val = (r == p.rank) ? ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff)
+                                            : ptx::ld_volatile_v4(slot0 + r * slot_stride);
+            float f[kVec];
+            unpack<T>(val, f);
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
+          }
+        }
+        add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) +
+                                                  (size_t)out_row * rv.row_bytes + voff
+                                            : nullptr);
+        const uint4 packed = pack<T>(x[v]);
+        if (p.residual_out)
+          ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)out_row * rv.row_bytes + voff, packed);
+        if (gather_back) {
+          if constexpr (kNvls) {
+            // one store, replicated by the switch into every rank's result area
+            ptx::multimem_st_v4(static_cast<char*>(p.mc_base) + result_off + (size_t)row * rv.row_bytes + voff, packed);
+          } else {
+#pragma unroll
+            for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
+              if (r >= nranks || r == p.rank) continue;
+              ptx::st_v4(static_cast<char*>(p.peer[r]) + result_off + (size_t)row * rv.row_bytes + voff, packed);
+            }
+          }
+        }
+      }
+      float rstd, sc;
+      finish_row<T, kVpt, kOut>(p, rv, out_row, x, gamma, red, parity, rstd, sc);
+      parity ^= 1;
+      if (gather_back) {
+        const uint4 trailer = make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u);
+        if constexpr (kNvls) {
+          if (threadIdx.x == 0)
+            ptx::multimem_st_v4(static_cast<char*>(p.mc_base) + result_off + g.trailer_off + (size_t)row * 16, trailer);
+        } else if (threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
+          ptx::st_v4(static_cast<char*>(p.peer[threadIdx.x]) + result_off + g.trailer_off + (size_t)row * 16, trailer);
+        }
+      }
+    }
+    flag_signal(p, 1, bepoch + (uint32_t)wv + 1u);
+    flag_wait(p, ctl, 1, bepoch + (uint32_t)wv + 1u, w, 2);
+
+    // ---- epilogue of the rows the peers own in this wave ----
+    if (gather_back) {
+      for (int k = wv * wave_len; k < (wv + 1) * wave_len && k < per_block; ++k) {
+        const int j = blockIdx.x + k * gridDim.x;
+        if (j >= g.groups) break;
+        for (int r = 0; r < nranks; ++r) {
+          const int row = j * nranks + r;
+          if (r == p.rank || row >= p.tokens) continue;
+          const char* src = self + result_off + (size_t)row * rv.row_bytes;
+          const uint4 trailer = ptx::ld_volatile_v4(self + result_off + g.trailer_off + (size_t)row * 16);
+          const float rstd = __uint_as_float(trailer.x);
+          const float sc = __uint_as_float(trailer.y);
+          float x[kVpt][kVec];
+#pragma unroll
+          for (int v = 0; v < kVpt; ++v) {
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
+            if (!rv.active(v)) continue;
+            const size_t voff = (size_t)rv.vec_index(v) * 16;
+            const uint4 val = ptx::ld_volatile_v4(src + voff);
+            unpack<T>(val, x[v]);
+            if (p.residual_out)
+              ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)row * rv.row_bytes + voff, val);
+          }
+          if (kOut == kOutFp8Token && threadIdx.x == 0) p.scale_out[row] = sc;
+          store_norm<T, kVpt, kOut>(p, rv, row, x, gamma, rstd, sc);
+        }
+      }
+    }
+  }
+  // every plane was used with values up to epoch + waves (other kernels use up to epoch + 2 on plane 0)
+  finish_launch(ctl, false, 0, 0, waves > 2 ? waves : 2);
+}
+
+template <typename T, int kN, int kVpt, int kOut>
+__device__ __forceinline__ void twoshot_barrier_body(const ArParams& p) {
+  twoshot_flag_body<T, kN, kVpt, kOut, false>(p);
+}
+
+// ---- NVLS (NVSwitch multicast) ---------------------------------------------------------------
+// Every rank's symmetric allocation is bound to one multicast object; `mc_base` addresses all
+// copies at once. multimem.ld_reduce returns the sum over ranks computed inside the switch
+// (fp32 accumulation for 16-bit types, one rounding to T; the order of the additions is the
+// switch's). The input is first copied into the NVLS staging buffer selected by the parity of the
+// barrier epoch, so that a rank that runs ahead never overwrites data a peer is still reducing.
 
 template <typename T, int kVpt>
 __device__ __forceinline__ void nvls_copy_in_row(const ArParams& p, const RowView<T, kVpt>& rv, char* dst_base, int row) {
@@ -710,86 +784,7 @@ __device__ __forceinline__ void nvls_oneshot_body(const ArParams& p) {
 
 template <typename T, int kN, int kVpt, int kOut>
 __device__ __forceinline__ void nvls_twoshot_body(const ArParams& p) {
-  constexpr int kVec = VecTraits<T>::kVec;
-  __shared__ float red[4][32];
-  const int nranks = kN > 0 ? kN : p.nranks;
-  const RowView<T, kVpt> rv(p.hidden);
-  char* self = static_cast<char*>(p.peer[p.rank]);
-  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
-  const uint32_t bepoch = ctl->barrier_epoch;
-  const size_t in_off = nvls_in_offset(p.layout, bepoch);
-  const size_t result_off = p.layout.off_nvls + 2 * p.layout.nvls_in_bytes;
-  const size_t trailer_off = (size_t)p.tokens * rv.row_bytes;
-  const int groups = (p.tokens + nranks - 1) / nranks;
-  const bool gather_back = p.scatter_only == 0;
-  Waiter w(p.timeout_ns);
-
-  for (int j = blockIdx.x; j < groups; j += gridDim.x)
-    for (int r = 0; r < nranks; ++r)
-      if (j * nranks + r < p.tokens) nvls_copy_in_row<T, kVpt>(p, rv, self + in_off, j * nranks + r);
-  flag_barrier(p, ctl, bepoch + 1u, w, 1);
-
-  uint4 gamma[kVpt];
-  load_gamma<T, kVpt>(p, rv, gamma);
-  const char* mc_in = static_cast<const char*>(p.mc_base) + in_off;
-  char* mc_result = static_cast<char*>(p.mc_base) + result_off;
-  int parity = 0;
-  for (int j = blockIdx.x; j < groups; j += gridDim.x) {
-    const int row = j * nranks + p.rank;
-    if (row >= p.tokens) continue;
-    const int64_t out_row = gather_back ? row : j;
-    float x[kVpt][kVec];
-#pragma unroll
-    for (int v = 0; v < kVpt; ++v) {
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
-      if (!rv.active(v)) continue;
-      const size_t voff = (size_t)rv.vec_index(v) * 16;
-      unpack<T>(mc_ld_reduce<T>(mc_in + (size_t)row * rv.row_bytes + voff), x[v]);
-      add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) +
-                                                (size_t)out_row * rv.row_bytes + voff
-                                          : nullptr);
-      const uint4 packed = pack<T>(x[v]);
-      if (p.residual_out)
-        ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)out_row * rv.row_bytes + voff, packed);
-      // one store, replicated by the switch into every rank's result area (this rank's included)
-      if (gather_back) ptx::multimem_st_v4(mc_result + (size_t)row * rv.row_bytes + voff, packed);
-    }
-    float rstd, sc;
-    finish_row<T, kVpt, kOut>(p, rv, out_row, x, gamma, red, parity, rstd, sc);
-    parity ^= 1;
-    if (gather_back && threadIdx.x == 0)
-      ptx::multimem_st_v4(mc_result + trailer_off + (size_t)row * 16,
-                          make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u));
-  }
-  if (gather_back) {
-    flag_barrier(p, ctl, bepoch + 2u, w, 2);
-    const char* result = self + result_off;
-    for (int j = blockIdx.x; j < groups; j += gridDim.x) {
-      for (int r = 0; r < nranks; ++r) {
-        const int row = j * nranks + r;
-        if (r == p.rank || row >= p.tokens) continue;
-        const uint4 trailer = ptx::ld_volatile_v4(result + trailer_off + (size_t)row * 16);
-        const float rstd = __uint_as_float(trailer.x);
-        const float sc = __uint_as_float(trailer.y);
-        float x[kVpt][kVec];
-#pragma unroll
-        for (int v = 0; v < kVpt; ++v) {
-#pragma unroll
-          for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
-          if (!rv.active(v)) continue;
-          const size_t voff = (size_t)rv.vec_index(v) * 16;
-          const uint4 val = ptx::ld_volatile_v4(result + (size_t)row * rv.row_bytes + voff);
-          unpack<T>(val, x[v]);
-          if (p.residual_out)
-            ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)row * rv.row_bytes + voff, val);
-        }
-        if (kOut == kOutFp8Token && threadIdx.x == 0) p.scale_out[row] = sc;
-        store_norm<T, kVpt, kOut>(p, rv, row, x, gamma, rstd, sc);
-      }
-    }
-  }
-  finish_launch(ctl, false, 0, 0, gather_back ? 2 : 1);
+  twoshot_flag_body<T, kN, kVpt, kOut, true>(p);
 }
 
 // ---- kernel wrappers ---------------------------------------------------------------------

@@ -22,12 +22,12 @@ constexpr uint32_t kSentinel = 0x80000000u;  // fp32 -0.0 / (bf16 -0.0, +0.0) pa
 
 // ---- region offsets inside one rank's symmetric allocation --------------------
 constexpr size_t kControlBytes = 4096;
-constexpr size_t kFlagBytes = size_t(kMaxBarrierBlocks) * kMaxRanks * sizeof(uint32_t);
+constexpr size_t kFlagBytes = 2 * size_t(kMaxBarrierBlocks) * kMaxRanks * sizeof(uint32_t);  // two planes
 constexpr size_t kAgFlagBytes = 256;    // all-gather->GEMM: one arrival word per source rank
 
 struct Layout {
   uint64_t off_control;   // Control block (touched by the owning rank only)
-  uint64_t off_flags;     // uint32 flags[kMaxBarrierBlocks][kMaxRanks], written by peers
+  uint64_t off_flags;     // uint32 flags[2 planes][kMaxBarrierBlocks][kMaxRanks], written by peers
   uint64_t off_lamport;   // 3 x lamport_bytes, sentinel-initialised
   uint64_t lamport_bytes; // capacity of ONE of the three Lamport buffers
   uint64_t off_stage;     // flag-synchronised staging of the peer-to-peer two-shot path
@@ -135,6 +135,7 @@ struct ArParams {
   // Reduce-scatter variant: only the rows this rank owns (row % nranks == rank) are
   // produced; outputs are then [ceil(tokens/nranks), hidden] and nothing is gathered.
   int32_t scatter_only;
+  int32_t waves;            // flag-synchronised two-shot paths: pipeline depth (1..4), 0 = 1
   uint64_t timeout_ns;      // budget of every device-side wait
   uint32_t* host_status;    // pinned, host-mapped mirror of Control::status (or null)
 };

@@ -18,9 +18,11 @@
 //    16384 * 130 * 4 bytes (about 8.1 MiB) on EVERY GPU that loads the library, until the process ends.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and opts the
 //    kernels in to their shared-memory size. Make that first call before any stream capture.
-//  * All calls share the one array and it keeps the previous call's contents. The kernels write every
-//    slot they later read, so nothing has to be cleared; but two calls that overlap on the GPU (two
-//    streams, two host threads) race on it. Issue calls on one stream, or serialise them yourself.
+//  * All calls share the one array and it keeps the previous call's contents. The partial rows are
+//    written before they are read, so they need no clearing; the 4096 arrival counters in front of
+//    them must start at zero, which holds when the library is loaded and is restored by every call
+//    that runs to its end. Two calls that overlap on the GPU (two streams, two host threads) race on
+//    both. Issue calls on one stream, or serialise them yourself.
 //  * No cudaMalloc, cudaFree, or allocating library routine is called; inputs and outputs are the caller's.
 #pragma once
 #include <cuda_runtime.h>

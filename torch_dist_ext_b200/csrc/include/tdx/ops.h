@@ -27,8 +27,9 @@ std::string rope_inplace(void* q, void* k, const int64_t* positions, const float
                          void* v_cache = nullptr, int64_t cache_stride_b = 0, int64_t cache_stride_s = 0);
 
 // Decode attention over a contiguous bf16 KV cache [B, S_max, Hkv, 128] for one new token per
-// sequence: q [B, Hq, 128] -> out [B, Hq, 128]. `partial` is fp32 scratch of at least
-// B * Hq * nsplit * 130 floats. Strides are in elements.
+// sequence: q [B, Hq, 128] -> out [B, Hq, 128]. `partial` is scratch of at least
+// 4096 + B * Hq * nsplit * 130 floats whose first 4096 words must be ZERO on entry (arrival counters;
+// the kernel leaves them zero again). Strides are in elements.
 std::string attention_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
                              float* partial, size_t partial_floats, void* out, int B, int Hq, int Hkv, int D, int S_max,
                              int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,

@@ -103,18 +103,25 @@ __device__ __forceinline__ void report_error(Control* ctl, uint32_t* host_status
 // into rank t's flags[b][my_rank], then waits for its own flags[b][t] to reach `target`.
 // Block b only ever synchronises with block b of the peers.
 
-__device__ __forceinline__ uint32_t* flag_ptr(void* base, const Layout& l, int block, int src) {
+// Two planes of flags: plane 0 carries "scatter done" / general barriers, plane 1 "results done".
+__device__ __forceinline__ uint32_t* flag_ptr(void* base, const Layout& l, int plane, int block, int src) {
   return reinterpret_cast<uint32_t*>(static_cast<char*>(base) + l.off_flags) +
-         (size_t)block * kMaxRanks + src;
+         ((size_t)plane * kMaxBarrierBlocks + block) * kMaxRanks + src;
 }
 
-__device__ __forceinline__ void flag_barrier(const ArParams& p, Control* ctl, uint32_t target,
-                                             Waiter& w, int phase) {
+// Publish `target` to every peer (release: everything this block wrote before is visible first).
+__device__ __forceinline__ void flag_signal(const ArParams& p, int plane, uint32_t target) {
   __syncthreads();
+  if ((int)threadIdx.x < p.nranks)
+    ptx::st_release_sys(flag_ptr(p.peer[threadIdx.x], p.layout, plane, blockIdx.x, p.rank), target);
+}
+
+// Wait (bounded) until every peer has published at least `target` for this block index.
+__device__ __forceinline__ void flag_wait(const ArParams& p, Control* ctl, int plane, uint32_t target,
+                                          Waiter& w, int phase) {
   if ((int)threadIdx.x < p.nranks) {
     const int peer = threadIdx.x;
-    ptx::st_release_sys(flag_ptr(p.peer[peer], p.layout, blockIdx.x, p.rank), target);
-    const uint32_t* mine = flag_ptr(p.peer[p.rank], p.layout, blockIdx.x, peer);
+    const uint32_t* mine = flag_ptr(p.peer[p.rank], p.layout, plane, blockIdx.x, peer);
     w.begin();
     while ((int32_t)(ptx::ld_acquire_sys(mine) - target) < 0) {
       if (!w.keep_waiting()) {
@@ -124,6 +131,12 @@ __device__ __forceinline__ void flag_barrier(const ArParams& p, Control* ctl, ui
     }
   }
   __syncthreads();
+}
+
+__device__ __forceinline__ void flag_barrier(const ArParams& p, Control* ctl, uint32_t target,
+                                             Waiter& w, int phase) {
+  flag_signal(p, 0, target);
+  flag_wait(p, ctl, 0, target, w, phase);
 }
 
 // ---- end of launch -------------------------------------------------------------------

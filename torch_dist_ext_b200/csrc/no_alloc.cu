@@ -15,7 +15,10 @@ constexpr int kRowFloats = 130;   // 128 output columns + running maximum + runn
 
 // Lives on every GPU that loads the library. In host code this name is only a handle for
 // cudaGetSymbolAddress - it is NOT a device address and must never be passed to a kernel.
-static __device__ __align__(256) float g_attn_scratch[(size_t)TDX_NOALLOC_ATTN_MAX_ROWS * kRowFloats];
+// Layout: 4096 arrival counters (zero when the library is loaded; every call leaves them zero again),
+// then the per-split partial rows.
+constexpr size_t kCounterWords = 4096;
+static __device__ __align__(256) float g_attn_scratch[kCounterWords + (size_t)TDX_NOALLOC_ATTN_MAX_ROWS * kRowFloats];
 
 constexpr int kMaxDevices = 64;
 std::mutex g_mu;
@@ -62,7 +65,7 @@ extern "C" int tdx_attention_decode_noalloc(const void* q, const void* k_cache, 
     scratch = g_scratch_ptr[dev];
   }
   const std::string why = tdx::attention_decode(q, k_cache, v_cache, seq_lens, scratch,
-                                                (size_t)TDX_NOALLOC_ATTN_MAX_ROWS * kRowFloats, out, batch, q_heads, kv_heads,
+                                                kCounterWords + (size_t)TDX_NOALLOC_ATTN_MAX_ROWS * kRowFloats, out, batch, q_heads, kv_heads,
                                                 128, s_max, q_stride_b, kv_stride_b, kv_stride_s, kv_splits, scale, stream,
                                                 nullptr);
   if (!why.empty()) return fail(err, err_len, why);

@@ -568,6 +568,11 @@ void Workspace::fill_params(ArParams* p) const {
   p->nranks = world_;
   p->timeout_ns = timeout_ns_;
   p->host_status = host_status_dev_;
+  static const int waves_env = [] {
+    const char* e = std::getenv("TDX_WAVES");
+    return e ? std::atoi(e) : 1;
+  }();
+  p->waves = waves_env;
 }
 
 void Workspace::reset() { init_device_state(); }

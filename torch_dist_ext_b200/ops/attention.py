@@ -14,7 +14,8 @@ _scratch = {}
 def _partial(device, floats: int) -> torch.Tensor:
     key = device.index if device.index is not None else torch.cuda.current_device()
     if key not in _scratch or _scratch[key].numel() < floats:
-        _scratch[key] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        # zeroed: the first 4096 words are arrival counters that the kernel expects (and leaves) at zero
+        _scratch[key] = torch.zeros(max(floats, 1 << 20), dtype=torch.float32, device=device)
     return _scratch[key]
 
 
@@ -33,7 +34,7 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     hkv = k_cache.shape[2]
     nsplit = pick_splits(b, hkv, max_len) if nsplit is None else nsplit
     out = torch.empty(b, hq, d, dtype=q.dtype, device=q.device) if out is None else out
-    part = _partial(q.device, b * hq * nsplit * (d + 2))
+    part = _partial(q.device, 4096 + b * hq * nsplit * (d + 2))
     from . import gemm as _gemm
 
     _lib.ops().attention_decode(q, k_cache, v_cache, seq_lens, out, part, nsplit, 1.0 / math.sqrt(d),

@@ -11,6 +11,7 @@ environment:
 ``TDX_TIMEOUT_MS``     budget of every device-side wait (default 5000)
 ``TDX_LAMPORT_MB``     capacity of each of the three Lamport buffers (default 32)
 ``TDX_NVLS``           ``0`` disables the NVSwitch-multicast mapping and kernels
+``TDX_WAVES``          pipeline depth (1..4) of the flag-synchronised two-shot paths (default 1)
 ``TDX_LOG``            Python logging level of the package logger
 ``TDX_POLICY_JSON``    path of a measured crossover table to load at ``setup_env``
 =====================  ============================================================
