@@ -20,8 +20,10 @@ def _partial(device, floats: int) -> torch.Tensor:
 
 
 def pick_splits(batch: int, kv_heads: int, max_len: int, sms: int = 148) -> int:
-    """Two CTAs fit on an SM; split the cache until the grid fills them, but keep >= 128 positions per split."""
-    want = max(1, (2 * sms + batch * kv_heads - 1) // (batch * kv_heads))
+    """KV splits such that the grid fits ONE wave of the two CTAs that an SM holds (a second,
+    partly filled wave costs more than shorter splits save), with at least 128 positions per split."""
+    pairs = batch * kv_heads
+    want = max(1, (2 * sms) // pairs)
     return max(1, min(want, (max_len + 127) // 128))
 
 
