@@ -65,16 +65,17 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
         from torch_dist_ext_b200.models.llama import LlamaConfig, TPLlama
 
         hidden_states = {}
+        nb = {2: 6, 4: 8}.get(world, 2 * world)      # sequences in the batch
         for mode in ("ar", "sp"):
-            model = TPLlama(LlamaConfig.tiny(), max_batch=8, max_seq=64, mode=mode, seed=3)
-            model.fill_cache_random(6, 12, seed=5)
-            tokens = torch.arange(6, device=dev) * 7 % 1024
-            positions = torch.full((6,), 12, device=dev, dtype=torch.long)
+            model = TPLlama(LlamaConfig.tiny(), max_batch=nb, max_seq=64, mode=mode, seed=3)
+            model.fill_cache_random(nb, 12, seed=5)
+            tokens = torch.arange(nb, device=dev) * 7 % 1024
+            positions = torch.full((nb,), 12, device=dev, dtype=torch.long)
             nxt = model.decode_step(tokens, positions, max_len=13)
             torch.cuda.synchronize()
             tdx.check_status()
             h = model.last_hidden.float()
-            hidden_states[mode] = model._gather_rows(model.last_hidden, 6).float() if mode == "sp" else h
+            hidden_states[mode] = model._gather_rows(model.last_hidden, nb).float() if mode == "sp" else h
             allt = [torch.empty_like(nxt) for _ in range(world)]
             dist.all_gather(allt, nxt)
             assert all(torch.equal(t, nxt) for t in allt), "ranks disagree on the next tokens"

@@ -32,12 +32,23 @@ def run_world(world, backend, cases, target=worker):
     for p in procs:
         p.start()
     results = []
-    for _ in range(world):
-        results.append(q.get(timeout=300))
-    for p in procs:
-        p.join(timeout=60)
+    try:
+        for _ in range(world):
+            r = q.get(timeout=300)
+            results.append(r)
+            if r[1] != "ok":
+                break       # the other ranks may now be stuck in a collective: do not wait for them
+    except Exception:
+        pass
     bad = [r for r in results if r[1] != "ok"]
+    for p in procs:
+        p.join(timeout=5 if bad or len(results) < world else 60)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()       # exactly the processes this test started
+            p.join(timeout=10)
     assert not bad, "\n".join(str(b[2]) for b in bad)
+    assert len(results) == world, f"only {len(results)} of {world} ranks reported within the time limit"
     return results
 
 

@@ -215,7 +215,13 @@ class TPLlama:
         res = self.embed[tokens]                                                  # [B, hidden]
         mode0 = self._norm_out_mode()
         if self.mode == "sp":
-            res = res[self.rank::self.world].contiguous()
+            # this rank's rows (rank, rank + world, ...), padded to the common shard height so that
+            # every rank - also one that owns a row less, or none - passes tensors of the same shape
+            rows = (b + self.world - 1) // self.world
+            shard = res[self.rank::self.world]
+            if shard.shape[0] < rows:
+                shard = torch.cat([shard, shard.new_zeros(rows - shard.shape[0], cfg.hidden)])
+            res = shard.contiguous()
         x, _, x_scale = norm.fused_add_rmsnorm(res, None, self.layers[0]["ln1"], cfg.eps, out_mode=mode0, want_residual=False)
         for i in range(cfg.n_layers):
             last = i + 1 == cfg.n_layers
