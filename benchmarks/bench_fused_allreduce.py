@@ -2,7 +2,7 @@
 """Latency sweep of the fused all-reduce + residual + RMSNorm (+ fp8 quant) op.
 
     python -m torch.distributed.run --nproc-per-node N benchmarks/bench_fused_allreduce.py --gpus N
-        [--impl own|reference] [--quick] [--out gpurun_out/sweep_tpN.json]
+        [--impl own|reference] [--quick] [--out <dir>/sweep_tpN.json]
 
 For every (tokens, hidden) it times, on the device and as the maximum over ranks:
   own arm        every algorithm (one-shot Lamport, two-shot Lamport, two-shot flag barrier,
@@ -176,7 +176,7 @@ def main():
                                          "lamport_max_bytes": max(lam) if lam else 0}}
         result["stats"] = {k: v for k, v in api.stats().items() if k != "status"}
     if rank == 0:
-        out = args.out or f"gpurun_out/sweep_{args.impl}_tp{world}.json"
+        out = args.out or os.path.join(common.out_dir(), f"sweep_{args.impl}_tp{world}.json")
         os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
         with open(out, "w") as f:
             json.dump(result, f, indent=1)

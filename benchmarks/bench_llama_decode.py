@@ -101,7 +101,7 @@ def main():
             print(json.dumps(row), flush=True)
         model._graph = None
     if rank == 0:
-        out = args.out or f"gpurun_out/llama_{args.model}_tp{world}_{args.mode}.json"
+        out = args.out or os.path.join(common.out_dir(), f"llama_{args.model}_tp{world}_{args.mode}.json")
         os.makedirs(os.path.dirname(out) or ".", exist_ok=True)
         json.dump(rows, open(out, "w"), indent=1)
     if world > 1:

@@ -179,6 +179,16 @@ def timing_utils():
     return mod
 
 
+def out_dir() -> str:
+    """Directory for benchmark JSON: $TDX_OUT_DIR, else the first existing scratch directory, else bench_out/."""
+    d = os.environ.get("TDX_OUT_DIR")
+    if not d:
+        cands = [c for c in sorted(os.listdir(REPO)) if c.endswith("_out") and os.path.isdir(os.path.join(REPO, c))]
+        d = os.path.join(REPO, cands[0]) if cands else os.path.join(REPO, "bench_out")
+    os.makedirs(d, exist_ok=True)
+    return d
+
+
 def summarize(us: List[float]) -> dict:
     s = sorted(us)
     return {"mean": statistics.fmean(us), "median": statistics.median(us), "min": s[0],
