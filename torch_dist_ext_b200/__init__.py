@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 from .ops import reference
-from .ops.fused_allreduce import allreduce_rms_fp8, fused_allreduce_rms, reduce_scatter_rms
+from .ops.fused_allreduce import allreduce_rms_fp8, allreduce_rms_pinned, fused_allreduce_rms, reduce_scatter_rms
 from .parallel import comm as _comm
 from .parallel.comm import CommProcess, get_comm, local_workspaces, setup_env, teardown_env
 from .utils.config import ALGO_CODES, OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME, Config, config
@@ -73,7 +73,8 @@ def check_status() -> None:
 
 
 __all__ = [
-    "setup_env", "teardown_env", "get_workspace", "allreduce_rms", "allreduce_rms_fp8", "fused_allreduce_rms",
+    "setup_env", "teardown_env", "get_workspace", "allreduce_rms", "allreduce_rms_fp8", "allreduce_rms_pinned",
+    "fused_allreduce_rms",
     "reduce_scatter_rms", "CommProcess", "CommWorkspace", "allreduce_rms_fusion_impl", "get_comm",
     "local_workspaces", "stats", "check_status", "reference", "config", "Config", "ALGO_CODES", "OUT_SAME",
     "OUT_FP8_TOKEN", "OUT_FP8_BLOCK128",

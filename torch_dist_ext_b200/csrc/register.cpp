@@ -110,50 +110,62 @@ void connect_local(std::vector<c10::intrusive_ptr<CommWorkspace>> all) {
 
 // ---- fused all-reduce -------------------------------------------------------------------------
 
+// Address under which the device sees a tensor's data. A CUDA tensor must live on `device`. With
+// `allow_pinned`, a CPU tensor in page-locked memory is accepted too: the kernels then read or write it
+// over PCIe themselves, which saves the staging copies of a caller whose data starts and ends on the host.
+static void* device_address(const Tensor& t, int device, bool allow_pinned, const char* name) {
+  if (t.is_cuda()) {
+    TORCH_CHECK(t.get_device() == device, name, " is on another device than the workspace");
+    return t.data_ptr();
+  }
+  TORCH_CHECK(allow_pinned && t.is_cpu(), name, " must be a CUDA tensor");
+  cudaPointerAttributes attr{};
+  const cudaError_t e = cudaPointerGetAttributes(&attr, t.data_ptr());
+  if (e != cudaSuccess) (void)cudaGetLastError();
+  TORCH_CHECK(e == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr, name,
+              " is a CPU tensor outside page-locked (pinned) memory: pin it or move it to the device");
+  return attr.devicePointer;
+}
+
 static void fill_tensor_params(tdx::ArParams& p, const Tensor& in, const c10::optional<Tensor>& residual_in,
                                const Tensor& gamma, const c10::optional<Tensor>& residual_out,
                                const Tensor& norm_out, const c10::optional<Tensor>& scale_out, double eps,
-                               int64_t out_mode, int64_t algo, bool scatter_only, int nranks) {
-  TORCH_CHECK(in.is_cuda() && in.is_contiguous(), "allreduce_in must be a contiguous CUDA tensor");
+                               int64_t out_mode, int64_t algo, bool scatter_only, int nranks, int device,
+                               bool allow_pinned) {
+  TORCH_CHECK(in.is_contiguous(), "allreduce_in must be contiguous");
   TORCH_CHECK(in.dim() >= 1, "allreduce_in must have at least one dimension");
   const int64_t hidden = in.size(-1);
   const int64_t tokens = hidden > 0 ? in.numel() / hidden : 0;
   TORCH_CHECK(in.numel() < (1ll << 31) * 8, "allreduce_in is too large");
-  TORCH_CHECK(gamma.is_cuda() && gamma.is_contiguous() && gamma.numel() == hidden && gamma.scalar_type() == in.scalar_type(),
-              "rms_gamma must be a contiguous CUDA tensor of shape [hidden] and the input dtype");
+  TORCH_CHECK(gamma.is_cuda() && gamma.get_device() == device && gamma.is_contiguous() && gamma.numel() == hidden &&
+                  gamma.scalar_type() == in.scalar_type(),
+              "rms_gamma must be a contiguous CUDA tensor of shape [hidden] and the input dtype, on the workspace's device");
   const int64_t out_rows = scatter_only ? (tokens + nranks - 1) / nranks : tokens;
-  auto check_like = [&](const Tensor& t, const char* name) {
-    TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == in.scalar_type() && t.numel() == out_rows * hidden,
-                name, " must be a contiguous CUDA tensor of the input dtype with ", out_rows, " x ", hidden, " elements");
-    TORCH_CHECK(t.get_device() == in.get_device(), name, " is on another device than allreduce_in");
+  auto check_like = [&](const Tensor& t, const char* name) -> void* {
+    TORCH_CHECK(t.is_contiguous() && t.scalar_type() == in.scalar_type() && t.numel() == out_rows * hidden, name,
+                " must be a contiguous tensor of the input dtype with ", out_rows, " x ", hidden, " elements");
+    return device_address(t, device, allow_pinned, name);
   };
-  p.in = in.data_ptr();
+  p.in = device_address(in, device, allow_pinned, "allreduce_in");
   p.residual_in = nullptr;
-  if (residual_in.has_value() && residual_in->defined()) {
-    check_like(*residual_in, "residual_in");
-    p.residual_in = residual_in->data_ptr();
-  }
+  if (residual_in.has_value() && residual_in->defined()) p.residual_in = check_like(*residual_in, "residual_in");
   p.residual_out = nullptr;
-  if (residual_out.has_value() && residual_out->defined()) {
-    check_like(*residual_out, "residual_out");
-    p.residual_out = residual_out->data_ptr();
-  }
+  if (residual_out.has_value() && residual_out->defined()) p.residual_out = check_like(*residual_out, "residual_out");
   p.gamma = gamma.data_ptr();
   if (out_mode == tdx::kOutSame) {
-    check_like(norm_out, "norm_out");
+    p.norm_out = check_like(norm_out, "norm_out");
     p.scale_out = nullptr;
   } else {
-    TORCH_CHECK(norm_out.is_cuda() && norm_out.is_contiguous() && norm_out.element_size() == 1 &&
-                    norm_out.numel() == out_rows * hidden,
-                "fp8 norm_out must be a contiguous 1-byte CUDA tensor with ", out_rows, " x ", hidden, " elements");
-    TORCH_CHECK(scale_out.has_value() && scale_out->defined() && scale_out->is_cuda() && scale_out->is_contiguous() &&
+    TORCH_CHECK(norm_out.is_contiguous() && norm_out.element_size() == 1 && norm_out.numel() == out_rows * hidden,
+                "fp8 norm_out must be a contiguous 1-byte tensor with ", out_rows, " x ", hidden, " elements");
+    TORCH_CHECK(scale_out.has_value() && scale_out->defined() && scale_out->is_contiguous() &&
                     scale_out->scalar_type() == at::kFloat,
-                "fp8 output needs a contiguous float32 CUDA scale tensor");
+                "fp8 output needs a contiguous float32 scale tensor");
     const int64_t nscale = out_mode == tdx::kOutFp8Token ? out_rows : out_rows * (hidden / 128);
     TORCH_CHECK(scale_out->numel() == nscale, "scale tensor must have ", nscale, " elements");
-    p.scale_out = scale_out->data_ptr<float>();
+    p.norm_out = device_address(norm_out, device, allow_pinned, "norm_out");
+    p.scale_out = static_cast<float*>(device_address(*scale_out, device, allow_pinned, "scale_out"));
   }
-  p.norm_out = norm_out.data_ptr();
   p.tokens = (int32_t)tokens;
   p.hidden = (int32_t)hidden;
   p.eps = (float)eps;
@@ -163,22 +175,41 @@ static void fill_tensor_params(tdx::ArParams& p, const Tensor& in, const c10::op
   p.scatter_only = scatter_only ? 1 : 0;
 }
 
-int64_t allreduce_rms_fusion_ex(const Tensor& in, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
-                                c10::optional<Tensor> residual_out, Tensor norm_out, c10::optional<Tensor> scale_out,
-                                double eps, const Tensor& workspace, int64_t out_mode, int64_t algo,
-                                bool scatter_only) {
+static int64_t launch_fused(const Tensor& in, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
+                            const c10::optional<Tensor>& residual_out, const Tensor& norm_out,
+                            const c10::optional<Tensor>& scale_out, double eps, const Tensor& workspace,
+                            int64_t out_mode, int64_t algo, bool scatter_only, bool allow_pinned) {
   TORCH_CHECK(workspace.is_cuda(), "workspace must be the CUDA tensor returned by get_workspace");
   tdx::Workspace* ws = tdx::Workspace::from_table(workspace.data_ptr());
   TORCH_CHECK(ws != nullptr, "workspace tensor does not belong to a registered CommWorkspace");
-  TORCH_CHECK(in.is_cuda() && in.get_device() == ws->device(), "allreduce_in must live on the workspace's device");
-  const c10::cuda::CUDAGuard guard(in.device());
+  const c10::cuda::CUDAGuard guard(workspace.device());
   tdx::ArParams p{};
   ws->fill_params(&p);
-  fill_tensor_params(p, in, residual_in, gamma, residual_out, norm_out, scale_out, eps, out_mode, algo, scatter_only, p.nranks);
+  fill_tensor_params(p, in, residual_in, gamma, residual_out, norm_out, scale_out, eps, out_mode, algo, scatter_only,
+                     p.nranks, ws->device(), allow_pinned);
   tdx::LaunchPlan used{};
   const std::string err = tdx::launch_allreduce(p, at::cuda::getCurrentCUDAStream().stream(), &used);
   TORCH_CHECK(err.empty(), "allreduce_rms_fusion: ", err);
   return used.algo;
+}
+
+int64_t allreduce_rms_fusion_ex(const Tensor& in, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
+                                c10::optional<Tensor> residual_out, Tensor norm_out, c10::optional<Tensor> scale_out,
+                                double eps, const Tensor& workspace, int64_t out_mode, int64_t algo,
+                                bool scatter_only) {
+  return launch_fused(in, residual_in, gamma, residual_out, norm_out, scale_out, eps, workspace, out_mode, algo,
+                      scatter_only, /*allow_pinned=*/false);
+}
+
+// Same op for callers whose data starts and ends in page-locked host memory: any of the data tensors (not
+// gamma) may be a pinned CPU tensor. The reference has no counterpart; its op takes device tensors only
+// (src/ops/all_reduce_fusion.cpp:14-61).
+int64_t allreduce_rms_fusion_hostio(const Tensor& in, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
+                                    c10::optional<Tensor> residual_out, Tensor norm_out,
+                                    c10::optional<Tensor> scale_out, double eps, const Tensor& workspace,
+                                    int64_t out_mode, int64_t algo, bool scatter_only) {
+  return launch_fused(in, residual_in, gamma, residual_out, norm_out, scale_out, eps, workspace, out_mode, algo,
+                      scatter_only, /*allow_pinned=*/true);
 }
 
 void allreduce_rms_fusion(c10::SymInt rank, c10::SymInt nranks, const Tensor& allreduce_in, const Tensor& residual_in,
@@ -210,11 +241,11 @@ int64_t allreduce_rms_emulated(std::vector<c10::intrusive_ptr<CommWorkspace>> wo
                        residual_ins.empty() ? c10::nullopt : c10::optional<Tensor>(residual_ins[r]), gamma,
                        residual_outs.empty() ? c10::nullopt : c10::optional<Tensor>(residual_outs[r]), norm_outs[r],
                        scale_outs.empty() ? c10::nullopt : c10::optional<Tensor>(scale_outs[r]), eps, out_mode, algo,
-                       scatter_only, n);
+                       scatter_only, n, ws->device(), /*allow_pinned=*/true);
   }
-  const c10::cuda::CUDAGuard guard(ins[0].device());
+  const c10::cuda::CUDAGuard guard(gamma.device());
   auto dev = torch::empty({(int64_t)(n * sizeof(tdx::ArParams))},
-                          torch::TensorOptions().dtype(torch::kUInt8).device(ins[0].device()));
+                          torch::TensorOptions().dtype(torch::kUInt8).device(gamma.device()));
   auto stream = at::cuda::getCurrentCUDAStream().stream();
   C10_CUDA_CHECK(cudaMemcpyAsync(dev.data_ptr(), params.data(), n * sizeof(tdx::ArParams), cudaMemcpyHostToDevice, stream));
   tdx::LaunchPlan used{};
@@ -292,6 +323,11 @@ TORCH_LIBRARY(torch_dist_ext, m) {
       "Tensor[] residual_ins, Tensor rms_gamma, Tensor[] residual_outs, Tensor[] norm_outs, Tensor[] scale_outs, "
       "float eps, int out_mode, int algo, bool scatter_only) -> int",
       &tdx_torch::allreduce_rms_emulated);
+  m.def(
+      "allreduce_rms_fusion_hostio(Tensor allreduce_in, Tensor? residual_in, Tensor rms_gamma, Tensor(a!)? residual_out, "
+      "Tensor(b!) norm_out, Tensor(c!)? scale_out, float eps, Tensor workspace, int out_mode, int algo, "
+      "bool scatter_only) -> int",
+      &tdx_torch::allreduce_rms_fusion_hostio);
   m.def("set_policy(int nranks, int oneshot_max_bytes, int lamport_max_bytes) -> ()", &tdx_torch::set_policy);
   m.def("get_policy(int nranks) -> int[]", &tdx_torch::get_policy);
   m.def(

@@ -158,7 +158,10 @@ class TPLlama:
             raise NotImplementedError("sequence-parallel mode is implemented for bf16 weights")
         return lin(x, x_scale)
 
-    def _layer(self, i: int, x, x_scale, res, positions, batch_idx, tokens: int, max_len: int):
+    def _layer(self, i: int, x, x_scale, res, positions, tokens: int, max_len: int, bf16_tail: bool = False):
+        """One decoder layer of a decode step. ``bf16_tail`` (last layer of an fp8 model): the
+        down projection is a plain GEMM followed by the all-reduce whose epilogue writes bf16,
+        because the final norm feeds the bf16 lm_head."""
         cfg, L, d = self.cfg, self.layers[i], self.cfg.head_dim
         qkv = self._col_parallel(x, L["wqkv"], tokens, x_scale)
         q = qkv[:, : self.hq * d].view(tokens, self.hq, d)
@@ -168,13 +171,13 @@ class TPLlama:
         attn = attention.decode_attention(q, self.k_cache[i][:tokens], self.v_cache[i][:tokens], self.seq_lens[:tokens], max_len)
         x, x_scale, res = self._row_parallel(attn.view(tokens, self.hq * d), L["wo"], res, L["ln2"])
         gu = self._col_parallel(x, L["wgu"], tokens, x_scale)
-        if cfg.fp8:
-            act, act_scale = activation.silu_mul(gu, quant_block128=True)
-        else:
-            (act, act_scale) = activation.silu_mul(gu)
+        act, act_scale = activation.silu_mul(gu, quant_block128=cfg.fp8)
+        if bf16_tail:
+            y = L["wd"](act, act_scale)
+            x, res, _ = fused_allreduce_rms(y, res, self.final_norm, cfg.eps, out_mode=OUT_SAME)
+            return x, None, res
         next_gamma = self.layers[i + 1]["ln1"] if i + 1 < cfg.n_layers else self.final_norm
-        x, x_scale, res = self._row_parallel(act, L["wd"], res, next_gamma, act_scale)
-        return x, x_scale, res
+        return self._row_parallel(act, L["wd"], res, next_gamma, act_scale)
 
     def _logits_argmax(self, x: torch.Tensor, tokens: int) -> torch.Tensor:
         if self.mode == "sp":
@@ -210,7 +213,6 @@ class TPLlama:
         """One token per sequence: ``tokens``/``positions`` int64 [B] on the device. Returns next tokens [B]."""
         b = tokens.shape[0]
         cfg = self.cfg
-        batch_idx = torch.arange(b, device=self.device)
         self.seq_lens[:b] = (positions + 1).to(torch.int32)
         res = self.embed[tokens]                                                  # [B, hidden]
         mode0 = self._norm_out_mode()
@@ -225,30 +227,9 @@ class TPLlama:
         x, _, x_scale = norm.fused_add_rmsnorm(res, None, self.layers[0]["ln1"], cfg.eps, out_mode=mode0, want_residual=False)
         for i in range(cfg.n_layers):
             last = i + 1 == cfg.n_layers
-            if last and cfg.fp8:
-                # the final norm feeds the bf16 lm_head: switch the last epilogue back to bf16
-                x, x_scale, res = self._layer_last_bf16(i, x, x_scale, res, positions, batch_idx, b, max_len)
-            else:
-                x, x_scale, res = self._layer(i, x, x_scale, res, positions, batch_idx, b, max_len)
+            x, x_scale, res = self._layer(i, x, x_scale, res, positions, b, max_len, bf16_tail=last and cfg.fp8)
         self.last_hidden = x          # final normalised hidden state (kept for tests and probes)
         return self._logits_argmax(x, b)
-
-    def _layer_last_bf16(self, i, x, x_scale, res, positions, batch_idx, tokens, max_len):
-        saved = self.cfg.fp8
-        cfg, L, d = self.cfg, self.layers[i], self.cfg.head_dim
-        qkv = self._col_parallel(x, L["wqkv"], tokens, x_scale)
-        q = qkv[:, : self.hq * d].view(tokens, self.hq, d)
-        k = qkv[:, self.hq * d: (self.hq + self.hkv) * d].view(tokens, self.hkv, d)
-        v = qkv[:, (self.hq + self.hkv) * d:].view(tokens, self.hkv, d)
-        rope.rope_append_kv_(q, k, v, positions, self.cos_sin, self.k_cache[i], self.v_cache[i])
-        attn = attention.decode_attention(q, self.k_cache[i][:tokens], self.v_cache[i][:tokens], self.seq_lens[:tokens], max_len)
-        x, x_scale, res = self._row_parallel(attn.view(tokens, self.hq * d), L["wo"], res, L["ln2"])
-        gu = self._col_parallel(x, L["wgu"], tokens, x_scale)
-        act, act_scale = activation.silu_mul(gu, quant_block128=True)
-        y = L["wd"](act, act_scale)
-        x, res, _ = fused_allreduce_rms(y, res, self.final_norm, cfg.eps, out_mode=OUT_SAME)
-        assert saved
-        return x, None, res
 
     # ---- CUDA graph ------------------------------------------------------------------------------------
     def capture_decode(self, batch: int, max_len: int) -> None:

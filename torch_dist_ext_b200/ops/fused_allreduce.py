@@ -73,6 +73,32 @@ def fused_allreduce_rms(allreduce_in: torch.Tensor, residual_in: Optional[torch.
     return norm_out, residual_out, scales
 
 
+def allreduce_rms_pinned(allreduce_in: torch.Tensor, residual_in: Optional[torch.Tensor], rms_gamma: torch.Tensor,
+                         eps: float, *, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, algo=None,
+                         ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The fused op for data that starts and ends in pinned host memory.
+
+    ``allreduce_in`` / ``residual_in`` may be pinned CPU tensors (or device tensors), ``out`` is an
+    optional pair of pinned ``(norm_out, residual_out)`` tensors to fill (allocated when omitted;
+    reuse them across calls). The kernel reads its inputs and writes its outputs over PCIe itself:
+    no staging copies, one launch, and with the two-shot algorithms each rank fetches only the
+    residual rows it owns. ``rms_gamma`` stays on the device (every row re-reads it). The outputs
+    are valid once the launching stream has been synchronised. Returns ``(norm_out, residual_out)``.
+    """
+    c = _comm.get_comm()
+    if c.comm is None:
+        raise RuntimeError("allreduce_rms_pinned needs the CUDA workspace (setup_env on a machine with a GPU)")
+    if out is None:
+        out = (torch.empty(allreduce_in.shape, dtype=allreduce_in.dtype).pin_memory(),
+               torch.empty(allreduce_in.shape, dtype=allreduce_in.dtype).pin_memory())
+    norm_out, residual_out = out
+    workspace = c.get_workspace(rms_gamma)
+    used = _lib.ops().allreduce_rms_fusion_hostio(allreduce_in, residual_in, rms_gamma, residual_out, norm_out, None,
+                                                  eps, workspace, OUT_SAME, _algo_code(algo), False)
+    c.algo_counts[used] = c.algo_counts.get(used, 0) + 1
+    return norm_out, residual_out
+
+
 def allreduce_rms_fp8(allreduce_in, residual_in, rms_gamma, eps, workspace=None, *, block_scaled: bool = False,
                       algo=None):
     """Fused op with e4m3 output. Returns ``(norm_fp8, scales, residual_out)``."""
