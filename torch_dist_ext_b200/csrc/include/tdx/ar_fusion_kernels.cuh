@@ -261,13 +261,18 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
   const size_t msg_bytes = rv.row_bytes * p.tokens;
   const char* in = static_cast<const char*>(p.in);
 
-  // 1. push this rank's rows into slot `rank` of every peer's current buffer
+  // 1. push this rank's rows into slot `rank` of every peer's current buffer. When no block has
+  //    more than one row, the vectors read here stay in registers for step 3, so that the input
+  //    is read once (it may live in pinned host memory, where a second read crosses PCIe again).
+  const bool single_row = p.tokens <= (int)gridDim.x;
+  uint4 own[kVpt];
   for (int row = blockIdx.x; row < p.tokens; row += gridDim.x) {
 #pragma unroll
     for (int v = 0; v < kVpt; ++v) {
       if (!rv.active(v)) continue;
       const size_t off = (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16;
       const uint4 val = scrub(ptx::ld_stream_v4(in + off));
+      own[v] = val;
 #pragma unroll
       for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
         if (r >= nranks || r == p.rank) continue;
@@ -298,7 +303,7 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
         // issue all polls first so that kN-1 loads are in flight together
 #pragma unroll
         for (int r = 0; r < kN; ++r)
-          vals[r] = (r == p.rank) ? scrub(ptx::ld_v4(in + off))
+          vals[r] = (r == p.rank) ? (single_row ? own[v] : scrub(ptx::ld_v4(in + off)))
                                   : ptx::ld_volatile_v4(mine + (size_t)r * msg_bytes + off);
 #pragma unroll
         for (int r = 0; r < kN; ++r)
@@ -314,7 +319,7 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
       } else {
         for (int r = 0; r < nranks; ++r) {
           const uint4 val = (r == p.rank)
-                                ? scrub(ptx::ld_v4(in + off))
+                                ? (single_row ? own[v] : scrub(ptx::ld_v4(in + off)))
                                 : poll_vec(mine + (size_t)r * msg_bytes + off, w, p, ctl, kTimeoutLamportGather, r, 1, row);
           float f[kVec];
           unpack<T>(val, f);
