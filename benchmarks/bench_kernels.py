@@ -1,0 +1,187 @@
+#!/usr/bin/env python
+"""Single-GPU roofline table of the library's kernels (no communication).
+
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_fp8|attention|elementwise|all] [--steps 30]
+
+Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
+over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
+the time, the achieved bandwidth and FLOP rate, their fractions of the measured peaks (a STREAM-style
+copy and a cuBLAS bf16 GEMM; read from MEASURED_PEAKS.json beside the repo's bench.py when present,
+else an earlier measurement of the same machine type, and the row says which), and the time of the
+library call that does the same work (cuBLAS through torch.matmul, PyTorch's attention and
+elementwise kernels) for comparison.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from benchmarks import common  # noqa: E402
+
+L2_BYTES = 126 << 20
+
+
+def peaks():
+    path = os.path.join(common.REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def rotating(make, nbytes: int):
+    """Copies of an operand such that consecutive calls touch different memory (> 2 x L2 in total)."""
+    n = max(2, math.ceil(2 * L2_BYTES / max(nbytes, 1)) + 1)
+    return [make() for _ in range(min(n, 64))]
+
+
+def time_us(fn_of_i, n_sets: int, steps: int) -> float:
+    state = {"i": 0}
+
+    def step():
+        state["i"] = (state["i"] + 1) % n_sets
+        fn_of_i(state["i"])
+
+    return common.region_time_us(step, steps, 3, lambda: None)
+
+
+def row(name, us, lib_us, nbytes, flops, hbm, tf, src):
+    gbs = nbytes / us / 1e3
+    tfl = flops / us / 1e6
+    return {"case": name, "us": round(us, 2), "library_us": None if lib_us is None else round(lib_us, 2),
+            "GB/s": round(gbs, 1), f"frac_hbm_of_{src}": round(gbs / hbm, 3),
+            "TFLOP/s": round(tfl, 1), f"frac_bf16_of_{src}": round(tfl / tf, 3)}
+
+
+def gemm_cases(dev, steps, shapes, ms, out):
+    from torch_dist_ext_b200.ops import gemm
+
+    hbm, tf, src = peaks()
+    for (n, k) in shapes:
+        ws = rotating(lambda: torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02, n * k * 2)
+        for m in ms:
+            a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+            us = time_us(lambda i: gemm.linear(a, ws[i]), len(ws), steps)
+            lib = time_us(lambda i: torch.matmul(a, ws[i].t()), len(ws), steps)
+            nbytes = (n * k + m * k + m * n) * 2
+            out.append(row(f"gemm bf16 m={m} n={n} k={k}", us, lib, nbytes, 2.0 * m * n * k, hbm, tf, src))
+            print(out[-1], flush=True)
+        del ws
+        torch.cuda.empty_cache()
+
+
+def gemm_fp8_cases(dev, steps, out):
+    from torch_dist_ext_b200.ops import gemm, quant
+
+    hbm, tf, src = peaks()
+    for (n, k) in [(28672, 8192), (8192, 28672)]:
+        w = torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05
+        wq, wscale = gemm.quantize_weight_block128(w)
+        del w
+        wqs = [wq] + [wq.clone() for _ in range(max(1, math.ceil(2 * L2_BYTES / (n * k))))]
+        for m in (16, 64, 2048):
+            a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+            aq, ascale = quant.quant_fp8(a, block_scaled=True)
+            us = time_us(lambda i: gemm.linear_fp8_blockscaled(aq, ascale, wqs[i], wscale), len(wqs), steps)
+            nbytes = n * k + m * k + m * n * 2
+            out.append(row(f"gemm fp8 block-scaled m={m} n={n} k={k}", us, None, nbytes, 2.0 * m * n * k, hbm, 2 * tf, src))
+            print(out[-1], flush=True)
+        del wqs, wq
+        torch.cuda.empty_cache()
+
+
+def attention_cases(dev, steps, out):
+    from torch_dist_ext_b200.ops import attention
+
+    hbm, tf, src = peaks()
+    for batch in (1, 16, 64):
+        length, hq, hkv, d = 2048, 32, 8, 128
+        kv_bytes = 2 * batch * length * hkv * d * 2
+        sets = rotating(lambda: (torch.randn(batch, length, hkv, d, device=dev, dtype=torch.bfloat16),
+                                 torch.randn(batch, length, hkv, d, device=dev, dtype=torch.bfloat16)), kv_bytes)
+        q = torch.randn(batch, hq, d, device=dev, dtype=torch.bfloat16)
+        lens = torch.full((batch,), length, device=dev, dtype=torch.int32)
+        us = time_us(lambda i: attention.decode_attention(q, sets[i][0], sets[i][1], lens, length), len(sets), steps)
+
+        def sdpa(i):
+            k, v = sets[i]
+            torch.nn.functional.scaled_dot_product_attention(
+                q.unsqueeze(2), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), enable_gqa=True)
+
+        lib = time_us(sdpa, len(sets), steps)
+        out.append(row(f"decode attention batch={batch} len={length} hq={hq} hkv={hkv}", us, lib, kv_bytes,
+                       4.0 * batch * hq * length * d, hbm, tf, src))
+        print(out[-1], flush=True)
+        del sets
+        torch.cuda.empty_cache()
+
+
+def elementwise_cases(dev, steps, out):
+    from torch_dist_ext_b200.ops import activation, norm, quant
+
+    hbm, tf, src = peaks()
+    rows, hidden = 8192, 8192
+    nb = rows * hidden * 2
+    xs = rotating(lambda: torch.randn(rows, hidden, device=dev, dtype=torch.bfloat16), nb)
+    r = torch.randn(rows, hidden, device=dev, dtype=torch.bfloat16)
+    g = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+    us = time_us(lambda i: norm.fused_add_rmsnorm(xs[i], r, g, 1e-6), len(xs), steps)
+
+    def torch_norm(i):
+        y = xs[i] + r
+        torch.nn.functional.rms_norm(y, (hidden,), g, 1e-6)
+
+    out.append(row("residual add + rmsnorm 8192x8192 bf16", us, time_us(torch_norm, len(xs), steps), 4 * nb, 0, hbm, tf, src))
+    print(out[-1], flush=True)
+    us = time_us(lambda i: quant.quant_fp8(xs[i]), len(xs), steps)
+    out.append(row("fp8 per-token quant 8192x8192", us, None, nb + nb // 2, 0, hbm, tf, src))
+    print(out[-1], flush=True)
+    us = time_us(lambda i: quant.quant_fp8(xs[i], block_scaled=True), len(xs), steps)
+    out.append(row("fp8 1x128 quant 8192x8192", us, None, nb + nb // 2, 0, hbm, tf, src))
+    print(out[-1], flush=True)
+    us = time_us(lambda i: activation.silu_mul(xs[i]), len(xs), steps)
+
+    def torch_silu(i):
+        a, b = xs[i].chunk(2, dim=-1)
+        torch.nn.functional.silu(a) * b
+
+    out.append(row("silu(gate)*up 8192x(2x4096)", us, time_us(torch_silu, len(xs), steps), nb + nb // 2, 0, hbm, tf, src))
+    print(out[-1], flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--group", default="all")
+    ap.add_argument("--steps", type=int, default=30)
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    import torch_dist_ext_b200  # noqa: F401  (loads the extension)
+
+    out = []
+    g = args.group
+    if g in ("gemm", "all"):        # decode: weight streaming (Llama-3-8B shapes at TP=1)
+        gemm_cases(dev, args.steps, [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)], (1, 16, 64), out)
+    if g in ("gemm_prefill", "all"):
+        gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out)
+    if g in ("gemm_fp8", "all"):
+        gemm_fp8_cases(dev, args.steps, out)
+    if g in ("attention", "all"):
+        attention_cases(dev, args.steps, out)
+    if g in ("elementwise", "all"):
+        elementwise_cases(dev, args.steps, out)
+    path = os.path.join(common.out_dir(), f"kernels_{g}.json")
+    with open(path, "w") as f:
+        json.dump(out, f, indent=1)
+    print("wrote", path)
+
+
+if __name__ == "__main__":
+    main()
