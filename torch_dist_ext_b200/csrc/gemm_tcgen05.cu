@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <mutex>
 #include "tdx/comm.h"
 #include "tdx/gemm.h"
@@ -269,8 +270,26 @@ std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs&
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
 }
 
+// TDX_GEMM_CTAS_PER_SM=2 halves the operand ring of the narrow tiles so that two CTAs share an SM:
+// a weight-streaming grid of up to 296 tiles is then resident at once and its CTAs finish together,
+// instead of a full wave followed by a partly filled one. Default 1 (the measured configuration).
+bool two_ctas_per_sm() {
+  static const bool on = [] {
+    const char* e = std::getenv("TDX_GEMM_CTAS_PER_SM");
+    return e != nullptr && std::atoi(e) == 2;
+  }();
+  return on;
+}
+
 template <bool kFp8, bool kScaled>
 std::string launch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs& a, dim3 grid, cudaStream_t s) {
+  if (two_ctas_per_sm()) {
+    switch (bn) {
+      case 16: return launch<16, 5, kFp8, kScaled>(mx, my, a, grid, s);
+      case 32: return launch<32, 4, kFp8, kScaled>(mx, my, a, grid, s);
+      case 64: return launch<64, 4, kFp8, kScaled>(mx, my, a, grid, s);
+    }
+  }
   switch (bn) {
     case 16: return launch<16, 10, kFp8, kScaled>(mx, my, a, grid, s);
     case 32: return launch<32, 8, kFp8, kScaled>(mx, my, a, grid, s);
