@@ -104,3 +104,17 @@ def test_config_env_and_policy_file(tmp_path, monkeypatch):
     monkeypatch.setenv("TDX_ALGO", "bogus")
     with pytest.raises(ValueError):
         Config.from_env()
+
+
+def test_pinned_entry_point_fails_cleanly_without_a_device():
+    x, g = torch.randn(4, 64), torch.ones(64)
+    o1, o2 = torch.empty_like(x), torch.empty_like(x)
+    with pytest.raises(RuntimeError, match="workspace must be the CUDA tensor"):
+        torch.ops.torch_dist_ext.allreduce_rms_fusion_hostio(x, x, g, o1, o2, None, 1e-6,
+                                                             torch.zeros(tdx.parallel.comm.table_nbytes(), dtype=torch.uint8),
+                                                             OUT_SAME, 0, False)
+    if torch.cuda.is_available():
+        return
+    tdx.setup_env(0, 1)
+    with pytest.raises(RuntimeError, match="needs the CUDA workspace"):
+        tdx.allreduce_rms_pinned(x, x, g, 1e-6, out=(o1, o2))
