@@ -126,7 +126,7 @@ def write_ninja() -> Path:
     ]
     lines += [f"build {LIB_PATH}: link {' '.join(objs)}", f"  ldflags = {' '.join(ld)}"]
     # Standalone C++ harness (no PyTorch): the kernels, the launcher and the workspace manager only.
-    core = [o for o in objs if o.startswith("ar_inst_") or o in ("workspace.o", "ar_fusion_launch.host.o")]
+    core = [o for o in objs if o.startswith("ar_inst_") or o in ("workspace.o", "ar_fusion_launch.host.o", "fd_channel.host.o")]
     lines += [
         "rule nvlink_exe",
         "  command = $nvcc $nvflags -o $out $in -lcudart",

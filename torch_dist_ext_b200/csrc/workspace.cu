@@ -18,9 +18,6 @@
 //     an address whose loads reduce, and whose stores replicate, inside the NVSwitch.
 // Tier B falls back to tier A when any step is refused (no multicast support, no fd export).
 #include <cuda.h>
-#include <poll.h>
-#include <sys/socket.h>
-#include <sys/un.h>
 #include <unistd.h>
 #include <atomic>
 #include <chrono>
@@ -31,6 +28,7 @@
 #include <stdexcept>
 #include <thread>
 #include "tdx/api.h"
+#include "tdx/fd_channel.h"
 #include "tdx/ptx.cuh"
 #include "tdx/vec.cuh"
 
@@ -145,68 +143,6 @@ Driver& driver() {
   return d;
 }
 
-// ---- fd passing over an abstract Unix-domain socket ------------------------------------------
-socklen_t abstract_addr(sockaddr_un* addr, const char* name) {
-  std::memset(addr, 0, sizeof(*addr));
-  addr->sun_family = AF_UNIX;
-  const size_t n = std::strlen(name);
-  std::memcpy(addr->sun_path + 1, name, n);  // sun_path[0] == 0: abstract namespace
-  return (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
-}
-
-bool send_fd(int sock, int fd) {
-  char byte = 'f';
-  iovec iov{&byte, 1};
-  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int))] = {};
-  msghdr msg{};
-  msg.msg_iov = &iov;
-  msg.msg_iovlen = 1;
-  msg.msg_control = ctrl;
-  msg.msg_controllen = sizeof(ctrl);
-  cmsghdr* c = CMSG_FIRSTHDR(&msg);
-  c->cmsg_level = SOL_SOCKET;
-  c->cmsg_type = SCM_RIGHTS;
-  c->cmsg_len = CMSG_LEN(sizeof(int));
-  std::memcpy(CMSG_DATA(c), &fd, sizeof(int));
-  return sendmsg(sock, &msg, 0) == 1;
-}
-
-int recv_fd(int sock) {
-  char byte = 0;
-  iovec iov{&byte, 1};
-  alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int))] = {};
-  msghdr msg{};
-  msg.msg_iov = &iov;
-  msg.msg_iovlen = 1;
-  msg.msg_control = ctrl;
-  msg.msg_controllen = sizeof(ctrl);
-  if (recvmsg(sock, &msg, 0) != 1) return -1;
-  cmsghdr* c = CMSG_FIRSTHDR(&msg);
-  if (c == nullptr || c->cmsg_level != SOL_SOCKET || c->cmsg_type != SCM_RIGHTS) return -1;
-  int fd = -1;
-  std::memcpy(&fd, CMSG_DATA(c), sizeof(int));
-  return fd;
-}
-
-// Ask the rank that listens on `name` for its memory fd ('m') or the multicast fd ('c').
-int request_fd(const char* name, char what) {
-  sockaddr_un addr;
-  const socklen_t len = abstract_addr(&addr, name);
-  for (int attempt = 0; attempt < 200; ++attempt) {
-    int s = socket(AF_UNIX, SOCK_STREAM, 0);
-    if (s < 0) return -1;
-    if (connect(s, reinterpret_cast<sockaddr*>(&addr), len) == 0) {
-      int fd = -1;
-      if (write(s, &what, 1) == 1) fd = recv_fd(s);
-      close(s);
-      return fd;
-    }
-    close(s);
-    std::this_thread::sleep_for(std::chrono::milliseconds(25));
-  }
-  return -1;
-}
-
 }  // namespace
 
 struct Workspace::Vmm {
@@ -219,25 +155,7 @@ struct Workspace::Vmm {
   CUdeviceptr mc_va = 0;
   CUmemGenericAllocationHandle peer_mem[kMaxRanks] = {};
   CUdeviceptr peer_va[kMaxRanks] = {};
-  char socket_name[64] = {};
-  int listen_fd = -1;
-  std::thread server;
-  std::atomic<bool> stop{false};
-
-  void serve() {
-    while (!stop.load()) {
-      pollfd p{listen_fd, POLLIN, 0};
-      if (poll(&p, 1, 100) <= 0) continue;
-      int c = accept(listen_fd, nullptr, nullptr);
-      if (c < 0) continue;
-      char what = 0;
-      if (read(c, &what, 1) == 1) {
-        const int fd = what == 'c' ? mc_fd : mem_fd;
-        if (fd >= 0) send_fd(c, fd);
-      }
-      close(c);
-    }
-  }
+  FdServer server;                 // hands mem_fd ('m') and mc_fd ('c') to the peers
 };
 
 Workspace::Workspace(int rank, int world_size, int nblocks, uint64_t max_message_bytes,
@@ -323,15 +241,10 @@ Workspace::Workspace(int rank, int world_size, int nblocks, uint64_t max_message
           }
         }
         // listener that hands this rank's fds to the peers
-        std::snprintf(vmm_->socket_name, sizeof(vmm_->socket_name), "tdx-b200-%d-%d-%llx", (int)getpid(), rank_,
-                      (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count());
-        vmm_->listen_fd = socket(AF_UNIX, SOCK_STREAM, 0);
-        sockaddr_un addr;
-        const socklen_t len = abstract_addr(&addr, vmm_->socket_name);
-        if (vmm_->listen_fd < 0 || bind(vmm_->listen_fd, reinterpret_cast<sockaddr*>(&addr), len) != 0 ||
-            listen(vmm_->listen_fd, 32) != 0)
+        vmm_->server.offer('m', vmm_->mem_fd);
+        vmm_->server.offer('c', vmm_->mc_fd);
+        if (!vmm_->server.start(std::to_string(rank_).c_str()))
           throw std::runtime_error("could not open the Unix-domain socket that shares the workspace with the peers");
-        vmm_->server = std::thread([v = vmm_] { v->serve(); });
       }
     }
   }
@@ -359,9 +272,7 @@ void Workspace::init_device_state() {
 void Workspace::release_vmm() {
   if (vmm_ == nullptr) return;
   Driver& d = driver();
-  vmm_->stop.store(true);
-  if (vmm_->server.joinable()) vmm_->server.join();
-  if (vmm_->listen_fd >= 0) close(vmm_->listen_fd);
+  vmm_->server.stop();
   if (vmm_->mc_va) {
     d.MemUnmap(vmm_->mc_va, vmm_->size);
     d.MemAddressFree(vmm_->mc_va, vmm_->size);
@@ -420,7 +331,7 @@ void Workspace::export_handle(uint8_t out[kHandleBytes]) const {
   h.local_ptr = reinterpret_cast<uint64_t>(base_);
   if (vmm_) {
     h.tier = 1;
-    std::memcpy(h.socket_name, vmm_->socket_name, sizeof(h.socket_name));
+    std::snprintf(h.socket_name, sizeof(h.socket_name), "%s", vmm_->server.name());
     h.has_multicast = vmm_->mc_fd >= 0 ? 1 : 0;
   } else {
     h.tier = 0;
