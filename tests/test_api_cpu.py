@@ -118,3 +118,24 @@ def test_pinned_entry_point_fails_cleanly_without_a_device():
     tdx.setup_env(0, 1)
     with pytest.raises(RuntimeError, match="needs the CUDA workspace"):
         tdx.allreduce_rms_pinned(x, x, g, 1e-6, out=(o1, o2))
+
+
+def test_nvtx_ranges_follow_the_flag():
+    from torch_dist_ext_b200.utils import tracing
+
+    calls = []
+    tracing.set_backend(lambda name: calls.append(("push", name)), lambda: calls.append(("pop",)))
+    tdx.setup_env(0, 1)
+    x, g = torch.randn(4, 64), torch.ones(64)
+    try:
+        tracing.enable(False)
+        tdx.fused_allreduce_rms(x, x, g, 1e-6)
+        assert calls == []
+        tracing.enable(True)
+        tdx.fused_allreduce_rms(x, x, g, 1e-6)
+        with tracing.nvtx_range("outer"):
+            pass
+        assert calls == [("push", "tdx.fused_allreduce_rms"), ("pop",), ("push", "outer"), ("pop",)]
+    finally:
+        tracing.enable(False)
+        tracing.set_backend(None, None)

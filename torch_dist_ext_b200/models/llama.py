@@ -34,6 +34,7 @@ from ..ops import activation, attention, fused_gemm, gemm, norm, quant, rope
 from ..ops.fused_allreduce import fused_allreduce_rms
 from ..parallel import comm as _comm
 from ..utils.config import OUT_FP8_BLOCK128, OUT_SAME
+from ..utils.tracing import nvtx_range, traced
 
 
 @dataclass
@@ -209,6 +210,7 @@ class TPLlama:
         return torch.stack(parts, dim=1).reshape(rows * n, -1)[:tokens].contiguous()
 
     # ---- decode -----------------------------------------------------------------------------------
+    @traced("tdx.decode_step")
     def decode_step(self, tokens: torch.Tensor, positions: torch.Tensor, max_len: int) -> torch.Tensor:
         """One token per sequence: ``tokens``/``positions`` int64 [B] on the device. Returns next tokens [B]."""
         b = tokens.shape[0]
@@ -227,7 +229,8 @@ class TPLlama:
         x, _, x_scale = norm.fused_add_rmsnorm(res, None, self.layers[0]["ln1"], cfg.eps, out_mode=mode0, want_residual=False)
         for i in range(cfg.n_layers):
             last = i + 1 == cfg.n_layers
-            x, x_scale, res = self._layer(i, x, x_scale, res, positions, b, max_len, bf16_tail=last and cfg.fp8)
+            with nvtx_range(f"tdx.layer{i}"):
+                x, x_scale, res = self._layer(i, x, x_scale, res, positions, b, max_len, bf16_tail=last and cfg.fp8)
         self.last_hidden = x          # final normalised hidden state (kept for tests and probes)
         return self._logits_argmax(x, b)
 
@@ -270,6 +273,7 @@ class TPLlama:
             k[:batch, :length] = torch.randn(batch, length, self.hkv, self.cfg.head_dim, device=self.device, generator=g).to(torch.bfloat16)
             v[:batch, :length] = torch.randn(batch, length, self.hkv, self.cfg.head_dim, device=self.device, generator=g).to(torch.bfloat16)
 
+    @traced("tdx.prefill")
     def prefill(self, token_ids: torch.Tensor, seq_index: int = 0) -> torch.Tensor:
         """Run one prompt ``[S]`` through all layers, filling row ``seq_index`` of the KV cache.
 

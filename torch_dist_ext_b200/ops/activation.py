@@ -6,8 +6,10 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 
 
+@traced("tdx.silu_mul")
 def silu_mul(gate_up: torch.Tensor, quant_block128: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """``gate_up`` is ``[..., 2 * inter]`` with the gate in the first half. Returns ``(out, scales)``."""
     inter = gate_up.shape[-1] // 2

@@ -7,6 +7,7 @@ from typing import Optional
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 
 _scratch = {}
 
@@ -27,6 +28,7 @@ def pick_splits(batch: int, kv_heads: int, max_len: int, sms: int = 148) -> int:
     return max(1, min(want, (max_len + 127) // 128))
 
 
+@traced("tdx.decode_attention")
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: torch.Tensor,
                      max_len: int, out: Optional[torch.Tensor] = None, nsplit: Optional[int] = None) -> torch.Tensor:
     """``q [B, Hq, 128]``, caches ``[B, S_max, Hkv, 128]``, ``seq_lens`` int32 ``[B]`` -> ``[B, Hq, 128]``.

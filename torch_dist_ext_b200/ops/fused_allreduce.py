@@ -12,6 +12,7 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 from ..parallel import comm as _comm
 from ..utils.config import ALGO_CODES, OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME, config
 from . import reference as _ref
@@ -37,6 +38,7 @@ def _cpu_path(allreduce_in, residual_in, rms_gamma, eps, out_mode, scatter_only)
     return norm, res, scale
 
 
+@traced("tdx.fused_allreduce_rms")
 def fused_allreduce_rms(allreduce_in: torch.Tensor, residual_in: Optional[torch.Tensor], rms_gamma: torch.Tensor,
                         eps: float, workspace: Optional[torch.Tensor] = None, *, out_mode: int = OUT_SAME,
                         algo=None, scatter_only: bool = False, want_residual: bool = True,
@@ -73,6 +75,7 @@ def fused_allreduce_rms(allreduce_in: torch.Tensor, residual_in: Optional[torch.
     return norm_out, residual_out, scales
 
 
+@traced("tdx.allreduce_rms_pinned")
 def allreduce_rms_pinned(allreduce_in: torch.Tensor, residual_in: Optional[torch.Tensor], rms_gamma: torch.Tensor,
                          eps: float, *, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, algo=None,
                          ) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -15,6 +15,7 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 from ..parallel import comm as _comm
 from ..utils.config import OUT_FP8_BLOCK128, OUT_SAME
 from . import gemm as _gemm
@@ -28,6 +29,7 @@ def _fits(tokens: int, rows: int) -> bool:
     return ((rows + 127) // 128) * ((tokens + bn - 1) // bn) <= _SM_COUNT
 
 
+@traced("tdx.gemm_allreduce_rms")
 def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor], gamma: torch.Tensor,
                        eps: float, *, out_mode: int = OUT_SAME, scatter_only: bool = False,
                        want_residual: bool = True, force_unfused: bool = False, splits: int = 0,
@@ -57,6 +59,7 @@ def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torc
     return norm, res_out, scales
 
 
+@traced("tdx.allgather_gemm")
 def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, tokens: int, *, force_unfused: bool = False) -> torch.Tensor:
     """``gather(x_shard) @ w.T`` where rank r holds the rows ``r::world`` of the ``[tokens, K]`` input."""
     c = _comm.get_comm()

@@ -15,6 +15,7 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 
 _SM_COUNT = 148
 _ws = {}
@@ -59,6 +60,7 @@ def plan(m: int, n: int, k: int, elem_size: int = 2, scaled: bool = False) -> Tu
     return swap, bn, splits
 
 
+@traced("tdx.linear")
 def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *, out_dtype=None,
            swap: Optional[bool] = None, block_n: int = 0, splits: Optional[int] = None) -> torch.Tensor:
     """``a [M, K] @ w [N, K]^T -> [M, N]`` (bf16 / fp16 / e4m3 operands, fp32 accumulation)."""
@@ -81,6 +83,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     return out
 
 
+@traced("tdx.linear_fp8_blockscaled")
 def linear_fp8_blockscaled(a_q: torch.Tensor, a_scale: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor,
                            out: Optional[torch.Tensor] = None, *, out_dtype=torch.bfloat16,
                            splits: Optional[int] = None) -> torch.Tensor:

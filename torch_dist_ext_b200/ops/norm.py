@@ -10,9 +10,11 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 from ..utils.config import OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME
 
 
+@traced("tdx.fused_add_rmsnorm")
 def fused_add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], gamma: torch.Tensor, eps: float,
                       out_mode: int = OUT_SAME, want_residual: bool = True,
                       ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:

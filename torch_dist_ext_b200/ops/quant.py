@@ -6,8 +6,10 @@ from typing import Tuple
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 
 
+@traced("tdx.quant_fp8")
 def quant_fp8(x: torch.Tensor, block_scaled: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Returns ``(q, scales)`` with ``x ~= q.float() * scales`` (scales ``[rows, 1]`` or ``[rows, cols/128]``)."""
     cols = x.shape[-1]

@@ -4,6 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
+from ..utils.tracing import traced
 
 
 def build_cos_sin_cache(max_pos: int, dim: int, theta: float = 5e5, device="cuda") -> torch.Tensor:
@@ -13,11 +14,13 @@ def build_cos_sin_cache(max_pos: int, dim: int, theta: float = 5e5, device="cuda
     return torch.cat([ang.cos(), ang.sin()], dim=-1).float().to(device).contiguous()
 
 
+@traced("tdx.rope_")
 def rope_(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, cos_sin_cache: torch.Tensor) -> None:
     """Rotate ``q`` ``[tokens, q_heads, dim]`` and ``k`` ``[tokens, k_heads, dim]`` in place."""
     _lib.ops().rope_(q, k, positions, cos_sin_cache)
 
 
+@traced("tdx.rope_append_kv_")
 def rope_append_kv_(q, k, v, positions, cos_sin_cache, k_cache, v_cache) -> None:
     """Decode step: rotate ``q``/``k`` in place and append the rotated key row and the value row of
     token ``t`` to ``k_cache``/``v_cache`` ``[B, S, k_heads, dim]`` at ``[t, positions[t]]`` - one kernel."""

@@ -13,6 +13,8 @@ environment:
 ``TDX_NVLS``           ``0`` disables the NVSwitch-multicast mapping and kernels
 ``TDX_WAVES``          pipeline depth (1..4) of the flag-synchronised two-shot paths (default 1)
 ``TDX_LOG``            Python logging level of the package logger
+``TDX_NVTX``           ``1`` opens an NVTX range around every public op and decoder layer
+                       (read by ``utils/tracing.py``)
 ``TDX_POLICY_JSON``    path of a measured crossover table to load at ``setup_env``
 =====================  ============================================================
 """
