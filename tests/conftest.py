@@ -11,8 +11,16 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "multigpu: needs two or more CUDA devices")
 
 
+# Run order: in-process kernel tests first, then the files that start child processes on the GPU or
+# work on page-locked host memory, then the allocation-free entry point (its file must come last).
+_LATE = ("test_multigpu.py", "test_cpp_harness_gpu.py", "test_zero_copy_io_gpu.py", "test_checked_build_gpu.py",
+         "test_zz_no_alloc.py")
+
+
 def pytest_collection_modifyitems(config, items):
     import torch
+
+    items.sort(key=lambda it: _LATE.index(it.fspath.basename) + 1 if it.fspath.basename in _LATE else 0)
 
     if torch.cuda.is_available():
         return

@@ -11,6 +11,7 @@ Usage::
 
     python -m torch_dist_ext_b200._build            # build if out of date
     python -m torch_dist_ext_b200._build --force    # rebuild everything
+    python -m torch_dist_ext_b200._build --bounds   # also the range-checking flavour (TDX_BOUNDS=1 loads it)
 """
 from __future__ import annotations
 
@@ -24,6 +25,10 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 BUILD_DIR = PKG_DIR.parent / "build" / "tdx"
 LIB_PATH = PKG_DIR / "_C.so"
+# Checked flavour: the fused all-reduce kernels and their launcher compiled with -DTDX_BOUNDS (every
+# store into a symmetric allocation is range-checked, see csrc/include/tdx/sync.cuh), everything else
+# shared with the release library. Loaded instead of _C.so when TDX_BOUNDS=1.
+CHECKED_LIB_PATH = PKG_DIR / "_C_bounds.so"
 UNIT_TEST_SRC = PKG_DIR.parent / "tests" / "cpp" / "unit_test.cu"
 UNIT_TEST_BIN = PKG_DIR.parent / "tests" / "cpp" / "unit_test.bin"
 
@@ -125,6 +130,17 @@ def write_ninja() -> Path:
         f"-Wl,-rpath,{torch_lib}", "-Wl,--no-as-needed",
     ]
     lines += [f"build {LIB_PATH}: link {' '.join(objs)}", f"  ldflags = {' '.join(ld)}"]
+    checked_objs = []
+    for obj in objs:
+        if obj.startswith("ar_inst_") or obj == "ar_fusion_launch.host.o":
+            checked_objs.append(obj.replace(".o", ".bounds.o", 1) if obj.startswith("ar_inst_") else "ar_fusion_launch.bounds.host.o")
+        else:
+            checked_objs.append(obj)
+    for src, stem, defs in _device_units():
+        if stem.startswith("ar_inst_"):
+            lines += [f"build {stem}.bounds.o: nvcc {CSRC / src}", f"  defs = {' '.join(defs)} -DTDX_BOUNDS"]
+    lines += [f"build ar_fusion_launch.bounds.host.o: cxx {CSRC / 'ar_fusion_launch.cpp'}", "  extra = -DTDX_BOUNDS"]
+    lines += [f"build {CHECKED_LIB_PATH}: link {' '.join(checked_objs)}", f"  ldflags = {' '.join(ld)}"]
     # Standalone C++ harness (no PyTorch): the kernels, the launcher and the workspace manager only.
     core = [o for o in objs if o.startswith("ar_inst_") or o in ("workspace.o", "ar_fusion_launch.host.o", "fd_channel.host.o")]
     lines += [
@@ -144,13 +160,16 @@ def write_ninja() -> Path:
     return path
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile (if needed) and return the path of the extension library."""
+def build(force: bool = False, verbose: bool = False, checked: bool = False) -> Path:
+    """Compile (if needed) and return the path of the extension library. ``checked`` also builds the
+    range-checking flavour ``_C_bounds.so``."""
     write_ninja()
     if force:
         subprocess.run(["ninja", "-C", str(BUILD_DIR), "-t", "clean"], check=False,
                        stdout=subprocess.DEVNULL)
     cmd = ["ninja", "-C", str(BUILD_DIR)] + (["-v"] if verbose else [])
+    if checked:
+        cmd += [str(LIB_PATH), str(UNIT_TEST_BIN), str(CHECKED_LIB_PATH)]
     jobs = os.environ.get("TDX_BUILD_JOBS")
     if jobs:
         cmd += ["-j", jobs]
@@ -159,18 +178,19 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError("native build failed:\n" + res.stdout[-8000:])
     if verbose:
         print(res.stdout)
-    return LIB_PATH
+    return CHECKED_LIB_PATH if checked else LIB_PATH
 
 
 def clean() -> None:
     """Remove build products (what the reference's `setup.py clean` does via .gitignore parsing)."""
     shutil.rmtree(BUILD_DIR, ignore_errors=True)
-    if LIB_PATH.exists():
-        LIB_PATH.unlink()
+    for lib in (LIB_PATH, CHECKED_LIB_PATH):
+        if lib.exists():
+            lib.unlink()
 
 
 if __name__ == "__main__":
     if "--clean" in sys.argv:
         clean()
     else:
-        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--bounds" in sys.argv))

@@ -15,7 +15,11 @@ import torch
 
 log = logging.getLogger("torch_dist_ext_b200")
 
-_LIB = Path(__file__).resolve().parent / "_C.so"
+# TDX_BOUNDS=1 selects the range-checking flavour (built by `python -m torch_dist_ext_b200._build --bounds`):
+# same ops, but every store of the fused all-reduce kernels into a symmetric allocation is checked
+# against the allocation's extent and a violation becomes a status code instead of a stray write.
+_CHECKED = os.environ.get("TDX_BOUNDS", "0") not in ("0", "", "false", "off")
+_LIB = Path(__file__).resolve().parent / ("_C_bounds.so" if _CHECKED else "_C.so")
 _loaded = False
 
 
@@ -32,7 +36,7 @@ def load() -> None:
         from . import _build
 
         log.info("building native extension (first use)")
-        _build.build()
+        _build.build(checked=_CHECKED)
     try:
         torch.ops.load_library(str(_LIB))
     except OSError as e:  # pragma: no cover - depends on the machine

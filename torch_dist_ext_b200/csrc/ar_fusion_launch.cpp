@@ -16,6 +16,14 @@
 
 namespace tdx {
 
+bool bounds_checked_build() {
+#ifdef TDX_BOUNDS
+  return true;
+#else
+  return false;
+#endif
+}
+
 Policy& policy() {
   static Policy pol = [] {
     Policy q{};

@@ -32,6 +32,9 @@ struct Policy {
 };
 Policy& policy();
 
+// True in the library flavour compiled with -DTDX_BOUNDS (range-checked stores into symmetric memory).
+bool bounds_checked_build();
+
 // Validates shapes, alignment and capacity, resolves kAlgoAuto and sizes the launch.
 // Returns an empty string on success, else the reason.
 std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan);
@@ -115,6 +118,9 @@ class Workspace {
   bool has_multicast() const { return table_host_.mc_base != nullptr; }
   const std::string& multicast_note() const { return mc_note_; }
   void set_timeout_ns(uint64_t t) { timeout_ns_ = t; }
+  // Checked build only: pretend the allocation ends after `bytes` (0 = its real size), so that a test can
+  // watch a store that leaves the extent being recorded and redirected.
+  void set_debug_extent(uint64_t bytes) { debug_extent_ = bytes; }
   uint64_t timeout_ns() const { return timeout_ns_; }
   int rank() const { return rank_; }
   int world_size() const { return world_; }
@@ -136,6 +142,7 @@ class Workspace {
   uint32_t* host_status_ = nullptr;   // pinned + mapped
   uint32_t* host_status_dev_ = nullptr;
   uint64_t timeout_ns_;
+  uint64_t debug_extent_ = 0;
   bool registered_ = false;
   struct Vmm;                // virtual-memory / multicast state (workspace.cu)
   Vmm* vmm_ = nullptr;

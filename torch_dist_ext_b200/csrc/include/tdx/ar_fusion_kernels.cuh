@@ -276,7 +276,7 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
 #pragma unroll
       for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
         if (r >= nranks || r == p.rank) continue;
-        ptx::st_v4(lamport_buf(p.peer[r], p.layout, epoch % 3u) + (size_t)p.rank * msg_bytes + off, val);
+        ptx::st_v4(symm(p, r, p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes + (size_t)p.rank * msg_bytes + off), val);
       }
     }
   }
@@ -371,14 +371,13 @@ __device__ __forceinline__ void twoshot_scatter(const ArParams& p, const RowView
     for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
       const int row = j * nranks + r;
       if (r >= nranks || r == p.rank || row >= p.tokens) continue;
-      char* dst = static_cast<char*>(p.peer[r]) + area_off +
-                  ((size_t)p.rank * g.groups + j) * rv.row_bytes;
+      const size_t dst_off = area_off + ((size_t)p.rank * g.groups + j) * rv.row_bytes;
 #pragma unroll
       for (int v = 0; v < kVpt; ++v) {
         if (!rv.active(v)) continue;
         uint4 val = ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16);
         if (kScrub) val = scrub(val);
-        ptx::st_v4(dst + (size_t)rv.vec_index(v) * 16, val);
+        ptx::st_v4(symm(p, r, dst_off + (size_t)rv.vec_index(v) * 16), val);
       }
     }
   }
@@ -394,12 +393,12 @@ __device__ __forceinline__ void twoshot_scatter_rows(const ArParams& p, const Ro
   for (int row = blockIdx.x; row < p.tokens; row += gridDim.x) {
     const int r = row % nranks, j = row / nranks;
     if (r == p.rank) continue;
-    char* dst = static_cast<char*>(p.peer[r]) + area_off + ((size_t)p.rank * g.groups + j) * rv.row_bytes;
+    const size_t dst_off = area_off + ((size_t)p.rank * g.groups + j) * rv.row_bytes;
 #pragma unroll
     for (int v = 0; v < kVpt; ++v) {
       if (!rv.active(v)) continue;
       const uint4 val = scrub(ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16));
-      ptx::st_v4(dst + (size_t)rv.vec_index(v) * 16, val);
+      ptx::st_v4(symm(p, r, dst_off + (size_t)rv.vec_index(v) * 16), val);
     }
   }
 }
@@ -484,7 +483,7 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
 #pragma unroll
         for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
           if (r >= nranks || r == p.rank) continue;
-          ptx::st_v4(static_cast<char*>(p.peer[r]) + result_off + (size_t)row * g.result_stride + voff, packed[v]);
+          ptx::st_v4(symm(p, r, result_off + (size_t)row * g.result_stride + voff), packed[v]);
         }
       }
     }
@@ -493,7 +492,7 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
     parity ^= 1;
     if (gather_back && threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
       const uint4 trailer = make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u);
-      ptx::st_v4(static_cast<char*>(p.peer[threadIdx.x]) + result_off + (size_t)row * g.result_stride + rv.row_bytes, trailer);
+      ptx::st_v4(symm(p, threadIdx.x, result_off + (size_t)row * g.result_stride + rv.row_bytes), trailer);
     }
   }
 
@@ -604,13 +603,14 @@ __device__ __forceinline__ void twoshot_flag_body(const ArParams& p) {
         const int row = j * nranks + r;
         if (r >= nranks || row >= p.tokens) continue;
         if (!kNvls && r == p.rank) continue;
-        char* dst = kNvls ? self + stage_off + (size_t)row * rv.row_bytes
-                          : static_cast<char*>(p.peer[r]) + stage_off + ((size_t)p.rank * g.groups + j) * rv.row_bytes;
+        const int dst_rank = kNvls ? p.rank : r;
+        const size_t dst_off = kNvls ? stage_off + (size_t)row * rv.row_bytes
+                                     : stage_off + ((size_t)p.rank * g.groups + j) * rv.row_bytes;
 #pragma unroll
         for (int v = 0; v < kVpt; ++v) {
           if (!rv.active(v)) continue;
           const size_t voff = (size_t)rv.vec_index(v) * 16;
-          ptx::st_v4(dst + voff, ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff));
+          ptx::st_v4(symm(p, dst_rank, dst_off + voff), ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff));
         }
       }
     }
@@ -673,7 +673,7 @@ __device__ __forceinline__ void twoshot_flag_body(const ArParams& p) {
 #pragma unroll
             for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
               if (r >= nranks || r == p.rank) continue;
-              ptx::st_v4(static_cast<char*>(p.peer[r]) + result_off + (size_t)row * rv.row_bytes + voff, packed);
+              ptx::st_v4(symm(p, r, result_off + (size_t)row * rv.row_bytes + voff), packed);
             }
           }
         }
@@ -687,7 +687,7 @@ __device__ __forceinline__ void twoshot_flag_body(const ArParams& p) {
           if (threadIdx.x == 0)
             ptx::multimem_st_v4(static_cast<char*>(p.mc_base) + result_off + g.trailer_off + (size_t)row * 16, trailer);
         } else if (threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
-          ptx::st_v4(static_cast<char*>(p.peer[threadIdx.x]) + result_off + g.trailer_off + (size_t)row * 16, trailer);
+          ptx::st_v4(symm(p, threadIdx.x, result_off + g.trailer_off + (size_t)row * 16), trailer);
         }
       }
     }

@@ -23,6 +23,7 @@ class CommWorkspace : public torch::CustomClassHolder {
   void disable_multicast();
   std::string multicast_note();
   void set_timeout_ms(int64_t ms);
+  void set_debug_extent(int64_t bytes);
   int64_t errors_seen();
   std::vector<int64_t> stats();
   tdx::Workspace* impl() { return impl_.get(); }

@@ -95,6 +95,7 @@ enum Status : uint32_t {
   kTimeoutNvls = 4,
   kTimeoutGemmPipeline = 5,    // an mbarrier of a GEMM pipeline never completed
   kTimeoutTileFlag = 6,        // all-gather->GEMM: a peer tile never became ready
+  kBoundsViolation = 7,        // checked build: an address left the symmetric allocation (access redirected)
 };
 
 // ---- op description ------------------------------------------------------------
@@ -138,6 +139,7 @@ struct ArParams {
   int32_t waves;            // flag-synchronised two-shot paths: pipeline depth (1..4), 0 = 1
   uint64_t timeout_ns;      // budget of every device-side wait
   uint32_t* host_status;    // pinned, host-mapped mirror of Control::status (or null)
+  uint64_t debug_extent;    // checked build (-DTDX_BOUNDS): extent to check against; 0 = layout.total_bytes
 };
 
 }  // namespace tdx

@@ -98,6 +98,31 @@ __device__ __forceinline__ void report_error(Control* ctl, uint32_t* host_status
   }
 }
 
+// ---- addresses inside a symmetric allocation -----------------------------------------
+// symm(p, r, off): address of the 16-byte vector at byte offset `off` of rank r's allocation; every
+// store into a peer's memory takes its address from here. Built with -DTDX_BOUNDS (the checked build,
+// which stands in for a memory checker that cannot see peer mappings), the range is first compared with
+// the allocation's extent: a range that leaves it is recorded once as {kBoundsViolation, rank, r, 0,
+// block, off / 1024} and the access goes to a scratch slot in the upper half of this rank's own control
+// block instead, so that a wrong offset shows up as a status code and invalid outputs, never as a
+// write into memory it does not own. The release build compiles to the pointer arithmetic alone.
+constexpr size_t kBoundsScratchOffset = 2048;
+static_assert(sizeof(Control) <= kBoundsScratchOffset, "scratch slots overlap the control fields");
+
+__device__ __forceinline__ char* symm(const ArParams& p, int r, size_t off) {
+#ifdef TDX_BOUNDS
+  constexpr size_t bytes = 16;   // every access through here is one 16-byte vector (or a 4-byte flag)
+  const uint64_t extent = p.debug_extent ? p.debug_extent : p.layout.total_bytes;
+  if ((uint64_t)off + bytes > extent || r < 0 || r >= p.nranks) {
+    char* self = static_cast<char*>(p.peer[p.rank]);
+    report_error(reinterpret_cast<Control*>(self + p.layout.off_control), p.host_status, kBoundsViolation, p.rank, r, 0,
+                 (int)(off >> 10));
+    return self + p.layout.off_control + kBoundsScratchOffset + (size_t)(threadIdx.x & 63) * 16;
+  }
+#endif
+  return static_cast<char*>(p.peer[r]) + off;
+}
+
 // ---- cross-GPU flag barrier ---------------------------------------------------------
 // flags[block][src_rank] on every rank. Thread t < nranks of block b publishes `target`
 // into rank t's flags[b][my_rank], then waits for its own flags[b][t] to reach `target`.
@@ -113,7 +138,10 @@ __device__ __forceinline__ uint32_t* flag_ptr(void* base, const Layout& l, int p
 __device__ __forceinline__ void flag_signal(const ArParams& p, int plane, uint32_t target) {
   __syncthreads();
   if ((int)threadIdx.x < p.nranks)
-    ptx::st_release_sys(flag_ptr(p.peer[threadIdx.x], p.layout, plane, blockIdx.x, p.rank), target);
+    ptx::st_release_sys(reinterpret_cast<uint32_t*>(symm(
+                            p, threadIdx.x,
+                            p.layout.off_flags + (((size_t)plane * kMaxBarrierBlocks + blockIdx.x) * kMaxRanks + p.rank) * sizeof(uint32_t))),
+                        target);
 }
 
 // Wait (bounded) until every peer has published at least `target` for this block index.

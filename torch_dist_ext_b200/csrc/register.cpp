@@ -87,6 +87,7 @@ bool CommWorkspace::has_multicast() { return impl_->has_multicast(); }
 void CommWorkspace::disable_multicast() { impl_->disable_multicast(); }
 std::string CommWorkspace::multicast_note() { return impl_->multicast_note(); }
 void CommWorkspace::set_timeout_ms(int64_t ms) { impl_->set_timeout_ns((uint64_t)ms * 1000000ull); }
+void CommWorkspace::set_debug_extent(int64_t bytes) { impl_->set_debug_extent((uint64_t)bytes); }
 int64_t CommWorkspace::errors_seen() { return impl_->errors_seen(); }
 
 std::vector<int64_t> CommWorkspace::stats() {
@@ -302,6 +303,7 @@ TORCH_LIBRARY(torch_dist_ext, m) {
       .def("get_workspace", &CommWorkspace::get_workspace)
       .def("reset", &CommWorkspace::reset)
       .def("set_timeout_ms", &CommWorkspace::set_timeout_ms)
+      .def("set_debug_extent", &CommWorkspace::set_debug_extent)
       .def("errors_seen", &CommWorkspace::errors_seen)
       .def("stats", &CommWorkspace::stats)
       .def("has_multicast", &CommWorkspace::has_multicast)
@@ -309,6 +311,7 @@ TORCH_LIBRARY(torch_dist_ext, m) {
       .def("multicast_note", &CommWorkspace::multicast_note);
   m.def("create_workspace(int rank, int world_size, int nblocks, int size_in_bytes, int lamport_bytes, int device, "
         "int multicast) -> __torch__.torch.classes.torch_dist_ext.CommWorkspace", &tdx_torch::create_workspace);
+  m.def("bounds_checked_build() -> bool", []() -> bool { return tdx::bounds_checked_build(); });
   m.def("table_nbytes() -> int", []() -> int64_t { return (int64_t)sizeof(tdx::CommTable); });
   m.def("connect_local(__torch__.torch.classes.torch_dist_ext.CommWorkspace[] workspaces) -> ()", &tdx_torch::connect_local);
   m.def(
