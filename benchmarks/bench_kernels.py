@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Single-GPU roofline table of the library's kernels (no communication).
 
-    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_fp8|attention|elementwise|all] [--steps 30]
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_fp8|attention|elementwise|all] [--steps 30]
 
 Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
 over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
@@ -60,7 +60,7 @@ def row(name, us, lib_us, nbytes, flops, hbm, tf, src):
             "TFLOP/s": round(tfl, 1), f"frac_bf16_of_{src}": round(tfl / tf, 3)}
 
 
-def gemm_cases(dev, steps, shapes, ms, out):
+def gemm_cases(dev, steps, shapes, ms, out, cta_pair=False):
     from torch_dist_ext_b200.ops import gemm
 
     hbm, tf, src = peaks()
@@ -68,10 +68,15 @@ def gemm_cases(dev, steps, shapes, ms, out):
         ws = rotating(lambda: torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02, n * k * 2)
         for m in ms:
             a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
-            us = time_us(lambda i: gemm.linear(a, ws[i]), len(ws), steps)
+            if cta_pair:   # a new kernel: check it before timing it
+                err = (gemm.linear(a, ws[0], cta_pair=True).float() - gemm.linear(a, ws[0], cta_pair=False).float()).abs().max().item()
+                if err > 0.05 or gemm.pipeline_status() != 0:
+                    raise SystemExit(f"two-CTA GEMM disagrees with the one-CTA kernel (max err {err}, status {gemm.pipeline_status()})")
+            us = time_us(lambda i: gemm.linear(a, ws[i], cta_pair=cta_pair), len(ws), steps)
             lib = time_us(lambda i: torch.matmul(a, ws[i].t()), len(ws), steps)
             nbytes = (n * k + m * k + m * n) * 2
-            out.append(row(f"gemm bf16 m={m} n={n} k={k}", us, lib, nbytes, 2.0 * m * n * k, hbm, tf, src))
+            tag = "gemm bf16 (CTA pairs)" if cta_pair else "gemm bf16"
+            out.append(row(f"{tag} m={m} n={n} k={k}", us, lib, nbytes, 2.0 * m * n * k, hbm, tf, src))
             print(out[-1], flush=True)
         del ws
         torch.cuda.empty_cache()
@@ -171,6 +176,8 @@ def main():
         gemm_cases(dev, args.steps, [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)], (1, 16, 64), out)
     if g in ("gemm_prefill", "all"):
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out)
+    if g == "gemm_pair":            # opt-in kernel: 256 x 256 tiles on CTA pairs (not part of "all")
+        gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out, cta_pair=True)
     if g in ("gemm_fp8", "all"):
         gemm_fp8_cases(dev, args.steps, out)
     if g in ("attention", "all"):

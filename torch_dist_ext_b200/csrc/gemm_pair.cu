@@ -1,0 +1,298 @@
+// Two-SM tcgen05 GEMM for prefill-sized problems:  D[x, y] = sum_k X[x, k] * Y[y, k], both K-major.
+//
+// A cluster of two CTAs (a "pair") computes one 256 x 256 tile with tcgen05.mma.cta_group::2:
+// CTA r of the pair loads rows [128 r, 128 r + 128) of the X tile and rows [128 r, 128 r + 128) of the
+// 256-row Y tile - each CTA fetches only its own half, with ordinary TMA copies - and the leader
+// (r = 0) issues the MMAs, which read both CTAs' shared memory. Compared with two independent
+// 128 x 256 tiles, every SM stages half as much of Y per K block (32 KB instead of 48 KB per stage),
+// so the operand ring is deeper and the shared-memory traffic per FLOP lower. The accumulator is
+// split by rows: rows 0-127 in the leader's tensor memory, rows 128-255 in the peer's; each CTA's
+// epilogue warps read their own half with tcgen05.ld and store it.
+//
+// Synchronisation (all waits bounded):
+//  * full[s]   leader only: armed by the leader's producer for the bytes of BOTH CTAs; the peer's
+//              copies credit the leader's barrier (address translated with mapa).
+//  * empty[s]  one per CTA: the leader's MMA thread commits to both with one tcgen05.commit.
+//  * acc_full  one per CTA, committed the same way after the last K block.
+//  * cluster barriers after barrier initialisation (no remote arrival before the target exists)
+//    and before tensor memory is freed (no CTA leaves while its peer may still read its shared
+//    memory or write its barriers).
+// A wait that runs out records a status word, raises the abort flag of both CTAs and falls through
+// to the common exit, where in-flight copies are given time to land and tensor memory is freed.
+//
+// Opt-in (ops/gemm.py: linear(..., cta_pair=True) or TDX_GEMM_PAIR=1) for bf16 / fp16 / unscaled e4m3
+// operands. The reference (xytpai/torch_dist_ext) has no GEMM.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <mutex>
+#include <string>
+#include "tdx/comm.h"
+#include "tdx/gemm.h"
+#include "tdx/tc.cuh"
+
+namespace tdx {
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kRowsPerCta = 128;                 // X rows and Y rows staged by one CTA
+constexpr int kTileM = 2 * kRowsPerCta;          // rows of the pair's output tile
+constexpr int kTileN = 2 * kRowsPerCta;          // columns of the pair's output tile (MMA N)
+constexpr int kStages = 6;
+constexpr int kOperandBytes = kRowsPerCta * 128; // 128 rows x one 128-byte swizzle span
+constexpr int kStageBytes = 2 * kOperandBytes;   // X half + Y half
+constexpr int kBarrierOffset = kStages * kStageBytes;
+constexpr int kSmemTotal = kBarrierOffset + 1024 /* barriers */ + 1024 /* alignment slack */;
+constexpr uint32_t kTmemCols = kTileN;           // fp32 accumulator columns
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+struct PairArgs {
+  int x_rows, y_rows, kblocks;
+  void* out;
+  int64_t sx, sy;
+  int out_dtype;
+  uint32_t idesc;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void store_one(const PairArgs& a, int64_t idx, float v) {
+  if (a.out_dtype == kBF16) static_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16(v);
+  else if (a.out_dtype == kF16) static_cast<__half*>(a.out)[idx] = __float2half(v);
+  else static_cast<float*>(a.out)[idx] = v;
+}
+
+// 16 consecutive y columns of row x.
+__device__ __forceinline__ void store_chunk(const PairArgs& a, int x, int y0, const float (&v)[16]) {
+  if (x >= a.x_rows) return;
+  if (a.sy == 1 && a.out_dtype != kF32 && y0 + 16 <= a.y_rows && ((a.sx * 2) % 16 == 0) &&
+      (reinterpret_cast<uintptr_t>(a.out) % 16 == 0)) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (a.out_dtype == kBF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(a.out) + ((int64_t)x * a.sx + y0) * 2);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (y0 + i < a.y_rows) store_one(a, (int64_t)x * a.sx + (int64_t)(y0 + i) * a.sy, v[i]);
+  }
+}
+
+template <bool kFp8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const PairArgs a) {
+  constexpr int kElemsPerBlock = kFp8 ? 128 : 64;   // K elements in one 128-byte span
+
+  // identical carve-up in both CTAs: descriptors, barriers and the TMEM slot sit at the same offsets
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kBarrierOffset);
+  uint64_t* empty = full + kStages;
+  uint64_t* acc_full = empty + kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_ctarank();      // 0: leader, 1: peer
+  const uint32_t leader = rank & ~1u, other = rank ^ 1u;
+  const int tile_m = blockIdx.x >> 1, tile_n = blockIdx.y;
+  const int nkb = a.kblocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&full[s], 1);
+      tc::mbar_init(&empty[s], 1);
+    }
+    tc::mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_x);
+    tc::tma_prefetch_desc(&map_y);
+  }
+  __syncthreads();
+  tc::cluster_arrive();
+  tc::cluster_wait();          // both CTAs' barriers exist before anyone arrives on them remotely
+  if (warp == 1) {
+    tc::tmem_alloc_pair(tmem_slot, kTmemCols);
+    tc::tmem_relinquish_pair();
+  }
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // a role that gives up tells the whole pair, so that the other roles stop early too
+  auto fail = [&]() {
+    *abort_flag = 1;
+    tc::st_cluster_u32(tc::map_to_cta(tc::smem_u32(const_cast<uint32_t*>(abort_flag)), other), 1u);
+    if (a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer (both CTAs): own halves of X and Y, bytes credited to the leader's barrier ----
+      const uint32_t leader_full = tc::map_to_cta(tc::smem_u32(&full[0]), leader);
+      const int x_row0 = tile_m * kTileM + (int)(rank & 1u) * kRowsPerCta;
+      const int y_row0 = tile_n * kTileN + (int)(rank & 1u) * kRowsPerCta;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % kStages;
+        if (i >= kStages && !tc::mbar_wait(&empty[s], ((i / kStages) - 1) & 1, kWaitLimit, abort_flag)) {
+          fail();
+          break;
+        }
+        if (rank == leader) tc::mbar_arrive_expect_tx(&full[s], 2 * kStageBytes);
+        const uint32_t dst = tc::smem_u32(smem + s * kStageBytes);
+        const uint32_t bar = leader_full + (uint32_t)s * 8u;
+        tc::tma_load_2d_pair(dst, &map_x, bar, i * kElemsPerBlock, x_row0);
+        tc::tma_load_2d_pair(dst + kOperandBytes, &map_y, bar, i * kElemsPerBlock, y_row0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == leader) {
+      // ---- MMA issue (leader only) ----
+      const uint16_t pair_mask = (uint16_t)(3u << leader);
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % kStages;
+        if (!tc::mbar_wait(&full[s], (i / kStages) & 1, kWaitLimit, abort_flag)) {
+          fail();
+          ok = false;
+          break;
+        }
+        tc::fence_after_thread_sync();
+        const uint32_t xa = tc::smem_u32(smem + s * kStageBytes);
+        const uint64_t dx = tc::make_smem_desc_sw128(xa);
+        const uint64_t dy = tc::make_smem_desc_sw128(xa + kOperandBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // 32 bytes of K per instruction, stepped inside the swizzle span
+          tc::umma_pair<kFp8>(tmem_base, dx + (uint64_t)(k * 2), dy + (uint64_t)(k * 2), a.idesc, (i > 0 || k > 0) ? 1u : 0u);
+        tc::umma_commit_pair(&empty[s], pair_mask);   // the stage is free again in both CTAs
+      }
+      if (ok) tc::umma_commit_pair(acc_full, pair_mask);
+    }
+  } else {
+    // ---- epilogue (warps 2..5 of both CTAs): TMEM lane quarter = warp % 4 ----
+    const int q = warp & 3;
+    const int x = tile_m * kTileM + (int)(rank & 1u) * kRowsPerCta + q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int y_base = tile_n * kTileN;
+    const bool ok = nkb > 0 && tc::mbar_wait(acc_full, 0, kWaitLimit, abort_flag);
+    tc::fence_after_thread_sync();
+    if (ok) {
+#pragma unroll 4
+      for (int c = 0; c < kTileN; c += 16) {
+        float v[16];
+        tc::tmem_ld_16(lane_addr + c, v);
+        if (y_base + c < a.y_rows) store_chunk(a, x, y_base + c, v);
+      }
+    } else if (nkb > 0 && lane == 0 && q == 0) {
+      fail();
+    }
+  }
+
+  // ---- common exit ----
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);   // copies already issued land before shared memory goes away
+  }
+  tc::cluster_arrive();
+  tc::cluster_wait();
+  if (warp == 1) {
+    tc::fence_after_thread_sync();
+    tc::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major [rows, k] with row pitch ld (elements); box = one 128-byte span of K x 128 rows.
+std::string make_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t ld, int elem_size, int elem_kind) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
+  if (reinterpret_cast<uintptr_t>(ptr) % 16) return "GEMM operands must be 16-byte aligned";
+  if ((ld * elem_size) % 16) return "GEMM operand row pitch must be a multiple of 16 bytes";
+  const CUtensorMapDataType dt = elem_size == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : elem_kind == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)(ld * elem_size)};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_size), (cuuint32_t)kRowsPerCta};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled failed (CUresult " + std::to_string((int)r) + ")";
+  return "";
+}
+
+template <bool kFp8>
+std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const PairArgs& a, dim3 grid, cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<kFp8>;
+  static thread_local int last_dev = -1;
+  static thread_local cudaError_t attr_err = cudaSuccess;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {   // the attribute is per device
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    last_dev = dev;
+  }
+  if (attr_err != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(attr_err);
+  kern<<<grid, kThreads, kSmemTotal, stream>>>(mx, my, a);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
+}
+
+}  // namespace
+
+std::string gemm_tn_pair(const GemmProblem& g, cudaStream_t stream) {
+  const bool fp8 = g.elem_size == 1;
+  if (g.x_scale != nullptr || g.y_scale != nullptr) return "the two-CTA kernel takes unscaled operands";
+  const int epb = 128 / g.elem_size;
+  if (g.k <= 0 || g.k % epb) return "K must be a positive multiple of " + std::to_string(epb);
+  if (g.x_rows <= 0 || g.y_rows <= 0) return "";
+  PairArgs a{};
+  a.x_rows = g.x_rows;
+  a.y_rows = g.y_rows;
+  a.kblocks = g.k / epb;
+  a.out = g.out;
+  a.sx = g.sx;
+  a.sy = g.sy;
+  a.out_dtype = g.out_dtype;
+  a.idesc = fp8 ? tc::make_idesc(kTileM, kTileN, 0, 0)
+                : tc::make_idesc(kTileM, kTileN, g.elem_kind == kBF16 ? 1 : 0, g.elem_kind == kBF16 ? 1 : 0);
+  a.status = g.status;
+  CUtensorMap mx, my;
+  std::string err = make_map(&mx, g.x, g.x_rows, g.k, g.ldx, g.elem_size, g.elem_kind);
+  if (!err.empty()) return err;
+  err = make_map(&my, g.y, g.y_rows, g.k, g.ldy, g.elem_size, g.elem_kind);
+  if (!err.empty()) return err;
+  const dim3 grid(2 * ((g.x_rows + kTileM - 1) / kTileM), (g.y_rows + kTileN - 1) / kTileN, 1);
+  if (grid.y > 65535) return "too many column tiles for one launch";
+  return fp8 ? launch<true>(mx, my, a, grid, stream) : launch<false>(mx, my, a, grid, stream);
+}
+
+}  // namespace tdx

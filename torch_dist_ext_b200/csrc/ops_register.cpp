@@ -126,14 +126,11 @@ void rope_impl(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_si
 }
 
 // D[x, y] = sum_k X[x, k] * Y[y, k] written to out.flatten()[x * sx + y * sy] (tcgen05 GEMM).
-void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, int64_t block_n, int64_t splits,
-             const c10::optional<Tensor>& ws, const c10::optional<Tensor>& counters, const c10::optional<Tensor>& status,
-             const c10::optional<Tensor>& x_scale, const c10::optional<Tensor>& y_scale, bool x_scale_per_row,
-             bool y_scale_per_row) {
+static tdx::GemmProblem gemm_problem(const Tensor& x, const Tensor& y, Tensor& out, int64_t sx, int64_t sy,
+                                     const c10::optional<Tensor>& status) {
   TORCH_CHECK(x.is_cuda() && y.is_cuda() && out.is_cuda() && x.dim() == 2 && y.dim() == 2, "gemm_tn: 2-D CUDA operands expected");
   TORCH_CHECK(x.stride(1) == 1 && y.stride(1) == 1, "gemm_tn: operands must be K-major (unit stride along K)");
   TORCH_CHECK(x.size(1) == y.size(1) && x.scalar_type() == y.scalar_type(), "gemm_tn: operands disagree in K or dtype");
-  const c10::cuda::CUDAGuard guard(x.device());
   tdx::GemmProblem g{};
   g.x = x.data_ptr();
   g.y = y.data_ptr();
@@ -152,6 +149,16 @@ void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t s
   g.out_dtype = dtype_code(out);
   const int64_t max_idx = (g.x_rows - 1) * sx + (g.y_rows - 1) * sy;
   TORCH_CHECK(g.x_rows == 0 || g.y_rows == 0 || (max_idx < out.numel() && sx >= 1 && sy >= 1), "gemm_tn: output strides exceed the output tensor");
+  if (status.has_value() && status->defined()) g.status = reinterpret_cast<uint32_t*>(status->data_ptr<int>());
+  return g;
+}
+
+void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, int64_t block_n, int64_t splits,
+             const c10::optional<Tensor>& ws, const c10::optional<Tensor>& counters, const c10::optional<Tensor>& status,
+             const c10::optional<Tensor>& x_scale, const c10::optional<Tensor>& y_scale, bool x_scale_per_row,
+             bool y_scale_per_row) {
+  tdx::GemmProblem g = gemm_problem(x, y, out, sx, sy, status);
+  const c10::cuda::CUDAGuard guard(x.device());
   g.block_n = (int)block_n;
   g.splits = (int)splits;
   if (ws.has_value() && ws->defined()) {
@@ -161,7 +168,6 @@ void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t s
     g.counters = reinterpret_cast<uint32_t*>(counters->data_ptr<int>());
     g.counter_count = (size_t)counters->numel();
   }
-  if (status.has_value() && status->defined()) g.status = reinterpret_cast<uint32_t*>(status->data_ptr<int>());
   if (x_scale.has_value() && x_scale->defined()) {
     TORCH_CHECK(y_scale.has_value() && y_scale->defined(), "gemm_tn: both operands need scales");
     TORCH_CHECK(x_scale->scalar_type() == at::kFloat && y_scale->scalar_type() == at::kFloat && x_scale->is_contiguous() && y_scale->is_contiguous(), "gemm_tn: scales must be contiguous float32");
@@ -175,6 +181,14 @@ void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t s
   }
   const std::string err = tdx::gemm_tn(g, cur_stream());
   TORCH_CHECK(err.empty(), "gemm_tn: ", err);
+}
+
+// The same product on 256 x 256 tiles computed by CTA pairs (tcgen05.mma.cta_group::2).
+void gemm_tn_pair(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, const c10::optional<Tensor>& status) {
+  tdx::GemmProblem g = gemm_problem(x, y, out, sx, sy, status);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const std::string err = tdx::gemm_tn_pair(g, cur_stream());
+  TORCH_CHECK(err.empty(), "gemm_tn_pair: ", err);
 }
 
 void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor out,
@@ -299,6 +313,7 @@ void register_extra_ops(torch::Library& m) {
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
         "bool y_scale_per_row) -> ()", &gemm_tn);
+  m.def("gemm_tn_pair(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_pair);
   m.def("fused_add_rmsnorm(Tensor x, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
         "Tensor(c!)? scale_out, float eps, int out_mode) -> int", &fused_add_rmsnorm);
   m.def("quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) scales, bool block128) -> ()", &quant_fp8);

@@ -10,6 +10,7 @@ efficiency; K is split over CTAs until the grid covers the 148 SMs.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -19,6 +20,9 @@ from ..utils.tracing import traced
 
 _SM_COUNT = 148
 _ws = {}
+
+
+_PAIR_DEFAULT = os.environ.get("TDX_GEMM_PAIR", "0") not in ("0", "", "false", "off")
 
 
 def _workspace(device: torch.device):
@@ -62,11 +66,21 @@ def plan(m: int, n: int, k: int, elem_size: int = 2, scaled: bool = False) -> Tu
 
 @traced("tdx.linear")
 def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *, out_dtype=None,
-           swap: Optional[bool] = None, block_n: int = 0, splits: Optional[int] = None) -> torch.Tensor:
-    """``a [M, K] @ w [N, K]^T -> [M, N]`` (bf16 / fp16 / e4m3 operands, fp32 accumulation)."""
+           swap: Optional[bool] = None, block_n: int = 0, splits: Optional[int] = None,
+           cta_pair: Optional[bool] = None) -> torch.Tensor:
+    """``a [M, K] @ w [N, K]^T -> [M, N]`` (bf16 / fp16 / e4m3 operands, fp32 accumulation).
+
+    ``cta_pair=True`` runs prefill-sized problems (M, N >= 256) on 256 x 256 tiles computed by pairs of
+    CTAs (``tcgen05.mma.cta_group::2``); the default follows ``TDX_GEMM_PAIR`` (off)."""
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "linear: a [M, K], w [N, K]"
     m, k = a.shape
     n = w.shape[0]
+    if (_PAIR_DEFAULT if cta_pair is None else cta_pair) and m >= 256 and n >= 256 and not swap and splits in (None, 1):
+        if out is None:
+            dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
+            out = torch.empty(m, n, dtype=dt, device=a.device)
+        _lib.ops().gemm_tn_pair(a, w, out, n, 1, _workspace(a.device)[2])
+        return out
     p_swap, p_bn, p_splits = plan(m, n, k, a.element_size())
     swap = p_swap if swap is None else swap
     if block_n == 0:
