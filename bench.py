@@ -224,6 +224,10 @@ def _pinned_io_e2e(step, timed_e2e, outs, host_x, host_r, gamma, world, rank):
         print(f"bench: pinned-memory path unavailable ({type(e).__name__}: {e})", file=sys.stderr, flush=True)
         ok = False
     if not bool(common.min_over_ranks(1.0 if ok else 0.0, world)):
+        # a rank may have launched while another refused: bring flags, epochs and sentinels back in step
+        import torch_dist_ext_b200 as tdx
+
+        tdx.get_comm().reset()
         return None
     return timed_e2e(step)
 
