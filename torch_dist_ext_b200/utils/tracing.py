@@ -9,7 +9,6 @@ from __future__ import annotations
 
 import functools
 import os
-from contextlib import contextmanager
 
 _enabled = os.environ.get("TDX_NVTX", "0") not in ("0", "", "false", "off")
 _push = _pop = None
@@ -39,17 +38,35 @@ def set_backend(push, pop) -> None:
     _push, _pop = push, pop
 
 
-@contextmanager
-def nvtx_range(name: str):
-    if not _enabled:
-        yield
-        return
-    _bind()
-    _push(name)
-    try:
-        yield
-    finally:
+class _Range:
+    __slots__ = ("name",)
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        _bind()
+        _push(self.name)
+
+    def __exit__(self, *exc):
         _pop()
+        return False
+
+
+class _Off:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_OFF = _Off()
+
+
+def nvtx_range(name: str):
+    """Context manager: an NVTX range called ``name`` when tracing is on, nothing otherwise."""
+    return _Range(name) if _enabled else _OFF
 
 
 def traced(name: str):
