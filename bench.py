@@ -236,7 +236,7 @@ def _extras(tdx, rank, world, tokens, hidden, xs, rs, gamma, flusher, align, K, 
     """Own arm only: every algorithm, the fp8 epilogues, and NCCL + separate kernels."""
     import torch.distributed as dist
 
-    from torch_dist_ext_b200.utils.config import OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME
+    from torch_dist_ext_b200.utils.config import OUT_FP8_BLOCK128, OUT_FP8_TOKEN
 
     K = min(K, 100)
     res = {}

@@ -3,9 +3,9 @@ from __future__ import annotations
 
 import torch
 
-import torch_dist_ext_b200 as tdx
+import torch_dist_ext_b200  # noqa: F401  (loads the library)
 from torch_dist_ext_b200.ops import reference as ref
-from torch_dist_ext_b200.utils.config import ALGO_CODES, OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME
+from torch_dist_ext_b200.utils.config import ALGO_CODES, OUT_FP8_TOKEN, OUT_SAME
 
 TOL = {torch.float32: 2e-5, torch.float16: 4e-3, torch.bfloat16: 3.2e-2}
 

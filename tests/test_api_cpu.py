@@ -6,7 +6,7 @@ import torch
 
 import torch_dist_ext_b200 as tdx
 from torch_dist_ext_b200.ops import reference as ref
-from torch_dist_ext_b200.utils.config import ALGO_CODES, OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME, Config
+from torch_dist_ext_b200.utils.config import ALGO_CODES, OUT_FP8_BLOCK128, OUT_SAME, Config
 
 MB = 1 << 20
 

@@ -9,7 +9,6 @@ fp8 e4m3 per-token quantisation with fp32 scales [128, 1].
 import socket
 from datetime import timedelta
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp

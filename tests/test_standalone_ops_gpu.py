@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-import torch_dist_ext_b200 as tdx
+import torch_dist_ext_b200  # noqa: F401  (loads the library)
 from torch_dist_ext_b200.ops import activation, norm, quant, rope
 from torch_dist_ext_b200.ops import reference as ref
 from torch_dist_ext_b200.utils.config import OUT_FP8_BLOCK128, OUT_FP8_TOKEN

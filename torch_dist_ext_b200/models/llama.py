@@ -23,9 +23,8 @@ checkpoint format.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
-from typing import List, Optional
+from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -11,7 +11,7 @@ import torch
 
 from .. import _lib
 from ..utils.tracing import traced
-from ..utils.config import OUT_FP8_BLOCK128, OUT_FP8_TOKEN, OUT_SAME
+from ..utils.config import OUT_FP8_TOKEN, OUT_SAME
 
 
 @traced("tdx.fused_add_rmsnorm")
