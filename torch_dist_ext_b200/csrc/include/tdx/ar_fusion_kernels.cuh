@@ -181,6 +181,32 @@ __device__ __forceinline__ void add_residual(float (&acc)[VecTraits<T>::kVec], c
   }
 }
 
+// The same with a residual vector that the caller requested earlier (before it started to wait for
+// its peers, so that the DRAM latency of the residual hides behind that wait).
+template <typename T>
+__device__ __forceinline__ void add_residual_loaded(float (&acc)[VecTraits<T>::kVec], bool has_residual, const uint4& res) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  round_through<T>(acc);
+  if (has_residual) {
+    float r[kVec];
+    unpack<T>(res, r);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) acc[i] += r[i];
+    round_through<T>(acc);
+  }
+}
+
+template <typename T, int kVpt>
+__device__ __forceinline__ void request_residual(const ArParams& p, const RowView<T, kVpt>& rv, int64_t res_row,
+                                                 uint4 (&res)[kVpt]) {
+#pragma unroll
+  for (int v = 0; v < kVpt; ++v)
+    res[v] = (p.residual_in != nullptr && rv.active(v))
+                 ? ptx::ld_stream_v4(static_cast<const char*>(p.residual_in) + (size_t)res_row * rv.row_bytes +
+                                     (size_t)rv.vec_index(v) * 16)
+                 : make_uint4(0u, 0u, 0u, 0u);
+}
+
 __device__ __forceinline__ char* lamport_buf(void* base, const Layout& l, uint32_t idx) {
   return static_cast<char*>(base) + l.off_lamport + (size_t)idx * l.lamport_bytes;
 }
@@ -292,6 +318,8 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
   int parity = 0;
   for (int row = blockIdx.x; row < p.tokens; row += gridDim.x, parity ^= 1) {
     float x[kVpt][kVec];
+    uint4 res[kVpt];
+    request_residual<T, kVpt>(p, rv, row, res);
 #pragma unroll
     for (int v = 0; v < kVpt; ++v) {
 #pragma unroll
@@ -327,7 +355,7 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
           for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
         }
       }
-      add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) + off : nullptr);
+      add_residual_loaded<T>(x[v], p.residual_in != nullptr, res[v]);
       if (p.residual_out) ptx::st_stream_v4(static_cast<char*>(p.residual_out) + off, pack<T>(x[v]));
     }
     float rstd, sc;
@@ -435,6 +463,8 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
     const int64_t out_row = gather_back ? row : j;
     float x[kVpt][kVec];
     uint4 packed[kVpt];
+    uint4 res[kVpt];
+    request_residual<T, kVpt>(p, rv, out_row, res);
 #pragma unroll
     for (int v = 0; v < kVpt; ++v) {
 #pragma unroll
@@ -472,9 +502,7 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
           for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
         }
       }
-      add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) +
-                                                (size_t)out_row * rv.row_bytes + voff
-                                          : nullptr);
+      add_residual_loaded<T>(x[v], p.residual_in != nullptr, res[v]);
       packed[v] = scrub(pack<T>(x[v]));
       unpack<T>(packed[v], x[v]);
       if (p.residual_out)
