@@ -1,0 +1,46 @@
+"""Host-side launch planning of the GEMM and of decode attention (pure Python, no GPU)."""
+import pytest
+
+from torch_dist_ext_b200.ops import attention, gemm
+
+SMS = 148
+
+
+@pytest.mark.parametrize("m", [1, 16, 64, 128])
+@pytest.mark.parametrize("n,k", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (768, 4096), (512, 1792)])
+def test_decode_shapes_run_swapped_and_fill_the_sms(m, n, k):
+    swap, bn, splits = gemm.plan(m, n, k)
+    assert swap, "up to 128 tokens the weights take the 128-row side of the tile"
+    assert bn in (16, 32, 64, 128) and bn >= min(m, 128)
+    tiles = -(-n // 128) * -(-m // bn)
+    kblocks = k // 64
+    assert 1 <= splits <= max(1, kblocks // 2)
+    if tiles >= SMS:
+        assert splits == 1
+    else:
+        assert tiles * splits <= SMS            # one wave
+        assert splits == max(1, min(kblocks // 2, SMS // tiles))
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 28672, 4096), (8192, 4096, 14336), (256, 256, 64), (300, 520, 512)])
+def test_prefill_shapes_run_unswapped_with_wide_tiles(m, n, k):
+    swap, bn, splits = gemm.plan(m, n, k)
+    assert not swap and bn in (128, 256)
+    if (m // 128) * (n // 256) >= SMS:
+        assert bn == 256 and splits == 1
+
+
+def test_block_scaled_plan_keeps_the_epilogue_in_registers():
+    for m in (1, 16, 64, 2048):
+        swap, bn, splits = gemm.plan(m, 28672, 8192, elem_size=1, scaled=True)
+        assert swap and bn <= 64, "the promoting epilogue holds one fp32 accumulator per column"
+        assert splits >= 1
+
+
+@pytest.mark.parametrize("batch,kv_heads,max_len", [(1, 8, 2048), (16, 8, 2048), (64, 8, 2048), (64, 1, 2048), (1, 1, 64),
+                                                     (256, 8, 4096), (3, 2, 100000)])
+def test_attention_splits_fit_one_wave_and_keep_128_positions(batch, kv_heads, max_len):
+    s = attention.pick_splits(batch, kv_heads, max_len)
+    assert s >= 1
+    assert s <= max(1, -(-max_len // 128))                       # at least 128 positions per split
+    assert s == 1 or batch * kv_heads * s <= 2 * SMS             # two CTAs per SM, one wave
