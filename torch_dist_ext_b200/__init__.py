@@ -44,9 +44,8 @@ def _get_workspace_fake(ref: torch.Tensor) -> torch.Tensor:
     return torch.empty(_comm.table_nbytes(), dtype=torch.uint8, device=ref.device)
 
 
-@torch.library.custom_op("torch_dist_ext::allreduce_rms", mutates_args=[])
-def allreduce_rms(rank: int, nranks: int, allreduce_in: torch.Tensor, residual_in: torch.Tensor,
-                  rms_gamma: torch.Tensor, eps: float, workspace: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def _allreduce_rms_impl(rank: int, nranks: int, allreduce_in: torch.Tensor, residual_in: torch.Tensor,
+                        rms_gamma: torch.Tensor, eps: float, workspace: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     c = _comm.get_comm()
     if rank != c.rank or nranks != c.world_size:
         raise ValueError(f"allreduce_rms(rank={rank}, nranks={nranks}) does not match setup_env"
@@ -54,6 +53,22 @@ def allreduce_rms(rank: int, nranks: int, allreduce_in: torch.Tensor, residual_i
     norm_out, residual_out, _ = fused_allreduce_rms(allreduce_in, residual_in, rms_gamma, eps,
                                                     workspace if allreduce_in.is_cuda else None)
     return norm_out, residual_out
+
+
+# The registered op (with its fake implementation below) is what tracing and export see.
+_allreduce_rms_op = torch.library.custom_op("torch_dist_ext::allreduce_rms", _allreduce_rms_impl, mutates_args=[])
+
+
+def allreduce_rms(rank: int, nranks: int, allreduce_in: torch.Tensor, residual_in: torch.Tensor,
+                  rms_gamma: torch.Tensor, eps: float, workspace: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All-reduce + residual add + RMSNorm; returns ``(norm_out, residual_out)`` (the reference's
+    signature and order, torch_dist_ext/__init__.py:64-73). Plain tensors in eager mode go straight
+    to the kernel launch; traced calls and tensor subclasses (fake tensors) go through the
+    registered op ``torch_dist_ext::allreduce_rms``, whose Python dispatch costs several times the
+    launch itself."""
+    if type(allreduce_in) is torch.Tensor and not torch.compiler.is_compiling():
+        return _allreduce_rms_impl(rank, nranks, allreduce_in, residual_in, rms_gamma, eps, workspace)
+    return _allreduce_rms_op(rank, nranks, allreduce_in, residual_in, rms_gamma, eps, workspace)
 
 
 @torch.library.register_fake("torch_dist_ext::allreduce_rms")
