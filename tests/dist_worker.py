@@ -78,6 +78,14 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
                 got, want = norm.cpu().float(), exp_norm.float()
                 step = torch.maximum(got.abs(), want.abs()) * 0.125 + 2.0 ** -9
                 assert bool(((got - want).abs() <= step).all()), f"case {i}: fp8 codes differ by more than a step"
+            if cuda and out_mode == OUT_SAME and not nvls and algo in (None, "oneshot", "twoshot", "twoshot_barrier"):
+                # the same call on pinned host tensors: the peer-to-peer paths are deterministic, so the kernel
+                # that reads and writes host memory itself must reproduce the device-tensor result bit for bit
+                outs = (torch.zeros(tokens, hidden, dtype=dtype).pin_memory(), torch.zeros(tokens, hidden, dtype=dtype).pin_memory())
+                p_norm, p_res = tdx.allreduce_rms_pinned(ins[rank].pin_memory(), residual.pin_memory(), w, 1e-6, out=outs, algo=algo)
+                torch.cuda.synchronize()
+                tdx.check_status()
+                assert torch.equal(p_res, res.cpu()) and torch.equal(p_norm, norm.cpu()), f"case {i}: pinned-memory path differs on rank {rank}"
         st = tdx.stats()
         if cuda:
             assert st["error_count"] == 0
