@@ -5,8 +5,8 @@
         --model 8b|70b|tiny [--layers L] [--batch 1,16,64] [--kv 2048] [--steps 128] [--mode ar|sp]
 
 Weights are random (N(0, 0.02)); the KV cache is filled with random bf16 for `--kv` positions per
-sequence (`--prefill` instead runs one real 2048-token prompt per sequence through the prefill
-path first). One decode step = one new token for every sequence of the batch, replayed from a CUDA
+sequence (`--prefill` instead runs one real `--kv`-token prompt per sequence through the prefill
+path first, times it, and adds prefill tokens/s and the end-to-end generated tokens/s of both phases). One decode step = one new token for every sequence of the batch, replayed from a CUDA
 graph; the timed region holds `--steps` steps between two CUDA events, maximum over ranks.
 Reports microseconds per step and per layer, tokens/s for the whole job, and the weight-streaming
 floor (weight bytes per rank / measured HBM copy bandwidth).
@@ -58,10 +58,18 @@ def main():
     wbytes = sum(sum(t.numel() * t.element_size() for t in (L[k].w,)) for L in model.layers for k in ("wqkv", "wo", "wgu", "wd"))
     rows = []
     for b in batches:
+        prefill_ms = None
         if args.prefill:
+            prompts = [torch.randint(0, cfg.vocab, (args.kv,), device=model.device) for _ in range(b)]
+            torch.cuda.synchronize()
+            common.barrier(world)
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record()
             for s in range(b):
-                prompt = torch.randint(0, cfg.vocab, (args.kv,), device=model.device)
-                model.prefill(prompt, seq_index=s)
+                model.prefill(prompts[s], seq_index=s)
+            p1.record()
+            torch.cuda.synchronize()
+            prefill_ms = common.max_over_ranks(p0.elapsed_time(p1), world)
         else:
             model.fill_cache_random(b, args.kv)
         tokens = torch.randint(0, cfg.vocab, (b,), device=model.device)
@@ -96,6 +104,11 @@ def main():
                "tokens_per_s": round(b / us * 1e6, 1), "weight_bytes_per_rank": wbytes,
                "hbm_floor_us_per_step": round(floor_us, 1), "fraction_of_hbm_floor": round(floor_us / us, 3),
                "cuda_graph": not args.no_graph}
+        if prefill_ms is not None:
+            # prompt processing + generation, as one job: generated tokens over the time of both phases
+            total_s = prefill_ms / 1e3 + us * args.steps / 1e6
+            row.update({"prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(b * args.kv / prefill_ms * 1e3, 1),
+                        "end_to_end_generated_tokens_per_s": round(b * args.steps / total_s, 1)})
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
