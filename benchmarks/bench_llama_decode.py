@@ -6,7 +6,8 @@
 
 Weights are random (N(0, 0.02)); the KV cache is filled with random bf16 for `--kv` positions per
 sequence (`--prefill` instead runs one real `--kv`-token prompt per sequence through the prefill
-path first, times it, and adds prefill tokens/s and the end-to-end generated tokens/s of both phases). One decode step = one new token for every sequence of the batch, replayed from a CUDA
+path first, times it, and adds prefill tokens/s and the end-to-end generated tokens/s of both
+phases). One decode step = one new token for every sequence of the batch, replayed from a CUDA
 graph; the timed region holds `--steps` steps between two CUDA events, maximum over ranks.
 Reports microseconds per step and per layer, tokens/s for the whole job, and the weight-streaming
 floor (weight bytes per rank / measured HBM copy bandwidth).
