@@ -115,3 +115,90 @@ def test_clearing_the_next_buffer_instead_of_the_previous_one_is_caught():
     # with three buffers, wiping (e + 1) % 3 can destroy what a rank that runs one call ahead already pushed
     violation, _ = explore(2, 1, 5, nbuffers=3, clear_distance=1)
     assert violation is not None
+
+
+# ---- flag-synchronised two-shot path ---------------------------------------------------------------
+# One staging area and one result area per rank, reused by every call (no rotation); two flag
+# barriers per call keep the reuse safe (`twoshot_flag_body`): ranks write their rows into the owners'
+# staging slots and raise flag plane 0; after all plane-0 flags of the call the owner reduces its
+# staging slots and writes the result into every rank's result area, then raises plane 1; after all
+# plane-1 flags every rank reads its result area. Flags carry the call number and are compared with
+# ">=", so a flag raised early by a rank that runs ahead is never lost.
+
+def explore_flags(nranks: int, ncalls: int, second_barrier: bool):
+    peers = [[p for p in range(nranks) if p != r] for r in range(nranks)]
+    prog = []
+    for r in range(nranks):
+        steps = [("stage", p) for p in peers[r]] + [("signal", 0), ("wait", 0)]
+        steps += [("reduce", p) for p in peers[r]] + [("publish", p) for p in peers[r]]
+        if second_barrier:
+            steps += [("signal", 1), ("wait", 1)]
+        steps += [("epilogue", p) for p in peers[r]]
+        prog.append(steps)
+    plen = len(prog[0])
+    none = tuple(SENTINEL for _ in range(nranks))
+    start = (tuple(0 for _ in range(nranks)),                       # call number per rank
+             tuple(0 for _ in range(nranks)),                       # program counter per rank
+             tuple(none for _ in range(nranks)),                    # staging[rank][src]
+             tuple(none for _ in range(nranks)),                    # result[rank][owner]
+             tuple((none, none) for _ in range(nranks)))            # flags[rank][plane][src]
+    seen = {start}
+    queue = deque([start])
+
+    def put(table, r, i, v):
+        row = table[r][:i] + (v,) + table[r][i + 1:]
+        return table[:r] + (row,) + table[r + 1:]
+
+    while queue:
+        calls, pcs, staging, result, flags = queue.popleft()
+        if all(c == ncalls for c in calls):
+            continue
+        moved = False
+        for r in range(nranks):
+            e = calls[r]
+            if e == ncalls:
+                continue
+            op, arg = prog[r][pcs[r]]
+            st, rs, fl = staging, result, flags
+            if op == "stage":
+                st = put(staging, arg, r, e)
+            elif op == "signal":
+                for p in peers[r]:
+                    planes = list(fl[p])
+                    planes[arg] = planes[arg][:r] + (e,) + planes[arg][r + 1:]
+                    fl = fl[:p] + (tuple(planes),) + fl[p + 1:]
+            elif op == "wait":
+                if any(flags[r][arg][p] < e for p in peers[r]):
+                    continue
+            elif op == "reduce":
+                if staging[r][arg] != e:
+                    return (f"rank {r} call {e}: staging slot of rank {arg} holds call {staging[r][arg]}", len(seen))
+            elif op == "publish":
+                rs = put(result, arg, r, e)
+            else:
+                if result[r][arg] != e:
+                    return (f"rank {r} call {e}: result of owner {arg} holds call {result[r][arg]}", len(seen))
+            npc = pcs[r] + 1
+            ncall = e
+            if npc == plen:
+                npc, ncall = 0, e + 1
+            state = (calls[:r] + (ncall,) + calls[r + 1:], pcs[:r] + (npc,) + pcs[r + 1:], st, rs, fl)
+            moved = True
+            if state not in seen:
+                seen.add(state)
+                queue.append(state)
+        if not moved:
+            return (f"deadlock at calls {calls}, program counters {pcs}", len(seen))
+    return (None, len(seen))
+
+
+@pytest.mark.parametrize("nranks,ncalls", [(2, 6), (3, 4), (4, 2)])
+def test_two_flag_barriers_make_the_shared_staging_safe(nranks, ncalls):
+    violation, states = explore_flags(nranks, ncalls, second_barrier=True)
+    assert violation is None, violation
+    assert states > 100
+
+
+def test_without_the_second_barrier_a_fast_rank_overwrites_what_a_slow_rank_still_reads():
+    violation, _ = explore_flags(2, 3, second_barrier=False)
+    assert violation is not None
