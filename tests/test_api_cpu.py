@@ -139,3 +139,25 @@ def test_nvtx_ranges_follow_the_flag():
     finally:
         tracing.enable(False)
         tracing.set_backend(None, None)
+
+
+def test_clock_sampler_parses_the_query_output(tmp_path, monkeypatch):
+    import importlib.util
+    import os
+    import stat
+    import time
+
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\necho '1342, 1965, 987.12, Not Active, Not Active, Not Active, Active'\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    spec = importlib.util.spec_from_file_location(
+        "_timing_under_test", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                           "torch_dist_ext_b200", "utils", "timing.py"))
+    timing = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(timing)
+    with timing.ClockSampler(0, period_s=0.01) as s:
+        time.sleep(0.3)
+    out = s.summary()
+    assert out["sm_mhz"] == 1342.0 and out["sm_max_mhz"] == 1965.0
+    assert out["reasons"] == ["sw_power_cap"] and out["samples"] >= 1
