@@ -658,64 +658,90 @@ __device__ __forceinline__ void twoshot_flag_body(const ArParams& p) {
     flag_wait(p, ctl, 0, bepoch + (uint32_t)wv + 1u, w, 1);
 
     // ---- reduce + publish the rows this rank owns in this wave ----
-    for (int k = wv * wave_len; k < (wv + 1) * wave_len && k < per_block; ++k) {
-      const int j = blockIdx.x + k * gridDim.x;
-      if (j >= g.groups) break;
-      const int row = j * nranks + p.rank;
-      if (row >= p.tokens) continue;
-      const int64_t out_row = gather_back ? row : j;
-      float x[kVpt][kVec];
+    // NVLS: the switch-side sums of up to `batch` rows are requested before the first of them is
+    // consumed. A multimem.ld_reduce takes several microseconds to come back, and one 16-byte
+    // request per thread does not keep the links busy (`nvls_batch`, default 1 = one row at a time).
+    constexpr int kMaxBatch = kNvls ? (kVpt == 1 ? 4 : (kVpt == 2 ? 2 : 1)) : 1;
+    const int batch = !kNvls || p.nvls_batch < 1 ? 1 : (p.nvls_batch > kMaxBatch ? kMaxBatch : p.nvls_batch);
+    const int k_end = min((wv + 1) * wave_len, per_block);
+    for (int k0 = wv * wave_len; k0 < k_end; k0 += batch) {
+      uint4 pre[kMaxBatch][kVpt];
+      if constexpr (kNvls) {
 #pragma unroll
-      for (int v = 0; v < kVpt; ++v) {
+        for (int b = 0; b < kMaxBatch; ++b) {
+          const int j = blockIdx.x + (k0 + b) * gridDim.x;
+          const int row = j * nranks + p.rank;
+          if (b < batch && k0 + b < k_end && j < g.groups && row < p.tokens) {
 #pragma unroll
-        for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
-        if (!rv.active(v)) continue;
-        const size_t voff = (size_t)rv.vec_index(v) * 16;
-        if constexpr (kNvls) {
-          unpack<T>(mc_ld_reduce<T>(static_cast<const char*>(p.mc_base) + stage_off + (size_t)row * rv.row_bytes + voff), x[v]);
-        } else {
-          const char* slot0 = self + stage_off + (size_t)j * rv.row_bytes + voff;
-          const size_t slot_stride = (size_t)g.groups * rv.row_bytes;
-#pragma unroll
-          for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
-            if (r >= nranks) continue;
-            const uint4 val = (r == p.rank) ? ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff)
-                                            : ptx::ld_volatile_v4(slot0 + r * slot_stride);
-            float f[kVec];
-            unpack<T>(val, f);
-#pragma unroll
-            for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
-          }
-        }
-        add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) +
-                                                  (size_t)out_row * rv.row_bytes + voff
-                                            : nullptr);
-        const uint4 packed = pack<T>(x[v]);
-        if (p.residual_out)
-          ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)out_row * rv.row_bytes + voff, packed);
-        if (gather_back) {
-          if constexpr (kNvls) {
-            // one store, replicated by the switch into every rank's result area
-            ptx::multimem_st_v4(static_cast<char*>(p.mc_base) + result_off + (size_t)row * rv.row_bytes + voff, packed);
-          } else {
-#pragma unroll
-            for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
-              if (r >= nranks || r == p.rank) continue;
-              ptx::st_v4(symm(p, r, result_off + (size_t)row * rv.row_bytes + voff), packed);
-            }
+            for (int v = 0; v < kVpt; ++v)
+              if (rv.active(v))
+                pre[b][v] = mc_ld_reduce<T>(static_cast<const char*>(p.mc_base) + stage_off + (size_t)row * rv.row_bytes +
+                                            (size_t)rv.vec_index(v) * 16);
           }
         }
       }
-      float rstd, sc;
-      finish_row<T, kVpt, kOut>(p, rv, out_row, x, gamma, red, parity, rstd, sc);
-      parity ^= 1;
-      if (gather_back) {
-        const uint4 trailer = make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u);
-        if constexpr (kNvls) {
-          if (threadIdx.x == 0)
-            ptx::multimem_st_v4(static_cast<char*>(p.mc_base) + result_off + g.trailer_off + (size_t)row * 16, trailer);
-        } else if (threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
-          ptx::st_v4(symm(p, threadIdx.x, result_off + g.trailer_off + (size_t)row * 16), trailer);
+#pragma unroll
+      for (int b = 0; b < kMaxBatch; ++b) {
+        const int k = k0 + b;
+        if (b >= batch || k >= k_end) continue;
+        const int j = blockIdx.x + k * gridDim.x;
+        if (j >= g.groups) continue;
+        const int row = j * nranks + p.rank;
+        if (row >= p.tokens) continue;
+        const int64_t out_row = gather_back ? row : j;
+        float x[kVpt][kVec];
+#pragma unroll
+        for (int v = 0; v < kVpt; ++v) {
+#pragma unroll
+          for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
+          if (!rv.active(v)) continue;
+          const size_t voff = (size_t)rv.vec_index(v) * 16;
+          if constexpr (kNvls) {
+            unpack<T>(pre[b][v], x[v]);
+          } else {
+            const char* slot0 = self + stage_off + (size_t)j * rv.row_bytes + voff;
+            const size_t slot_stride = (size_t)g.groups * rv.row_bytes;
+#pragma unroll
+            for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
+              if (r >= nranks) continue;
+              const uint4 val = (r == p.rank) ? ptx::ld_stream_v4(in + (size_t)row * rv.row_bytes + voff)
+                                              : ptx::ld_volatile_v4(slot0 + r * slot_stride);
+              float f[kVec];
+              unpack<T>(val, f);
+#pragma unroll
+              for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
+            }
+          }
+          add_residual<T>(x[v], p.residual_in ? static_cast<const char*>(p.residual_in) +
+                                                    (size_t)out_row * rv.row_bytes + voff
+                                              : nullptr);
+          const uint4 packed = pack<T>(x[v]);
+          if (p.residual_out)
+            ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)out_row * rv.row_bytes + voff, packed);
+          if (gather_back) {
+            if constexpr (kNvls) {
+              // one store, replicated by the switch into every rank's result area
+              ptx::multimem_st_v4(static_cast<char*>(p.mc_base) + result_off + (size_t)row * rv.row_bytes + voff, packed);
+            } else {
+#pragma unroll
+              for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
+                if (r >= nranks || r == p.rank) continue;
+                ptx::st_v4(symm(p, r, result_off + (size_t)row * rv.row_bytes + voff), packed);
+              }
+            }
+          }
+        }
+        float rstd, sc;
+        finish_row<T, kVpt, kOut>(p, rv, out_row, x, gamma, red, parity, rstd, sc);
+        parity ^= 1;
+        if (gather_back) {
+          const uint4 trailer = make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u);
+          if constexpr (kNvls) {
+            if (threadIdx.x == 0)
+              ptx::multimem_st_v4(static_cast<char*>(p.mc_base) + result_off + g.trailer_off + (size_t)row * 16, trailer);
+          } else if (threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
+            ptx::st_v4(symm(p, threadIdx.x, result_off + g.trailer_off + (size_t)row * 16), trailer);
+          }
         }
       }
     }

@@ -137,6 +137,7 @@ struct ArParams {
   // produced; outputs are then [ceil(tokens/nranks), hidden] and nothing is gathered.
   int32_t scatter_only;
   int32_t waves;            // flag-synchronised two-shot paths: pipeline depth (1..4), 0 = 1
+  int32_t nvls_batch;       // NVLS two-shot: rows whose switch-side sums are requested together (1..4), 0 = 1
   uint64_t timeout_ns;      // budget of every device-side wait
   uint32_t* host_status;    // pinned, host-mapped mirror of Control::status (or null)
   uint64_t debug_extent;    // checked build (-DTDX_BOUNDS): extent to check against; 0 = layout.total_bytes

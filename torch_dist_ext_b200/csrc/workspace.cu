@@ -485,6 +485,11 @@ void Workspace::fill_params(ArParams* p) const {
     return e ? std::atoi(e) : 1;
   }();
   p->waves = waves_env;
+  static const int batch_env = [] {
+    const char* e = std::getenv("TDX_NVLS_BATCH");
+    return e ? std::atoi(e) : 1;
+  }();
+  p->nvls_batch = batch_env;
 }
 
 void Workspace::reset() { init_device_state(); }

@@ -12,6 +12,7 @@ environment:
 ``TDX_LAMPORT_MB``     capacity of each of the three Lamport buffers (default 32)
 ``TDX_NVLS``           ``0`` disables the NVSwitch-multicast mapping and kernels
 ``TDX_WAVES``          pipeline depth (1..4) of the flag-synchronised two-shot paths (default 1)
+``TDX_NVLS_BATCH``     NVLS two-shot: rows whose switch-side sums are requested together (1..4, default 1)
 ``TDX_LOG``            Python logging level of the package logger
 ``TDX_NVTX``           ``1`` opens an NVTX range around every public op and decoder layer
                        (read by ``utils/tracing.py``)
