@@ -12,7 +12,8 @@
 // Synchronisation (all waits bounded):
 //  * full[s]   leader only: armed by the leader's producer for the bytes of BOTH CTAs; the peer's
 //              copies credit the leader's barrier (address translated with mapa).
-//  * empty[s]  one per CTA: the leader's MMA thread commits to both with one tcgen05.commit.
+//  * empty[s]  one per CTA: the leader's MMA thread commits to its own and (through the cluster's
+//              shared window) to the peer's.
 //  * acc_full  one per CTA, committed the same way after the last K block.
 //  * cluster barriers after barrier initialisation (no remote arrival before the target exists)
 //    and before tensor memory is freed (no CTA leaves while its peer may still read its shared
@@ -160,7 +161,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0 && rank == leader) {
       // ---- MMA issue (leader only) ----
-      const uint16_t pair_mask = (uint16_t)(3u << leader);
       bool ok = true;
       for (int i = 0; i < nkb; ++i) {
         const int s = i % kStages;
@@ -176,9 +176,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
         for (int k = 0; k < 4; ++k)   // 32 bytes of K per instruction, stepped inside the swizzle span
           tc::umma_pair<kFp8>(tmem_base, dx + (uint64_t)(k * 2), dy + (uint64_t)(k * 2), a.idesc, (i > 0 || k > 0) ? 1u : 0u);
-        tc::umma_commit_pair(&empty[s], pair_mask);   // the stage is free again in both CTAs
+        tc::umma_commit_pair(&empty[s], other);   // the stage is free again in both CTAs
       }
-      if (ok) tc::umma_commit_pair(acc_full, pair_mask);
+      if (ok) tc::umma_commit_pair(acc_full, other);
     }
   } else {
     // ---- epilogue (warps 2..5 of both CTAs): TMEM lane quarter = warp % 4 ----

@@ -206,12 +206,13 @@ __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint
   }
 }
 // Arrive on the mbarrier `bar` of BOTH CTAs of the pair (same offset in each CTA's shared memory) once all
-// MMAs issued so far by this thread have completed. `pair_mask` has one bit per CTA rank of the cluster
-// (0b11 for a cluster that is one pair). This is a barrier signal sent to two CTAs, not a data copy.
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t pair_mask) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(smem_u32(bar)), "h"(pair_mask)
-               : "memory");
+// MMAs issued so far by this thread have completed: one commit per CTA, the peer's barrier addressed
+// through the cluster's shared window (map_to_cta). Called by the leader's MMA thread.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint32_t peer_rank) {
+  const uint32_t own = smem_u32(bar);
+  const uint32_t peer = map_to_cta(own, peer_rank);
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(own) : "memory");
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
 }
 
 }  // namespace tc
