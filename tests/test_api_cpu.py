@@ -161,3 +161,11 @@ def test_clock_sampler_parses_the_query_output(tmp_path, monkeypatch):
     out = s.summary()
     assert out["sm_mhz"] == 1342.0 and out["sm_max_mhz"] == 1965.0
     assert out["reasons"] == ["sw_power_cap"] and out["samples"] >= 1
+
+
+def test_drop_in_module_keeps_the_reference_globals():
+    import torch_dist_ext as ref_name
+
+    ref_name.setup_env(0, 1)
+    assert type(ref_name.comm).__name__ == "CommProcess" and ref_name.world_size_ == 1
+    assert ref_name.allreduce_rms is tdx.allreduce_rms
