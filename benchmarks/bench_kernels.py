@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Single-GPU roofline table of the library's kernels (no communication).
 
-    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_fp8|attention|elementwise|all] [--steps 30]
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_fp8|attention|attention_tc|elementwise|all] [--steps 30]
 
 Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
 over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
@@ -102,7 +102,7 @@ def gemm_fp8_cases(dev, steps, out):
         torch.cuda.empty_cache()
 
 
-def attention_cases(dev, steps, out):
+def attention_cases(dev, steps, out, tensor_cores=False):
     from torch_dist_ext_b200.ops import attention
 
     hbm, tf, src = peaks()
@@ -113,7 +113,13 @@ def attention_cases(dev, steps, out):
                                  torch.randn(batch, length, hkv, d, device=dev, dtype=torch.bfloat16)), kv_bytes)
         q = torch.randn(batch, hq, d, device=dev, dtype=torch.bfloat16)
         lens = torch.full((batch,), length, device=dev, dtype=torch.int32)
-        us = time_us(lambda i: attention.decode_attention(q, sets[i][0], sets[i][1], lens, length), len(sets), steps)
+        if tensor_cores:   # a new kernel: check it before timing it
+            a = attention.decode_attention(q, sets[0][0], sets[0][1], lens, length, tensor_cores=True).float()
+            r = attention.decode_attention(q, sets[0][0], sets[0][1], lens, length, tensor_cores=False).float()
+            if not (a - r).abs().max().item() <= 3e-2:
+                raise SystemExit("tensor-core decode attention disagrees with the SIMT kernel")
+        us = time_us(lambda i: attention.decode_attention(q, sets[i][0], sets[i][1], lens, length, tensor_cores=tensor_cores),
+                     len(sets), steps)
 
         def sdpa(i):
             k, v = sets[i]
@@ -121,7 +127,8 @@ def attention_cases(dev, steps, out):
                 q.unsqueeze(2), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), enable_gqa=True)
 
         lib = time_us(sdpa, len(sets), steps)
-        out.append(row(f"decode attention batch={batch} len={length} hq={hq} hkv={hkv}", us, lib, kv_bytes,
+        tag = "decode attention (tcgen05)" if tensor_cores else "decode attention"
+        out.append(row(f"{tag} batch={batch} len={length} hq={hq} hkv={hkv}", us, lib, kv_bytes,
                        4.0 * batch * hq * length * d, hbm, tf, src))
         print(out[-1], flush=True)
         del sets
@@ -182,6 +189,8 @@ def main():
         gemm_fp8_cases(dev, args.steps, out)
     if g in ("attention", "all"):
         attention_cases(dev, args.steps, out)
+    if g == "attention_tc":         # opt-in kernel (not part of "all")
+        attention_cases(dev, args.steps, out, tensor_cores=True)
     if g in ("elementwise", "all"):
         elementwise_cases(dev, args.steps, out)
     path = os.path.join(common.out_dir(), f"kernels_{g}.json")

@@ -1,0 +1,35 @@
+"""Tensor-core (tcgen05) decode attention against an fp32 softmax(QK^T)V written in PyTorch.
+
+Opt-in: the kernel is off by default in the library, and this file runs only with
+TDX_TEST_ATTN_TC=1 until the kernel has been brought up on hardware (compiled and desk-checked
+only). The probabilities are rounded to bf16 before the second product, hence the slightly wider
+tolerance than for the SIMT kernel, which is also used as a cross-check."""
+import os
+
+import pytest
+import torch
+
+from torch_dist_ext_b200.ops import attention, gemm
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("TDX_TEST_ATTN_TC") != "1",
+                                 reason="tensor-core decode attention is opt-in (TDX_TEST_ATTN_TC=1) until validated on hardware")]
+
+
+@pytest.mark.parametrize("b,hq,hkv,smax", [(1, 4, 1, 128), (1, 4, 1, 2048), (16, 4, 1, 2048), (64, 8, 1, 300), (3, 32, 8, 777),
+                                           (2, 8, 8, 129), (2, 2, 1, 500), (2, 8, 1, 640)])
+def test_decode_attention_tc(b, hq, hkv, smax):
+    g = torch.Generator(device="cuda").manual_seed(b * 1000 + smax)
+    q = torch.randn(b, hq, 128, device="cuda", dtype=torch.bfloat16, generator=g)
+    k = torch.randn(b, smax, hkv, 128, device="cuda", dtype=torch.bfloat16, generator=g)
+    v = torch.randn(b, smax, hkv, 128, device="cuda", dtype=torch.bfloat16, generator=g)
+    lens = torch.randint(1, smax + 1, (b,), device="cuda", dtype=torch.int32, generator=g)
+    lens[0] = smax
+    want = attention.decode_attention_reference(q, k, v, lens)
+    for nsplit in (None, 1, 3):
+        got = attention.decode_attention(q, k, v, lens, smax, nsplit=nsplit, tensor_cores=True)
+        torch.cuda.synchronize()
+        assert gemm.pipeline_status() == 0
+        assert (got.float() - want.float()).abs().max().item() <= 3e-2, nsplit
+        simt = attention.decode_attention(q, k, v, lens, smax, nsplit=nsplit, tensor_cores=False)
+        assert (got.float() - simt.float()).abs().max().item() <= 3e-2, nsplit

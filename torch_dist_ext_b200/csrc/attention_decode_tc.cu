@@ -1,0 +1,424 @@
+// Split-KV decode attention on the tensor cores (tcgen05 / TMEM), head dimension 128, bf16 KV cache.
+//
+// Same interface and split/merge format as attention_decode.cu, whose arithmetic runs on the SIMT
+// pipes and is issue-bound well below the HBM roofline. Here both products of a 128-position chunk
+// are tcgen05 MMAs, with the cache positions (or the head dimension) on the 128-row side of the
+// instruction and the few query heads that share the KV head padded to the narrowest N (16):
+//
+//   S^T[keys 128, heads 16] = K[keys, d] * Q[heads, d]^T     A = K chunk as TMA delivers it (K-major over d)
+//   O^T[d 128,   heads 16] = V[keys, d]^T * P[heads, keys]^T  A = V chunk read MN-major (d contiguous), K = keys
+//
+// so neither K nor V is transposed or touched by a thread: TMA -> shared memory -> tensor core.
+// Per chunk the four softmax warps read S^T from tensor memory (one cache position per thread),
+// do the online-softmax bookkeeping, write the probabilities as a bf16 [heads, keys] tile (128-byte
+// swizzle, the B operand of the second product) and, once that product has completed, add its
+// result to their running output (one head-dimension index per thread, G registers).
+// A fifth warp issues the TMA copies (3-stage ring) and the MMAs; S^T is double-buffered in TMEM so
+// that the scores of chunk i+1 are computed while the softmax warps work on chunk i.
+//
+// Every wait is bounded; a wait that runs out records a status word, raises the CTA's abort flag
+// (which ends every other wait early) and all threads still reach the common exit, where copies in
+// flight are given time to land and the tensor memory is freed.
+//
+// Opt-in (ops/attention.py: decode_attention(..., tensor_cores=True) or TDX_ATTN_TC=1).
+// Not part of the reference (it has no attention).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cfloat>
+#include <mutex>
+#include <set>
+#include <string>
+#include "tdx/comm.h"
+#include "tdx/ops.h"
+#include "tdx/sync.cuh"
+#include "tdx/tc.cuh"
+
+namespace tdx {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kKeys = 128;                        // cache positions per chunk = MMA M of the score product
+constexpr int kNq = 16;                           // MMA N: query heads of one KV head, padded
+constexpr int kStages = 3;
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = kSoftmaxThreads + 32;    // + the copy / MMA warp
+constexpr int kMaxG = 8;
+constexpr int kHalfBytes = kKeys * 128;           // one 64-column half of a K or V chunk
+constexpr int kStageBytes = 4 * kHalfBytes;       // K lo, K hi, V lo, V hi
+constexpr int kSmallTileBytes = 2 * kNq * 128;    // Q or P: two 64-wide K blocks of 16 rows x 128 bytes
+constexpr int kSmem = kStages * kStageBytes + 2 * kSmallTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+constexpr uint32_t kTmemCols = 64;                // S^T buffers at columns 0 and 16, O^T chunk at 32
+constexpr uint32_t kColO = 32;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr int kCounterWords = 4096;               // head of the scratch buffer reserved by the other kernel
+
+struct TcAttnArgs {
+  const __nv_bfloat16* q;      // [B, Hq, D]
+  const int32_t* seq_lens;     // [B]
+  float* partial;              // [B, Hq, nsplit, D + 2]
+  __nv_bfloat16* out;          // [B, Hq, D]
+  int B, Hq, Hkv, nsplit;
+  int64_t q_stride_b;
+  float scale;
+  uint32_t idesc_s, idesc_pv;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(tc::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Operand read MN-major from a tile that TMA wrote as [rows = K index][128 bytes of the MN index], 128-byte
+// swizzle: eight K rows of one 64-element MN slice are 1024 bytes (stride offset), the next 64-element MN
+// slice of the same rows starts `mn_slice_bytes` further (leading offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_slice_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((mn_slice_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Byte offset of element (row, col) of a [16 rows x 128 columns] bf16 tile stored as two 64-column
+// K blocks of [16 rows x 128 bytes] with the 128-byte swizzle (what tcgen05.mma reads as a K-major B operand).
+__device__ __forceinline__ int small_tile_offset(int row, int col) {
+  const int kb = col >> 6, c = (col & 63) >> 3;
+  return kb * (kNq * 128) + row * 128 + ((c ^ (row & 7)) << 4) + (col & 7) * 2;
+}
+
+template <int kG>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ float wred[2][kG][4];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_tile = ring + kStages * kStageBytes;
+  uint8_t* p_tile = q_tile + kSmallTileBytes;
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(p_tile + kSmallTileBytes);
+  uint64_t* kv_free = kv_full + kStages;
+  uint64_t* s_full = kv_free + kStages;     // [2]
+  uint64_t* s_free = s_full + 2;            // [2]
+  uint64_t* p_full = s_free + 2;
+  uint64_t* o_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int len = a.seq_lens[b];
+  const int per = (len + a.nsplit - 1) / a.nsplit;
+  const int s0 = split * per, s1 = min(len, s0 + per);
+  const int nchunks = s1 > s0 ? (s1 - s0 + kKeys - 1) / kKeys : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&kv_full[s], 1);
+      tc::mbar_init(&kv_free[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&s_full[i], 1);
+      tc::mbar_init(&s_free[i], kSoftmaxThreads);
+    }
+    tc::mbar_init(p_full, kSoftmaxThreads);
+    tc::mbar_init(o_full, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_k);
+    tc::tma_prefetch_desc(&map_v);
+  }
+  // Q and P tiles: zero everything (rows beyond the G real heads stay zero), then the query rows
+  for (int i = tid; i < 2 * kSmallTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  for (int i = tid; i < kG * kD; i += kThreads) {
+    const int g = i / kD, d = i % kD;
+    *reinterpret_cast<__nv_bfloat16*>(q_tile + small_tile_offset(g, d)) =
+        a.q[(int64_t)b * a.q_stride_b + (int64_t)(hkv * kG + g) * kD + d];
+  }
+  tc::fence_proxy_async();   // the tiles were written by threads and are read by the tensor core
+  if (warp == 4) {
+    tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&]() {
+    *abort_flag = 1;
+    if (a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
+  };
+
+  float m_run[kG], l_run[kG], o[kG];
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    m_run[g] = -FLT_MAX;
+    l_run[g] = 0.f;
+    o[g] = 0.f;
+  }
+
+  if (warp == 4) {
+    if (lane == 0 && nchunks > 0) {
+      // ---- copies and MMAs ----
+      auto issue_copy = [&](int c) {
+        const int st = c % kStages;
+        uint8_t* base = ring + st * kStageBytes;
+        tc::mbar_arrive_expect_tx(&kv_full[st], kStageBytes);
+        const int pos0 = s0 + c * kKeys;
+        tma_load_4d(base, &map_k, &kv_full[st], 0, hkv, pos0, b);
+        tma_load_4d(base + kHalfBytes, &map_k, &kv_full[st], 64, hkv, pos0, b);
+        tma_load_4d(base + 2 * kHalfBytes, &map_v, &kv_full[st], 0, hkv, pos0, b);
+        tma_load_4d(base + 3 * kHalfBytes, &map_v, &kv_full[st], 64, hkv, pos0, b);
+      };
+      auto issue_scores = [&](int c) {   // S^T[buf c & 1] = K chunk * Q^T
+        const uint32_t kbase = tc::smem_u32(ring + (c % kStages) * kStageBytes);
+        const uint32_t qbase = tc::smem_u32(q_tile);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            tc::umma<false>(tmem_base + (uint32_t)(c & 1) * kNq, tc::make_smem_desc_sw128(kbase + kb * kHalfBytes) + (uint64_t)(ks * 2),
+                            tc::make_smem_desc_sw128(qbase + kb * (kNq * 128)) + (uint64_t)(ks * 2), a.idesc_s, (kb | ks) ? 1u : 0u);
+        tc::umma_commit(&s_full[c & 1]);
+      };
+      auto issue_pv = [&](int c) {       // O^T chunk = V chunk^T * P^T, 16 cache positions per instruction
+        const uint32_t vbase = tc::smem_u32(ring + (c % kStages) * kStageBytes + 2 * kHalfBytes);
+        const uint32_t pbase = tc::smem_u32(p_tile);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          tc::umma<false>(tmem_base + kColO, make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes),
+                          tc::make_smem_desc_sw128(pbase + (j >> 2) * (kNq * 128)) + (uint64_t)((j & 3) * 2), a.idesc_pv, j ? 1u : 0u);
+        tc::umma_commit(o_full);
+        tc::umma_commit(&kv_free[c % kStages]);
+      };
+      bool ok = true;
+      for (int c = 0; c < nchunks && c < kStages; ++c) issue_copy(c);
+      ok = tc::mbar_wait(&kv_full[0], 0, kWaitLimit, abort_flag);
+      if (ok) {
+        tc::fence_after_thread_sync();
+        issue_scores(0);
+      }
+      for (int i = 0; i < nchunks && ok; ++i) {
+        if (i + 1 < nchunks) {
+          const int n = i + 1;
+          ok = tc::mbar_wait(&kv_full[n % kStages], (n / kStages) & 1, kWaitLimit, abort_flag) &&
+               (n < 2 || tc::mbar_wait(&s_free[n & 1], ((n >> 1) - 1) & 1, kWaitLimit, abort_flag));
+          if (!ok) break;
+          tc::fence_after_thread_sync();
+          issue_scores(n);
+        }
+        ok = tc::mbar_wait(p_full, i & 1, kWaitLimit, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        issue_pv(i);
+        if (i + kStages < nchunks) {
+          ok = tc::mbar_wait(&kv_free[i % kStages], (i / kStages) & 1, kWaitLimit, abort_flag);
+          if (!ok) break;
+          issue_copy(i + kStages);
+        }
+      }
+      if (!ok) fail();
+    }
+  } else {
+    // ---- softmax warps: thread t owns cache position t of the chunk and head-dimension index t of the output ----
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    for (int i = 0; i < nchunks; ++i) {
+      const int buf = i & 1;
+      float sv[16];
+      bool ok = tc::mbar_wait(&s_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag);
+      if (ok) {
+        tc::fence_after_thread_sync();
+        tc::tmem_ld_16(lane_addr + (uint32_t)buf * kNq, sv);
+        tc::fence_before_thread_sync();
+        tc::mbar_arrive(&s_free[buf]);
+      } else {
+        fail();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sv[j] = 0.f;
+      }
+      const bool live = s0 + i * kKeys + tid < s1;
+      float s[kG], corr[kG];
+#pragma unroll
+      for (int g = 0; g < kG; ++g) {
+        s[g] = live ? sv[g] * a.scale : -FLT_MAX;
+        const float v = warp_max(s[g]);
+        if (lane == 0) wred[0][g][warp] = v;
+      }
+      tc::named_barrier_sync(1, kSoftmaxThreads);
+#pragma unroll
+      for (int g = 0; g < kG; ++g) {
+        const float cmax = fmaxf(fmaxf(wred[0][g][0], wred[0][g][1]), fmaxf(wred[0][g][2], wred[0][g][3]));
+        const float m_new = fmaxf(m_run[g], cmax);
+        corr[g] = __expf(m_run[g] - m_new);
+        const float p = live ? __expf(s[g] - m_new) : 0.f;
+        *reinterpret_cast<__nv_bfloat16*>(p_tile + small_tile_offset(g, tid)) = __float2bfloat16(p);
+        const float ps = warp_sum(p);
+        if (lane == 0) wred[1][g][warp] = ps;
+        m_run[g] = m_new;
+      }
+      tc::fence_proxy_async();        // P was written by threads and is read by the tensor core
+      tc::mbar_arrive(p_full);
+      tc::named_barrier_sync(1, kSoftmaxThreads);
+#pragma unroll
+      for (int g = 0; g < kG; ++g)
+        l_run[g] = l_run[g] * corr[g] + (wred[1][g][0] + wred[1][g][1] + wred[1][g][2] + wred[1][g][3]);
+      float ov[16];
+      ok = tc::mbar_wait(o_full, i & 1, kWaitLimit, abort_flag);
+      if (ok) {
+        tc::fence_after_thread_sync();
+        tc::tmem_ld_16(lane_addr + kColO, ov);
+        tc::fence_before_thread_sync();
+#pragma unroll
+        for (int g = 0; g < kG; ++g) o[g] = o[g] * corr[g] + ov[g];
+      } else {
+        fail();
+      }
+      // every flag raised in this iteration is visible after this barrier: all threads leave together
+      tc::named_barrier_sync(1, kSoftmaxThreads);
+      if (*abort_flag) break;
+    }
+    // ---- result: thread t holds output column t of the G heads ----
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      const int h = hkv * kG + g;
+      if (a.nsplit == 1) {
+        a.out[((int64_t)b * a.Hq + h) * kD + tid] = __float2bfloat16(l_run[g] > 0.f ? o[g] / l_run[g] : 0.f);
+      } else {
+        float* dst = a.partial + (((int64_t)b * a.Hq + h) * a.nsplit + split) * (kD + 2);
+        dst[tid] = o[g];
+        if (tid == 0) {
+          dst[kD] = m_run[g];
+          dst[kD + 1] = l_run[g];
+        }
+      }
+    }
+  }
+
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);   // copies already issued land before shared memory goes away
+  }
+  if (warp == 4) {
+    tc::fence_after_thread_sync();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// out[b, h, :] = sum_s exp(m_s - m) * acc_s / sum_s exp(m_s - m) * l_s
+__global__ void __launch_bounds__(kD) attn_tc_combine_kernel(const TcAttnArgs a) {
+  const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const float* src = a.partial + ((int64_t)b * a.Hq + h) * a.nsplit * (kD + 2);
+  float m = -FLT_MAX;
+  for (int s = 0; s < a.nsplit; ++s) m = fmaxf(m, src[s * (kD + 2) + kD]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < a.nsplit; ++s) {
+    const float w = __expf(src[s * (kD + 2) + kD] - m);
+    num = fmaf(w, src[s * (kD + 2) + d], num);
+    den = fmaf(w, src[s * (kD + 2) + kD + 1], den);
+  }
+  a.out[((int64_t)b * a.Hq + h) * kD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encoder() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// cache [B, S, Hkv, 128] bf16 -> 4-D map (128, Hkv, S, B); one box = 64 columns x 128 positions of one head
+std::string cache_map(CUtensorMap* map, const void* ptr, int B, int S, int Hkv, int64_t stride_b, int64_t stride_s) {
+  EncodeFn enc = encoder();
+  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
+  const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)Hkv, (cuuint64_t)S, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)stride_s * 2, (cuuint64_t)stride_b * 2};
+  const cuuint32_t box[4] = {64, 1, (cuuint32_t)kKeys, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? "" : "cuTensorMapEncodeTiled failed for the KV cache (CUresult " + std::to_string((int)r) + ")";
+}
+
+template <int kG>
+std::string launch(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnArgs& a, dim3 grid, cudaStream_t stream) {
+  auto kern = attn_decode_tc_kernel<kG>;
+  static std::mutex mu;
+  static std::set<int> done;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done.count(dev)) {
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+      if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
+      done.insert(dev);
+    }
+  }
+  kern<<<grid, kThreads, kSmem, stream>>>(mk, mv, a);
+  return "";
+}
+
+}  // namespace
+
+std::string attention_decode_tc(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
+                                float* partial, size_t partial_floats, void* out, int B, int Hq, int Hkv, int D, int S_max,
+                                int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,
+                                cudaStream_t stream, uint32_t* status) {
+  if (D != kD) return "decode attention supports head dimension 128";
+  if (Hkv <= 0 || Hq % Hkv) return "query heads must be a multiple of KV heads";
+  const int G = Hq / Hkv;
+  if (G > kMaxG || (G & (G - 1))) return "query heads per KV head must be 1, 2, 4 or 8";
+  if (nsplit < 1) nsplit = 1;
+  // the first words of the scratch buffer belong to the other kernel's arrival counters and stay untouched
+  const size_t head = partial_floats > (size_t)kCounterWords ? (size_t)kCounterWords : 0;
+  if (head + (size_t)B * Hq * nsplit * (kD + 2) > partial_floats) return "attention scratch buffer is too small";
+  if ((kv_stride_s * 2) % 16 || (kv_stride_b * 2) % 16 || reinterpret_cast<uintptr_t>(k_cache) % 16 ||
+      reinterpret_cast<uintptr_t>(v_cache) % 16)
+    return "KV cache rows must be 16-byte aligned";
+  if (B == 0) return "";
+  TcAttnArgs a{};
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.seq_lens = seq_lens;
+  a.partial = partial + head;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.nsplit = nsplit;
+  a.q_stride_b = q_stride_b;
+  a.scale = scale;
+  a.idesc_s = tc::make_idesc(kKeys, kNq, 1, 1);                    // both operands K-major bf16
+  a.idesc_pv = tc::make_idesc(kD, kNq, 1, 1) | (1u << 15);         // A (the V chunk) is read MN-major
+  a.status = status;
+  CUtensorMap mk, mv;
+  std::string err = cache_map(&mk, k_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s);
+  if (!err.empty()) return err;
+  err = cache_map(&mv, v_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s);
+  if (!err.empty()) return err;
+  const dim3 grid(B, Hkv, nsplit);
+  switch (G) {
+    case 1: err = launch<1>(mk, mv, a, grid, stream); break;
+    case 2: err = launch<2>(mk, mv, a, grid, stream); break;
+    case 4: err = launch<4>(mk, mv, a, grid, stream); break;
+    case 8: err = launch<8>(mk, mv, a, grid, stream); break;
+  }
+  if (!err.empty()) return err;
+  if (nsplit > 1) attn_tc_combine_kernel<<<dim3(B, Hq), kD, 0, stream>>>(a);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : cudaGetErrorString(e);
+}
+
+}  // namespace tdx

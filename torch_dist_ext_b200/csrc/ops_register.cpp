@@ -191,8 +191,9 @@ void gemm_tn_pair(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int6
   TORCH_CHECK(err.empty(), "gemm_tn_pair: ", err);
 }
 
-void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor out,
-                      Tensor partial, int64_t nsplit, double scale, const c10::optional<Tensor>& status) {
+static void attention_decode_impl(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor& out,
+                                  Tensor& partial, int64_t nsplit, double scale, const c10::optional<Tensor>& status,
+                                  bool tensor_cores) {
   TORCH_CHECK(q.is_cuda() && q.dim() == 3 && k_cache.dim() == 4 && v_cache.dim() == 4, "attention_decode: q [B, Hq, D], caches [B, S, Hkv, D]");
   TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k_cache.scalar_type() == at::kBFloat16 && v_cache.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "attention_decode: bfloat16 tensors");
   TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == q.size(2) && out.is_contiguous(), "attention_decode: q heads densely packed, out contiguous");
@@ -200,12 +201,24 @@ void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
   TORCH_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.is_cuda() && seq_lens.numel() == q.size(0), "attention_decode: seq_lens int32 [B]");
   TORCH_CHECK(partial.scalar_type() == at::kFloat && partial.is_contiguous(), "attention_decode: partial must be contiguous fp32");
   const c10::cuda::CUDAGuard guard(q.device());
-  const std::string err = tdx::attention_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), seq_lens.data_ptr<int>(),
+  const auto fn = tensor_cores ? &tdx::attention_decode_tc : &tdx::attention_decode;
+  const std::string err = fn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), seq_lens.data_ptr<int>(),
                                                 partial.data_ptr<float>(), (size_t)partial.numel(), out.data_ptr(), (int)q.size(0),
                                                 (int)q.size(1), (int)k_cache.size(2), (int)q.size(2), (int)k_cache.size(1),
                                                 q.stride(0), k_cache.stride(0), k_cache.stride(1), (int)nsplit, (float)scale, cur_stream(),
                                                 status.has_value() && status->defined() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr);
   TORCH_CHECK(err.empty(), "attention_decode: ", err);
+}
+
+void attention_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor out,
+                      Tensor partial, int64_t nsplit, double scale, const c10::optional<Tensor>& status) {
+  attention_decode_impl(q, k_cache, v_cache, seq_lens, out, partial, nsplit, scale, status, false);
+}
+
+// Both products of a chunk on the tensor cores (tcgen05).
+void attention_decode_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor out,
+                         Tensor partial, int64_t nsplit, double scale, const c10::optional<Tensor>& status) {
+  attention_decode_impl(q, k_cache, v_cache, seq_lens, out, partial, nsplit, scale, status, true);
 }
 
 static tdx::Workspace* workspace_of(const Tensor& table) {
@@ -309,6 +322,8 @@ void register_extra_ops(torch::Library& m) {
         &gemm_ar_rmsnorm);
   m.def("attention_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor seq_lens, Tensor(a!) out, Tensor(b!) partial, "
         "int nsplit, float scale, Tensor(c!)? status) -> ()", &attention_decode);
+  m.def("attention_decode_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor seq_lens, Tensor(a!) out, Tensor(b!) partial, "
+        "int nsplit, float scale, Tensor(c!)? status) -> ()", &attention_decode_tc);
   m.def("ag_gemm(Tensor x_shard, Tensor w, Tensor(a!) out, int tokens, Tensor workspace, Tensor(b!)? status) -> ()", &ag_gemm);
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "

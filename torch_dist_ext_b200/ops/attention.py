@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -10,6 +11,7 @@ from .. import _lib
 from ..utils.tracing import traced
 
 _scratch = {}
+_TC_DEFAULT = os.environ.get("TDX_ATTN_TC", "0") not in ("0", "", "false", "off")
 
 
 def _partial(device, floats: int) -> torch.Tensor:
@@ -20,29 +22,34 @@ def _partial(device, floats: int) -> torch.Tensor:
     return _scratch[key]
 
 
-def pick_splits(batch: int, kv_heads: int, max_len: int, sms: int = 148) -> int:
-    """KV splits such that the grid fits ONE wave of the two CTAs that an SM holds (a second,
-    partly filled wave costs more than shorter splits save), with at least 128 positions per split."""
+def pick_splits(batch: int, kv_heads: int, max_len: int, sms: int = 148, ctas_per_sm: int = 2) -> int:
+    """KV splits such that the grid fits ONE wave of the CTAs that the SMs hold at a time (two per SM
+    for the SIMT kernel, one for the tensor-core kernel; a second, partly filled wave costs more
+    than shorter splits save), with at least 128 positions per split."""
     pairs = batch * kv_heads
-    want = max(1, (2 * sms) // pairs)
+    want = max(1, (ctas_per_sm * sms) // pairs)
     return max(1, min(want, (max_len + 127) // 128))
 
 
 @traced("tdx.decode_attention")
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: torch.Tensor,
-                     max_len: int, out: Optional[torch.Tensor] = None, nsplit: Optional[int] = None) -> torch.Tensor:
+                     max_len: int, out: Optional[torch.Tensor] = None, nsplit: Optional[int] = None,
+                     tensor_cores: Optional[bool] = None) -> torch.Tensor:
     """``q [B, Hq, 128]``, caches ``[B, S_max, Hkv, 128]``, ``seq_lens`` int32 ``[B]`` -> ``[B, Hq, 128]``.
 
-    ``max_len`` (a host integer >= every sequence length) only sizes the KV split."""
+    ``max_len`` (a host integer >= every sequence length) only sizes the KV split. ``tensor_cores=True``
+    runs both products of every 128-position chunk as tcgen05 MMAs (default: ``TDX_ATTN_TC``, off)."""
     b, hq, d = q.shape
     hkv = k_cache.shape[2]
-    nsplit = pick_splits(b, hkv, max_len) if nsplit is None else nsplit
+    use_tc = _TC_DEFAULT if tensor_cores is None else tensor_cores
+    if nsplit is None:
+        nsplit = pick_splits(b, hkv, max_len, ctas_per_sm=1 if use_tc else 2)
     out = torch.empty(b, hq, d, dtype=q.dtype, device=q.device) if out is None else out
     part = _partial(q.device, 4096 + b * hq * nsplit * (d + 2))
     from . import gemm as _gemm
 
-    _lib.ops().attention_decode(q, k_cache, v_cache, seq_lens, out, part, nsplit, 1.0 / math.sqrt(d),
-                                _gemm._workspace(q.device)[2])
+    op = _lib.ops().attention_decode_tc if use_tc else _lib.ops().attention_decode
+    op(q, k_cache, v_cache, seq_lens, out, part, nsplit, 1.0 / math.sqrt(d), _gemm._workspace(q.device)[2])
     return out
 
 
