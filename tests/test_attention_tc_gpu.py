@@ -33,3 +33,18 @@ def test_decode_attention_tc(b, hq, hkv, smax):
         assert (got.float() - want.float()).abs().max().item() <= 3e-2, nsplit
         simt = attention.decode_attention(q, k, v, lens, smax, nsplit=nsplit, tensor_cores=False)
         assert (got.float() - simt.float()).abs().max().item() <= 3e-2, nsplit
+
+
+@pytest.mark.parametrize("s,hq,hkv", [(128, 1, 1), (256, 4, 1), (300, 4, 2), (1000, 8, 8), (2048, 4, 1)])
+def test_prefill_attention_tc(s, hq, hkv):
+    g = torch.Generator(device="cuda").manual_seed(s + hq)
+    # q, k, v as views of one fused projection, the way the model produces them
+    qkv = torch.randn(s, (hq + 2 * hkv) * 128, device="cuda", dtype=torch.bfloat16, generator=g)
+    q = qkv[:, : hq * 128].view(s, hq, 128)
+    k = qkv[:, hq * 128: (hq + hkv) * 128].view(s, hkv, 128)
+    v = qkv[:, (hq + hkv) * 128:].view(s, hkv, 128)
+    got = attention.prefill_attention(q, k, v)
+    torch.cuda.synchronize()
+    assert gemm.pipeline_status() == 0
+    want = attention.prefill_attention_reference(q, k, v)
+    assert (got.float() - want.float()).abs().max().item() <= 3e-2

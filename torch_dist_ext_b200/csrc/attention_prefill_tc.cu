@@ -1,0 +1,366 @@
+// Causal self-attention for the prompt phase on the tensor cores (tcgen05 / TMEM), head dimension 128,
+// bf16, grouped-query heads. One CTA owns 128 consecutive query positions of one query head and walks
+// the key/value positions 0 .. (its last query) in chunks of 128:
+//
+//   S[q 128, keys 128] = Q[q, d] * K[keys, d]^T        both operands K-major, as TMA delivers them
+//   O[q 128, d 128]   += P[q, keys] * V[keys, d]        P written by the softmax warps (K-major over keys),
+//                                                       V read MN-major (d contiguous) straight from its TMA tile
+//
+// The four softmax warps hold one query row per thread: the row maximum, the row sum and the 128
+// running outputs of the row live in that thread's registers, so the online softmax needs no
+// cross-thread reduction at all. S is double-buffered in tensor memory (the scores of chunk c+1 are
+// computed while chunk c is in the softmax), the P*V product of a chunk goes to its own TMEM buffer
+// and is folded into the registers with the rescale factor of the row. A fifth warp issues the TMA
+// copies (2-stage ring of K and V chunks, the Q tile once) and all MMAs.
+//
+// Every wait is bounded; a wait that runs out records a status word and raises the CTA's abort flag,
+// and all threads still reach the common exit. Opt-in (models/llama.py uses it for prefill when
+// TDX_PREFILL_ATTN=tc; the default is PyTorch's scaled_dot_product_attention).
+// Not part of the reference (it has no attention).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cfloat>
+#include <mutex>
+#include <set>
+#include <string>
+#include "tdx/comm.h"
+#include "tdx/ops.h"
+#include "tdx/tc.cuh"
+
+namespace tdx {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kRows = 128;                        // query rows per CTA = key positions per chunk
+constexpr int kStages = 2;
+constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = kSoftmaxThreads + 32;
+constexpr int kHalfBytes = kRows * 128;           // one 64-column half of a 128-row tile
+constexpr int kTileBytes = 2 * kHalfBytes;        // Q, P, one K chunk or one V chunk
+constexpr int kStageBytes = 2 * kTileBytes;       // K chunk + V chunk
+constexpr int kSmem = kStages * kStageBytes + 2 * kTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+constexpr uint32_t kTmemCols = 512;               // S buffers at columns 0 and 128, P*V of one chunk at 256
+constexpr uint32_t kColPV = 256;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+struct PrefillArgs {
+  __nv_bfloat16* out;          // [S, Hq, D] contiguous
+  int S, Hq, Hkv;
+  float scale_log2;            // softmax scale * log2(e)
+  uint32_t idesc_s, idesc_pv;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(tc::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// Operand read MN-major from a tile that TMA wrote as [rows = K index][128 bytes of the MN index] with
+// the 128-byte swizzle: eight K rows of a 64-element MN slice are 1024 bytes apart from the next eight
+// (stride offset); the next 64-element MN slice starts `mn_slice_bytes` further (leading offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_slice_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((mn_slice_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_tile = ring + kStages * kStageBytes;
+  uint8_t* p_tile = q_tile + kTileBytes;
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(p_tile + kTileBytes);
+  uint64_t* kv_free = kv_full + kStages;
+  uint64_t* s_full = kv_free + kStages;     // [2]
+  uint64_t* s_free = s_full + 2;            // [2]
+  uint64_t* q_full = s_free + 2;
+  uint64_t* p_full = q_full + 1;
+  uint64_t* o_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  // the blocks with the most key chunks start first
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y;
+  const int hkv = h / (a.Hq / a.Hkv);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int q0 = qb * kRows;
+  const int nchunks = qb + 1;               // key positions 0 .. q0 + 127 (causal)
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&kv_full[s], 1);
+      tc::mbar_init(&kv_free[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&s_full[i], 1);
+      tc::mbar_init(&s_free[i], kSoftmaxThreads);
+    }
+    tc::mbar_init(q_full, 1);
+    tc::mbar_init(p_full, kSoftmaxThreads);
+    tc::mbar_init(o_full, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::tma_prefetch_desc(&map_q);
+    tc::tma_prefetch_desc(&map_k);
+    tc::tma_prefetch_desc(&map_v);
+  }
+  if (warp == 4) {
+    tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  tc::fence_after_thread_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&]() {
+    *abort_flag = 1;
+    if (a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
+  };
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---- copies and MMAs ----
+      auto issue_copy = [&](int c) {
+        const int st = c % kStages;
+        uint8_t* base = ring + st * kStageBytes;
+        tc::mbar_arrive_expect_tx(&kv_full[st], kStageBytes);
+        tma_load_3d(base, &map_k, &kv_full[st], 0, hkv, c * kRows);
+        tma_load_3d(base + kHalfBytes, &map_k, &kv_full[st], 64, hkv, c * kRows);
+        tma_load_3d(base + kTileBytes, &map_v, &kv_full[st], 0, hkv, c * kRows);
+        tma_load_3d(base + kTileBytes + kHalfBytes, &map_v, &kv_full[st], 64, hkv, c * kRows);
+      };
+      auto issue_scores = [&](int c) {   // S[buf c & 1] = Q * K chunk^T
+        const uint32_t kbase = tc::smem_u32(ring + (c % kStages) * kStageBytes);
+        const uint32_t qbase = tc::smem_u32(q_tile);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            tc::umma<false>(tmem_base + (uint32_t)(c & 1) * kRows, tc::make_smem_desc_sw128(qbase + kb * kHalfBytes) + (uint64_t)(ks * 2),
+                            tc::make_smem_desc_sw128(kbase + kb * kHalfBytes) + (uint64_t)(ks * 2), a.idesc_s, (kb | ks) ? 1u : 0u);
+        tc::umma_commit(&s_full[c & 1]);
+      };
+      auto issue_pv = [&](int c) {       // P*V of one chunk, 16 key positions per instruction
+        const uint32_t vbase = tc::smem_u32(ring + (c % kStages) * kStageBytes + kTileBytes);
+        const uint32_t pbase = tc::smem_u32(p_tile);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          tc::umma<false>(tmem_base + kColPV, tc::make_smem_desc_sw128(pbase + (j >> 2) * kHalfBytes) + (uint64_t)((j & 3) * 2),
+                          make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes), a.idesc_pv, j ? 1u : 0u);
+        tc::umma_commit(o_full);
+        tc::umma_commit(&kv_free[c % kStages]);
+      };
+      tc::mbar_arrive_expect_tx(q_full, kTileBytes);
+      tma_load_3d(q_tile, &map_q, q_full, 0, h, q0);
+      tma_load_3d(q_tile + kHalfBytes, &map_q, q_full, 64, h, q0);
+      for (int c = 0; c < nchunks && c < kStages; ++c) issue_copy(c);
+      bool ok = tc::mbar_wait(q_full, 0, kWaitLimit, abort_flag) && tc::mbar_wait(&kv_full[0], 0, kWaitLimit, abort_flag);
+      if (ok) {
+        tc::fence_after_thread_sync();
+        issue_scores(0);
+      }
+      for (int i = 0; i < nchunks && ok; ++i) {
+        if (i + 1 < nchunks) {
+          const int n = i + 1;
+          ok = tc::mbar_wait(&kv_full[n % kStages], (n / kStages) & 1, kWaitLimit, abort_flag) &&
+               (n < 2 || tc::mbar_wait(&s_free[n & 1], ((n >> 1) - 1) & 1, kWaitLimit, abort_flag));
+          if (!ok) break;
+          tc::fence_after_thread_sync();
+          issue_scores(n);
+        }
+        ok = tc::mbar_wait(p_full, i & 1, kWaitLimit, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        issue_pv(i);
+        if (i + kStages < nchunks) {
+          ok = tc::mbar_wait(&kv_free[i % kStages], (i / kStages) & 1, kWaitLimit, abort_flag);
+          if (!ok) break;
+          issue_copy(i + kStages);
+        }
+      }
+      if (!ok) fail();
+    }
+  } else {
+    // ---- softmax warps: thread t owns query row q0 + t ----
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const int q_pos = q0 + tid;
+    float m_run = -FLT_MAX, l_run = 0.f;
+    float o[kD];
+#pragma unroll
+    for (int j = 0; j < kD; ++j) o[j] = 0.f;
+    bool ok = true;
+    for (int i = 0; i < nchunks && ok; ++i) {
+      const int buf = i & 1;
+      ok = tc::mbar_wait(&s_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag);
+      if (!ok) break;
+      tc::fence_after_thread_sync();
+      const uint32_t s_addr = lane_addr + (uint32_t)buf * kRows;
+      const int key0 = i * kRows;
+      const bool diagonal = i == nchunks - 1;   // only the last chunk crosses the causal boundary
+      // pass 1: row maximum (in units of log2: scores are multiplied by scale * log2 e)
+      float cmax = -FLT_MAX;
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        float sv[16];
+        tc::tmem_ld_16(s_addr + cc * 16, sv);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const bool live = !diagonal || key0 + cc * 16 + j <= q_pos;
+          cmax = fmaxf(cmax, live ? sv[j] * a.scale_log2 : -FLT_MAX);
+        }
+      }
+      const float m_new = fmaxf(m_run, cmax);   // the diagonal element is always live, so m_new is finite
+      const float corr = exp2f(m_run - m_new);
+      // pass 2: probabilities, row sum, P tile (bf16, K-major over the key positions, 128-byte swizzle)
+      float psum = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        float sv[16];
+        tc::tmem_ld_16(s_addr + cc * 16, sv);
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          const bool live0 = !diagonal || key0 + cc * 16 + j <= q_pos;
+          const bool live1 = !diagonal || key0 + cc * 16 + j + 1 <= q_pos;
+          const float p0 = live0 ? exp2f(sv[j] * a.scale_log2 - m_new) : 0.f;
+          const float p1 = live1 ? exp2f(sv[j + 1] * a.scale_log2 - m_new) : 0.f;
+          psum += p0 + p1;
+          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+          w[j >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        // 16 key positions = two 16-byte chunks of this row inside K block (cc / 4)
+        uint8_t* row = p_tile + (cc >> 2) * kHalfBytes + tid * 128;
+        const int c0 = (cc & 3) * 2;
+        *reinterpret_cast<uint4*>(row + (((c0) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(row + (((c0 + 1) ^ (tid & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      tc::fence_before_thread_sync();
+      tc::mbar_arrive(&s_free[buf]);
+      tc::fence_proxy_async();          // P was written by threads and is read by the tensor core
+      tc::mbar_arrive(p_full);
+      l_run = l_run * corr + psum;
+      m_run = m_new;
+      ok = tc::mbar_wait(o_full, i & 1, kWaitLimit, abort_flag);
+      if (!ok) break;
+      tc::fence_after_thread_sync();
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        float pv[16];
+        tc::tmem_ld_16(lane_addr + kColPV + cc * 16, pv);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[cc * 16 + j] = fmaf(o[cc * 16 + j], corr, pv[j]);
+      }
+      tc::fence_before_thread_sync();
+    }
+    if (!ok) fail();
+    if (ok && q_pos < a.S) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(a.out + ((int64_t)q_pos * a.Hq + h) * kD);
+#pragma unroll
+      for (int c = 0; c < kD / 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 hh = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
+          w[j] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+
+  tc::fence_before_thread_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);   // copies already issued land before shared memory goes away
+  }
+  if (warp == 4) {
+    tc::fence_after_thread_sync();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encoder() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// [S, heads, 128] bf16 with row pitch `stride_s` elements -> 3-D map (128, heads, S); box = 64 columns x 128 rows of one head
+std::string rows_map(CUtensorMap* map, const void* ptr, int S, int heads, int64_t stride_s, const char* what) {
+  EncodeFn enc = encoder();
+  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
+  if (reinterpret_cast<uintptr_t>(ptr) % 16 || (stride_s * 2) % 16) return std::string(what) + " rows must be 16-byte aligned";
+  const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)S};
+  const cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)stride_s * 2};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)kRows};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? "" : std::string("cuTensorMapEncodeTiled failed for ") + what + " (CUresult " + std::to_string((int)r) + ")";
+}
+
+}  // namespace
+
+std::string attention_prefill_tc(const void* q, const void* k, const void* v, void* out, int S, int Hq, int Hkv, int D,
+                                 int64_t q_stride_s, int64_t k_stride_s, int64_t v_stride_s, float scale, cudaStream_t stream,
+                                 uint32_t* status) {
+  if (D != kD) return "prefill attention supports head dimension 128";
+  if (Hkv <= 0 || Hq % Hkv) return "query heads must be a multiple of KV heads";
+  if (S <= 0) return "";
+  PrefillArgs a{};
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.S = S; a.Hq = Hq; a.Hkv = Hkv;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.idesc_s = tc::make_idesc(kRows, kRows, 1, 1);                  // both operands K-major bf16
+  a.idesc_pv = tc::make_idesc(kRows, kD, 1, 1) | (1u << 16);       // B (the V chunk) is read MN-major
+  a.status = status;
+  CUtensorMap mq, mk, mv;
+  std::string err = rows_map(&mq, q, S, Hq, q_stride_s, "q");
+  if (!err.empty()) return err;
+  err = rows_map(&mk, k, S, Hkv, k_stride_s, "k");
+  if (!err.empty()) return err;
+  err = rows_map(&mv, v, S, Hkv, v_stride_s, "v");
+  if (!err.empty()) return err;
+  auto kern = attn_prefill_tc_kernel;
+  static std::mutex mu;
+  static std::set<int> done;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done.count(dev)) {
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+      if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
+      done.insert(dev);
+    }
+  }
+  const dim3 grid((S + kRows - 1) / kRows, Hq, 1);
+  kern<<<grid, kThreads, kSmem, stream>>>(mq, mk, mv, a);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : cudaGetErrorString(e);
+}
+
+}  // namespace tdx

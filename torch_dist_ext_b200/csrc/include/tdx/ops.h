@@ -41,4 +41,12 @@ std::string attention_decode_tc(const void* q, const void* k_cache, const void* 
                                 int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,
                                 cudaStream_t stream, uint32_t* status = nullptr);
 
+// Causal self-attention over one prompt on the tensor cores (attention_prefill_tc.cu): q [S, Hq, 128],
+// k / v [S, Hkv, 128] bf16 with unit stride inside a head, heads 128 elements apart and rows `*_stride_s`
+// elements apart (views into a fused qkv projection are fine); out [S, Hq, 128] contiguous. Query i
+// attends to keys 0 .. i.
+std::string attention_prefill_tc(const void* q, const void* k, const void* v, void* out, int S, int Hq, int Hkv, int D,
+                                 int64_t q_stride_s, int64_t k_stride_s, int64_t v_stride_s, float scale, cudaStream_t stream,
+                                 uint32_t* status = nullptr);
+
 }  // namespace tdx

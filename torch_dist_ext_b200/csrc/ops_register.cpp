@@ -221,6 +221,25 @@ void attention_decode_tc(const Tensor& q, const Tensor& k_cache, const Tensor& v
   attention_decode_impl(q, k_cache, v_cache, seq_lens, out, partial, nsplit, scale, status, true);
 }
 
+// Causal attention over one prompt, both products on the tensor cores (tcgen05).
+void attention_prefill_tc(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, double scale,
+                          const c10::optional<Tensor>& status) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "attention_prefill_tc: q [S, Hq, D], k / v [S, Hkv, D]");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 &&
+                  out.scalar_type() == at::kBFloat16, "attention_prefill_tc: bfloat16 tensors");
+  auto dense_heads = [](const Tensor& t) { return t.stride(2) == 1 && t.stride(1) == t.size(2); };
+  TORCH_CHECK(dense_heads(q) && dense_heads(k) && dense_heads(v) && out.is_contiguous(),
+              "attention_prefill_tc: heads densely packed inside a row, out contiguous");
+  TORCH_CHECK(k.size(0) == q.size(0) && v.sizes() == k.sizes() && out.numel() == q.size(0) * q.size(1) * q.size(2),
+              "attention_prefill_tc: shapes disagree");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const std::string err = tdx::attention_prefill_tc(
+      q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), (int)q.size(0), (int)q.size(1), (int)k.size(1), (int)q.size(2),
+      q.stride(0), k.stride(0), v.stride(0), (float)scale, cur_stream(),
+      status.has_value() && status->defined() ? reinterpret_cast<uint32_t*>(status->data_ptr<int>()) : nullptr);
+  TORCH_CHECK(err.empty(), "attention_prefill_tc: ", err);
+}
+
 static tdx::Workspace* workspace_of(const Tensor& table) {
   TORCH_CHECK(table.is_cuda(), "workspace must be the CUDA tensor returned by get_workspace");
   tdx::Workspace* ws = tdx::Workspace::from_table(table.data_ptr());
@@ -324,6 +343,8 @@ void register_extra_ops(torch::Library& m) {
         "int nsplit, float scale, Tensor(c!)? status) -> ()", &attention_decode);
   m.def("attention_decode_tc(Tensor q, Tensor k_cache, Tensor v_cache, Tensor seq_lens, Tensor(a!) out, Tensor(b!) partial, "
         "int nsplit, float scale, Tensor(c!)? status) -> ()", &attention_decode_tc);
+  m.def("attention_prefill_tc(Tensor q, Tensor k, Tensor v, Tensor(a!) out, float scale, Tensor(b!)? status) -> ()",
+        &attention_prefill_tc);
   m.def("ag_gemm(Tensor x_shard, Tensor w, Tensor(a!) out, int tokens, Tensor workspace, Tensor(b!)? status) -> ()", &ag_gemm);
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "

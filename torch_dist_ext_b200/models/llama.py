@@ -23,6 +23,7 @@ checkpoint format.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -34,6 +35,9 @@ from ..ops.fused_allreduce import fused_allreduce_rms
 from ..parallel import comm as _comm
 from ..utils.config import OUT_FP8_BLOCK128, OUT_SAME
 from ..utils.tracing import nvtx_range, traced
+
+# prompt-phase attention: "tc" = this library's tcgen05 kernel (opt-in), anything else = PyTorch's SDPA
+_PREFILL_ATTN_TC = os.environ.get("TDX_PREFILL_ATTN", "sdpa").lower() == "tc"
 
 
 @dataclass
@@ -278,7 +282,8 @@ class TPLlama:
 
         GEMMs and the fused all-reduce+norm run on this library's kernels (normal-orientation
         tcgen05 tiles, two-shot / NVLS all-reduce); causal attention over the prompt uses PyTorch's
-        scaled_dot_product_attention. Returns the first generated token."""
+        scaled_dot_product_attention, or this library's tcgen05 kernel with ``TDX_PREFILL_ATTN=tc``.
+        Returns the first generated token."""
         cfg, d = self.cfg, self.cfg.head_dim
         assert self.mode == "ar", "prefill is implemented for the replicated (all-reduce) mode"
         s = token_ids.shape[0]
@@ -293,9 +298,12 @@ class TPLlama:
             rope.rope_(q, k, positions, self.cos_sin)
             self.k_cache[i][seq_index, :s] = k
             self.v_cache[i][seq_index, :s] = v
-            attn = torch.nn.functional.scaled_dot_product_attention(
-                q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0),
-                is_causal=True, enable_gqa=True).squeeze(0).transpose(0, 1).reshape(s, self.hq * d)
+            if _PREFILL_ATTN_TC:
+                attn = attention.prefill_attention(q, k, v).view(s, self.hq * d)
+            else:
+                attn = torch.nn.functional.scaled_dot_product_attention(
+                    q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0),
+                    is_causal=True, enable_gqa=True).squeeze(0).transpose(0, 1).reshape(s, self.hq * d)
             y = L["wo"](attn.contiguous())
             last = i + 1 == cfg.n_layers
             x, res, x_scale = fused_allreduce_rms(y, res, L["ln2"], cfg.eps, out_mode=self._norm_out_mode())

@@ -53,6 +53,27 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
+@traced("tdx.prefill_attention")
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal self-attention over one prompt on the tensor cores: ``q [S, Hq, 128]``, ``k``/``v`` ``[S, Hkv, 128]``
+    (views into a fused qkv projection are fine) -> ``[S, Hq, 128]``; query i attends to keys 0..i."""
+    s, hq, d = q.shape
+    out = torch.empty(s, hq, d, dtype=q.dtype, device=q.device) if out is None else out
+    from . import gemm as _gemm
+
+    _lib.ops().attention_prefill_tc(q, k, v, out, 1.0 / math.sqrt(d), _gemm._workspace(q.device)[2])
+    return out
+
+
+def prefill_attention_reference(q, k, v):
+    hq, hkv = q.shape[1], k.shape[1]
+    kk = k.float().repeat_interleave(hq // hkv, dim=1)
+    vv = v.float().repeat_interleave(hq // hkv, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q.float(), kk) / math.sqrt(q.shape[-1])
+    s = s.masked_fill(torch.ones(q.shape[0], q.shape[0], dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(s, dim=-1), vv).to(q.dtype)
+
+
 def decode_attention_reference(q, k_cache, v_cache, seq_lens):
     b, hq, d = q.shape
     hkv = k_cache.shape[2]
