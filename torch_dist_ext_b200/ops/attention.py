@@ -1,4 +1,6 @@
-"""Decode attention (one new token per sequence) over a contiguous bf16 KV cache, grouped-query heads."""
+"""Attention for grouped-query heads of dimension 128: decode (one new token per sequence over a
+contiguous bf16 KV cache; SIMT kernel, or tcgen05 kernel on request) and causal attention over one
+prompt (tcgen05 kernel)."""
 from __future__ import annotations
 
 import math
