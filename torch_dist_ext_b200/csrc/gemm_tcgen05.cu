@@ -270,7 +270,7 @@ std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs&
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
 }
 
-// TDX_GEMM_CTAS_PER_SM=2 halves the operand ring of the narrow tiles so that two CTAs share an SM:
+// TDX_GEMM_CTAS_PER_SM=2 halves the operand ring of the tiles up to 128 columns so that two CTAs share an SM:
 // a weight-streaming grid of up to 296 tiles is then resident at once and its CTAs finish together,
 // instead of a full wave followed by a partly filled one. Default 1 (the measured configuration).
 bool two_ctas_per_sm() {
@@ -288,6 +288,9 @@ std::string launch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, cons
       case 16: return launch<16, 5, kFp8, kScaled>(mx, my, a, grid, s);
       case 32: return launch<32, 4, kFp8, kScaled>(mx, my, a, grid, s);
       case 64: return launch<64, 4, kFp8, kScaled>(mx, my, a, grid, s);
+      case 128:   // 3 x 32 KB per CTA: the epilogue of one CTA overlaps the main loop of the other
+        if constexpr (!kScaled) return launch<128, 3, kFp8, kScaled>(mx, my, a, grid, s);
+        break;
     }
   }
   switch (bn) {
