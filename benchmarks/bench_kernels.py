@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Single-GPU roofline table of the library's kernels (no communication).
 
-    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_fp8|attention|attention_tc|elementwise|all] [--steps 30]
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_persist|gemm_fp8|attention|attention_tc|elementwise|all] [--steps 30]
 
 Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
 over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
@@ -60,7 +60,7 @@ def row(name, us, lib_us, nbytes, flops, hbm, tf, src):
             "TFLOP/s": round(tfl, 1), f"frac_bf16_of_{src}": round(tfl / tf, 3)}
 
 
-def gemm_cases(dev, steps, shapes, ms, out, cta_pair=False):
+def gemm_cases(dev, steps, shapes, ms, out, cta_pair=False, persistent=False):
     from torch_dist_ext_b200.ops import gemm
 
     hbm, tf, src = peaks()
@@ -68,14 +68,14 @@ def gemm_cases(dev, steps, shapes, ms, out, cta_pair=False):
         ws = rotating(lambda: torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02, n * k * 2)
         for m in ms:
             a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
-            if cta_pair:   # a new kernel: check it before timing it
-                err = (gemm.linear(a, ws[0], cta_pair=True).float() - gemm.linear(a, ws[0], cta_pair=False).float()).abs().max().item()
+            if cta_pair or persistent:   # a new kernel: check it before timing it
+                err = (gemm.linear(a, ws[0], cta_pair=cta_pair, persistent=persistent).float() - gemm.linear(a, ws[0]).float()).abs().max().item()
                 if err > 0.05 or gemm.pipeline_status() != 0:
-                    raise SystemExit(f"two-CTA GEMM disagrees with the one-CTA kernel (max err {err}, status {gemm.pipeline_status()})")
-            us = time_us(lambda i: gemm.linear(a, ws[i], cta_pair=cta_pair), len(ws), steps)
+                    raise SystemExit(f"opt-in GEMM disagrees with the default kernel (max err {err}, status {gemm.pipeline_status()})")
+            us = time_us(lambda i: gemm.linear(a, ws[i], cta_pair=cta_pair, persistent=persistent), len(ws), steps)
             lib = time_us(lambda i: torch.matmul(a, ws[i].t()), len(ws), steps)
             nbytes = (n * k + m * k + m * n) * 2
-            tag = "gemm bf16 (CTA pairs)" if cta_pair else "gemm bf16"
+            tag = "gemm bf16 (CTA pairs)" if cta_pair else "gemm bf16 (persistent)" if persistent else "gemm bf16"
             out.append(row(f"{tag} m={m} n={n} k={k}", us, lib, nbytes, 2.0 * m * n * k, hbm, tf, src))
             print(out[-1], flush=True)
         del ws
@@ -185,6 +185,8 @@ def main():
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out)
     if g == "gemm_pair":            # opt-in kernel: 256 x 256 tiles on CTA pairs (not part of "all")
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out, cta_pair=True)
+    if g == "gemm_persist":         # opt-in kernel: persistent grid, double-buffered accumulator (not part of "all")
+        gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out, persistent=True)
     if g in ("gemm_fp8", "all"):
         gemm_fp8_cases(dev, args.steps, out)
     if g in ("attention", "all"):

@@ -1,0 +1,36 @@
+"""The persistent tcgen05 GEMM (one CTA per SM walks the tiles, double-buffered accumulator) against
+fp32 PyTorch math and against the one-tile-per-CTA kernel.
+
+Opt-in: the kernel is off by default in the library, and this file runs only with
+TDX_TEST_GEMM_PERSIST=1 until the kernel has been brought up on hardware (compiled and desk-checked
+only; unlike the CTA-pair kernel it uses only instruction forms that the default kernel already uses).
+Shapes cover fewer tiles than SMs, several tiles per CTA (accumulator buffers reused), ragged M and N,
+one K block, and K loops longer than the operand ring."""
+import os
+
+import pytest
+import torch
+
+from torch_dist_ext_b200.ops import gemm
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("TDX_TEST_GEMM_PERSIST") != "1",
+                                 reason="persistent GEMM is opt-in (TDX_TEST_GEMM_PERSIST=1) until validated on hardware")]
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (256, 512, 1024), (300, 520, 512), (2048, 4096, 256), (4096, 28672, 128),
+                                   (1024, 256, 8192)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_persistent_gemm_matches_fp32(m, n, k, dtype):
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(dtype)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.5).to(dtype)
+    out = gemm.linear(a, w, persistent=True)
+    torch.cuda.synchronize()
+    assert gemm.pipeline_status() == 0
+    base = gemm.linear(a, w, persistent=False, splits=1)
+    # same products accumulated in fp32 in the same K order: at most a last-bit difference of the output type
+    assert torch.allclose(out.float(), base.float(), rtol=1e-2, atol=1e-2)
+    if m * n * k <= 1 << 32:
+        ref = a.float() @ w.float().t()
+        assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2

@@ -35,6 +35,10 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream);
 // Same product on 256 x 256 tiles computed by CTA pairs (tcgen05.mma.cta_group::2, gemm_pair.cu). Unscaled
 // operands, no split-K; block_n, splits and the scratch fields are ignored.
 std::string gemm_tn_pair(const GemmProblem& g, cudaStream_t stream);
+// Same product by a persistent grid (one CTA per SM walks the 128 x 256 tiles, the accumulator double-buffered in
+// tensor memory so that the epilogue of a tile overlaps the main loop of the next; gemm_persist.cu). Unscaled
+// operands, no split-K; block_n, splits and the scratch fields are ignored.
+std::string gemm_tn_persistent(const GemmProblem& g, cudaStream_t stream);
 
 // Row-parallel linear fused with reduce(-scatter) + residual + RMSNorm (gemm_fused.cu).
 // `ar` carries the communication state (Workspace::fill_params) and describes the tail: tokens,

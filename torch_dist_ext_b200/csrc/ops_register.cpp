@@ -191,6 +191,14 @@ void gemm_tn_pair(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int6
   TORCH_CHECK(err.empty(), "gemm_tn_pair: ", err);
 }
 
+// The same product by a persistent grid with the accumulator double-buffered in tensor memory.
+void gemm_tn_persistent(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, const c10::optional<Tensor>& status) {
+  tdx::GemmProblem g = gemm_problem(x, y, out, sx, sy, status);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const std::string err = tdx::gemm_tn_persistent(g, cur_stream());
+  TORCH_CHECK(err.empty(), "gemm_tn_persistent: ", err);
+}
+
 static void attention_decode_impl(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seq_lens, Tensor& out,
                                   Tensor& partial, int64_t nsplit, double scale, const c10::optional<Tensor>& status,
                                   bool tensor_cores) {
@@ -350,6 +358,7 @@ void register_extra_ops(torch::Library& m) {
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
         "bool y_scale_per_row) -> ()", &gemm_tn);
   m.def("gemm_tn_pair(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_pair);
+  m.def("gemm_tn_persistent(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_persistent);
   m.def("fused_add_rmsnorm(Tensor x, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
         "Tensor(c!)? scale_out, float eps, int out_mode) -> int", &fused_add_rmsnorm);
   m.def("quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) scales, bool block128) -> ()", &quant_fp8);

@@ -23,6 +23,7 @@ _ws = {}
 
 
 _PAIR_DEFAULT = os.environ.get("TDX_GEMM_PAIR", "0") not in ("0", "", "false", "off")
+_PERSIST_DEFAULT = os.environ.get("TDX_GEMM_PERSIST", "0") not in ("0", "", "false", "off")
 
 
 def _workspace(device: torch.device):
@@ -67,11 +68,13 @@ def plan(m: int, n: int, k: int, elem_size: int = 2, scaled: bool = False) -> Tu
 @traced("tdx.linear")
 def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *, out_dtype=None,
            swap: Optional[bool] = None, block_n: int = 0, splits: Optional[int] = None,
-           cta_pair: Optional[bool] = None) -> torch.Tensor:
+           cta_pair: Optional[bool] = None, persistent: Optional[bool] = None) -> torch.Tensor:
     """``a [M, K] @ w [N, K]^T -> [M, N]`` (bf16 / fp16 / e4m3 operands, fp32 accumulation).
 
     ``cta_pair=True`` runs prefill-sized problems (M, N >= 256) on 256 x 256 tiles computed by pairs of
-    CTAs (``tcgen05.mma.cta_group::2``); the default follows ``TDX_GEMM_PAIR`` (off)."""
+    CTAs (``tcgen05.mma.cta_group::2``); the default follows ``TDX_GEMM_PAIR`` (off). ``persistent=True`` runs
+    them on a persistent grid (one CTA per SM, accumulator double-buffered in tensor memory so that the epilogue
+    of a tile overlaps the main loop of the next); the default follows ``TDX_GEMM_PERSIST`` (off)."""
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "linear: a [M, K], w [N, K]"
     m, k = a.shape
     n = w.shape[0]
@@ -80,6 +83,12 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
             dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
             out = torch.empty(m, n, dtype=dt, device=a.device)
         _lib.ops().gemm_tn_pair(a, w, out, n, 1, _workspace(a.device)[2])
+        return out
+    if (_PERSIST_DEFAULT if persistent is None else persistent) and m > 128 and n >= 256 and not swap and splits in (None, 1):
+        if out is None:
+            dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
+            out = torch.empty(m, n, dtype=dt, device=a.device)
+        _lib.ops().gemm_tn_persistent(a, w, out, n, 1, _workspace(a.device)[2])
         return out
     p_swap, p_bn, p_splits = plan(m, n, k, a.element_size())
     swap = p_swap if swap is None else swap
