@@ -1,0 +1,300 @@
+"""Randomised interleaving checks of the mbarrier pipelines of the tcgen05 kernels (models, no GPU).
+
+The kernels synchronise their roles (TMA producer, MMA thread, epilogue / softmax warps) with
+mbarriers that are waited on by PHASE PARITY. The parity expressions - ``(it / stages) & 1``,
+``((it / stages) - 1) & 1``, ``((n >> 1) - 1) & 1`` and friends - are the classic place for an
+off-by-one that shows up on hardware as a hang or as a tile computed from the wrong data. These
+models replay the role programs of
+
+ * the persistent GEMM (csrc/gemm_persist.cu): operand ring that runs across tile boundaries,
+   two accumulator buffers handed between the MMA thread and the epilogue warps;
+ * the tensor-core attention kernels (csrc/attention_decode_tc.cu, attention_prefill_tc.cu):
+   K/V ring, double-buffered scores, one probability tile, one P*V buffer
+
+with the same parity expressions, under random schedules in which TMA completions and MMA
+completions (tcgen05.commit arrivals) land late and at arbitrary moments, and check that every
+consumer sees exactly the data it expects, that no buffer is overwritten before its reader is
+done, and that nothing deadlocks. An mbarrier is modelled as the PTX ISA describes
+mbarrier.try_wait.parity: the wait for parity p succeeds iff the barrier's current (incomplete) phase
+has the other parity.
+"""
+import random
+
+import pytest
+
+
+class MBar:
+    def __init__(self, count):
+        self.count, self.pending, self.completed = count, count, 0
+
+    def arrive(self):
+        self.pending -= 1
+        assert self.pending >= 0, "more arrivals than the barrier expects in one phase"
+        if self.pending == 0:
+            self.completed += 1
+            self.pending = self.count
+
+    def ready(self, parity):
+        return parity != (self.completed & 1)
+
+
+def run(actors, events, rng, max_steps=200000):
+    """`actors`: generators that yield ("wait", bar, parity) until the wait can pass, or ("step",).
+    `events`: list of pending asynchronous completions (callables), drained in random order per queue."""
+    live = {i: a for i, a in enumerate(actors)}
+    blocked = {}
+    for _ in range(max_steps):
+        if not live and not any(events.values()):
+            return
+        choices = []
+        for i in live:
+            w = blocked.get(i)
+            if w is None or w[0].ready(w[1]):
+                choices.append(("actor", i))
+        for q, lst in events.items():
+            if lst:
+                choices.append(("event", q))
+        assert choices, f"deadlock: actors {sorted(live)} blocked, no completion pending"
+        kind, key = rng.choice(choices)
+        if kind == "event":
+            events[key].pop(0)()
+            continue
+        blocked.pop(key, None)
+        try:
+            req = next(live[key])
+        except StopIteration:
+            del live[key]
+            continue
+        if req[0] == "wait" and not req[1].ready(req[2]):
+            blocked[key] = (req[1], req[2])
+            # the generator re-yields the same wait when resumed: see wait() below
+    raise AssertionError("did not finish")
+
+
+def wait(bar, parity):
+    while not bar.ready(parity):
+        yield ("wait", bar, parity)
+
+
+# ---- persistent GEMM ------------------------------------------------------------------------------
+
+def persistent_gemm(ntiles_of_cta, nkb, stages, rng):
+    full = [MBar(1) for _ in range(stages)]
+    empty = [MBar(1) for _ in range(stages)]
+    acc_full = [MBar(1) for _ in range(2)]
+    n_epi = 2                                            # stands for the 128 epilogue threads
+    acc_empty = [MBar(n_epi) for _ in range(2)]
+    stage_data = [None] * stages
+    stage_busy = [False] * stages                        # an MMA that read the stage has not completed yet
+    acc = [None, None]                                   # (tile, list of k blocks) accumulated so far
+    acc_readers = [0, 0]
+    done_tiles = []
+    events = {"tma": [], "mma": []}
+
+    def producer():
+        it = 0
+        for t in range(ntiles_of_cta):
+            for kb in range(nkb):
+                s = it % stages
+                if it >= stages:
+                    yield from wait(empty[s], ((it // stages) - 1) & 1)
+                assert not stage_busy[s], "stage overwritten while an MMA still reads it"
+
+                def land(s=s, tag=(t, kb)):
+                    stage_data[s] = tag
+                    full[s].arrive()
+                events["tma"].append(land)
+                it += 1
+                yield ("step",)
+
+    def mma():
+        it = 0
+        for n in range(ntiles_of_cta):
+            buf = n & 1
+            if n >= 2:
+                yield from wait(acc_empty[buf], ((n >> 1) - 1) & 1)
+            assert acc_readers[buf] == 0, "accumulator overwritten while the epilogue reads it"
+            for kb in range(nkb):
+                s = it % stages
+                yield from wait(full[s], (it // stages) & 1)
+                assert stage_data[s] == (n, kb), f"MMA read {stage_data[s]} instead of {(n, kb)}"
+                stage_busy[s] = True
+                acc[buf] = (n, [kb]) if kb == 0 else (acc[buf][0], acc[buf][1] + [kb])
+
+                def retire(s=s):
+                    stage_busy[s] = False
+                    empty[s].arrive()
+                events["mma"].append(retire)
+                it += 1
+                yield ("step",)
+            events["mma"].append(acc_full[buf].arrive)
+
+    def epilogue(_who):
+        for n in range(ntiles_of_cta):
+            buf = n & 1
+            yield from wait(acc_full[buf], (n >> 1) & 1)
+            acc_readers[buf] += 1
+            yield ("step",)
+            assert acc[buf] == (n, list(range(nkb))), f"epilogue of tile {n} read {acc[buf]}"
+            acc_readers[buf] -= 1
+            if _who == 0:
+                done_tiles.append(n)
+            acc_empty[buf].arrive()
+
+    run([producer(), mma()] + [epilogue(w) for w in range(n_epi)], events, rng)
+    assert done_tiles == list(range(ntiles_of_cta))
+
+
+@pytest.mark.parametrize("ntiles,nkb,stages", [(1, 1, 4), (1, 9, 4), (2, 3, 4), (5, 1, 4), (5, 6, 4), (7, 2, 3), (4, 13, 4)])
+def test_persistent_gemm_pipeline(ntiles, nkb, stages):
+    for seed in range(60):
+        persistent_gemm(ntiles, nkb, stages, random.Random(seed))
+
+
+# ---- tensor-core attention ------------------------------------------------------------------------
+
+def attention(nchunks, stages, rng):
+    kv_full = [MBar(1) for _ in range(stages)]
+    kv_free = [MBar(1) for _ in range(stages)]
+    s_full = [MBar(1) for _ in range(2)]
+    n_sm = 2                                             # stands for the 128 softmax threads
+    s_free = [MBar(n_sm) for _ in range(2)]
+    p_full = MBar(n_sm)
+    o_full = MBar(1)
+    kv = [None] * stages
+    kv_reads_pending = [0] * stages
+    s_buf = [None, None]
+    s_readers = [0, 0]
+    p_tile = {"chunk": None, "writers": 0, "reads_pending": 0}
+    pv = {"chunk": None, "readers": 0}
+    outputs = [[] for _ in range(n_sm)]
+    events = {"tma": [], "mma": []}
+
+    def copy(c):
+        s = c % stages
+        assert kv_reads_pending[s] == 0, "K/V stage overwritten while an MMA still reads it"
+
+        def land():
+            kv[s] = c
+            kv_full[s].arrive()
+        events["tma"].append(land)
+
+    def issue_scores(c):
+        s = c % stages
+        assert kv[s] == c, f"scores of chunk {c} read stage holding {kv[s]}"
+        assert s_readers[c & 1] == 0, "score buffer overwritten while the softmax warps read it"
+        kv_reads_pending[s] += 1
+
+        def retire():
+            s_buf[c & 1] = c
+            kv_reads_pending[s] -= 1
+            s_full[c & 1].arrive()
+        events["mma"].append(retire)
+
+    def issue_pv(c):
+        s = c % stages
+        assert kv[s] == c and p_tile["chunk"] == c and p_tile["writers"] == 0
+        assert pv["readers"] == 0, "P*V buffer overwritten while the softmax warps read it"
+        kv_reads_pending[s] += 1
+        p_tile["reads_pending"] += 1
+
+        def retire():
+            pv["chunk"] = c
+            kv_reads_pending[s] -= 1
+            p_tile["reads_pending"] -= 1
+            o_full.arrive()
+            kv_free[s].arrive()
+        events["mma"].append(retire)
+
+    def mma():
+        for c in range(min(nchunks, stages)):
+            copy(c)
+        yield from wait(kv_full[0], 0)
+        issue_scores(0)
+        for i in range(nchunks):
+            if i + 1 < nchunks:
+                n = i + 1
+                yield from wait(kv_full[n % stages], (n // stages) & 1)
+                if n >= 2:
+                    yield from wait(s_free[n & 1], ((n >> 1) - 1) & 1)
+                issue_scores(n)
+                yield ("step",)
+            yield from wait(p_full, i & 1)
+            issue_pv(i)
+            yield ("step",)
+            if i + stages < nchunks:
+                yield from wait(kv_free[i % stages], (i // stages) & 1)
+                copy(i + stages)
+
+    def softmax(who):
+        for i in range(nchunks):
+            buf = i & 1
+            yield from wait(s_full[buf], (i >> 1) & 1)
+            s_readers[buf] += 1
+            yield ("step",)
+            assert s_buf[buf] == i, f"softmax of chunk {i} read scores of {s_buf[buf]}"
+            s_readers[buf] -= 1
+            s_free[buf].arrive()
+            # the P tile is free: P*V of the previous chunk completed before its o_full was seen
+            assert p_tile["chunk"] in (None, i - 1, i) and p_tile["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
+            p_tile["writers"] += 1
+            yield ("step",)
+            p_tile["chunk"] = i
+            p_tile["writers"] -= 1
+            p_full.arrive()
+            yield from wait(o_full, i & 1)
+            pv["readers"] += 1
+            yield ("step",)
+            assert pv["chunk"] == i, f"output update of chunk {i} read P*V of {pv['chunk']}"
+            pv["readers"] -= 1
+            outputs[who].append(i)
+
+    run([mma()] + [softmax(w) for w in range(n_sm)], events, rng)
+    assert all(o == list(range(nchunks)) for o in outputs)
+
+
+@pytest.mark.parametrize("nchunks,stages", [(1, 3), (2, 3), (3, 3), (4, 3), (9, 3), (1, 2), (2, 2), (3, 2), (8, 2)])
+def test_attention_pipeline(nchunks, stages):
+    for seed in range(60):
+        attention(nchunks, stages, random.Random(seed))
+
+
+def test_the_checker_sees_a_wrong_parity():
+    # the same GEMM program with the classic slip in the producer's wait (parity of the current ring pass
+    # instead of the previous one) must deadlock or corrupt data in at least one schedule
+    def broken(rng):
+        stages, nkb, ntiles = 2, 5, 2
+        full = [MBar(1) for _ in range(stages)]
+        empty = [MBar(1) for _ in range(stages)]
+        data = [None] * stages
+        events = {"tma": [], "mma": []}
+
+        def producer():
+            for it in range(ntiles * nkb):
+                s = it % stages
+                if it >= stages:
+                    yield from wait(empty[s], (it // stages) & 1)      # wrong: should be ((it // stages) - 1) & 1
+
+                def land(s=s, it=it):
+                    data[s] = it
+                    full[s].arrive()
+                events["tma"].append(land)
+                yield ("step",)
+
+        def mma():
+            for it in range(ntiles * nkb):
+                s = it % stages
+                yield from wait(full[s], (it // stages) & 1)
+                assert data[s] == it
+                events["mma"].append(empty[s].arrive)
+                yield ("step",)
+
+        run([producer(), mma()], events, rng)
+
+    failures = 0
+    for seed in range(40):
+        try:
+            broken(random.Random(seed))
+        except AssertionError:
+            failures += 1
+    assert failures > 0
