@@ -20,7 +20,11 @@ _LATE = ("test_multigpu.py", "test_cpp_harness_gpu.py", "test_zero_copy_io_gpu.p
 def pytest_collection_modifyitems(config, items):
     import torch
 
-    items.sort(key=lambda it: _LATE.index(it.fspath.basename) + 1 if it.fspath.basename in _LATE else 0)
+    def rank(item):
+        name = os.path.basename(str(getattr(item, "path", None) or item.fspath))
+        return _LATE.index(name) + 1 if name in _LATE else 0
+
+    items.sort(key=rank)
 
     if torch.cuda.is_available():
         return
