@@ -9,7 +9,9 @@ models replay the role programs of
  * the persistent GEMM (csrc/gemm_persist.cu): operand ring that runs across tile boundaries,
    two accumulator buffers handed between the MMA thread and the epilogue warps;
  * the tensor-core attention kernels (csrc/attention_decode_tc.cu, attention_prefill_tc.cu):
-   K/V ring, double-buffered scores, one probability tile, one P*V buffer
+   K/V ring, double-buffered scores, one probability tile, one P*V buffer;
+ * the CTA-pair GEMM (csrc/gemm_pair.cu): two producers crediting the leader's transaction-counting
+   barriers, stages released in both CTAs by the leader's MMA thread
 
 with the same parity expressions, under random schedules in which TMA completions and MMA
 completions (tcgen05.commit arrivals) land late and at arbitrary moments, and check that every
@@ -298,3 +300,89 @@ def test_the_checker_sees_a_wrong_parity():
         except AssertionError:
             failures += 1
     assert failures > 0
+
+
+# ---- CTA-pair GEMM (csrc/gemm_pair.cu) ----------------------------------------------------------------
+# Two CTAs, each with its own ring and producer. Only the LEADER's full[s] barriers are used: the leader's
+# producer arms them for the bytes of both CTAs, and both CTAs' copies credit them - the peer's copy may land
+# BEFORE the leader has armed the barrier for that ring pass (the transaction count goes negative for a while).
+# The leader's MMA thread releases a stage in both CTAs and hands the accumulator to both epilogues.
+
+class TxBar(MBar):
+    """mbarrier with a transaction count: a phase completes when no arrival is pending and tx == 0."""
+
+    def __init__(self, count):
+        super().__init__(count)
+        self.tx = 0
+
+    def _maybe_complete(self):
+        if self.pending == 0 and self.tx == 0:
+            self.completed += 1
+            self.pending = self.count
+
+    def arrive_expect(self, nbytes):
+        self.tx += nbytes
+        self.pending -= 1
+        assert self.pending >= 0
+        self._maybe_complete()
+
+    def complete_tx(self, nbytes):
+        self.tx -= nbytes
+        self._maybe_complete()
+
+
+def pair_gemm(nkb, stages, rng):
+    full = [TxBar(1) for _ in range(stages)]                       # leader's barriers
+    empty = [[MBar(1) for _ in range(stages)] for _ in range(2)]   # per CTA
+    acc_full = [MBar(1), MBar(1)]
+    data = [[None] * stages for _ in range(2)]
+    busy = [[False] * stages for _ in range(2)]
+    got = []
+    events = {"tma0": [], "tma1": [], "mma": []}
+
+    def producer(rank):
+        for i in range(nkb):
+            s = i % stages
+            if i >= stages:
+                yield from wait(empty[rank][s], ((i // stages) - 1) & 1)
+            assert not busy[rank][s], "stage overwritten while the MMA still reads it"
+            if rank == 0:
+                full[s].arrive_expect(2)                            # one unit per CTA
+
+            def land(s=s, i=i):
+                data[rank][s] = i
+                full[s].complete_tx(1)
+            events[f"tma{rank}"].append(land)
+            yield ("step",)
+
+    def mma():
+        for i in range(nkb):
+            s = i % stages
+            yield from wait(full[s], (i // stages) & 1)
+            assert data[0][s] == i and data[1][s] == i, f"K block {i}: stages hold {data[0][s]}, {data[1][s]}"
+            busy[0][s] = busy[1][s] = True
+            got.append(i)
+
+            def retire(s=s):
+                busy[0][s] = busy[1][s] = False
+                empty[0][s].arrive()
+                empty[1][s].arrive()
+            events["mma"].append(retire)
+            yield ("step",)
+
+        def done():
+            acc_full[0].arrive()
+            acc_full[1].arrive()
+        events["mma"].append(done)
+
+    def epilogue(rank):
+        yield from wait(acc_full[rank], 0)
+        assert got == list(range(nkb))
+
+    run([producer(0), producer(1), mma(), epilogue(0), epilogue(1)], events, rng)
+
+
+@pytest.mark.parametrize("nkb,stages", [(1, 6), (6, 6), (7, 6), (25, 6), (9, 2)])
+def test_cta_pair_gemm_pipeline(nkb, stages):
+    for seed in range(80):
+        pair_gemm(nkb, stages, random.Random(seed))
