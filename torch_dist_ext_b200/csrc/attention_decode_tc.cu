@@ -33,6 +33,7 @@
 #include "tdx/ops.h"
 #include "tdx/sync.cuh"
 #include "tdx/tc.cuh"
+#include "tdx/tma_host.h"
 
 namespace tdx {
 namespace {
@@ -326,35 +327,6 @@ __global__ void __launch_bounds__(kD) attn_tc_combine_kernel(const TcAttnArgs a)
   a.out[((int64_t)b * a.Hq + h) * kD + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeFn encoder() {
-  static EncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeFn>(p);
-  }();
-  return fn;
-}
-
-// cache [B, S, Hkv, 128] bf16 -> 4-D map (128, Hkv, S, B); one box = 64 columns x 128 positions of one head
-std::string cache_map(CUtensorMap* map, const void* ptr, int B, int S, int Hkv, int64_t stride_b, int64_t stride_s) {
-  EncodeFn enc = encoder();
-  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
-  const cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)Hkv, (cuuint64_t)S, (cuuint64_t)B};
-  const cuuint64_t strides[3] = {(cuuint64_t)kD * 2, (cuuint64_t)stride_s * 2, (cuuint64_t)stride_b * 2};
-  const cuuint32_t box[4] = {64, 1, (cuuint32_t)kKeys, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? "" : "cuTensorMapEncodeTiled failed for the KV cache (CUresult " + std::to_string((int)r) + ")";
-}
-
 template <int kG>
 std::string launch(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnArgs& a, dim3 grid, cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<kG>;
@@ -404,9 +376,9 @@ std::string attention_decode_tc(const void* q, const void* k_cache, const void* 
   a.idesc_pv = tc::make_idesc(kD, kNq, 1, 1) | (1u << 15);         // A (the V chunk) is read MN-major
   a.status = status;
   CUtensorMap mk, mv;
-  std::string err = cache_map(&mk, k_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s);
+  std::string err = tma::kv_cache_4d(&mk, k_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s, kKeys);
   if (!err.empty()) return err;
-  err = cache_map(&mv, v_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s);
+  err = tma::kv_cache_4d(&mv, v_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s, kKeys);
   if (!err.empty()) return err;
   const dim3 grid(B, Hkv, nsplit);
   switch (G) {

@@ -27,6 +27,7 @@
 #include "tdx/comm.h"
 #include "tdx/ops.h"
 #include "tdx/tc.cuh"
+#include "tdx/tma_host.h"
 
 namespace tdx {
 namespace {
@@ -292,36 +293,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeFn encoder() {
-  static EncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeFn>(p);
-  }();
-  return fn;
-}
-
-// [S, heads, 128] bf16 with row pitch `stride_s` elements -> 3-D map (128, heads, S); box = 64 columns x 128 rows of one head
-std::string rows_map(CUtensorMap* map, const void* ptr, int S, int heads, int64_t stride_s, const char* what) {
-  EncodeFn enc = encoder();
-  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
-  if (reinterpret_cast<uintptr_t>(ptr) % 16 || (stride_s * 2) % 16) return std::string(what) + " rows must be 16-byte aligned";
-  const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)heads, (cuuint64_t)S};
-  const cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)stride_s * 2};
-  const cuuint32_t box[3] = {64, 1, (cuuint32_t)kRows};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? "" : std::string("cuTensorMapEncodeTiled failed for ") + what + " (CUresult " + std::to_string((int)r) + ")";
-}
-
 }  // namespace
 
 std::string attention_prefill_tc(const void* q, const void* k, const void* v, void* out, int S, int Hq, int Hkv, int D,
@@ -338,11 +309,11 @@ std::string attention_prefill_tc(const void* q, const void* k, const void* v, vo
   a.idesc_pv = tc::make_idesc(kRows, kD, 1, 1) | (1u << 16);       // B (the V chunk) is read MN-major
   a.status = status;
   CUtensorMap mq, mk, mv;
-  std::string err = rows_map(&mq, q, S, Hq, q_stride_s, "q");
+  std::string err = tma::head_rows_3d(&mq, q, S, Hq, q_stride_s, kRows, "q");
   if (!err.empty()) return err;
-  err = rows_map(&mk, k, S, Hkv, k_stride_s, "k");
+  err = tma::head_rows_3d(&mk, k, S, Hkv, k_stride_s, kRows, "k");
   if (!err.empty()) return err;
-  err = rows_map(&mv, v, S, Hkv, v_stride_s, "v");
+  err = tma::head_rows_3d(&mv, v, S, Hkv, v_stride_s, kRows, "v");
   if (!err.empty()) return err;
   auto kern = attn_prefill_tc_kernel;
   static std::mutex mu;

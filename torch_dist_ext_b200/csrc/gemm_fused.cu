@@ -31,6 +31,7 @@
 #include "tdx/gemm.h"
 #include "tdx/gemm_core.cuh"
 #include "tdx/tc.cuh"
+#include "tdx/tma_host.h"
 
 #ifndef TDX_FUSED_N
 #define TDX_FUSED_N 0
@@ -280,33 +281,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // ---- host side ---------------------------------------------------------------------------------------
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeFn encoder() {
-  static EncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeFn>(p);
-  }();
-  return fn;
-}
-
 std::string bf16_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t ld, int box_rows) {
-  EncodeFn enc = encoder();
-  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
-  if (reinterpret_cast<uintptr_t>(ptr) % 16 || (ld * 2) % 16) return "GEMM operands must be 16-byte aligned with a 16-byte row pitch";
-  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)(ld * 2)};
-  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? "" : "cuTensorMapEncodeTiled failed (CUresult " + std::to_string((int)r) + ")";
+  return tma::kmajor_2d(map, ptr, rows, k, ld, 2, kBF16, box_rows);
 }
 
 // Opt in to the large dynamic shared-memory size once per kernel and device.

@@ -26,6 +26,7 @@
 #include "tdx/comm.h"
 #include "tdx/gemm.h"
 #include "tdx/tc.cuh"
+#include "tdx/tma_host.h"
 
 namespace tdx {
 namespace {
@@ -223,41 +224,6 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   }
 }
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeFn>(p);
-  }();
-  return fn;
-}
-
-// Row-major [rows, k] with row pitch ld (elements); box = one 128-byte span of K x box_rows rows.
-std::string make_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t ld, int elem_size, int elem_kind, int box_rows) {
-  EncodeFn enc = encode_fn();
-  if (!enc) return "cuTensorMapEncodeTiled is not available from this driver";
-  if (reinterpret_cast<uintptr_t>(ptr) % 16) return "GEMM operands must be 16-byte aligned";
-  if ((ld * elem_size) % 16) return "GEMM operand row pitch must be a multiple of 16 bytes";
-  const CUtensorMapDataType dt = elem_size == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                 : elem_kind == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)(ld * elem_size)};
-  const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_size), (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled failed (CUresult " + std::to_string((int)r) + ")";
-  return "";
-}
-
 template <bool kFp8>
 std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const PersistArgs& a, int grid, cudaStream_t stream) {
   auto kern = gemm_persist_kernel<kFp8>;
@@ -296,9 +262,9 @@ std::string gemm_tn_persistent(const GemmProblem& g, cudaStream_t stream) {
   a.idesc = fp8 ? tc::make_idesc(kBM, kBN, 0, 0) : tc::make_idesc(kBM, kBN, g.elem_kind == kBF16 ? 1 : 0, g.elem_kind == kBF16 ? 1 : 0);
   a.status = g.status;
   CUtensorMap mx, my;
-  std::string err = make_map(&mx, g.x, g.x_rows, g.k, g.ldx, g.elem_size, g.elem_kind, kBM);
+  std::string err = tma::kmajor_2d(&mx, g.x, g.x_rows, g.k, g.ldx, g.elem_size, g.elem_kind, kBM);
   if (!err.empty()) return err;
-  err = make_map(&my, g.y, g.y_rows, g.k, g.ldy, g.elem_size, g.elem_kind, kBN);
+  err = tma::kmajor_2d(&my, g.y, g.y_rows, g.k, g.ldy, g.elem_size, g.elem_kind, kBN);
   if (!err.empty()) return err;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
