@@ -73,19 +73,6 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
-// Operand read MN-major from a tile that TMA wrote as [rows = K index][128 bytes of the MN index], 128-byte
-// swizzle: eight K rows of one 64-element MN slice are 1024 bytes (stride offset), the next 64-element MN
-// slice of the same rows starts `mn_slice_bytes` further (leading offset).
-__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_slice_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)((mn_slice_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
 // Byte offset of element (row, col) of a [16 rows x 128 columns] bf16 tile stored as two 64-column
 // K blocks of [16 rows x 128 bytes] with the 128-byte swizzle (what tcgen05.mma reads as a K-major B operand).
 __device__ __forceinline__ int small_tile_offset(int row, int col) {
@@ -193,7 +180,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         const uint32_t pbase = tc::smem_u32(p_tile);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          tc::umma<false>(tmem_base + kColO, make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes),
+          tc::umma<false>(tmem_base + kColO, tc::make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes),
                           tc::make_smem_desc_sw128(pbase + (j >> 2) * (kNq * 128)) + (uint64_t)((j & 3) * 2), a.idesc_pv, j ? 1u : 0u);
         tc::umma_commit(o_full);
         tc::umma_commit(&kv_free[c % kStages]);
@@ -373,7 +360,7 @@ std::string attention_decode_tc(const void* q, const void* k_cache, const void* 
   a.q_stride_b = q_stride_b;
   a.scale = scale;
   a.idesc_s = tc::make_idesc(kKeys, kNq, 1, 1);                    // both operands K-major bf16
-  a.idesc_pv = tc::make_idesc(kD, kNq, 1, 1) | (1u << 15);         // A (the V chunk) is read MN-major
+  a.idesc_pv = tc::make_idesc(kD, kNq, 1, 1) | tc::kIdescAMnMajor;         // A (the V chunk) is read MN-major
   a.status = status;
   CUtensorMap mk, mv;
   std::string err = tma::kv_cache_4d(&mk, k_cache, B, S_max, Hkv, kv_stride_b, kv_stride_s, kKeys);

@@ -60,19 +60,6 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
-// Operand read MN-major from a tile that TMA wrote as [rows = K index][128 bytes of the MN index] with
-// the 128-byte swizzle: eight K rows of a 64-element MN slice are 1024 bytes apart from the next eight
-// (stride offset); the next 64-element MN slice starts `mn_slice_bytes` further (leading offset).
-__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_slice_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)((mn_slice_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
@@ -159,7 +146,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           tc::umma<false>(tmem_base + kColPV, tc::make_smem_desc_sw128(pbase + (j >> 2) * kHalfBytes) + (uint64_t)((j & 3) * 2),
-                          make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes), a.idesc_pv, j ? 1u : 0u);
+                          tc::make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes), a.idesc_pv, j ? 1u : 0u);
         tc::umma_commit(o_full);
         tc::umma_commit(&kv_free[c % kStages]);
       };
@@ -306,7 +293,7 @@ std::string attention_prefill_tc(const void* q, const void* k, const void* v, vo
   a.S = S; a.Hq = Hq; a.Hkv = Hkv;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.idesc_s = tc::make_idesc(kRows, kRows, 1, 1);                  // both operands K-major bf16
-  a.idesc_pv = tc::make_idesc(kRows, kD, 1, 1) | (1u << 16);       // B (the V chunk) is read MN-major
+  a.idesc_pv = tc::make_idesc(kRows, kD, 1, 1) | tc::kIdescBMnMajor;       // B (the V chunk) is read MN-major
   a.status = status;
   CUtensorMap mq, mk, mv;
   std::string err = tma::head_rows_3d(&mq, q, S, Hq, q_stride_s, kRows, "q");

@@ -25,11 +25,14 @@
 #include <string>
 #include "tdx/comm.h"
 #include "tdx/gemm.h"
+#include "tdx/gemm_core.cuh"
 #include "tdx/tc.cuh"
 #include "tdx/tma_host.h"
 
 namespace tdx {
 namespace {
+
+using gemm_core::store_chunk;
 
 constexpr int kThreads = 192;
 constexpr int kBM = 128;
@@ -52,38 +55,6 @@ struct PersistArgs {
   uint32_t idesc;
   uint32_t* status;
 };
-
-__device__ __forceinline__ void store_one(const PersistArgs& a, int64_t idx, float v) {
-  if (a.out_dtype == kBF16) static_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16(v);
-  else if (a.out_dtype == kF16) static_cast<__half*>(a.out)[idx] = __float2half(v);
-  else static_cast<float*>(a.out)[idx] = v;
-}
-
-// 16 consecutive y columns of row x.
-__device__ __forceinline__ void store_chunk(const PersistArgs& a, int x, int y0, const float (&v)[16]) {
-  if (x >= a.x_rows) return;
-  if (a.sy == 1 && a.out_dtype != kF32 && y0 + 16 <= a.y_rows && ((a.sx * 2) % 16 == 0) &&
-      (reinterpret_cast<uintptr_t>(a.out) % 16 == 0)) {
-    uint32_t w[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (a.out_dtype == kBF16) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        w[i] = *reinterpret_cast<uint32_t*>(&h);
-      } else {
-        __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-        w[i] = *reinterpret_cast<uint32_t*>(&h);
-      }
-    }
-    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(a.out) + ((int64_t)x * a.sx + y0) * 2);
-    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (y0 + i < a.y_rows) store_one(a, (int64_t)x * a.sx + (int64_t)(y0 + i) * a.sy, v[i]);
-  }
-}
 
 template <bool kFp8>
 __global__ void __launch_bounds__(kThreads, 1)

@@ -4,6 +4,8 @@
 // a push of the tile into a peer GPU's memory).
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include "tdx/comm.h"
 #include "tdx/tc.cuh"
@@ -14,6 +16,44 @@ namespace gemm_core {
 constexpr int kBM = 128;            // tile rows (tcgen05.mma M)
 constexpr int kSwizzleBytes = 128;  // one K block = 128 bytes per row (64 bf16 / 128 fp8)
 constexpr uint32_t kWaitLimit = 1u << 22;
+
+// ---- output of a tile -----------------------------------------------------------------------------------
+// `Args` describes the destination: out, sx, sy (D[x, y] -> out[x * sx + y * sy]), out_dtype (kF32 / kF16 /
+// kBF16), x_rows, y_rows.
+template <typename Args>
+__device__ __forceinline__ void store_out(const Args& a, int64_t idx, float v) {
+  if (a.out_dtype == kBF16) static_cast<__nv_bfloat16*>(a.out)[idx] = __float2bfloat16(v);
+  else if (a.out_dtype == kF16) static_cast<__half*>(a.out)[idx] = __float2half(v);
+  else static_cast<float*>(a.out)[idx] = v;
+}
+
+// Writes 16 consecutive y columns of row x (values already final): two 16-byte stores when the 16 columns are
+// contiguous 16-bit values at an aligned address, else element by element with bounds checks.
+template <typename Args>
+__device__ __forceinline__ void store_chunk(const Args& a, int x, int y0, const float (&v)[16]) {
+  if (x >= a.x_rows) return;
+  if (a.sy == 1 && a.out_dtype != kF32 && y0 + 16 <= a.y_rows && ((a.sx * 2) % 16 == 0) && (y0 % 8 == 0) &&
+      (reinterpret_cast<uintptr_t>(a.out) % 16 == 0)) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (a.out_dtype == kBF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(a.out) + ((int64_t)x * a.sx + y0) * 2);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (y0 + i < a.y_rows) store_out(a, (int64_t)x * a.sx + (int64_t)(y0 + i) * a.sy, v[i]);
+  }
+}
 
 template <int kBN, int kStages>
 struct SmemLayout {

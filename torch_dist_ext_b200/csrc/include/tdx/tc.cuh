@@ -106,6 +106,23 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Operand read MN-major (the MN index contiguous) from a tile that TMA wrote as [rows = K index][128 bytes of
+// the MN index] with the 128-byte swizzle: eight K rows of one 64-element MN slice are 1024 bytes (stride
+// offset); the next 64-element MN slice of the same rows starts `mn_slice_bytes` further (leading offset). The
+// instruction descriptor must mark that operand MN-major (bit 15 for A, bit 16 for B). One instruction
+// consumes 16 K rows: step the start address by 2048 bytes per instruction.
+__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_slice_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((mn_slice_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+constexpr uint32_t kIdescAMnMajor = 1u << 15;
+constexpr uint32_t kIdescBMnMajor = 1u << 16;
+
 // kind::f16 (bf16 or fp16 inputs) / kind::f8f6f4 (e4m3 inputs), fp32 accumulate, both operands K-major.
 // fmt: 0 = f16, 1 = bf16 for kind::f16; 0 = e4m3 for kind::f8f6f4.
 __host__ __device__ inline uint32_t make_idesc(int m, int n, int a_fmt, int b_fmt) {
