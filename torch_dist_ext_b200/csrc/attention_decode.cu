@@ -53,13 +53,6 @@ struct AttnArgs {
   uint32_t* status;
 };
 
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(tc::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
 // 16 bytes (8 bf16) of row `r`, logical 16-byte chunk `c` (0..7) of a 128-byte-swizzled half tile.
 __device__ __forceinline__ uint4 ld_swizzled(const uint8_t* half_tile, int r, int c) {
   return *reinterpret_cast<const uint4*>(half_tile + r * 128 + ((c ^ (r & 7)) << 4));
@@ -95,10 +88,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const _
     uint8_t* base = ring + st * kStageBytesKV;
     tc::mbar_arrive_expect_tx(&full[st], kStageBytesKV);
     const int pos0 = s0 + i * kChunk;
-    tma_load_4d(base, &map_k, &full[st], 0, hkv, pos0, b);
-    tma_load_4d(base + kHalfBytes, &map_k, &full[st], 64, hkv, pos0, b);
-    tma_load_4d(base + 2 * kHalfBytes, &map_v, &full[st], 0, hkv, pos0, b);
-    tma_load_4d(base + 3 * kHalfBytes, &map_v, &full[st], 64, hkv, pos0, b);
+    tc::tma_load_4d(base, &map_k, &full[st], 0, hkv, pos0, b);
+    tc::tma_load_4d(base + kHalfBytes, &map_k, &full[st], 64, hkv, pos0, b);
+    tc::tma_load_4d(base + 2 * kHalfBytes, &map_v, &full[st], 0, hkv, pos0, b);
+    tc::tma_load_4d(base + 3 * kHalfBytes, &map_v, &full[st], 64, hkv, pos0, b);
   };
   if (tid == 0) {
     for (int st = 0; st < kStagesKV; ++st) tc::mbar_init(&full[st], 1);

@@ -66,13 +66,6 @@ struct TcAttnArgs {
   uint32_t* status;
 };
 
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(tc::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
 // Byte offset of element (row, col) of a [16 rows x 128 columns] bf16 tile stored as two 64-column
 // K blocks of [16 rows x 128 bytes] with the 128-byte swizzle (what tcgen05.mma reads as a K-major B operand).
 __device__ __forceinline__ int small_tile_offset(int row, int col) {
@@ -159,10 +152,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         uint8_t* base = ring + st * kStageBytes;
         tc::mbar_arrive_expect_tx(&kv_full[st], kStageBytes);
         const int pos0 = s0 + c * kKeys;
-        tma_load_4d(base, &map_k, &kv_full[st], 0, hkv, pos0, b);
-        tma_load_4d(base + kHalfBytes, &map_k, &kv_full[st], 64, hkv, pos0, b);
-        tma_load_4d(base + 2 * kHalfBytes, &map_v, &kv_full[st], 0, hkv, pos0, b);
-        tma_load_4d(base + 3 * kHalfBytes, &map_v, &kv_full[st], 64, hkv, pos0, b);
+        tc::tma_load_4d(base, &map_k, &kv_full[st], 0, hkv, pos0, b);
+        tc::tma_load_4d(base + kHalfBytes, &map_k, &kv_full[st], 64, hkv, pos0, b);
+        tc::tma_load_4d(base + 2 * kHalfBytes, &map_v, &kv_full[st], 0, hkv, pos0, b);
+        tc::tma_load_4d(base + 3 * kHalfBytes, &map_v, &kv_full[st], 64, hkv, pos0, b);
       };
       auto issue_scores = [&](int c) {   // S^T[buf c & 1] = K chunk * Q^T
         const uint32_t kbase = tc::smem_u32(ring + (c % kStages) * kStageBytes);

@@ -53,13 +53,6 @@ struct PrefillArgs {
   uint32_t* status;
 };
 
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(tc::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
@@ -124,10 +117,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int st = c % kStages;
         uint8_t* base = ring + st * kStageBytes;
         tc::mbar_arrive_expect_tx(&kv_full[st], kStageBytes);
-        tma_load_3d(base, &map_k, &kv_full[st], 0, hkv, c * kRows);
-        tma_load_3d(base + kHalfBytes, &map_k, &kv_full[st], 64, hkv, c * kRows);
-        tma_load_3d(base + kTileBytes, &map_v, &kv_full[st], 0, hkv, c * kRows);
-        tma_load_3d(base + kTileBytes + kHalfBytes, &map_v, &kv_full[st], 64, hkv, c * kRows);
+        tc::tma_load_3d(base, &map_k, &kv_full[st], 0, hkv, c * kRows);
+        tc::tma_load_3d(base + kHalfBytes, &map_k, &kv_full[st], 64, hkv, c * kRows);
+        tc::tma_load_3d(base + kTileBytes, &map_v, &kv_full[st], 0, hkv, c * kRows);
+        tc::tma_load_3d(base + kTileBytes + kHalfBytes, &map_v, &kv_full[st], 64, hkv, c * kRows);
       };
       auto issue_scores = [&](int c) {   // S[buf c & 1] = Q * K chunk^T
         const uint32_t kbase = tc::smem_u32(ring + (c % kStages) * kStageBytes);
@@ -151,8 +144,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc::umma_commit(&kv_free[c % kStages]);
       };
       tc::mbar_arrive_expect_tx(q_full, kTileBytes);
-      tma_load_3d(q_tile, &map_q, q_full, 0, h, q0);
-      tma_load_3d(q_tile + kHalfBytes, &map_q, q_full, 64, h, q0);
+      tc::tma_load_3d(q_tile, &map_q, q_full, 0, h, q0);
+      tc::tma_load_3d(q_tile + kHalfBytes, &map_q, q_full, 64, h, q0);
       for (int c = 0; c < nchunks && c < kStages; ++c) issue_copy(c);
       bool ok = tc::mbar_wait(q_full, 0, kWaitLimit, abort_flag) && tc::mbar_wait(&kv_full[0], 0, kWaitLimit, abort_flag);
       if (ok) {
