@@ -285,18 +285,8 @@ namespace {
 template <int kG>
 std::string launch_attn(const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, dim3 grid, cudaStream_t stream) {
   auto kern = attn_decode_split_kernel<kG>;
-  static std::mutex mu;
-  static std::set<int> done;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (!done.count(dev)) {
-      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
-      if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
-      done.insert(dev);
-    }
-  }
+  const std::string smem_err = reserve_dynamic_smem(kern, kAttnSmem);
+  if (!smem_err.empty()) return smem_err;
   kern<<<grid, kAttnThreads, kAttnSmem, stream>>>(mk, mv, a);
   return "";
 }

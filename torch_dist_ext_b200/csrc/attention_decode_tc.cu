@@ -310,18 +310,8 @@ __global__ void __launch_bounds__(kD) attn_tc_combine_kernel(const TcAttnArgs a)
 template <int kG>
 std::string launch(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnArgs& a, dim3 grid, cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<kG>;
-  static std::mutex mu;
-  static std::set<int> done;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (!done.count(dev)) {
-      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-      if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
-      done.insert(dev);
-    }
-  }
+  const std::string smem_err = reserve_dynamic_smem(kern, kSmem);
+  if (!smem_err.empty()) return smem_err;
   kern<<<grid, kThreads, kSmem, stream>>>(mk, mv, a);
   return "";
 }

@@ -296,18 +296,8 @@ std::string attention_prefill_tc(const void* q, const void* k, const void* v, vo
   err = tma::head_rows_3d(&mv, v, S, Hkv, v_stride_s, kRows, "v");
   if (!err.empty()) return err;
   auto kern = attn_prefill_tc_kernel;
-  static std::mutex mu;
-  static std::set<int> done;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (!done.count(dev)) {
-      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-      if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
-      done.insert(dev);
-    }
-  }
+  const std::string smem_err = reserve_dynamic_smem(kern, kSmem);
+  if (!smem_err.empty()) return smem_err;
   const dim3 grid((S + kRows - 1) / kRows, Hq, 1);
   kern<<<grid, kThreads, kSmem, stream>>>(mq, mk, mv, a);
   const cudaError_t e = cudaGetLastError();

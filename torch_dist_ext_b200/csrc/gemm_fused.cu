@@ -285,22 +285,6 @@ std::string bf16_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t
   return tma::kmajor_2d(map, ptr, rows, k, ld, 2, kBF16, box_rows);
 }
 
-// Opt in to the large dynamic shared-memory size once per kernel and device.
-template <typename Kern>
-std::string prepare(Kern kern, int smem) {
-  static std::mutex mu;
-  static std::set<std::pair<const void*, int>> done;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const auto key = std::make_pair(reinterpret_cast<const void*>(kern), dev);
-  std::lock_guard<std::mutex> lock(mu);
-  if (done.count(key)) return "";
-  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
-  done.insert(key);
-  return "";
-}
-
 int sm_count() {
   int dev = 0, n = 0;
   cudaGetDevice(&dev);
@@ -311,7 +295,7 @@ int sm_count() {
 template <int kBN, int kStages, int kVpt, int kOut>
 std::string launch_ar(const CUtensorMap& mw, const CUtensorMap& ma, const FusedArgs& f, dim3 grid, cudaStream_t s) {
   auto kern = gemm_ar_rmsnorm_kernel<kBN, kStages, TDX_FUSED_N, kVpt, kOut>;
-  std::string err = prepare(kern, SmemLayout<kBN, kStages>::kTotal);
+  std::string err = reserve_dynamic_smem(kern, SmemLayout<kBN, kStages>::kTotal);
   if (!err.empty()) return err;
   kern<<<grid, kThreads, SmemLayout<kBN, kStages>::kTotal, s>>>(mw, ma, f);
   const cudaError_t e = cudaGetLastError();
@@ -422,12 +406,12 @@ std::string ag_gemm(const AgGemmProblem& g, cudaStream_t stream) {
   if (!err.empty()) return err;
   if (bn == 16) {
     auto kern = ag_gemm_kernel<16, 10>;
-    err = prepare(kern, SmemLayout<16, 10>::kTotal);
+    err = reserve_dynamic_smem(kern, SmemLayout<16, 10>::kTotal);
     if (!err.empty()) return err;
     kern<<<grid, kThreads, SmemLayout<16, 10>::kTotal, stream>>>(mw, m0, m1, a);
   } else {
     auto kern = ag_gemm_kernel<64, 8>;
-    err = prepare(kern, SmemLayout<64, 8>::kTotal);
+    err = reserve_dynamic_smem(kern, SmemLayout<64, 8>::kTotal);
     if (!err.empty()) return err;
     kern<<<grid, kThreads, SmemLayout<64, 8>::kTotal, stream>>>(mw, m0, m1, a);
   }

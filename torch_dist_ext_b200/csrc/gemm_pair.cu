@@ -189,15 +189,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 template <bool kFp8>
 std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const PairArgs& a, dim3 grid, cudaStream_t stream) {
   auto kern = gemm_pair_kernel<kFp8>;
-  static thread_local int last_dev = -1;
-  static thread_local cudaError_t attr_err = cudaSuccess;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev != last_dev) {   // the attribute is per device
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    last_dev = dev;
-  }
-  if (attr_err != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(attr_err);
+  const std::string err = reserve_dynamic_smem(kern, kSmemTotal);
+  if (!err.empty()) return err;
   kern<<<grid, kThreads, kSmemTotal, stream>>>(mx, my, a);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);

@@ -188,18 +188,8 @@ template <int kBN, int kStages, bool kFp8, bool kScaled>
 std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   using L = SmemLayout<kBN, kStages>;
   auto kern = gemm_tn_kernel<kBN, kStages, kFp8, kScaled>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal); });
-  // the attribute is per device; set it again cheaply when several devices are used by one process
-  static thread_local int last_dev = -1;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev != last_dev) {
-    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-    last_dev = dev;
-  }
-  if (attr_err != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(attr_err);
+  const std::string err = reserve_dynamic_smem(kern, L::kTotal);
+  if (!err.empty()) return err;
   kern<<<grid, kThreads, L::kTotal, stream>>>(mx, my, a);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);

@@ -1,15 +1,36 @@
-// Host-side construction of TMA tensor maps (cuTensorMapEncodeTiled through the runtime's driver entry
-// point, so that nothing links against libcuda). Every map of this library is bf16 / fp16 / 8-bit data
+// Host-side launch helpers: the opt-in to large dynamic shared memory, and construction of TMA tensor maps
+// (cuTensorMapEncodeTiled through the runtime's driver entry point, so that nothing links against libcuda). Every map of this library is bf16 / fp16 / 8-bit data
 // with the innermost box equal to one 128-byte swizzle span, L2 promotion to 256 bytes and zero fill
 // outside the tensor. The reference has no TMA code.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <mutex>
+#include <set>
 #include <string>
+#include <utility>
 #include "tdx/comm.h"
 
 namespace tdx {
+
+// Opt in to a dynamic shared-memory size above the 48 KB default, once per kernel and device (the
+// attribute belongs to the device's copy of the kernel). Returns an empty string or the reason.
+template <typename Kernel>
+std::string reserve_dynamic_smem(Kernel kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const auto key = std::make_pair(reinterpret_cast<const void*>(kernel), dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count(key)) return "";
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return std::string("cannot reserve shared memory: ") + cudaGetErrorString(e);
+  done.insert(key);
+  return "";
+}
+
 namespace tma {
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
