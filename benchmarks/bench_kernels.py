@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Single-GPU roofline table of the library's kernels (no communication).
 
-    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_persist|gemm_fp8|attention|attention_tc|elementwise|all] [--steps 30]
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_persist|gemm_fp8|attention|attention_tc|attention_prefill_tc|elementwise|all] [--steps 30]
 
 Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
 over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
@@ -135,6 +135,33 @@ def attention_cases(dev, steps, out, tensor_cores=False):
         torch.cuda.empty_cache()
 
 
+def prefill_attention_cases(dev, steps, out):
+    """Causal attention over one prompt: this library's tcgen05 kernel against PyTorch's SDPA (opt-in kernel)."""
+    from torch_dist_ext_b200.ops import attention
+
+    hbm, tf, src = peaks()
+    for s_len, hq, hkv in [(2048, 32, 8), (8192, 32, 8), (2048, 8, 1)]:
+        qkv = torch.randn(s_len, (hq + 2 * hkv) * 128, device=dev, dtype=torch.bfloat16)
+        q = qkv[:, : hq * 128].view(s_len, hq, 128)
+        k = qkv[:, hq * 128: (hq + hkv) * 128].view(s_len, hkv, 128)
+        v = qkv[:, (hq + hkv) * 128:].view(s_len, hkv, 128)
+        got = attention.prefill_attention(q, k, v).float()
+
+        def sdpa(_i=0):
+            return torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0),
+                is_causal=True, enable_gqa=True).squeeze(0).transpose(0, 1)
+
+        if not (got - sdpa().float()).abs().max().item() <= 3e-2:
+            raise SystemExit("tensor-core prefill attention disagrees with scaled_dot_product_attention")
+        us = time_us(lambda i: attention.prefill_attention(q, k, v), 1, steps)
+        lib = time_us(sdpa, 1, steps)
+        flops = 4.0 * hq * 128 * s_len * s_len / 2          # causal: half of the score matrix
+        out.append(row(f"prefill attention (tcgen05) s={s_len} hq={hq} hkv={hkv}", us, lib, qkv.numel() * 2 + s_len * hq * 256,
+                       flops, hbm, tf, src))
+        print(out[-1], flush=True)
+
+
 def elementwise_cases(dev, steps, out):
     from torch_dist_ext_b200.ops import activation, norm, quant
 
@@ -193,6 +220,8 @@ def main():
         attention_cases(dev, args.steps, out)
     if g == "attention_tc":         # opt-in kernel (not part of "all")
         attention_cases(dev, args.steps, out, tensor_cores=True)
+    if g == "attention_prefill_tc":  # opt-in kernel (not part of "all")
+        prefill_attention_cases(dev, max(5, args.steps // 3), out)
     if g in ("elementwise", "all"):
         elementwise_cases(dev, args.steps, out)
     path = os.path.join(common.out_dir(), f"kernels_{g}.json")
