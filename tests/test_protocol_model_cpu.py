@@ -125,7 +125,10 @@ def test_clearing_the_next_buffer_instead_of_the_previous_one_is_caught():
 # plane-1 flags every rank reads its result area. Flags carry the call number and are compared with
 # ">=", so a flag raised early by a rank that runs ahead is never lost.
 
-def explore_flags(nranks: int, ncalls: int, second_barrier: bool):
+CLOBBERED = -7
+
+
+def explore_flags(nranks: int, ncalls: int, second_barrier: bool, stage_overwrites_results: bool = False):
     peers = [[p for p in range(nranks) if p != r] for r in range(nranks)]
     prog = []
     for r in range(nranks):
@@ -162,6 +165,11 @@ def explore_flags(nranks: int, ncalls: int, second_barrier: bool):
             st, rs, fl = staging, result, flags
             if op == "stage":
                 st = put(staging, arg, r, e)
+                if stage_overwrites_results:
+                    # the result area starts where the gather area of the call ends: a LARGER next call's
+                    # gather slots reach into the rows that the previous call's results occupy
+                    for owner in range(nranks):
+                        rs = put(rs, arg, owner, CLOBBERED)
             elif op == "signal":
                 for p in peers[r]:
                     planes = list(fl[p])
@@ -202,3 +210,14 @@ def test_two_flag_barriers_make_the_shared_staging_safe(nranks, ncalls):
 def test_without_the_second_barrier_a_fast_rank_overwrites_what_a_slow_rank_still_reads():
     violation, _ = explore_flags(2, 3, second_barrier=False)
     assert violation is not None
+
+
+def test_result_area_behind_a_size_dependent_gather_area_is_unsafe_when_messages_grow():
+    """The epilogue of a call reads the result area after the last flag wait, and nothing follows that wait. If
+    the result area started right behind the gather area, a rank that runs ahead into a larger call would push
+    gather rows over result rows that a slow rank is still reading. The kernels therefore keep the result area
+    at a fixed offset (second half of the staging region), which is the model without the overwrite."""
+    violation, _ = explore_flags(2, 3, second_barrier=True, stage_overwrites_results=True)
+    assert violation is not None and "result" in violation
+    violation, _ = explore_flags(2, 3, second_barrier=True, stage_overwrites_results=False)
+    assert violation is None

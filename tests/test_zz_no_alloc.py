@@ -60,6 +60,27 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
         assert (got.float() - ref.float()).abs().max().item() <= 2e-2
 
 
+def test_more_sequence_head_pairs_than_arrival_counters_leaves_the_counters_intact():
+    """More (sequence, KV head) pairs than the 4096 arrival counters: the splits are merged by the separate
+    combine kernel and the partial rows still start behind the counters, so the small call that follows
+    (which merges inside the kernel and relies on zeroed counters) is correct too."""
+    fn = _entry()
+    torch.manual_seed(1)
+    for b, hq, hkv, smax, nsplit in [(4100, 1, 1, 256, 2), (3, 8, 2, 512, 4)]:
+        q = torch.randn(b, hq, 128, device="cuda", dtype=torch.bfloat16)
+        k = torch.randn(b, smax, hkv, 128, device="cuda", dtype=torch.bfloat16)
+        v = torch.randn_like(k)
+        lens = torch.randint(1, smax + 1, (b,), device="cuda", dtype=torch.int32)
+        rc, got, msg = _call(fn, q, k, v, lens, nsplit)
+        assert rc == 0, msg
+        want = attention.decode_attention(q, k, v, lens, smax, nsplit=nsplit)
+        torch.cuda.synchronize()
+        assert (got.float() - want.float()).abs().max().item() <= 2e-2
+        if b <= 16:
+            ref = attention.decode_attention_reference(q, k, v, lens)
+            assert (got.float() - ref.float()).abs().max().item() <= 2e-2
+
+
 def test_oversized_request_is_refused_with_a_message():
     fn = _entry()
     q = torch.zeros(64, 32, 128, device="cuda", dtype=torch.bfloat16)

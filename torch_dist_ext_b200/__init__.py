@@ -33,9 +33,10 @@ allreduce_rms_fusion_impl = torch.ops.torch_dist_ext.allreduce_rms_fusion
 
 @torch.library.custom_op("torch_dist_ext::get_workspace", mutates_args=[])
 def get_workspace(ref: torch.Tensor) -> torch.Tensor:
-    # The table never changes after registration; clone so that the op's output does not alias
-    # library-owned memory (a custom-op rule). The clone holds the same peer pointers.
-    return _comm.get_comm().get_workspace(ref)
+    # An op's output must be a fresh tensor, never a view of memory the library owns, so this returns a
+    # copy of the device-resident table and tells the workspace about it (the ops find their workspace by
+    # the table's address). The table never changes after registration; the copy holds the same pointers.
+    return _comm.get_comm().get_workspace_copy(ref)
 
 
 @torch.library.register_fake("torch_dist_ext::get_workspace")

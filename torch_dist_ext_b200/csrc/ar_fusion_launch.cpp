@@ -125,7 +125,6 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
   const uint64_t gather_bytes = uint64_t(n) * groups * row_bytes;
   const uint64_t need_oneshot = uint64_t(n) * msg_bytes;
   const uint64_t need_ts_lamport = gather_bytes + (p.scatter_only ? 0 : uint64_t(p.tokens) * (row_bytes + 16));
-  const uint64_t need_ts_barrier = gather_bytes + (p.scatter_only ? 0 : uint64_t(p.tokens) * (row_bytes + 16));
 
   int algo = p.algo;
   if (n == 1) {
@@ -156,8 +155,12 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
       if (need_ts_lamport > p.layout.lamport_bytes)
         return fmt("two-shot (Lamport) needs %lld bytes of Lamport buffer, capacity is %lld", need_ts_lamport, p.layout.lamport_bytes);
     } else if (algo == kAlgoTwoShotBarrier) {
-      if (need_ts_barrier > p.layout.stage_bytes)
-        return fmt("message of %lld bytes exceeds the workspace capacity (needs %lld of %lld staging bytes)", msg_bytes, need_ts_barrier, p.layout.stage_bytes);
+      // gather area in the first half of the staging region, result rows + trailers in the second
+      const uint64_t half = p.layout.stage_bytes / 2;
+      const uint64_t need_result = p.scatter_only ? 0 : uint64_t(p.tokens) * (row_bytes + 16);
+      if (gather_bytes > half || need_result > half)
+        return fmt("message of %lld bytes exceeds the workspace capacity (needs %lld of %lld staging bytes)", msg_bytes,
+                   2 * (gather_bytes > need_result ? gather_bytes : need_result), p.layout.stage_bytes);
     } else if (algo == kAlgoNvlsOneShot || algo == kAlgoNvlsTwoShot) {
       if (p.mc_base == nullptr || p.layout.nvls_in_bytes == 0)
         return "NVLS algorithms need a workspace with an NVSwitch multicast mapping (not available here)";

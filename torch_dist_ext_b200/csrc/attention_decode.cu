@@ -125,9 +125,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const _
   for (int i = 0; i < nchunks; ++i) {
     const int st = i % kStagesKV;
     const uint8_t* base = ring + st * kStageBytesKV;
-    if (!tc::mbar_wait(&full[st], (i / kStagesKV) & 1, kAttnWaitLimit, abort_flag)) {
-      *abort_flag = 1;
-      if (a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
+    // The threads leave the loop together: a thread whose wait ran out while its neighbours' succeeded would
+    // otherwise skip block-wide barriers that the others still execute.
+    const bool arrived = tc::mbar_wait(&full[st], (i / kStagesKV) & 1, kAttnWaitLimit, abort_flag);
+    if (__syncthreads_or(!arrived)) {
+      if (!arrived) {
+        *abort_flag = 1;
+        if (a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
+      }
       break;
     }
     const int c0 = s0 + i * kChunk;
@@ -303,8 +308,11 @@ std::string attention_decode(const void* q, const void* k_cache, const void* v_c
   if (G > kMaxG || (G & (G - 1))) return "query heads per KV head must be 1, 2, 4 or 8";
   if (nsplit < 1) nsplit = 1;
   // scratch layout: kAttnCounters arrival counters (zero on entry, zeroed again by the kernel), then the partials
-  const bool in_kernel_merge = (size_t)B * Hkv <= (size_t)kAttnCounters && partial_floats > (size_t)kAttnCounters;
-  const size_t head = in_kernel_merge ? (size_t)kAttnCounters : 0;
+  // A buffer longer than the counter block always carries it: the partial rows start behind it even when the
+  // separate combine kernel is used, so that a cached scratch buffer never has its counters overwritten.
+  const bool has_counters = partial_floats > (size_t)kAttnCounters;
+  const bool in_kernel_merge = has_counters && (size_t)B * Hkv <= (size_t)kAttnCounters;
+  const size_t head = has_counters ? (size_t)kAttnCounters : 0;
   if (head + (size_t)B * Hq * nsplit * (kD + 2) > partial_floats) return "attention scratch buffer is too small";
   if ((kv_stride_s * 2) % 16 || (kv_stride_b * 2) % 16 || reinterpret_cast<uintptr_t>(k_cache) % 16 ||
       reinterpret_cast<uintptr_t>(v_cache) % 16)

@@ -129,6 +129,9 @@ class Workspace {
 
   // Looks up the workspace that owns a device table pointer (what the op receives).
   static Workspace* from_table(const void* table_dev);
+  // Makes from_table() also recognise a device copy of the table (what a traced op returns, since an
+  // op's output must not alias memory that the library owns). Forgotten when the workspace is destroyed.
+  void adopt_table_copy(const void* copy_dev);
 
  private:
   void init_device_state();

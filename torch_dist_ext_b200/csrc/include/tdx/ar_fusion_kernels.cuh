@@ -611,7 +611,10 @@ __device__ __forceinline__ void twoshot_flag_body(const ArParams& p) {
   const TwoShotGeometry g = twoshot_geometry<T, kVpt>(p, rv, nranks, false);
   // staging: gather slots [src][group][hidden] (peer-to-peer) or my rows in natural order (NVLS)
   const size_t stage_off = kNvls ? nvls_in_offset(p.layout, bepoch) : p.layout.off_stage;
-  const size_t result_off = kNvls ? p.layout.off_nvls + 2 * p.layout.nvls_in_bytes : p.layout.off_stage + g.gather_bytes;
+  // The result area sits at an offset that does not depend on the message: the epilogue reads it after the last
+  // wait of the call, so a peer that runs ahead into a LARGER call must find its gather slots (pushed before any
+  // wait) clear of the rows that a slower rank is still reading.
+  const size_t result_off = kNvls ? p.layout.off_nvls + 2 * p.layout.nvls_in_bytes : p.layout.off_stage + p.layout.stage_bytes / 2;
   const char* in = static_cast<const char*>(p.in);
   const bool gather_back = p.scatter_only == 0;
   Waiter w(p.timeout_ns);

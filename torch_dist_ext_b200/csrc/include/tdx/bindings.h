@@ -18,6 +18,7 @@ class CommWorkspace : public torch::CustomClassHolder {
   at::Tensor get_handle();
   void open_handles(std::vector<at::Tensor> handles);
   at::Tensor get_workspace(const at::Tensor& ref);
+  void adopt_table(const at::Tensor& copy);
   void reset();
   bool has_multicast();
   void disable_multicast();

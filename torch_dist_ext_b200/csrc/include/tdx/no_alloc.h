@@ -21,7 +21,8 @@
 //  * All calls share the one array and it keeps the previous call's contents. The partial rows are
 //    written before they are read, so they need no clearing; the 4096 arrival counters in front of
 //    them must start at zero, which holds when the library is loaded and is restored by every call
-//    that runs to its end. Two calls that overlap on the GPU (two streams, two host threads) race on
+//    that runs to its end (the partial rows always start behind the counters, also when batch * kv_heads
+//    exceeds 4096 and a separate kernel merges the splits). Two calls that overlap on the GPU (two streams, two host threads) race on
 //    both. Issue calls on one stream, or serialise them yourself.
 //  * No cudaMalloc, cudaFree, or allocating library routine is called; inputs and outputs are the caller's.
 #pragma once

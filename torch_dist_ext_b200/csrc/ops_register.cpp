@@ -208,6 +208,13 @@ static void attention_decode_impl(const Tensor& q, const Tensor& k_cache, const 
   TORCH_CHECK(k_cache.stride(3) == 1 && k_cache.stride(2) == k_cache.size(3) && k_cache.strides() == v_cache.strides() && k_cache.sizes() == v_cache.sizes(), "attention_decode: cache layout [B, S, Hkv, D] with dense heads");
   TORCH_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.is_cuda() && seq_lens.numel() == q.size(0), "attention_decode: seq_lens int32 [B]");
   TORCH_CHECK(partial.scalar_type() == at::kFloat && partial.is_contiguous(), "attention_decode: partial must be contiguous fp32");
+  TORCH_CHECK(q.size(2) == 128 && k_cache.size(3) == 128, "attention_decode: head dimension must be 128");
+  TORCH_CHECK(out.numel() == q.size(0) * q.size(1) * q.size(2), "attention_decode: out must hold [B, Hq, D] elements");
+  TORCH_CHECK(k_cache.size(0) == q.size(0), "attention_decode: q and the caches disagree on the batch size");
+  for (const Tensor* t : {&k_cache, &v_cache, &seq_lens, (const Tensor*)&out, (const Tensor*)&partial})
+    TORCH_CHECK(t->is_cuda() && t->device() == q.device(), "attention_decode: every tensor must live on q's device");
+  if (status.has_value() && status->defined())
+    TORCH_CHECK(status->is_cuda() && status->device() == q.device() && status->scalar_type() == at::kInt, "attention_decode: status must be an int32 tensor on q's device");
   const c10::cuda::CUDAGuard guard(q.device());
   const auto fn = tensor_cores ? &tdx::attention_decode_tc : &tdx::attention_decode;
   const std::string err = fn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), seq_lens.data_ptr<int>(),

@@ -79,7 +79,17 @@ Tensor CommWorkspace::get_workspace(const Tensor& ref) {
   TORCH_CHECK(!ref.defined() || !ref.is_cuda() || ref.get_device() == impl_->device(),
               "CommWorkspace.get_workspace: reference tensor is on another device than the workspace");
   auto opts = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, impl_->device());
-  return torch::from_blob(const_cast<tdx::CommTable*>(impl_->device_table()), {(int64_t)sizeof(tdx::CommTable)}, opts);
+  // The tensor views memory that the workspace owns, so it holds a reference that keeps the workspace alive.
+  auto keep = c10::intrusive_ptr<CommWorkspace>::unsafe_reclaim_from_nonowning(this);
+  return torch::from_blob(const_cast<tdx::CommTable*>(impl_->device_table()), {(int64_t)sizeof(tdx::CommTable)},
+                          [keep](void*) mutable { keep.reset(); }, opts);
+}
+
+void CommWorkspace::adopt_table(const Tensor& copy) {
+  TORCH_CHECK(copy.is_cuda() && copy.scalar_type() == at::kByte && copy.is_contiguous() &&
+                  copy.numel() == (int64_t)sizeof(tdx::CommTable) && copy.get_device() == impl_->device(),
+              "CommWorkspace.adopt_table: expected a device copy of the tensor returned by get_workspace");
+  impl_->adopt_table_copy(copy.data_ptr());
 }
 
 void CommWorkspace::reset() { impl_->reset(); }
@@ -301,6 +311,7 @@ TORCH_LIBRARY(torch_dist_ext, m) {
       .def("get_handle", &CommWorkspace::get_handle)
       .def("open_handles", &CommWorkspace::open_handles)
       .def("get_workspace", &CommWorkspace::get_workspace)
+      .def("adopt_table", &CommWorkspace::adopt_table)
       .def("reset", &CommWorkspace::reset)
       .def("set_timeout_ms", &CommWorkspace::set_timeout_ms)
       .def("set_debug_extent", &CommWorkspace::set_debug_extent)

@@ -305,7 +305,8 @@ void Workspace::release_vmm() {
 Workspace::~Workspace() {
   {
     std::lock_guard<std::mutex> lock(g_registry_mu);
-    registry().erase(table_dev_);
+    for (auto it = registry().begin(); it != registry().end();)
+      it = (it->second == this) ? registry().erase(it) : std::next(it);
   }
   int prev = -1;
   cudaGetDevice(&prev);
@@ -513,6 +514,11 @@ WorkspaceStats Workspace::stats() const {
 
 uint32_t Workspace::errors_seen() const {
   return reinterpret_cast<volatile uint32_t*>(host_status_)[0];
+}
+
+void Workspace::adopt_table_copy(const void* copy_dev) {
+  std::lock_guard<std::mutex> lock(g_registry_mu);
+  registry()[copy_dev] = this;
 }
 
 Workspace* Workspace::from_table(const void* table_dev) {

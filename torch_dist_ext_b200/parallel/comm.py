@@ -85,6 +85,14 @@ class CommProcess:
             return torch.zeros(table_nbytes(), dtype=torch.uint8)
         return self._table
 
+    def get_workspace_copy(self, ref: torch.Tensor) -> torch.Tensor:
+        """A fresh tensor with the table's contents that the ops accept like the table itself."""
+        if self.comm is None:
+            return torch.zeros(table_nbytes(), dtype=torch.uint8)
+        copy = self._table.clone()
+        self.comm.adopt_table(copy)
+        return copy
+
     def reset(self) -> None:
         """Collective re-initialisation of flags, epochs and sentinels."""
         if self.comm is None:
