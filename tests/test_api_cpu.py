@@ -93,14 +93,17 @@ def test_cpu_world1_op_equals_oracle():
 
 def test_config_env_and_policy_file(tmp_path, monkeypatch):
     p = tmp_path / "policy.json"
-    p.write_text(json.dumps({"8": {"oneshot_max_bytes": 123, "lamport_max_bytes": 456}}))
+    p.write_text(json.dumps({"8": {"oneshot_max_bytes": 123, "lamport_max_bytes": 456},
+                             "4": {"oneshot_max_bytes": 1, "lamport_max_bytes": 2, "mc_oneshot": 1, "mc_twoshot": 0,
+                                   "nvls_min_bytes": 789}}))
     monkeypatch.setenv("TDX_ALGO", "twoshot")
     monkeypatch.setenv("TDX_TIMEOUT_MS", "250")
     monkeypatch.setenv("TDX_NVLS", "0")
     monkeypatch.setenv("TDX_POLICY_JSON", str(p))
     c = Config.from_env()
     assert c.algo_code == ALGO_CODES["twoshot"] and c.timeout_ms == 250 and not c.nvls
-    assert c.policy[8] == (123, 456)
+    assert c.policy[8] == (123, 456, -1, -1, -1)      # -1: keep the built-in value
+    assert c.policy[4] == (1, 2, 1, 0, 789)
     monkeypatch.setenv("TDX_ALGO", "bogus")
     with pytest.raises(ValueError):
         Config.from_env()

@@ -1,19 +1,13 @@
 """Tensor-core (tcgen05) decode attention against an fp32 softmax(QK^T)V written in PyTorch.
 
-Opt-in: the kernel is off by default in the library, and this file runs only with
-TDX_TEST_ATTN_TC=1 until the kernel has been brought up on hardware (compiled and desk-checked
-only). The probabilities are rounded to bf16 before the second product, hence the slightly wider
+These kernels are the library's defaults for decode and prompt attention. The probabilities are rounded to bf16 before the second product, hence the slightly wider
 tolerance than for the SIMT kernel, which is also used as a cross-check."""
-import os
-
 import pytest
 import torch
 
 from torch_dist_ext_b200.ops import attention, gemm
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("TDX_TEST_ATTN_TC") != "1",
-                                 reason="tensor-core decode attention is opt-in (TDX_TEST_ATTN_TC=1) until validated on hardware")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("b,hq,hkv,smax", [(1, 4, 1, 128), (1, 4, 1, 2048), (16, 4, 1, 2048), (64, 8, 1, 300), (3, 32, 8, 777),

@@ -1,19 +1,13 @@
 """The two-CTA (tcgen05.mma.cta_group::2) GEMM against fp32 PyTorch math.
 
-Opt-in: the kernel is off by default in the library, and this file runs only with
-TDX_TEST_GEMM_PAIR=1 until the kernel has been brought up on hardware (it has been compiled and
-desk-checked only). Shapes cover full tiles, ragged M and N, a single K block and a K loop longer
+The kernel is selected with ``linear(..., cta_pair=True)`` or ``TDX_GEMM_PAIR=1``. Shapes cover full tiles, ragged M and N, a single K block and a K loop longer
 than the operand ring; every wait in the kernel is bounded, and the device status word is checked."""
-import os
-
 import pytest
 import torch
 
 from torch_dist_ext_b200.ops import gemm
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("TDX_TEST_GEMM_PAIR") != "1",
-                                 reason="two-CTA GEMM is opt-in (TDX_TEST_GEMM_PAIR=1) until validated on hardware")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 256, 64), (256, 256, 1024), (512, 768, 4096), (300, 520, 512), (1024, 256, 8192)])

@@ -1,21 +1,15 @@
 """The persistent tcgen05 GEMM (one CTA per SM walks the tiles, double-buffered accumulator) against
 fp32 PyTorch math and against the one-tile-per-CTA kernel.
 
-Opt-in: the kernel is off by default in the library, and this file runs only with
-TDX_TEST_GEMM_PERSIST=1 until the kernel has been brought up on hardware (compiled and desk-checked
-only; unlike the CTA-pair kernel it uses only instruction forms that the default kernel already uses).
+The kernel is the library's default for prefill-sized problems (``TDX_GEMM_PERSIST=0`` turns it off).
 Shapes cover fewer tiles than SMs, several tiles per CTA (accumulator buffers reused), ragged M and N,
 one K block, and K loops longer than the operand ring."""
-import os
-
 import pytest
 import torch
 
 from torch_dist_ext_b200.ops import gemm
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("TDX_TEST_GEMM_PERSIST") != "1",
-                                 reason="persistent GEMM is opt-in (TDX_TEST_GEMM_PERSIST=1) until validated on hardware")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 256, 64), (256, 512, 1024), (300, 520, 512), (2048, 4096, 256), (4096, 28672, 128),

@@ -14,7 +14,9 @@ def _member(rank, world, port, q, scenario):
     from torch_dist_ext_b200.parallel.health import Membership, PeerLeft
 
     store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20))
-    m = Membership(rank, world, store=store, max_age_s=1.0)
+    # the announced departure must be noticed through the announcement: a generous heartbeat age keeps a slow
+    # machine (process start-up under load) from reporting a stale peer first
+    m = Membership(rank, world, store=store, max_age_s=1.0 if scenario == "silent" else 10.0)
     store.add("ready", 1)
     while int(store.add("ready", 0)) < world:
         time.sleep(0.01)

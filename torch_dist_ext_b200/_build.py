@@ -12,6 +12,7 @@ Usage::
     python -m torch_dist_ext_b200._build            # build if out of date
     python -m torch_dist_ext_b200._build --force    # rebuild everything
     python -m torch_dist_ext_b200._build --bounds   # also the range-checking flavour (TDX_BOUNDS=1 loads it)
+    python -m torch_dist_ext_b200._build --trace    # also the tracing flavour (TDX_TRACE=1 loads it)
 """
 from __future__ import annotations
 
@@ -29,6 +30,10 @@ LIB_PATH = PKG_DIR / "_C.so"
 # store into a symmetric allocation is range-checked, see csrc/include/tdx/sync.cuh), everything else
 # shared with the release library. Loaded instead of _C.so when TDX_BOUNDS=1.
 CHECKED_LIB_PATH = PKG_DIR / "_C_bounds.so"
+# Tracing flavour: the same units compiled with -DTDX_TRACE (phase time stamps per block, see
+# csrc/include/tdx/comm.h: TraceSlot). Loaded instead of _C.so when TDX_TRACE=1.
+TRACED_LIB_PATH = PKG_DIR / "_C_trace.so"
+FLAVOURS = {"bounds": ("-DTDX_BOUNDS", CHECKED_LIB_PATH), "trace": ("-DTDX_TRACE", TRACED_LIB_PATH)}
 UNIT_TEST_SRC = PKG_DIR.parent / "tests" / "cpp" / "unit_test.cu"
 UNIT_TEST_BIN = PKG_DIR.parent / "tests" / "cpp" / "unit_test.bin"
 
@@ -130,17 +135,20 @@ def write_ninja() -> Path:
         f"-Wl,-rpath,{torch_lib}", "-Wl,--no-as-needed",
     ]
     lines += [f"build {LIB_PATH}: link {' '.join(objs)}", f"  ldflags = {' '.join(ld)}"]
-    checked_objs = []
-    for obj in objs:
-        if obj.startswith("ar_inst_") or obj == "ar_fusion_launch.host.o":
-            checked_objs.append(obj.replace(".o", ".bounds.o", 1) if obj.startswith("ar_inst_") else "ar_fusion_launch.bounds.host.o")
-        else:
-            checked_objs.append(obj)
-    for src, stem, defs in _device_units():
-        if stem.startswith("ar_inst_"):
-            lines += [f"build {stem}.bounds.o: nvcc {CSRC / src}", f"  defs = {' '.join(defs)} -DTDX_BOUNDS"]
-    lines += [f"build ar_fusion_launch.bounds.host.o: cxx {CSRC / 'ar_fusion_launch.cpp'}", "  extra = -DTDX_BOUNDS"]
-    lines += [f"build {CHECKED_LIB_PATH}: link {' '.join(checked_objs)}", f"  ldflags = {' '.join(ld)}"]
+    for flavour, (define, lib_path) in FLAVOURS.items():
+        flavour_objs = []
+        for obj in objs:
+            if obj.startswith("ar_inst_"):
+                flavour_objs.append(obj.replace(".o", f".{flavour}.o", 1))
+            elif obj == "ar_fusion_launch.host.o":
+                flavour_objs.append(f"ar_fusion_launch.{flavour}.host.o")
+            else:
+                flavour_objs.append(obj)
+        for src, stem, defs in _device_units():
+            if stem.startswith("ar_inst_"):
+                lines += [f"build {stem}.{flavour}.o: nvcc {CSRC / src}", f"  defs = {' '.join(defs)} {define}"]
+        lines += [f"build ar_fusion_launch.{flavour}.host.o: cxx {CSRC / 'ar_fusion_launch.cpp'}", f"  extra = {define}"]
+        lines += [f"build {lib_path}: link {' '.join(flavour_objs)}", f"  ldflags = {' '.join(ld)}"]
     # Standalone C++ harness (no PyTorch): the kernels, the launcher and the workspace manager only.
     core = [o for o in objs if o.startswith("ar_inst_") or o in ("workspace.o", "ar_fusion_launch.host.o", "fd_channel.host.o")]
     lines += [
@@ -160,16 +168,16 @@ def write_ninja() -> Path:
     return path
 
 
-def build(force: bool = False, verbose: bool = False, checked: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, checked: bool = False, traced: bool = False) -> Path:
     """Compile (if needed) and return the path of the extension library. ``checked`` also builds the
-    range-checking flavour ``_C_bounds.so``."""
+    range-checking flavour ``_C_bounds.so``, ``traced`` the tracing flavour ``_C_trace.so``."""
     write_ninja()
     if force:
         subprocess.run(["ninja", "-C", str(BUILD_DIR), "-t", "clean"], check=False,
                        stdout=subprocess.DEVNULL)
     cmd = ["ninja", "-C", str(BUILD_DIR)] + (["-v"] if verbose else [])
-    if checked:
-        cmd += [str(LIB_PATH), str(UNIT_TEST_BIN), str(CHECKED_LIB_PATH)]
+    if checked or traced:
+        cmd += [str(LIB_PATH), str(UNIT_TEST_BIN)] + ([str(CHECKED_LIB_PATH)] if checked else []) + ([str(TRACED_LIB_PATH)] if traced else [])
     jobs = os.environ.get("TDX_BUILD_JOBS")
     if jobs:
         cmd += ["-j", jobs]
@@ -178,13 +186,13 @@ def build(force: bool = False, verbose: bool = False, checked: bool = False) -> 
         raise RuntimeError("native build failed:\n" + res.stdout[-8000:])
     if verbose:
         print(res.stdout)
-    return CHECKED_LIB_PATH if checked else LIB_PATH
+    return CHECKED_LIB_PATH if checked else TRACED_LIB_PATH if traced else LIB_PATH
 
 
 def clean() -> None:
     """Remove build products (what the reference's `setup.py clean` does via .gitignore parsing)."""
     shutil.rmtree(BUILD_DIR, ignore_errors=True)
-    for lib in (LIB_PATH, CHECKED_LIB_PATH):
+    for lib in (LIB_PATH, CHECKED_LIB_PATH, TRACED_LIB_PATH):
         if lib.exists():
             lib.unlink()
 
@@ -193,4 +201,5 @@ if __name__ == "__main__":
     if "--clean" in sys.argv:
         clean()
     else:
-        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--bounds" in sys.argv))
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checked="--bounds" in sys.argv,
+                    traced="--trace" in sys.argv))

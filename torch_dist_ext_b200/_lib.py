@@ -19,7 +19,10 @@ log = logging.getLogger("torch_dist_ext_b200")
 # same ops, but every store of the fused all-reduce kernels into a symmetric allocation is checked
 # against the allocation's extent and a violation becomes a status code instead of a stray write.
 _CHECKED = os.environ.get("TDX_BOUNDS", "0") not in ("0", "", "false", "off")
-_LIB = Path(__file__).resolve().parent / ("_C_bounds.so" if _CHECKED else "_C.so")
+# TDX_TRACE=1 selects the tracing flavour (`--trace`): the fused all-reduce kernels record when each block
+# passed each phase of its protocol (utils/tracing.py: PhaseTrace reads the record).
+_TRACED = not _CHECKED and os.environ.get("TDX_TRACE", "0") not in ("0", "", "false", "off")
+_LIB = Path(__file__).resolve().parent / ("_C_bounds.so" if _CHECKED else "_C_trace.so" if _TRACED else "_C.so")
 _loaded = False
 
 
@@ -36,7 +39,7 @@ def load() -> None:
         from . import _build
 
         log.info("building native extension (first use)")
-        _build.build(checked=_CHECKED)
+        _build.build(checked=_CHECKED, traced=_TRACED)
     try:
         torch.ops.load_library(str(_LIB))
     except OSError as e:  # pragma: no cover - depends on the machine

@@ -72,6 +72,12 @@ const void* select(const LaunchPlan& plan, int out) {
     case kAlgoNvlsTwoShot:
       if constexpr (!kEmu) return by_n<kAlgoNvlsTwoShot>(plan.n_tmpl, plan.vpt, out);
       break;
+    case kAlgoOneShotMc:
+      if constexpr (!kEmu) return by_n<kAlgoOneShotMc>(plan.n_tmpl, plan.vpt, out);
+      break;
+    case kAlgoTwoShotMc:
+      if constexpr (!kEmu) return by_n<kAlgoTwoShotMc>(plan.n_tmpl, plan.vpt, out);
+      break;
   }
   return nullptr;
 }
@@ -84,8 +90,19 @@ cudaError_t do_launch(const LaunchPlan& plan, int out, const ArParams& p, const 
     void* args[] = {const_cast<ArParams**>(&dev_ranks)};
     return cudaLaunchCooperativeKernel(fn, dim3(plan.grid, plan.emu_ranks), dim3(plan.threads), args, 0, stream);
   } else {
+    // Programmatic stream serialisation: the blocks may be scheduled before the previous kernel of the stream has
+    // finished; the kernel begins with griddepcontrol.wait, so nothing is read or written early.
     void* args[] = {const_cast<ArParams*>(&p)};
-    return cudaLaunchKernel(fn, dim3(plan.grid), dim3(plan.threads), args, 0, stream);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(plan.threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelExC(&cfg, fn, args);
   }
 }
 

@@ -9,6 +9,7 @@
 // token count, any rank count from 1 to 8 is accepted, and co-residency is obtained by sizing
 // the grid from the occupancy API rather than by an unchecked cooperative launch.
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -24,6 +25,22 @@ bool bounds_checked_build() {
 #endif
 }
 
+bool tracing_build() {
+#ifdef TDX_TRACE
+  return true;
+#else
+  return false;
+#endif
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("TDX_PDL");
+    return !(e != nullptr && (e[0] == '0' || e[0] == 'o' || e[0] == 'f'));
+  }();
+  return on;
+}
+
 Policy& policy() {
   static Policy pol = [] {
     Policy q{};
@@ -34,6 +51,9 @@ Policy& policy() {
       q.lamport_max_bytes[n] = 12u << 20;
       // in-switch reduction pays off once N-1 peers' worth of traffic is saved: never at 2 ranks
       q.nvls_min_bytes[n] = n <= 2 ? ~0ull : n <= 4 ? (32ull << 20) : (12ull << 20);
+      // one multimem.st instead of n - 1 stores pays off from three peers on
+      q.mc_oneshot[n] = n >= 4;
+      q.mc_twoshot[n] = n >= 4;
     }
     q.prefer_nvls = 1;
     return q;
@@ -133,6 +153,7 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
     for (int r = 0; r < n; ++r)
       if (p.peer[r] == nullptr) return "workspace is not registered with all peers (null peer pointer)";
     if (algo == kAlgoLocal) return "the local algorithm needs nranks == 1";
+    const bool mc_ok = p.mc_base != nullptr && emu_ranks == 0;
     if (algo == kAlgoAuto) {
       const Policy& pol = policy();
       const bool nvls_ok = p.mc_base != nullptr && pol.prefer_nvls && emu_ranks == 0 &&
@@ -141,17 +162,19 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
       if (nvls_ok && msg_bytes >= pol.nvls_min_bytes[n])
         algo = kAlgoNvlsTwoShot;
       else if (!p.scatter_only && msg_bytes <= pol.oneshot_max_bytes[n] && need_oneshot <= p.layout.lamport_bytes)
-        algo = kAlgoOneShotLamport;
+        algo = (mc_ok && pol.mc_oneshot[n]) ? kAlgoOneShotMc : kAlgoOneShotLamport;
       else if (msg_bytes <= pol.lamport_max_bytes[n] && need_ts_lamport <= p.layout.lamport_bytes)
-        algo = kAlgoTwoShotLamport;
+        algo = (mc_ok && pol.mc_twoshot[n] && !p.scatter_only) ? kAlgoTwoShotMc : kAlgoTwoShotLamport;
       else
         algo = kAlgoTwoShotBarrier;
     }
-    if (algo == kAlgoOneShotLamport) {
+    if ((algo == kAlgoOneShotMc || algo == kAlgoTwoShotMc) && !mc_ok)
+      return "the multicast-push algorithms need a workspace with an NVSwitch multicast mapping (not available here) and real ranks";
+    if (algo == kAlgoOneShotLamport || algo == kAlgoOneShotMc) {
       if (p.scatter_only) return "the one-shot algorithm cannot produce scattered output";
       if (need_oneshot > p.layout.lamport_bytes)
         return fmt("one-shot needs %lld bytes of Lamport buffer, capacity is %lld", need_oneshot, p.layout.lamport_bytes);
-    } else if (algo == kAlgoTwoShotLamport) {
+    } else if (algo == kAlgoTwoShotLamport || algo == kAlgoTwoShotMc) {
       if (need_ts_lamport > p.layout.lamport_bytes)
         return fmt("two-shot (Lamport) needs %lld bytes of Lamport buffer, capacity is %lld", need_ts_lamport, p.layout.lamport_bytes);
     } else if (algo == kAlgoTwoShotBarrier) {

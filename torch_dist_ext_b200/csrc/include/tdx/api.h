@@ -29,11 +29,18 @@ struct Policy {
   uint64_t lamport_max_bytes[kMaxRanks + 1];   // above: flag-barrier two-shot
   int prefer_nvls;                             // use NVLS paths when a multicast mapping exists
   uint64_t nvls_min_bytes[kMaxRanks + 1];      // per rank count; NVLS two-shot at or above this size
+  // With a multicast mapping: push through multimem.st (the switch replicates) instead of one store per peer.
+  uint8_t mc_oneshot[kMaxRanks + 1];
+  uint8_t mc_twoshot[kMaxRanks + 1];
 };
 Policy& policy();
 
 // True in the library flavour compiled with -DTDX_BOUNDS (range-checked stores into symmetric memory).
 bool bounds_checked_build();
+// True in the flavour compiled with -DTDX_TRACE (the kernels record phase time stamps, see TraceSlot).
+bool tracing_build();
+// Programmatic dependent launch of the fused all-reduce kernels (on unless TDX_PDL=0).
+bool pdl_enabled();
 
 // Validates shapes, alignment and capacity, resolves kAlgoAuto and sizes the launch.
 // Returns an empty string on success, else the reason.
@@ -121,6 +128,9 @@ class Workspace {
   // Checked build only: pretend the allocation ends after `bytes` (0 = its real size), so that a test can
   // watch a store that leaves the extent being recorded and redirected.
   void set_debug_extent(uint64_t bytes) { debug_extent_ = bytes; }
+  // Tracing build only: device buffer of kTraceSlots 64-bit words per block that the kernels fill with phase
+  // time stamps (null = off). The release build ignores it.
+  void set_trace(uint64_t* dev_buffer) { trace_ = dev_buffer; }
   uint64_t timeout_ns() const { return timeout_ns_; }
   int rank() const { return rank_; }
   int world_size() const { return world_; }
@@ -146,6 +156,7 @@ class Workspace {
   uint32_t* host_status_dev_ = nullptr;
   uint64_t timeout_ns_;
   uint64_t debug_extent_ = 0;
+  uint64_t* trace_ = nullptr;
   bool registered_ = false;
   struct Vmm;                // virtual-memory / multicast state (workspace.cu)
   Vmm* vmm_ = nullptr;

@@ -274,7 +274,10 @@ __device__ __forceinline__ void local_body(const ArParams& p) {
 
 // ---- one-shot Lamport ------------------------------------------------------------------
 
-template <typename T, int kN, int kVpt, int kOut>
+// kMc: the push is one multimem.st per vector into slot `rank` of the multicast mapping; NVSwitch replicates it
+// into every rank's buffer (this rank's own slot included, which nobody reads), so the sender's links carry the
+// message once instead of N - 1 times and a thread issues one store instead of N - 1.
+template <typename T, int kN, int kVpt, int kOut, bool kMc = false>
 __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
   constexpr int kVec = VecTraits<T>::kVec;
   __shared__ float red[4][32];
@@ -299,16 +302,23 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
       const size_t off = (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16;
       const uint4 val = scrub(ptx::ld_stream_v4(in + off));
       own[v] = val;
+      const size_t dst = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes + (size_t)p.rank * msg_bytes + off;
+      if constexpr (kMc) {
+        ptx::multimem_st_v4(symm_mc(p, dst), val);
+      } else {
 #pragma unroll
-      for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
-        if (r >= nranks || r == p.rank) continue;
-        ptx::st_v4(symm(p, r, p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes + (size_t)p.rank * msg_bytes + off), val);
+        for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
+          if (r >= nranks || r == p.rank) continue;
+          ptx::st_v4(symm(p, r, dst), val);
+        }
       }
     }
   }
+  trace_mark(p, kTracePushed);
 
   // 2. restore the sentinels in the buffer the previous call used
   clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev);
+  trace_mark(p, kTraceCleared);
 
   // 3. gather, reduce, epilogue
   uint4 gamma[kVpt];
@@ -358,9 +368,12 @@ __device__ __forceinline__ void oneshot_lamport_body(const ArParams& p) {
       add_residual_loaded<T>(x[v], p.residual_in != nullptr, res[v]);
       if (p.residual_out) ptx::st_stream_v4(static_cast<char*>(p.residual_out) + off, pack<T>(x[v]));
     }
+    trace_mark(p, kTraceGathered);
     float rstd, sc;
     finish_row<T, kVpt, kOut>(p, rv, row, x, gamma, red, parity, rstd, sc);
   }
+  trace_mark(p, kTraceEndClk);
+  trace_mark_ns(p, kTraceEndNs);
   finish_launch(ctl, true, epoch, (uint64_t)nranks * msg_bytes, 0);
 }
 
@@ -437,7 +450,9 @@ __device__ __forceinline__ void twoshot_scatter_rows(const ArParams& p, const Ro
 // kOwnFromBuffer: this rank's own partial row is polled from its gather slot like the peers'
 // (used when the partial rows are produced by a GEMM epilogue instead of being an input tensor).
 // Returns the number of bytes of the Lamport buffer that hold data after this call.
-template <typename T, int kN, int kVpt, int kOut, bool kOwnFromBuffer>
+// kMc: finished rows and their trailers leave the owner as one multimem.st each, replicated by NVSwitch into every
+// rank's result area (the owner's own included, which it never reads).
+template <typename T, int kN, int kVpt, int kOut, bool kOwnFromBuffer, bool kMc = false>
 __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int cta, int nctas, uint32_t epoch,
                                                          float (*red)[32]) {
   constexpr int kVec = VecTraits<T>::kVec;
@@ -508,20 +523,30 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
       if (p.residual_out)
         ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)out_row * rv.row_bytes + voff, packed[v]);
       if (gather_back) {
+        if constexpr (kMc) {
+          ptx::multimem_st_v4(symm_mc(p, result_off + (size_t)row * g.result_stride + voff), packed[v]);
+        } else {
 #pragma unroll
-        for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
-          if (r >= nranks || r == p.rank) continue;
-          ptx::st_v4(symm(p, r, result_off + (size_t)row * g.result_stride + voff), packed[v]);
+          for (int r = 0; r < (kN > 0 ? kN : kMaxRanks); ++r) {
+            if (r >= nranks || r == p.rank) continue;
+            ptx::st_v4(symm(p, r, result_off + (size_t)row * g.result_stride + voff), packed[v]);
+          }
         }
       }
     }
+    trace_mark(p, kTraceGathered);
     float rstd, sc;
     finish_row<T, kVpt, kOut>(p, rv, out_row, x, gamma, red, parity, rstd, sc);
     parity ^= 1;
-    if (gather_back && threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
+    if (gather_back) {
       const uint4 trailer = make_uint4(__float_as_uint(rstd), __float_as_uint(sc), 0u, 0u);
-      ptx::st_v4(symm(p, threadIdx.x, result_off + (size_t)row * g.result_stride + rv.row_bytes), trailer);
+      if constexpr (kMc) {
+        if (threadIdx.x == 0) ptx::multimem_st_v4(symm_mc(p, result_off + (size_t)row * g.result_stride + rv.row_bytes), trailer);
+      } else if (threadIdx.x < nranks && (int)threadIdx.x != p.rank) {
+        ptx::st_v4(symm(p, threadIdx.x, result_off + (size_t)row * g.result_stride + rv.row_bytes), trailer);
+      }
     }
+    trace_mark(p, kTraceOwnerDone);
   }
 
   // receive phase: rows owned by the peers, split by row over all blocks
@@ -532,6 +557,7 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
       {
         const char* src = self + result_off + (size_t)row * g.result_stride;
         const uint4 trailer = poll_vec(src + rv.row_bytes, w, p, ctl, kTimeoutLamportResult, r, 2, row);
+        trace_mark(p, kTraceTrailer);
         const float rstd = __uint_as_float(trailer.x);
         const float sc = __uint_as_float(trailer.y);
         float x[kVpt][kVec];
@@ -546,6 +572,7 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
           if (p.residual_out)
             ptx::st_stream_v4(static_cast<char*>(p.residual_out) + (size_t)row * rv.row_bytes + voff, val);
         }
+        trace_mark(p, kTraceReceived);
         if (kOut == kOutFp8Token && threadIdx.x == 0) p.scale_out[row] = sc;
         store_norm<T, kVpt, kOut>(p, rv, row, x, gamma, rstd, sc);
       }
@@ -554,7 +581,7 @@ __device__ __forceinline__ uint64_t twoshot_lamport_tail(const ArParams& p, int 
   return g.gather_bytes + (gather_back ? (uint64_t)p.tokens * g.result_stride : 0);
 }
 
-template <typename T, int kN, int kVpt, int kOut>
+template <typename T, int kN, int kVpt, int kOut, bool kMc = false>
 __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
   __shared__ float red[4][32];
   const int nranks = kN > 0 ? kN : p.nranks;
@@ -567,8 +594,12 @@ __device__ __forceinline__ void twoshot_lamport_body(const ArParams& p) {
   const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
 
   twoshot_scatter_rows<T, kVpt>(p, rv, g, nranks, buf_off);
+  trace_mark(p, kTracePushed);
   clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev);
-  const uint64_t dirty = twoshot_lamport_tail<T, kN, kVpt, kOut, false>(p, blockIdx.x, gridDim.x, epoch, red);
+  trace_mark(p, kTraceCleared);
+  const uint64_t dirty = twoshot_lamport_tail<T, kN, kVpt, kOut, false, kMc>(p, blockIdx.x, gridDim.x, epoch, red);
+  trace_mark(p, kTraceEndClk);
+  trace_mark_ns(p, kTraceEndNs);
   finish_launch(ctl, true, epoch, dirty, 0);
 }
 
@@ -859,6 +890,8 @@ __device__ __forceinline__ void ar_dispatch_body(const ArParams& p) {
   else if constexpr (kAlgo == kAlgoTwoShotBarrier) twoshot_barrier_body<T, kN, kVpt, kOut>(p);
   else if constexpr (kAlgo == kAlgoNvlsOneShot) nvls_oneshot_body<T, kN, kVpt, kOut>(p);
   else if constexpr (kAlgo == kAlgoNvlsTwoShot) nvls_twoshot_body<T, kN, kVpt, kOut>(p);
+  else if constexpr (kAlgo == kAlgoOneShotMc) oneshot_lamport_body<T, kN, kVpt, kOut, true>(p);
+  else if constexpr (kAlgo == kAlgoTwoShotMc) twoshot_lamport_body<T, kN, kVpt, kOut, true>(p);
 }
 
 // kVpt == 1 kernels may run with up to 1024 threads (64 registers); wider rows use at most
@@ -868,6 +901,13 @@ constexpr int kMaxThreadsFor = (kVpt == 1) ? 1024 : 512;
 
 template <typename T, int kAlgo, int kN, int kVpt, int kOut>
 __global__ void __launch_bounds__(kMaxThreadsFor<kVpt>, 1) ar_fused_kernel(const __grid_constant__ ArParams p) {
+  // Launched with programmatic stream serialisation (ar_fusion_inst.cu), the blocks of this kernel are scheduled
+  // while the previous kernel of the stream still runs, and wait here until it has completed and its memory
+  // is visible; the next kernel may then be scheduled in the same way. A plain launch passes straight through.
+  ptx::pdl_wait();
+  ptx::pdl_launch_dependents();
+  trace_mark_ns(p, kTraceStartNs);
+  trace_mark(p, kTraceStartClk);
   ar_dispatch_body<T, kAlgo, kN, kVpt, kOut>(p);
 }
 

@@ -25,12 +25,14 @@ class CommWorkspace : public torch::CustomClassHolder {
   std::string multicast_note();
   void set_timeout_ms(int64_t ms);
   void set_debug_extent(int64_t bytes);
+  void set_trace(const c10::optional<at::Tensor>& buffer);
   int64_t errors_seen();
   std::vector<int64_t> stats();
   tdx::Workspace* impl() { return impl_.get(); }
 
  private:
   std::unique_ptr<tdx::Workspace> impl_;
+  at::Tensor trace_;   // keeps the trace buffer alive while the kernels may write to it
 };
 
 // Registers the standalone ops, GEMMs and model kernels (defined in ops_register.cpp).

@@ -113,6 +113,8 @@ enum Algo : int32_t {
   kAlgoTwoShotBarrier = 4,   // same data flow, flag barriers, any size up to the capacity
   kAlgoNvlsOneShot = 5,      // multimem.ld_reduce of every row by every rank
   kAlgoNvlsTwoShot = 6,      // multimem.ld_reduce own rows -> epilogue -> multimem.st
+  kAlgoOneShotMc = 7,        // one-shot Lamport whose push is ONE multimem.st per vector (the switch replicates it)
+  kAlgoTwoShotMc = 8,        // two-shot Lamport whose result hop is one multimem.st per vector and trailer
 };
 
 struct ArParams {
@@ -141,6 +143,23 @@ struct ArParams {
   uint64_t timeout_ns;      // budget of every device-side wait
   uint32_t* host_status;    // pinned, host-mapped mirror of Control::status (or null)
   uint64_t debug_extent;    // checked build (-DTDX_BOUNDS): extent to check against; 0 = layout.total_bytes
+  uint64_t* trace;          // tracing build (-DTDX_TRACE): kTraceSlots time stamps per block, or null
+};
+
+// Tracing build: what block b writes to trace[b * kTraceSlots + slot] (thread 0's view).
+constexpr int kTraceSlots = 16;
+enum TraceSlot : int32_t {
+  kTraceStartNs = 0,      // %globaltimer when the block starts working (after the dependency wait)
+  kTraceStartClk = 1,     // clock64 at the same point; the slots below are clock64 values
+  kTracePushed = 2,       // own rows pushed (one-shot: to every peer; two-shot: to their owners)
+  kTraceCleared = 3,      // previous Lamport buffer re-filled with sentinels
+  kTraceGathered = 4,     // owner / one-shot: every peer's vector of the (last) row has arrived
+  kTraceOwnerDone = 5,    // two-shot owner: reduced row and trailer pushed
+  kTraceTrailer = 6,      // two-shot receiver: trailer of the (last) received row has arrived
+  kTraceReceived = 7,     // two-shot receiver: data of that row has arrived
+  kTraceEndClk = 8,       // before the end-of-launch bookkeeping
+  kTraceEndNs = 9,        // %globaltimer at the same point
+  kTraceSm = 10,          // SM the block ran on
 };
 
 }  // namespace tdx

@@ -123,6 +123,42 @@ __device__ __forceinline__ char* symm(const ArParams& p, int r, size_t off) {
   return static_cast<char*>(p.peer[r]) + off;
 }
 
+// Address of the same 16-byte vector in the NVSwitch multicast mapping: one multimem.st to it lands in EVERY
+// rank's allocation (this rank's included).
+__device__ __forceinline__ char* symm_mc(const ArParams& p, size_t off) {
+#ifdef TDX_BOUNDS
+  const uint64_t extent = p.debug_extent ? p.debug_extent : p.layout.total_bytes;
+  if ((uint64_t)off + 16 > extent) {
+    char* self = static_cast<char*>(p.peer[p.rank]);
+    report_error(reinterpret_cast<Control*>(self + p.layout.off_control), p.host_status, kBoundsViolation, p.rank, -1, 0,
+                 (int)(off >> 10));
+    off = p.layout.off_control + kBoundsScratchOffset + (size_t)(threadIdx.x & 63) * 16;
+  }
+#endif
+  return static_cast<char*>(p.mc_base) + off;
+}
+
+// ---- phase time stamps (tracing build only) ---------------------------------------------------
+// Compiled with -DTDX_TRACE, thread 0 of every block records when it passed each phase of the protocol
+// (see TraceSlot); the release build compiles these calls to nothing.
+__device__ __forceinline__ void trace_mark(const ArParams& p, int slot) {
+#ifdef TDX_TRACE
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * kTraceSlots + slot] = (uint64_t)clock64();
+#endif
+}
+__device__ __forceinline__ void trace_mark_ns(const ArParams& p, int slot) {
+#ifdef TDX_TRACE
+  if (p.trace != nullptr && threadIdx.x == 0) {
+    p.trace[(size_t)blockIdx.x * kTraceSlots + slot] = ptx::globaltimer_ns();
+    if (slot == kTraceStartNs) {
+      uint32_t sm;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+      p.trace[(size_t)blockIdx.x * kTraceSlots + kTraceSm] = sm;
+    }
+  }
+#endif
+}
+
 // ---- cross-GPU flag barrier ---------------------------------------------------------
 // flags[block][src_rank] on every rank. Thread t < nranks of block b publishes `target`
 // into rank t's flags[b][my_rank], then waits for its own flags[b][t] to reach `target`.

@@ -99,6 +99,19 @@ std::string CommWorkspace::multicast_note() { return impl_->multicast_note(); }
 void CommWorkspace::set_timeout_ms(int64_t ms) { impl_->set_timeout_ns((uint64_t)ms * 1000000ull); }
 void CommWorkspace::set_debug_extent(int64_t bytes) { impl_->set_debug_extent((uint64_t)bytes); }
 int64_t CommWorkspace::errors_seen() { return impl_->errors_seen(); }
+void CommWorkspace::set_trace(const c10::optional<Tensor>& buffer) {
+  if (!buffer.has_value() || !buffer->defined()) {
+    impl_->set_trace(nullptr);
+    trace_ = Tensor();
+    return;
+  }
+  TORCH_CHECK(buffer->is_cuda() && buffer->get_device() == impl_->device() && buffer->scalar_type() == at::kLong &&
+                  buffer->is_contiguous() && buffer->numel() >= (int64_t)tdx::kMaxBarrierBlocks * tdx::kTraceSlots,
+              "CommWorkspace.set_trace: need a contiguous int64 tensor of at least ", tdx::kMaxBarrierBlocks * tdx::kTraceSlots,
+              " elements on the workspace's device");
+  trace_ = *buffer;
+  impl_->set_trace(reinterpret_cast<uint64_t*>(trace_.data_ptr<int64_t>()));
+}
 
 std::vector<int64_t> CommWorkspace::stats() {
   tdx::WorkspaceStats s = impl_->stats();
@@ -268,15 +281,23 @@ int64_t allreduce_rms_emulated(std::vector<c10::intrusive_ptr<CommWorkspace>> wo
   return used.algo;
 }
 
-void set_policy(int64_t nranks, int64_t oneshot_max_bytes, int64_t lamport_max_bytes) {
+// Negative values leave the entry as it is.
+void set_policy(int64_t nranks, int64_t oneshot_max_bytes, int64_t lamport_max_bytes, int64_t mc_oneshot, int64_t mc_twoshot,
+                int64_t nvls_min_bytes) {
   TORCH_CHECK(nranks >= 1 && nranks <= tdx::kMaxRanks, "nranks out of range");
-  tdx::policy().oneshot_max_bytes[nranks] = (uint64_t)oneshot_max_bytes;
-  tdx::policy().lamport_max_bytes[nranks] = (uint64_t)lamport_max_bytes;
+  tdx::Policy& pol = tdx::policy();
+  if (oneshot_max_bytes >= 0) pol.oneshot_max_bytes[nranks] = (uint64_t)oneshot_max_bytes;
+  if (lamport_max_bytes >= 0) pol.lamport_max_bytes[nranks] = (uint64_t)lamport_max_bytes;
+  if (mc_oneshot >= 0) pol.mc_oneshot[nranks] = mc_oneshot != 0;
+  if (mc_twoshot >= 0) pol.mc_twoshot[nranks] = mc_twoshot != 0;
+  if (nvls_min_bytes >= 0) pol.nvls_min_bytes[nranks] = (uint64_t)nvls_min_bytes;
 }
 
 std::vector<int64_t> get_policy(int64_t nranks) {
   TORCH_CHECK(nranks >= 1 && nranks <= tdx::kMaxRanks, "nranks out of range");
-  return {(int64_t)tdx::policy().oneshot_max_bytes[nranks], (int64_t)tdx::policy().lamport_max_bytes[nranks]};
+  const tdx::Policy& pol = tdx::policy();
+  return {(int64_t)pol.oneshot_max_bytes[nranks], (int64_t)pol.lamport_max_bytes[nranks], (int64_t)pol.mc_oneshot[nranks],
+          (int64_t)pol.mc_twoshot[nranks], (int64_t)(pol.nvls_min_bytes[nranks] > (uint64_t)INT64_MAX ? INT64_MAX : pol.nvls_min_bytes[nranks])};
 }
 
 std::vector<int64_t> plan_allreduce(int64_t nranks, int64_t tokens, int64_t hidden, int64_t dtype, int64_t out_mode,
@@ -312,6 +333,7 @@ TORCH_LIBRARY(torch_dist_ext, m) {
       .def("open_handles", &CommWorkspace::open_handles)
       .def("get_workspace", &CommWorkspace::get_workspace)
       .def("adopt_table", &CommWorkspace::adopt_table)
+      .def("set_trace", &CommWorkspace::set_trace)
       .def("reset", &CommWorkspace::reset)
       .def("set_timeout_ms", &CommWorkspace::set_timeout_ms)
       .def("set_debug_extent", &CommWorkspace::set_debug_extent)
@@ -342,7 +364,7 @@ TORCH_LIBRARY(torch_dist_ext, m) {
       "Tensor(b!) norm_out, Tensor(c!)? scale_out, float eps, Tensor workspace, int out_mode, int algo, "
       "bool scatter_only) -> int",
       &tdx_torch::allreduce_rms_fusion_hostio);
-  m.def("set_policy(int nranks, int oneshot_max_bytes, int lamport_max_bytes) -> ()", &tdx_torch::set_policy);
+  m.def("set_policy(int nranks, int oneshot_max_bytes, int lamport_max_bytes, int mc_oneshot=-1, int mc_twoshot=-1, int nvls_min_bytes=-1) -> ()", &tdx_torch::set_policy);
   m.def("get_policy(int nranks) -> int[]", &tdx_torch::get_policy);
   m.def(
       "plan_allreduce(int nranks, int tokens, int hidden, int dtype, int out_mode, int algo, int max_message_bytes, "

@@ -481,6 +481,7 @@ void Workspace::fill_params(ArParams* p) const {
   p->timeout_ns = timeout_ns_;
   p->host_status = host_status_dev_;
   p->debug_extent = debug_extent_;
+  p->trace = trace_;
   static const int waves_env = [] {
     const char* e = std::getenv("TDX_WAVES");
     return e ? std::atoi(e) : 1;

@@ -36,8 +36,8 @@ from ..parallel import comm as _comm
 from ..utils.config import OUT_FP8_BLOCK128, OUT_SAME
 from ..utils.tracing import nvtx_range, traced
 
-# prompt-phase attention: "tc" = this library's tcgen05 kernel (opt-in), anything else = PyTorch's SDPA
-_PREFILL_ATTN_TC = os.environ.get("TDX_PREFILL_ATTN", "sdpa").lower() == "tc"
+# prompt-phase attention: this library's tcgen05 kernel; "sdpa" selects PyTorch's kernel for comparisons
+_PREFILL_ATTN_TC = os.environ.get("TDX_PREFILL_ATTN", "tc").lower() != "sdpa"
 
 
 @dataclass
@@ -281,8 +281,8 @@ class TPLlama:
         """Run one prompt ``[S]`` through all layers, filling row ``seq_index`` of the KV cache.
 
         GEMMs and the fused all-reduce+norm run on this library's kernels (normal-orientation
-        tcgen05 tiles, two-shot / NVLS all-reduce); causal attention over the prompt uses PyTorch's
-        scaled_dot_product_attention, or this library's tcgen05 kernel with ``TDX_PREFILL_ATTN=tc``.
+        tcgen05 tiles, two-shot / NVLS all-reduce), causal attention over the prompt included
+        (``TDX_PREFILL_ATTN=sdpa`` swaps in PyTorch's scaled_dot_product_attention for comparisons).
         Returns the first generated token."""
         cfg, d = self.cfg, self.cfg.head_dim
         assert self.mode == "ar", "prefill is implemented for the replicated (all-reduce) mode"

@@ -1,5 +1,5 @@
 """Attention for grouped-query heads of dimension 128: decode (one new token per sequence over a
-contiguous bf16 KV cache; SIMT kernel, or tcgen05 kernel on request) and causal attention over one
+contiguous bf16 KV cache; tcgen05 kernel, or the SIMT kernel with ``TDX_ATTN_TC=0``) and causal attention over one
 prompt (tcgen05 kernel)."""
 from __future__ import annotations
 
@@ -13,7 +13,7 @@ from .. import _lib
 from ..utils.tracing import traced
 
 _scratch = {}
-_TC_DEFAULT = os.environ.get("TDX_ATTN_TC", "0") not in ("0", "", "false", "off")
+_TC_DEFAULT = os.environ.get("TDX_ATTN_TC", "1") not in ("0", "", "false", "off")
 
 
 def _partial(device, floats: int) -> torch.Tensor:
@@ -40,7 +40,7 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     """``q [B, Hq, 128]``, caches ``[B, S_max, Hkv, 128]``, ``seq_lens`` int32 ``[B]`` -> ``[B, Hq, 128]``.
 
     ``max_len`` (a host integer >= every sequence length) only sizes the KV split. ``tensor_cores=True``
-    runs both products of every 128-position chunk as tcgen05 MMAs (default: ``TDX_ATTN_TC``, off)."""
+    runs both products of every 128-position chunk as tcgen05 MMAs (default: ``TDX_ATTN_TC``, on)."""
     b, hq, d = q.shape
     hkv = k_cache.shape[2]
     use_tc = _TC_DEFAULT if tensor_cores is None else tensor_cores

@@ -23,7 +23,7 @@ _ws = {}
 
 
 _PAIR_DEFAULT = os.environ.get("TDX_GEMM_PAIR", "0") not in ("0", "", "false", "off")
-_PERSIST_DEFAULT = os.environ.get("TDX_GEMM_PERSIST", "0") not in ("0", "", "false", "off")
+_PERSIST_DEFAULT = os.environ.get("TDX_GEMM_PERSIST", "1") not in ("0", "", "false", "off")
 
 
 def _workspace(device: torch.device):
@@ -74,7 +74,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     ``cta_pair=True`` runs prefill-sized problems (M, N >= 256) on 256 x 256 tiles computed by pairs of
     CTAs (``tcgen05.mma.cta_group::2``); the default follows ``TDX_GEMM_PAIR`` (off). ``persistent=True`` runs
     them on a persistent grid (one CTA per SM, accumulator double-buffered in tensor memory so that the epilogue
-    of a tile overlaps the main loop of the next); the default follows ``TDX_GEMM_PERSIST`` (off)."""
+    of a tile overlaps the main loop of the next); the default follows ``TDX_GEMM_PERSIST`` (on)."""
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "linear: a [M, K], w [N, K]"
     m, k = a.shape
     n = w.shape[0]

@@ -68,8 +68,8 @@ class CommProcess:
             if not all(flags):
                 log.info("NVLS disabled: %s", self.comm.multicast_note() or "a peer could not join the multicast object")
             dist.barrier(group=group)
-        for n, (a, b) in config.policy.items():
-            _lib.ops().set_policy(n, a, b)
+        for n, entry in config.policy.items():
+            _lib.ops().set_policy(n, *entry)
         self._table = self.comm.get_workspace(torch.empty(0, device=self.device))
 
     def _exchange_cpu(self) -> None:

@@ -7,7 +7,10 @@ environment:
 
 =====================  ============================================================
 ``TDX_ALGO``           ``auto`` | ``oneshot`` | ``twoshot`` | ``twoshot_barrier`` |
-                       ``nvls_oneshot`` | ``nvls_twoshot``
+                       ``nvls_oneshot`` | ``nvls_twoshot`` | ``oneshot_mc`` | ``twoshot_mc``
+                       (the ``_mc`` forms push through ``multimem.st``: NVSwitch replicates the store)
+``TDX_PDL``            ``0`` launches the fused all-reduce kernels without programmatic stream
+                       serialisation (read by the native launcher)
 ``TDX_TIMEOUT_MS``     budget of every device-side wait (default 5000)
 ``TDX_LAMPORT_MB``     capacity of each of the three Lamport buffers (default 32)
 ``TDX_NVLS``           ``0`` disables the NVSwitch-multicast mapping and kernels
@@ -35,6 +38,8 @@ ALGO_CODES = {
     "twoshot_barrier": 4,
     "nvls_oneshot": 5,
     "nvls_twoshot": 6,
+    "oneshot_mc": 7,
+    "twoshot_mc": 8,
 }
 ALGO_NAMES = {v: k for k, v in ALGO_CODES.items()}
 
@@ -47,8 +52,9 @@ class Config:
     timeout_ms: int = 5000
     lamport_mb: int = 32
     nvls: bool = True
-    # nranks -> (oneshot_max_bytes, lamport_max_bytes); empty = built-in defaults
-    policy: Dict[int, Tuple[int, int]] = field(default_factory=dict)
+    # nranks -> (oneshot_max_bytes, lamport_max_bytes, mc_oneshot, mc_twoshot, nvls_min_bytes), -1 = keep the
+    # built-in value; empty = built-in defaults
+    policy: Dict[int, Tuple[int, ...]] = field(default_factory=dict)
 
     @staticmethod
     def from_env() -> "Config":
@@ -68,11 +74,13 @@ class Config:
         return c
 
     def load_policy(self, path: str) -> None:
-        """Read ``{"<nranks>": {"oneshot_max_bytes": .., "lamport_max_bytes": ..}, ...}``."""
+        """Read ``{"<nranks>": {"oneshot_max_bytes": .., "lamport_max_bytes": .., "mc_oneshot": 0|1,
+        "mc_twoshot": 0|1, "nvls_min_bytes": ..}, ...}`` (the last three are optional)."""
         with open(path) as f:
             table = json.load(f)
         for k, v in table.items():
-            self.policy[int(k)] = (int(v["oneshot_max_bytes"]), int(v["lamport_max_bytes"]))
+            self.policy[int(k)] = (int(v["oneshot_max_bytes"]), int(v["lamport_max_bytes"]), int(v.get("mc_oneshot", -1)),
+                                   int(v.get("mc_twoshot", -1)), int(v.get("nvls_min_bytes", -1)))
 
     @property
     def algo_code(self) -> int:
