@@ -132,7 +132,7 @@ def main():
             if hidden in hidden_list:
                 algos = ["auto"] if world == 1 else ["oneshot", "twoshot", "twoshot_barrier"]
                 if world > 1 and api.stats().get("has_multicast"):
-                    algos += ["nvls_oneshot", "nvls_twoshot"]
+                    algos += ["oneshot_mc", "twoshot_mc", "nvls_oneshot", "nvls_twoshot"]
                 if world > 1:
                     algos += ["auto"]
                 for algo in algos:
@@ -172,8 +172,23 @@ def main():
         # measured crossover: largest message for which one-shot is not slower than two-shot
         one = [r["bytes"] for r in rows if r.get("oneshot") and r.get("twoshot") and r["oneshot"] <= r["twoshot"]]
         lam = [r["bytes"] for r in rows if r.get("twoshot") and r.get("twoshot_barrier") and r["twoshot"] <= r["twoshot_barrier"]]
+        def best(r, *names):
+            vals = [r[n] for n in names if r.get(n)]
+            return min(vals) if vals else None
+
+        # the same crossovers with the multicast-push variants taken into account, and whether those win
+        one = [r["bytes"] for r in rows if best(r, "oneshot", "oneshot_mc") and best(r, "twoshot", "twoshot_mc")
+               and best(r, "oneshot", "oneshot_mc") <= best(r, "twoshot", "twoshot_mc")]
+        small = [r for r in rows if r["bytes"] <= (4 << 20)]
+        mc1 = sum(1 if r["oneshot_mc"] < r["oneshot"] else -1 for r in small if r.get("oneshot_mc") and r.get("oneshot"))
+        mc2 = sum(1 if r["twoshot_mc"] < r["twoshot"] else -1 for r in small if r.get("twoshot_mc") and r.get("twoshot"))
+        p2p = [best(r, "twoshot", "twoshot_mc", "twoshot_barrier") for r in rows]
+        nvls = [r["bytes"] for r, b in zip(rows, p2p) if r.get("nvls_twoshot") and b and r["nvls_twoshot"] < b]
         result["policy"] = {str(world): {"oneshot_max_bytes": max(one) if one else 0,
-                                         "lamport_max_bytes": max(lam) if lam else 0}}
+                                         "lamport_max_bytes": max(lam) if lam else 0,
+                                         "mc_oneshot": int(mc1 > 0), "mc_twoshot": int(mc2 > 0),
+                                         "nvls_min_bytes": min(nvls) if nvls else (1 << 62)}}
+        result["pdl"] = bool(torch.ops.torch_dist_ext.pdl_enabled())
         result["stats"] = {k: v for k, v in api.stats().items() if k != "status"}
     if rank == 0:
         out = args.out or os.path.join(common.out_dir(), f"sweep_{args.impl}_tp{world}.json")

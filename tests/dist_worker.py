@@ -35,7 +35,7 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
         has_mc = cuda and tdx.stats().get("has_multicast", False)
         for i, (tokens, hidden, dtype, algo, out_mode) in enumerate(cases):
             nvls = isinstance(algo, str) and algo.startswith("nvls")
-            if nvls and not has_mc:
+            if (nvls or (isinstance(algo, str) and algo.endswith("_mc"))) and not has_mc:
                 continue
             # the automatic choice moves large messages onto the NVLS path when there is one
             nvls_min = {2: 1 << 62, 4: 32 << 20}.get(world, 12 << 20)

@@ -21,6 +21,12 @@ def cases():
         out.append((64, 8192, torch.bfloat16, algo, OUT_SAME))
         out.append((257, 4096, torch.bfloat16, algo, OUT_FP8_TOKEN))
         out.append((37, 5120, torch.bfloat16, algo, OUT_FP8_BLOCK128))
+    for algo in ("oneshot_mc", "twoshot_mc"):               # multicast pushes; skipped by the worker without multicast
+        out.append((64, 8192, torch.bfloat16, algo, OUT_SAME))
+        out.append((129, 1024, torch.float32, algo, OUT_SAME))
+        out.append((257, 4096, torch.bfloat16, algo, OUT_FP8_TOKEN))
+        out.append((37, 5120, torch.bfloat16, algo, OUT_FP8_BLOCK128))
+        out.append((3, 1024, torch.float16, algo, OUT_SAME))
     for algo in ("nvls_oneshot", "nvls_twoshot"):           # skipped by the worker without multicast
         out.append((64, 8192, torch.bfloat16, algo, OUT_SAME))
         out.append((1, 4096, torch.float32, algo, OUT_SAME))

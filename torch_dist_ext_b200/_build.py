@@ -137,15 +137,17 @@ def write_ninja() -> Path:
     lines += [f"build {LIB_PATH}: link {' '.join(objs)}", f"  ldflags = {' '.join(ld)}"]
     for flavour, (define, lib_path) in FLAVOURS.items():
         flavour_objs = []
+        # the tracing flavour instruments the real launches only; the single-GPU emulation is shared
+        own_unit = (lambda stem: stem.startswith("ar_inst_") and not (flavour == "trace" and stem.endswith("_emu")))
         for obj in objs:
-            if obj.startswith("ar_inst_"):
+            if own_unit(obj[:-2]):
                 flavour_objs.append(obj.replace(".o", f".{flavour}.o", 1))
             elif obj == "ar_fusion_launch.host.o":
                 flavour_objs.append(f"ar_fusion_launch.{flavour}.host.o")
             else:
                 flavour_objs.append(obj)
         for src, stem, defs in _device_units():
-            if stem.startswith("ar_inst_"):
+            if own_unit(stem):
                 lines += [f"build {stem}.{flavour}.o: nvcc {CSRC / src}", f"  defs = {' '.join(defs)} {define}"]
         lines += [f"build ar_fusion_launch.{flavour}.host.o: cxx {CSRC / 'ar_fusion_launch.cpp'}", f"  extra = {define}"]
         lines += [f"build {lib_path}: link {' '.join(flavour_objs)}", f"  ldflags = {' '.join(ld)}"]

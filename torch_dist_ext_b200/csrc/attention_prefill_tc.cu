@@ -6,17 +6,18 @@
 //   O[q 128, d 128]   += P[q, keys] * V[keys, d]        P written by the softmax warps (K-major over keys),
 //                                                       V read MN-major (d contiguous) straight from its TMA tile
 //
-// The four softmax warps hold one query row per thread: the row maximum, the row sum and the 128
-// running outputs of the row live in that thread's registers, so the online softmax needs no
-// cross-thread reduction at all. S is double-buffered in tensor memory (the scores of chunk c+1 are
-// computed while chunk c is in the softmax), the P*V product of a chunk goes to its own TMEM buffer
-// and is folded into the registers with the rescale factor of the row. A fifth warp issues the TMA
-// copies (2-stage ring of K and V chunks, the Q tile once) and all MMAs.
+// The four softmax warps hold one query row per thread, so the online softmax needs no cross-thread
+// reduction. A thread fetches its 128 scores of a chunk with ONE tcgen05.ld (one TMEM round trip per
+// chunk) and gives the score buffer back at once; S is double-buffered, so the scores of chunk c+1 are
+// computed while chunk c is in the softmax. O stays in tensor memory and is accumulated there by the
+// P*V products of all chunks. A row's running maximum is only raised - and its part of O rescaled in
+// tensor memory - when the new maximum exceeds it by more than 2^8 (a warp-uniform decision); until
+// then the probabilities are taken against the older maximum, which changes neither O / l nor the
+// accuracy of bf16 probabilities below 256. A fifth warp issues the TMA copies (separate rings for
+// K, 2 stages, freed as soon as the scores are computed, and V, 3 stages, freed after P*V) and all MMAs.
 //
 // Every wait is bounded; a wait that runs out records a status word and raises the CTA's abort flag,
-// and all threads still reach the common exit. Opt-in (models/llama.py uses it for prefill when
-// TDX_PREFILL_ATTN=tc; the default is PyTorch's scaled_dot_product_attention).
-// Not part of the reference (it has no attention).
+// and all threads still reach the common exit. Not part of the reference (it has no attention).
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -34,16 +35,17 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kRows = 128;                        // query rows per CTA = key positions per chunk
-constexpr int kStages = 2;
+constexpr int kStagesK = 2;
+constexpr int kStagesV = 3;
 constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = kSoftmaxThreads + 32;
 constexpr int kHalfBytes = kRows * 128;           // one 64-column half of a 128-row tile
 constexpr int kTileBytes = 2 * kHalfBytes;        // Q, P, one K chunk or one V chunk
-constexpr int kStageBytes = 2 * kTileBytes;       // K chunk + V chunk
-constexpr int kSmem = kStages * kStageBytes + 2 * kTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
-constexpr uint32_t kTmemCols = 512;               // S buffers at columns 0 and 128, P*V of one chunk at 256
-constexpr uint32_t kColPV = 256;
+constexpr int kSmem = (kStagesK + kStagesV + 2) * kTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+constexpr uint32_t kTmemCols = 512;               // S buffers at columns 0 and 128, O at 256
+constexpr uint32_t kColO = 256;
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr float kRescaleThreshold = 8.f;          // log2 units
 
 struct PrefillArgs {
   __nv_bfloat16* out;          // [S, Hq, D] contiguous
@@ -57,12 +59,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* q_tile = ring + kStages * kStageBytes;
+  uint8_t* k_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* v_ring = k_ring + kStagesK * kTileBytes;
+  uint8_t* q_tile = v_ring + kStagesV * kTileBytes;
   uint8_t* p_tile = q_tile + kTileBytes;
-  uint64_t* kv_full = reinterpret_cast<uint64_t*>(p_tile + kTileBytes);
-  uint64_t* kv_free = kv_full + kStages;
-  uint64_t* s_full = kv_free + kStages;     // [2]
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(p_tile + kTileBytes);
+  uint64_t* k_free = k_full + kStagesK;
+  uint64_t* v_full = k_free + kStagesK;
+  uint64_t* v_free = v_full + kStagesV;
+  uint64_t* s_full = v_free + kStagesV;     // [2]
   uint64_t* s_free = s_full + 2;            // [2]
   uint64_t* q_full = s_free + 2;
   uint64_t* p_full = q_full + 1;
@@ -79,9 +84,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int nchunks = qb + 1;               // key positions 0 .. q0 + 127 (causal)
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      tc::mbar_init(&kv_full[s], 1);
-      tc::mbar_init(&kv_free[s], 1);
+    for (int s = 0; s < kStagesK; ++s) {
+      tc::mbar_init(&k_full[s], 1);
+      tc::mbar_init(&k_free[s], 1);
+    }
+    for (int s = 0; s < kStagesV; ++s) {
+      tc::mbar_init(&v_full[s], 1);
+      tc::mbar_init(&v_free[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&s_full[i], 1);
@@ -113,17 +122,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (warp == 4) {
     if (lane == 0) {
       // ---- copies and MMAs ----
-      auto issue_copy = [&](int c) {
-        const int st = c % kStages;
-        uint8_t* base = ring + st * kStageBytes;
-        tc::mbar_arrive_expect_tx(&kv_full[st], kStageBytes);
-        tc::tma_load_3d(base, &map_k, &kv_full[st], 0, hkv, c * kRows);
-        tc::tma_load_3d(base + kHalfBytes, &map_k, &kv_full[st], 64, hkv, c * kRows);
-        tc::tma_load_3d(base + kTileBytes, &map_v, &kv_full[st], 0, hkv, c * kRows);
-        tc::tma_load_3d(base + kTileBytes + kHalfBytes, &map_v, &kv_full[st], 64, hkv, c * kRows);
+      auto load_k = [&](int c) {
+        uint8_t* base = k_ring + (c % kStagesK) * kTileBytes;
+        tc::mbar_arrive_expect_tx(&k_full[c % kStagesK], kTileBytes);
+        tc::tma_load_3d(base, &map_k, &k_full[c % kStagesK], 0, hkv, c * kRows);
+        tc::tma_load_3d(base + kHalfBytes, &map_k, &k_full[c % kStagesK], 64, hkv, c * kRows);
       };
-      auto issue_scores = [&](int c) {   // S[buf c & 1] = Q * K chunk^T
-        const uint32_t kbase = tc::smem_u32(ring + (c % kStages) * kStageBytes);
+      auto load_v = [&](int c) {
+        uint8_t* base = v_ring + (c % kStagesV) * kTileBytes;
+        tc::mbar_arrive_expect_tx(&v_full[c % kStagesV], kTileBytes);
+        tc::tma_load_3d(base, &map_v, &v_full[c % kStagesV], 0, hkv, c * kRows);
+        tc::tma_load_3d(base + kHalfBytes, &map_v, &v_full[c % kStagesV], 64, hkv, c * kRows);
+      };
+      auto issue_scores = [&](int c) {   // S[buf c & 1] = Q * K chunk^T; the K stage is free once these complete
+        const uint32_t kbase = tc::smem_u32(k_ring + (c % kStagesK) * kTileBytes);
         const uint32_t qbase = tc::smem_u32(q_tile);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
@@ -132,44 +144,55 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc::umma<false>(tmem_base + (uint32_t)(c & 1) * kRows, tc::make_smem_desc_sw128(qbase + kb * kHalfBytes) + (uint64_t)(ks * 2),
                             tc::make_smem_desc_sw128(kbase + kb * kHalfBytes) + (uint64_t)(ks * 2), a.idesc_s, (kb | ks) ? 1u : 0u);
         tc::umma_commit(&s_full[c & 1]);
+        tc::umma_commit(&k_free[c % kStagesK]);
       };
-      auto issue_pv = [&](int c) {       // P*V of one chunk, 16 key positions per instruction
-        const uint32_t vbase = tc::smem_u32(ring + (c % kStages) * kStageBytes + kTileBytes);
+      auto issue_pv = [&](int c) {       // O (+)= P * V chunk, 16 key positions per instruction
+        const uint32_t vbase = tc::smem_u32(v_ring + (c % kStagesV) * kTileBytes);
         const uint32_t pbase = tc::smem_u32(p_tile);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          tc::umma<false>(tmem_base + kColPV, tc::make_smem_desc_sw128(pbase + (j >> 2) * kHalfBytes) + (uint64_t)((j & 3) * 2),
-                          tc::make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes), a.idesc_pv, j ? 1u : 0u);
+          tc::umma<false>(tmem_base + kColO, tc::make_smem_desc_sw128(pbase + (j >> 2) * kHalfBytes) + (uint64_t)((j & 3) * 2),
+                          tc::make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes), a.idesc_pv, (c | j) ? 1u : 0u);
         tc::umma_commit(o_full);
-        tc::umma_commit(&kv_free[c % kStages]);
+        tc::umma_commit(&v_free[c % kStagesV]);
       };
       tc::mbar_arrive_expect_tx(q_full, kTileBytes);
       tc::tma_load_3d(q_tile, &map_q, q_full, 0, h, q0);
       tc::tma_load_3d(q_tile + kHalfBytes, &map_q, q_full, 64, h, q0);
-      for (int c = 0; c < nchunks && c < kStages; ++c) issue_copy(c);
-      bool ok = tc::mbar_wait(q_full, 0, kWaitLimit, abort_flag) && tc::mbar_wait(&kv_full[0], 0, kWaitLimit, abort_flag);
+      for (int c = 0; c < nchunks && c < kStagesK; ++c) load_k(c);
+      for (int c = 0; c < nchunks && c < kStagesV; ++c) load_v(c);
+      bool ok = tc::mbar_wait(q_full, 0, kWaitLimit, abort_flag) && tc::mbar_wait(&k_full[0], 0, kWaitLimit, abort_flag);
       if (ok) {
         tc::fence_after_thread_sync();
         issue_scores(0);
       }
       for (int i = 0; i < nchunks && ok; ++i) {
         if (i + 1 < nchunks) {
+          // scores of the next chunk: its K tile has landed and the softmax has taken chunk i - 1 out of the buffer
           const int n = i + 1;
-          ok = tc::mbar_wait(&kv_full[n % kStages], (n / kStages) & 1, kWaitLimit, abort_flag) &&
+          ok = tc::mbar_wait(&k_full[n % kStagesK], (n / kStagesK) & 1, kWaitLimit, abort_flag) &&
                (n < 2 || tc::mbar_wait(&s_free[n & 1], ((n >> 1) - 1) & 1, kWaitLimit, abort_flag));
           if (!ok) break;
           tc::fence_after_thread_sync();
           issue_scores(n);
         }
-        ok = tc::mbar_wait(p_full, i & 1, kWaitLimit, abort_flag);
+        if (i + kStagesK < nchunks) {
+          // K stage of chunk i is free once its scores are complete (long before P*V of the chunk)
+          ok = tc::mbar_wait(&k_free[i % kStagesK], (i / kStagesK) & 1, kWaitLimit, abort_flag);
+          if (!ok) break;
+          load_k(i + kStagesK);
+        }
+        if (i >= 1 && i - 1 + kStagesV < nchunks) {
+          // V stage of chunk i - 1 is free once its P*V product is complete
+          ok = tc::mbar_wait(&v_free[(i - 1) % kStagesV], ((i - 1) / kStagesV) & 1, kWaitLimit, abort_flag);
+          if (!ok) break;
+          load_v(i - 1 + kStagesV);
+        }
+        ok = tc::mbar_wait(p_full, i & 1, kWaitLimit, abort_flag) &&
+             tc::mbar_wait(&v_full[i % kStagesV], (i / kStagesV) & 1, kWaitLimit, abort_flag);
         if (!ok) break;
         tc::fence_after_thread_sync();
         issue_pv(i);
-        if (i + kStages < nchunks) {
-          ok = tc::mbar_wait(&kv_free[i % kStages], (i / kStages) & 1, kWaitLimit, abort_flag);
-          if (!ok) break;
-          issue_copy(i + kStages);
-        }
       }
       if (!ok) fail();
     }
@@ -178,87 +201,100 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     const int q_pos = q0 + tid;
     float m_run = -FLT_MAX, l_run = 0.f;
-    float o[kD];
-#pragma unroll
-    for (int j = 0; j < kD; ++j) o[j] = 0.f;
     bool ok = true;
     for (int i = 0; i < nchunks && ok; ++i) {
       const int buf = i & 1;
-      ok = tc::mbar_wait(&s_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag);
+      // (the tensor-memory accesses below are warp-wide instructions: a warp gives up as a whole)
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag));
       if (!ok) break;
       tc::fence_after_thread_sync();
-      const uint32_t s_addr = lane_addr + (uint32_t)buf * kRows;
+      uint32_t sv[kRows];
+      tc::tmem_ld_x128(lane_addr + (uint32_t)buf * kRows, sv);
+      tc::fence_before_thread_sync();
+      tc::mbar_arrive(&s_free[buf]);            // the scores are in registers: the buffer can take chunk i + 2
       const int key0 = i * kRows;
       const bool diagonal = i == nchunks - 1;   // only the last chunk crosses the causal boundary
-      // pass 1: row maximum (in units of log2: scores are multiplied by scale * log2 e)
+      // scores in units of log2 (multiplied by scale * log2 e), masked on the diagonal chunk; row maximum
       float cmax = -FLT_MAX;
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        float sv[16];
-        tc::tmem_ld_16(s_addr + cc * 16, sv);
+      for (int j = 0; j < kRows; ++j) {
+        float x = __uint_as_float(sv[j]) * a.scale_log2;
+        if (diagonal && key0 + j > q_pos) x = -FLT_MAX;
+        sv[j] = __float_as_uint(x);
+        cmax = fmaxf(cmax, x);
+      }
+      if (i == 0) {
+        m_run = cmax;                           // the diagonal element is always live, so this is finite
+      } else {
+        // P*V of the previous chunk is complete: the P tile may be overwritten and O is stable
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(o_full, (i - 1) & 1, kWaitLimit, abort_flag));
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        const bool grow = cmax - m_run > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float f = grow ? exp2f(m_run - cmax) : 1.f;
+          if (grow) {
+            m_run = cmax;
+            l_run *= f;
+          }
+#pragma unroll 1
+          for (int c = 0; c < kD; c += 32) {
+            uint32_t ov[32];
+            tc::tmem_ld_x32(lane_addr + kColO + c, ov);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const bool live = !diagonal || key0 + cc * 16 + j <= q_pos;
-          cmax = fmaxf(cmax, live ? sv[j] * a.scale_log2 : -FLT_MAX);
+            for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * f);
+            tc::tmem_st_x32(lane_addr + kColO + c, ov);
+          }
         }
       }
-      const float m_new = fmaxf(m_run, cmax);   // the diagonal element is always live, so m_new is finite
-      const float corr = exp2f(m_run - m_new);
-      // pass 2: probabilities, row sum, P tile (bf16, K-major over the key positions, 128-byte swizzle)
+      // probabilities against m_run, row sum, P tile (bf16, K-major over the key positions, 128-byte swizzle)
       float psum = 0.f;
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        float sv[16];
-        tc::tmem_ld_16(s_addr + cc * 16, sv);
-        uint32_t w[8];
-#pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-          const bool live0 = !diagonal || key0 + cc * 16 + j <= q_pos;
-          const bool live1 = !diagonal || key0 + cc * 16 + j + 1 <= q_pos;
-          const float p0 = live0 ? exp2f(sv[j] * a.scale_log2 - m_new) : 0.f;
-          const float p1 = live1 ? exp2f(sv[j + 1] * a.scale_log2 - m_new) : 0.f;
-          psum += p0 + p1;
-          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          w[j >> 1] = *reinterpret_cast<uint32_t*>(&hh);
-        }
-        // 16 key positions = two 16-byte chunks of this row inside K block (cc / 4)
-        uint8_t* row = p_tile + (cc >> 2) * kHalfBytes + tid * 128;
-        const int c0 = (cc & 3) * 2;
-        *reinterpret_cast<uint4*>(row + (((c0) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(row + (((c0 + 1) ^ (tid & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-      }
-      tc::fence_before_thread_sync();
-      tc::mbar_arrive(&s_free[buf]);
-      tc::fence_proxy_async();          // P was written by threads and is read by the tensor core
-      tc::mbar_arrive(p_full);
-      l_run = l_run * corr + psum;
-      m_run = m_new;
-      ok = tc::mbar_wait(o_full, i & 1, kWaitLimit, abort_flag);
-      if (!ok) break;
-      tc::fence_after_thread_sync();
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        float pv[16];
-        tc::tmem_ld_16(lane_addr + kColPV + cc * 16, pv);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) o[cc * 16 + j] = fmaf(o[cc * 16 + j], corr, pv[j]);
-      }
-      tc::fence_before_thread_sync();
-    }
-    if (!ok) fail();
-    if (ok && q_pos < a.S) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint4* dst = reinterpret_cast<uint4*>(a.out + ((int64_t)q_pos * a.Hq + h) * kD);
-#pragma unroll
-      for (int c = 0; c < kD / 8; ++c) {
+      for (int cc = 0; cc < 16; ++cc) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 hh = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
+          const float p0 = exp2f(__uint_as_float(sv[cc * 8 + 2 * j]) - m_run);
+          const float p1 = exp2f(__uint_as_float(sv[cc * 8 + 2 * j + 1]) - m_run);
+          psum += p0 + p1;
+          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           w[j] = *reinterpret_cast<uint32_t*>(&hh);
         }
-        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+        // 8 key positions = one 16-byte chunk of this row inside K block (cc / 8)
+        uint8_t* row = p_tile + (cc >> 3) * kHalfBytes + tid * 128;
+        *reinterpret_cast<uint4*>(row + (((cc & 7) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      l_run += psum;
+      tc::fence_proxy_async();          // P was written by threads and is read by the tensor core
+      tc::fence_before_thread_sync();   // orders the rescaled O (tcgen05.st) before the MMA that the arrival releases
+      tc::mbar_arrive(p_full);
+    }
+    if (ok) {
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(o_full, (nchunks - 1) & 1, kWaitLimit, abort_flag));
+      tc::fence_after_thread_sync();
+    }
+    if (!ok) fail();
+    if (ok) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(a.out + ((int64_t)q_pos * a.Hq + h) * kD);
+#pragma unroll 1
+      for (int c = 0; c < kD; c += 32) {
+        uint32_t ov[32];
+        tc::tmem_ld_x32(lane_addr + kColO + c, ov);   // every lane of the warp takes part, rows beyond S included
+        if (q_pos < a.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(ov[g * 8 + 2 * j]) * inv, __uint_as_float(ov[g * 8 + 2 * j + 1]) * inv);
+              w[j] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            dst[c / 8 + g] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      tc::fence_before_thread_sync();
     }
   }
 

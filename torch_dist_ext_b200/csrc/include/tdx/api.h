@@ -165,6 +165,10 @@ class Workspace {
   void upload_table();
 };
 
+// Run-time override of the pipeline depth of the flag-synchronised two-shot paths (TDX_WAVES) and of the number of
+// rows whose switch-side sums the NVLS two-shot requests together (TDX_NVLS_BATCH); negative = keep the environment's.
+void set_tuning(int waves, int nvls_batch);
+
 // Every (device, peer) pair of this process: check and enable peer access. Returns the number
 // of visible devices. Used by single-process multi-GPU harnesses.
 int enable_all_peer_access();

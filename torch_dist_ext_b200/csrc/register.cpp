@@ -345,6 +345,9 @@ TORCH_LIBRARY(torch_dist_ext, m) {
   m.def("create_workspace(int rank, int world_size, int nblocks, int size_in_bytes, int lamport_bytes, int device, "
         "int multicast) -> __torch__.torch.classes.torch_dist_ext.CommWorkspace", &tdx_torch::create_workspace);
   m.def("bounds_checked_build() -> bool", []() -> bool { return tdx::bounds_checked_build(); });
+  m.def("set_tuning(int waves, int nvls_batch) -> ()", [](int64_t w, int64_t b) { tdx::set_tuning((int)w, (int)b); });
+  m.def("tracing_build() -> bool", []() -> bool { return tdx::tracing_build(); });
+  m.def("pdl_enabled() -> bool", []() -> bool { return tdx::pdl_enabled(); });
   m.def("table_nbytes() -> int", []() -> int64_t { return (int64_t)sizeof(tdx::CommTable); });
   m.def("connect_local(__torch__.torch.classes.torch_dist_ext.CommWorkspace[] workspaces) -> ()", &tdx_torch::connect_local);
   m.def(

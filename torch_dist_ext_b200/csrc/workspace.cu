@@ -472,6 +472,14 @@ void Workspace::connect_local(const std::vector<Workspace*>& all) {
   for (auto* w : all) w->open_handles(ptrs);
 }
 
+namespace {
+std::atomic<int> g_waves_override{-1}, g_nvls_batch_override{-1};
+}
+void set_tuning(int waves, int nvls_batch) {
+  g_waves_override.store(waves);
+  g_nvls_batch_override.store(nvls_batch);
+}
+
 void Workspace::fill_params(ArParams* p) const {
   for (int r = 0; r < kMaxRanks; ++r) p->peer[r] = r < world_ ? peer_[r] : nullptr;
   p->mc_base = table_host_.mc_base;
@@ -486,12 +494,12 @@ void Workspace::fill_params(ArParams* p) const {
     const char* e = std::getenv("TDX_WAVES");
     return e ? std::atoi(e) : 1;
   }();
-  p->waves = waves_env;
+  p->waves = g_waves_override.load() >= 0 ? g_waves_override.load() : waves_env;
   static const int batch_env = [] {
     const char* e = std::getenv("TDX_NVLS_BATCH");
     return e ? std::atoi(e) : 1;
   }();
-  p->nvls_batch = batch_env;
+  p->nvls_batch = g_nvls_batch_override.load() >= 0 ? g_nvls_batch_override.load() : batch_env;
 }
 
 void Workspace::reset() { init_device_state(); }
