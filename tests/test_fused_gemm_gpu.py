@@ -51,6 +51,39 @@ def test_gemm_allreduce_rms_fp8_output_world1():
     assert (back - e_norm.float()).abs().max().item() <= e_norm.float().abs().max().item() * 2.0 ** -3
 
 
+@pytest.mark.parametrize("tokens,hidden,k", [(1, 4096, 512), (16, 8192, 1024), (64, 8192, 3584), (33, 1024, 256)])
+@pytest.mark.parametrize("out_mode", [OUT_SAME, OUT_FP8_BLOCK128])
+def test_gemm_allreduce_rms_block_scaled_fp8_operands_world1(tokens, hidden, k, out_mode):
+    """e4m3 activations (1x128 scales) times e4m3 weights (128x128 scales) inside the fused kernel, against the
+    dequantised operands multiplied in fp32."""
+    from torch_dist_ext_b200.ops import quant
+
+    a = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(hidden, k, device="cuda") * 0.05).to(torch.bfloat16)
+    r = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(hidden, device="cuda")).to(torch.bfloat16)
+    aq, ascale = quant.quant_fp8(a, block_scaled=True)
+    wq, wscale = gemm.quantize_weight_block128(w)
+    for _ in range(3):
+        norm, res, scales = fused_gemm.gemm_allreduce_rms(aq, wq, r, g, 1e-6, out_mode=out_mode, a_scale=ascale, w_scale=wscale)
+    a_deq = (aq.float().view(tokens, k // 128, 128) * ascale.view(tokens, k // 128, 1)).view(tokens, k)
+    w_deq = (wq.float().view(hidden // 128, 128, k // 128, 128) * wscale.view(hidden // 128, 1, k // 128, 1)).view(hidden, k)
+    y = (a_deq @ w_deq.t()).to(torch.bfloat16)
+    e_norm, e_res, _ = ref.residual_rmsnorm_reference(y.float(), r, g, 1e-6, OUT_SAME)
+    assert (res.float() - e_res.float()).abs().max().item() <= 0.07
+    if out_mode == OUT_SAME:
+        assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07
+    else:
+        back = ref.dequantize_fp8(norm, scales)
+        assert (back - e_norm.float()).abs().max().item() <= e_norm.float().abs().max().item() * 2.0 ** -3
+    # the unfused route (block-scaled GEMM, then the all-reduce op) agrees
+    u_norm, u_res, _ = fused_gemm.gemm_allreduce_rms(aq, wq, r, g, 1e-6, out_mode=OUT_SAME, a_scale=ascale, w_scale=wscale,
+                                                     force_unfused=True)
+    assert (res.float() - u_res.float()).abs().max().item() <= 0.07
+    tdx.check_status()
+    assert gemm.pipeline_status() == 0
+
+
 @pytest.mark.parametrize("tokens,n_out,k", [(1, 768, 4096), (16, 3584, 4096), (64, 1280, 8192), (40, 256, 128)])
 def test_allgather_gemm_world1(tokens, n_out, k):
     x = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)

@@ -117,7 +117,9 @@ def write_ninja() -> Path:
         "  deps = gcc",
         "  description = CXX $out",
         "rule link",
-        "  command = $cxx -shared -o $out $in $ldflags",
+        # linked under a temporary name and renamed, so that a process that loads (or a tool that copies) the library
+        # while a rebuild runs never sees a partly written file
+        "  command = $cxx -shared -o $out.tmp $in $ldflags && mv -f $out.tmp $out",
         "  description = LINK $out",
     ]
     objs = []
@@ -155,7 +157,7 @@ def write_ninja() -> Path:
     core = [o for o in objs if o.startswith("ar_inst_") or o in ("workspace.o", "ar_fusion_launch.host.o", "fd_channel.host.o")]
     lines += [
         "rule nvlink_exe",
-        "  command = $nvcc $nvflags -o $out $in -lcudart",
+        "  command = $nvcc $nvflags -o $out.tmp $in -lcudart && mv -f $out.tmp $out",
         "  description = NVCC-LINK $out",
         f"build unit_test.o: nvcc {UNIT_TEST_SRC}",
         "  defs = ",

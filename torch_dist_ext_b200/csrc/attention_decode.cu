@@ -19,6 +19,7 @@
 #include <mutex>
 #include <set>
 #include "tdx/comm.h"
+#include "tdx/launch.h"
 #include "tdx/ops.h"
 #include "tdx/tc.cuh"
 #include "tdx/tma_host.h"
@@ -78,6 +79,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const _
 
   const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  ptx::pdl_wait();                // q, the caches and seq_lens come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
   const int len = a.seq_lens[b];
   const int per = (len + a.nsplit - 1) / a.nsplit;
   const int s0 = split * per, s1 = min(len, s0 + per);
@@ -270,6 +273,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_split_kernel(const _
 
 // out[b, h, :] = sum_s exp(m_s - m) * acc_s / sum_s exp(m_s - m) * l_s
 __global__ void __launch_bounds__(kD) attn_combine_kernel(const AttnArgs a) {
+  ptx::pdl_wait();
+  ptx::pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const float* src = a.partial + ((int64_t)b * a.Hq + h) * a.nsplit * (kD + 2);
   float m = -FLT_MAX;
@@ -292,8 +297,8 @@ std::string launch_attn(const CUtensorMap& mk, const CUtensorMap& mv, const Attn
   auto kern = attn_decode_split_kernel<kG>;
   const std::string smem_err = reserve_dynamic_smem(kern, kAttnSmem);
   if (!smem_err.empty()) return smem_err;
-  kern<<<grid, kAttnThreads, kAttnSmem, stream>>>(mk, mv, a);
-  return "";
+  const cudaError_t e = launch_chained(kern, grid, dim3(kAttnThreads), kAttnSmem, stream, mk, mv, a);
+  return e == cudaSuccess ? "" : std::string("attention launch failed: ") + cudaGetErrorString(e);
 }
 
 }  // namespace
@@ -341,7 +346,7 @@ std::string attention_decode(const void* q, const void* k_cache, const void* v_c
     case 8: err = launch_attn<8>(mk, mv, a, grid, stream); break;
   }
   if (!err.empty()) return err;
-  if (nsplit > 1 && !in_kernel_merge) attn_combine_kernel<<<dim3(B, Hq), kD, 0, stream>>>(a);
+  if (nsplit > 1 && !in_kernel_merge) launch_chained(attn_combine_kernel, dim3(B, Hq), dim3(kD), 0, stream, a);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }

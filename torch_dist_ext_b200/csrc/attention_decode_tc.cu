@@ -20,7 +20,7 @@
 // (which ends every other wait early) and all threads still reach the common exit, where copies in
 // flight are given time to land and the tensor memory is freed.
 //
-// Opt-in (ops/attention.py: decode_attention(..., tensor_cores=True) or TDX_ATTN_TC=1).
+// The default decode-attention kernel (ops/attention.py; TDX_ATTN_TC=0 selects the SIMT kernel).
 // Not part of the reference (it has no attention).
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -30,6 +30,7 @@
 #include <set>
 #include <string>
 #include "tdx/comm.h"
+#include "tdx/launch.h"
 #include "tdx/ops.h"
 #include "tdx/sync.cuh"
 #include "tdx/tc.cuh"
@@ -58,6 +59,7 @@ struct TcAttnArgs {
   const __nv_bfloat16* q;      // [B, Hq, D]
   const int32_t* seq_lens;     // [B]
   float* partial;              // [B, Hq, nsplit, D + 2]
+  uint32_t* counters;          // [B * Hkv] arrival counters (zero on entry, zeroed again by the kernel), or null
   __nv_bfloat16* out;          // [B, Hq, D]
   int B, Hq, Hkv, nsplit;
   int64_t q_stride_b;
@@ -78,6 +80,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ float wred[2][kG][4];
+  __shared__ uint32_t s_last;
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_tile = ring + kStages * kStageBytes;
   uint8_t* p_tile = q_tile + kSmallTileBytes;
@@ -92,6 +95,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
   const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  ptx::pdl_wait();                // q, the caches and seq_lens come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
   const int len = a.seq_lens[b];
   const int per = (len + a.nsplit - 1) / a.nsplit;
   const int s0 = split * per, s1 = min(len, s0 + per);
@@ -279,6 +284,33 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         }
       }
     }
+    if (a.nsplit > 1 && a.counters != nullptr) {
+      // the split that arrives last merges all of them (saves a launch per layer)
+      __threadfence();
+      tc::named_barrier_sync(1, kSoftmaxThreads);
+      if (tid == 0) {
+        const uint32_t prev = atomicAdd(&a.counters[b * a.Hkv + hkv], 1u);
+        s_last = (prev == (uint32_t)a.nsplit - 1u) ? 1u : 0u;
+        if (s_last) a.counters[b * a.Hkv + hkv] = 0;
+      }
+      tc::named_barrier_sync(1, kSoftmaxThreads);
+      if (s_last) {
+        __threadfence();
+#pragma unroll
+        for (int g = 0; g < kG; ++g) {
+          const float* src = a.partial + ((int64_t)b * a.Hq + hkv * kG + g) * a.nsplit * (kD + 2);
+          float m = -FLT_MAX;
+          for (int sp = 0; sp < a.nsplit; ++sp) m = fmaxf(m, __ldcg(src + sp * (kD + 2) + kD));
+          float num = 0.f, den = 0.f;
+          for (int sp = 0; sp < a.nsplit; ++sp) {
+            const float wgt = __expf(__ldcg(src + sp * (kD + 2) + kD) - m);
+            num = fmaf(wgt, __ldcg(src + sp * (kD + 2) + tid), num);
+            den = fmaf(wgt, __ldcg(src + sp * (kD + 2) + kD + 1), den);
+          }
+          a.out[((int64_t)b * a.Hq + hkv * kG + g) * kD + tid] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+        }
+      }
+    }
   }
 
   tc::fence_before_thread_sync();
@@ -294,6 +326,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
 // out[b, h, :] = sum_s exp(m_s - m) * acc_s / sum_s exp(m_s - m) * l_s
 __global__ void __launch_bounds__(kD) attn_tc_combine_kernel(const TcAttnArgs a) {
+  ptx::pdl_wait();
+  ptx::pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const float* src = a.partial + ((int64_t)b * a.Hq + h) * a.nsplit * (kD + 2);
   float m = -FLT_MAX;
@@ -312,8 +346,8 @@ std::string launch(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnArg
   auto kern = attn_decode_tc_kernel<kG>;
   const std::string smem_err = reserve_dynamic_smem(kern, kSmem);
   if (!smem_err.empty()) return smem_err;
-  kern<<<grid, kThreads, kSmem, stream>>>(mk, mv, a);
-  return "";
+  const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), kSmem, stream, mk, mv, a);
+  return e == cudaSuccess ? "" : std::string("attention launch failed: ") + cudaGetErrorString(e);
 }
 
 }  // namespace
@@ -327,8 +361,9 @@ std::string attention_decode_tc(const void* q, const void* k_cache, const void* 
   const int G = Hq / Hkv;
   if (G > kMaxG || (G & (G - 1))) return "query heads per KV head must be 1, 2, 4 or 8";
   if (nsplit < 1) nsplit = 1;
-  // the first words of the scratch buffer belong to the other kernel's arrival counters and stay untouched
+  // scratch layout as in attention_decode.cu: kCounterWords arrival counters (zero on entry, left zero), then the partials
   const size_t head = partial_floats > (size_t)kCounterWords ? (size_t)kCounterWords : 0;
+  const bool in_kernel_merge = head != 0 && (size_t)B * Hkv <= (size_t)kCounterWords;
   if (head + (size_t)B * Hq * nsplit * (kD + 2) > partial_floats) return "attention scratch buffer is too small";
   if ((kv_stride_s * 2) % 16 || (kv_stride_b * 2) % 16 || reinterpret_cast<uintptr_t>(k_cache) % 16 ||
       reinterpret_cast<uintptr_t>(v_cache) % 16)
@@ -338,6 +373,7 @@ std::string attention_decode_tc(const void* q, const void* k_cache, const void* 
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.seq_lens = seq_lens;
   a.partial = partial + head;
+  a.counters = in_kernel_merge ? reinterpret_cast<uint32_t*>(partial) : nullptr;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.nsplit = nsplit;
   a.q_stride_b = q_stride_b;
@@ -358,7 +394,7 @@ std::string attention_decode_tc(const void* q, const void* k_cache, const void* 
     case 8: err = launch<8>(mk, mv, a, grid, stream); break;
   }
   if (!err.empty()) return err;
-  if (nsplit > 1) attn_tc_combine_kernel<<<dim3(B, Hq), kD, 0, stream>>>(a);
+  if (nsplit > 1 && !in_kernel_merge) launch_chained(attn_tc_combine_kernel, dim3(B, Hq), dim3(kD), 0, stream, a);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }

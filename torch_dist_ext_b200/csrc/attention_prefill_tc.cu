@@ -6,14 +6,15 @@
 //   O[q 128, d 128]   += P[q, keys] * V[keys, d]        P written by the softmax warps (K-major over keys),
 //                                                       V read MN-major (d contiguous) straight from its TMA tile
 //
-// The four softmax warps hold one query row per thread, so the online softmax needs no cross-thread
-// reduction. A thread fetches its 128 scores of a chunk with ONE tcgen05.ld (one TMEM round trip per
-// chunk) and gives the score buffer back at once; S is double-buffered, so the scores of chunk c+1 are
-// computed while chunk c is in the softmax. O stays in tensor memory and is accumulated there by the
-// P*V products of all chunks. A row's running maximum is only raised - and its part of O rescaled in
+// Eight softmax warps: two threads per query row, one per 64-key half of a chunk (so that every warp
+// scheduler has two of them to alternate between); the two halves exchange their partial row maxima
+// through shared memory once per chunk. A thread fetches its 64 scores of a chunk with ONE tcgen05.ld
+// (one TMEM round trip per chunk) and gives the score buffer back at once; S is double-buffered, so the
+// scores of chunk c+1 are computed while chunk c is in the softmax. O stays in tensor memory and is
+// accumulated there by the P*V products of all chunks. A row's running maximum is only raised - and its part of O rescaled in
 // tensor memory - when the new maximum exceeds it by more than 2^8 (a warp-uniform decision); until
 // then the probabilities are taken against the older maximum, which changes neither O / l nor the
-// accuracy of bf16 probabilities below 256. A fifth warp issues the TMA copies (separate rings for
+// accuracy of bf16 probabilities below 256. A ninth warp issues the TMA copies (separate rings for
 // K, 2 stages, freed as soon as the scores are computed, and V, 3 stages, freed after P*V) and all MMAs.
 //
 // Every wait is bounded; a wait that runs out records a status word and raises the CTA's abort flag,
@@ -26,7 +27,9 @@
 #include <set>
 #include <string>
 #include "tdx/comm.h"
+#include "tdx/launch.h"
 #include "tdx/ops.h"
+#include "tdx/ptx.cuh"
 #include "tdx/tc.cuh"
 #include "tdx/tma_host.h"
 
@@ -37,11 +40,15 @@ constexpr int kD = 128;
 constexpr int kRows = 128;                        // query rows per CTA = key positions per chunk
 constexpr int kStagesK = 2;
 constexpr int kStagesV = 3;
-constexpr int kSoftmaxThreads = 128;
+constexpr int kSoftmaxThreads = 256;          // two warp groups: 64 key positions of every chunk each
+constexpr int kHalfKeys = 64;
 constexpr int kThreads = kSoftmaxThreads + 32;
+constexpr int kMmaWarp = kSoftmaxThreads / 32;
 constexpr int kHalfBytes = kRows * 128;           // one 64-column half of a 128-row tile
 constexpr int kTileBytes = 2 * kHalfBytes;        // Q, P, one K chunk or one V chunk
-constexpr int kSmem = (kStagesK + kStagesV + 2) * kTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+constexpr int kBarrierBytes = 128;                // 13 mbarriers, the TMEM address and the abort flag
+constexpr int kSmem = (kStagesK + kStagesV + 2) * kTileBytes + kBarrierBytes + 2 * 2 * kRows * (int)sizeof(float);
+static_assert(kSmem <= 227 * 1024, "shared memory of one CTA");
 constexpr uint32_t kTmemCols = 512;               // S buffers at columns 0 and 128, O at 256
 constexpr uint32_t kColO = 256;
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -58,8 +65,15 @@ struct PrefillArgs {
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* k_ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The tiles need 1024-byte alignment (128-byte swizzle) and fill the shared memory of the SM to within a
+  // kilobyte, so there is no room for alignment slack: the dynamic region is declared aligned, and a kernel
+  // that finds it otherwise reports that instead of running.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if ((tc::smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0 && a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
+    return;
+  }
+  uint8_t* k_ring = smem_raw;
   uint8_t* v_ring = k_ring + kStagesK * kTileBytes;
   uint8_t* q_tile = v_ring + kStagesV * kTileBytes;
   uint8_t* p_tile = q_tile + kTileBytes;
@@ -74,6 +88,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* o_full = p_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  // partial row maxima (and, at the end, sums) of the two warp groups: [chunk parity][warp group][row]
+  float (*xmax)[2][kRows] = reinterpret_cast<float (*)[2][kRows]>(p_tile + kTileBytes + kBarrierBytes);
 
   // the blocks with the most key chunks start first
   const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;
@@ -105,7 +121,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc::tma_prefetch_desc(&map_k);
     tc::tma_prefetch_desc(&map_v);
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tc::tmem_alloc(tmem_slot, kTmemCols);
     tc::tmem_relinquish();
   }
@@ -113,13 +129,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc::fence_after_thread_sync();
   const uint32_t tmem_base = *tmem_slot;
+  ptx::pdl_wait();                // q, k and v come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
 
   auto fail = [&]() {
     *abort_flag = 1;
     if (a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
   };
 
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     if (lane == 0) {
       // ---- copies and MMAs ----
       auto load_k = [&](int c) {
@@ -197,60 +215,77 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!ok) fail();
     }
   } else {
-    // ---- softmax warps: thread t owns query row q0 + t ----
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const int q_pos = q0 + tid;
-    float m_run = -FLT_MAX, l_run = 0.f;
+    // ---- softmax warps: two threads per query row, one per 64-key half of a chunk ----
+    // Thread (wg, t): row q0 + t, keys [64 wg, 64 wg + 64) of every chunk and columns [64 wg, 64 wg + 64) of O.
+    // Both warp groups reach all 128 TMEM lanes (a warp addresses the lane quarter warp % 4). The two threads
+    // of a row exchange their partial row maxima through shared memory once per chunk (one named barrier among
+    // the 256 softmax threads; the exchange buffer alternates with the chunk parity, so no second barrier is
+    // needed) and therefore take identical decisions on the running maximum. A thread whose wait ran out keeps
+    // walking the loop (its waits return at once because the abort flag is up) so that every thread executes
+    // the same number of barriers.
+    const int wg = warp >> 2;
+    const int t = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const int q_pos = q0 + t;
+    float m_run = -FLT_MAX, l_part = 0.f;
     bool ok = true;
-    for (int i = 0; i < nchunks && ok; ++i) {
+    for (int i = 0; i < nchunks; ++i) {
       const int buf = i & 1;
-      // (the tensor-memory accesses below are warp-wide instructions: a warp gives up as a whole)
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(&s_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag));
-      if (!ok) break;
+      if (!tc::mbar_wait(&s_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag) && ok) {
+        ok = false;
+        fail();
+      }
       tc::fence_after_thread_sync();
-      uint32_t sv[kRows];
-      tc::tmem_ld_x128(lane_addr + (uint32_t)buf * kRows, sv);
+      uint32_t sv[kHalfKeys];
+      tc::tmem_ld_x64(lane_addr + (uint32_t)buf * kRows + (uint32_t)wg * kHalfKeys, sv);
       tc::fence_before_thread_sync();
       tc::mbar_arrive(&s_free[buf]);            // the scores are in registers: the buffer can take chunk i + 2
-      const int key0 = i * kRows;
+      const int key0 = i * kRows + wg * kHalfKeys;
       const bool diagonal = i == nchunks - 1;   // only the last chunk crosses the causal boundary
-      // scores in units of log2 (multiplied by scale * log2 e), masked on the diagonal chunk; row maximum
+      // scores in units of log2 (multiplied by scale * log2 e), masked on the diagonal chunk; partial row maximum
       float cmax = -FLT_MAX;
 #pragma unroll
-      for (int j = 0; j < kRows; ++j) {
+      for (int j = 0; j < kHalfKeys; ++j) {
         float x = __uint_as_float(sv[j]) * a.scale_log2;
         if (diagonal && key0 + j > q_pos) x = -FLT_MAX;
         sv[j] = __float_as_uint(x);
         cmax = fmaxf(cmax, x);
       }
+      xmax[buf][wg][t] = cmax;
+      tc::named_barrier_sync(1, kSoftmaxThreads);
+      cmax = fmaxf(cmax, xmax[buf][wg ^ 1][t]);
       if (i == 0) {
         m_run = cmax;                           // the diagonal element is always live, so this is finite
       } else {
         // P*V of the previous chunk is complete: the P tile may be overwritten and O is stable
-        ok = __all_sync(0xffffffffu, tc::mbar_wait(o_full, (i - 1) & 1, kWaitLimit, abort_flag));
-        if (!ok) break;
+        if (!tc::mbar_wait(o_full, (i - 1) & 1, kWaitLimit, abort_flag) && ok) {
+          ok = false;
+          fail();
+        }
         tc::fence_after_thread_sync();
         const bool grow = cmax - m_run > kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
           const float f = grow ? exp2f(m_run - cmax) : 1.f;
           if (grow) {
             m_run = cmax;
-            l_run *= f;
+            l_part *= f;
           }
 #pragma unroll 1
-          for (int c = 0; c < kD; c += 32) {
+          for (int c = 0; c < kHalfKeys; c += 32) {
             uint32_t ov[32];
-            tc::tmem_ld_x32(lane_addr + kColO + c, ov);
+            tc::tmem_ld_x32(lane_addr + kColO + wg * kHalfKeys + c, ov);
 #pragma unroll
             for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * f);
-            tc::tmem_st_x32(lane_addr + kColO + c, ov);
+            tc::tmem_st_x32(lane_addr + kColO + wg * kHalfKeys + c, ov);
           }
         }
       }
-      // probabilities against m_run, row sum, P tile (bf16, K-major over the key positions, 128-byte swizzle)
+      // probabilities against m_run, partial row sum, this thread's half of the P row (bf16, K-major over the key
+      // positions, 128-byte swizzle: key block wg of the tile)
       float psum = 0.f;
+      uint8_t* row = p_tile + wg * kHalfBytes + t * 128;
 #pragma unroll
-      for (int cc = 0; cc < 16; ++cc) {
+      for (int cc = 0; cc < 8; ++cc) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -260,42 +295,42 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           w[j] = *reinterpret_cast<uint32_t*>(&hh);
         }
-        // 8 key positions = one 16-byte chunk of this row inside K block (cc / 8)
-        uint8_t* row = p_tile + (cc >> 3) * kHalfBytes + tid * 128;
-        *reinterpret_cast<uint4*>(row + (((cc & 7) ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(row + ((cc ^ (t & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l_run += psum;
+      l_part += psum;
       tc::fence_proxy_async();          // P was written by threads and is read by the tensor core
       tc::fence_before_thread_sync();   // orders the rescaled O (tcgen05.st) before the MMA that the arrival releases
       tc::mbar_arrive(p_full);
     }
-    if (ok) {
-      ok = __all_sync(0xffffffffu, tc::mbar_wait(o_full, (nchunks - 1) & 1, kWaitLimit, abort_flag));
-      tc::fence_after_thread_sync();
+    if (!tc::mbar_wait(o_full, (nchunks - 1) & 1, kWaitLimit, abort_flag) && ok) {
+      ok = false;
+      fail();
     }
-    if (!ok) fail();
-    if (ok) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint4* dst = reinterpret_cast<uint4*>(a.out + ((int64_t)q_pos * a.Hq + h) * kD);
+    tc::fence_after_thread_sync();
+    // row sum = the two halves' partial sums (same running maximum in both threads of a row)
+    xmax[0][wg][t] = l_part;
+    tc::named_barrier_sync(1, kSoftmaxThreads);
+    const float l_run = l_part + xmax[0][wg ^ 1][t];
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    uint4* dst = reinterpret_cast<uint4*>(a.out + ((int64_t)q_pos * a.Hq + h) * kD + wg * kHalfKeys);
 #pragma unroll 1
-      for (int c = 0; c < kD; c += 32) {
-        uint32_t ov[32];
-        tc::tmem_ld_x32(lane_addr + kColO + c, ov);   // every lane of the warp takes part, rows beyond S included
-        if (q_pos < a.S) {
+    for (int c = 0; c < kHalfKeys; c += 32) {
+      uint32_t ov[32];
+      tc::tmem_ld_x32(lane_addr + kColO + wg * kHalfKeys + c, ov);   // every lane of the warp takes part, rows beyond S included
+      if (ok && q_pos < a.S) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint32_t w[4];
+        for (int g = 0; g < 4; ++g) {
+          uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(ov[g * 8 + 2 * j]) * inv, __uint_as_float(ov[g * 8 + 2 * j + 1]) * inv);
-              w[j] = *reinterpret_cast<uint32_t*>(&hh);
-            }
-            dst[c / 8 + g] = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(ov[g * 8 + 2 * j]) * inv, __uint_as_float(ov[g * 8 + 2 * j + 1]) * inv);
+            w[j] = *reinterpret_cast<uint32_t*>(&hh);
           }
+          dst[c / 8 + g] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
-      tc::fence_before_thread_sync();
     }
+    tc::fence_before_thread_sync();
   }
 
   tc::fence_before_thread_sync();
@@ -303,7 +338,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (*abort_flag) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);   // copies already issued land before shared memory goes away
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tc::fence_after_thread_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -335,8 +370,7 @@ std::string attention_prefill_tc(const void* q, const void* k, const void* v, vo
   const std::string smem_err = reserve_dynamic_smem(kern, kSmem);
   if (!smem_err.empty()) return smem_err;
   const dim3 grid((S + kRows - 1) / kRows, Hq, 1);
-  kern<<<grid, kThreads, kSmem, stream>>>(mq, mk, mv, a);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), kSmem, stream, mq, mk, mv, a);
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }
 

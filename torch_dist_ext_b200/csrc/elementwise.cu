@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include "tdx/launch.h"
 #include "tdx/ops.h"
 #include "tdx/ptx.cuh"
 #include "tdx/sync.cuh"
@@ -39,6 +40,8 @@ __global__ void __launch_bounds__(512) quant_fp8_kernel(const T* __restrict__ x,
                                                         float* __restrict__ scales, int rows, int cols) {
   constexpr int kVec = VecTraits<T>::kVec;
   __shared__ float red[32];
+  ptx::pdl_wait();                // inputs come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
   const int nvec = cols / kVec;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const char* src = reinterpret_cast<const char*>(x + (size_t)row * cols);
@@ -96,6 +99,8 @@ template <typename T, bool kQuant>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ in, void* __restrict__ out,
                                                        float* __restrict__ scales, int rows, int inter) {
   constexpr int kVec = VecTraits<T>::kVec;
+  ptx::pdl_wait();                // inputs come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
   const int nvec = inter / kVec;
   const size_t total = (size_t)rows * nvec;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -149,6 +154,8 @@ __global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ q, T* __restr
                                                    T* __restrict__ v_cache, int64_t cache_stride_b,
                                                    int64_t cache_stride_s) {
   constexpr int kVec = VecTraits<T>::kVec;
+  ptx::pdl_wait();                // inputs come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
   const int half = dim / 2;
   const int per_head = half / kVec;
   const int items = (q_heads + k_heads) * per_head;
@@ -217,9 +224,9 @@ std::string quant_fp8(const void* x, void* q, float* scales, int rows, int cols,
   const int grid = rows < 148 * 4 ? rows : 148 * 4;
   TDX_DISPATCH_DTYPE(dtype, {
     if (block128)
-      quant_fp8_kernel<T, true><<<grid, threads, 0, stream>>>(static_cast<const T*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
+      launch_chained(quant_fp8_kernel<T, true>, dim3(grid), dim3(threads), 0, stream, static_cast<const T*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
     else
-      quant_fp8_kernel<T, false><<<grid, threads, 0, stream>>>(static_cast<const T*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
+      launch_chained(quant_fp8_kernel<T, false>, dim3(grid), dim3(threads), 0, stream, static_cast<const T*>(x), static_cast<uint8_t*>(q), scales, rows, cols);
   });
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
@@ -235,9 +242,9 @@ std::string silu_mul(const void* in, void* out, float* scales, int rows, int int
   const int grid = grid_for(total, 256);
   TDX_DISPATCH_DTYPE(dtype, {
     if (quant_block128)
-      silu_mul_kernel<T, true><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), out, scales, rows, inter);
+      launch_chained(silu_mul_kernel<T, true>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(in), out, scales, rows, inter);
     else
-      silu_mul_kernel<T, false><<<grid, 256, 0, stream>>>(static_cast<const T*>(in), out, scales, rows, inter);
+      launch_chained(silu_mul_kernel<T, false>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(in), out, scales, rows, inter);
   });
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
@@ -252,7 +259,7 @@ std::string rope_inplace(void* q, void* k, const int64_t* positions, const float
   if (tokens == 0) return "";
   const int grid = tokens < 148 * 8 ? tokens : 148 * 8;
   TDX_DISPATCH_DTYPE(dtype, {
-    rope_kernel<T><<<grid, 256, 0, stream>>>(static_cast<T*>(q), static_cast<T*>(k), positions, cos_sin_cache, tokens,
+    launch_chained(rope_kernel<T>, dim3(grid), dim3(256), 0, stream, static_cast<T*>(q), static_cast<T*>(k), positions, cos_sin_cache, tokens,
                                              q_heads, k_heads, dim, q_stride, k_stride, static_cast<const T*>(v), v_stride,
                                              static_cast<T*>(k_cache), static_cast<T*>(v_cache), cache_stride_b,
                                              cache_stride_s);

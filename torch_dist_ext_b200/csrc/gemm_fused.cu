@@ -30,6 +30,7 @@
 #include "tdx/ar_fusion_kernels.cuh"
 #include "tdx/gemm.h"
 #include "tdx/gemm_core.cuh"
+#include "tdx/launch.h"
 #include "tdx/tc.cuh"
 #include "tdx/tma_host.h"
 
@@ -54,16 +55,23 @@ struct FusedArgs {
   uint32_t* status;
   float* ws;          // split-K scratch, zero on entry and on exit
   uint32_t* counters;
+  // e4m3 operands with block scales (kScaled kernels): weights one scale per 128 x 128 block, activations one per
+  // token and 128-wide K block; fp32, row length scale_kb = K / 128
+  const float* w_scale;
+  const float* a_scale;
+  int scale_kb;
 };
 
 // D tile (TMEM) -> bf16 rows in shared memory -> 16-byte pushes into the owners' gather slots.
 // With K split over gridDim.z the partial tiles are first summed in an fp32 scratch tile with
 // red.global.add; the CTA that arrives last at the tile converts and pushes it (and leaves the
 // scratch tile and its counter zeroed for the next call).
-template <int kBN>
+// kFromRegs: the tile's values come from `acc` (this thread's row of the tile, promoted block by block from the
+// scaled fp8 partial products) instead of tensor memory.
+template <int kBN, bool kFromRegs>
 __device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const FusedArgs& f, uint8_t* stage,
                                                     uint32_t* shared_flag, uint32_t tmem_base, int tile_x, int tile_y,
-                                                    size_t buf_off, int groups) {
+                                                    size_t buf_off, int groups, const float* acc) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = warp & 3;
   const int te = threadIdx.x - 64;                 // 0..127 among the epilogue threads
@@ -77,7 +85,12 @@ __device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const Fus
 #pragma unroll
     for (int c = 0; c < kBN; c += 16) {
       float v[16];
-      tc::tmem_ld_16(lane_addr + c, v);
+      if constexpr (kFromRegs) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
+      } else {
+        tc::tmem_ld_16(lane_addr + c, v);
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j) atomicAdd(tile + (size_t)(c + j) * kBM, v[j]);
     }
@@ -102,7 +115,12 @@ __device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const Fus
 #pragma unroll
     for (int c = 0; c < kBN; c += 16) {
       float v[16];
-      tc::tmem_ld_16(lane_addr + c, v);
+      if constexpr (kFromRegs) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
+      } else {
+        tc::tmem_ld_16(lane_addr + c, v);
+      }
 #pragma unroll
       for (int j = 0; j < 16; ++j) st[(c + j) * kBM + xl] = __float2bfloat16(v[j]);
     }
@@ -123,10 +141,13 @@ __device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const Fus
   }
 }
 
-template <int kBN, int kStages, int kN, int kVpt, int kOut>
+template <int kBN, int kStages, int kN, int kVpt, int kOut, bool kScaled>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const FusedArgs f) {
-  constexpr uint32_t kTmemCols = kBN < 32 ? 32 : kBN;
+  // kScaled: e4m3 operands with block scales; every 128-wide K block is multiplied into its own TMEM buffer (two,
+  // alternating) and promoted in fp32 by the epilogue warps while the next block's MMAs run.
+  constexpr uint32_t kTmemCols = kScaled ? (2 * kBN < 32 ? 32 : 2 * kBN) : (kBN < 32 ? 32 : kBN);
+  constexpr int kEpb = kScaled ? 128 : kElemsPerBlock;   // K elements per 128-byte block
   extern __shared__ uint8_t smem_raw[];
   __shared__ float red[4][32];
   gemm_core::Pipeline<kBN, kStages> pipe;
@@ -134,9 +155,6 @@ gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   const ArParams& p = f.ar;
   char* self = static_cast<char*>(p.peer[p.rank]);
   Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
-  const uint32_t epoch = ctl->lamport_epoch;
-  const uint64_t dirty_prev = ctl->lamport_dirty[(epoch + 2u) % 3u];
-  const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
   const int groups = (p.tokens + p.nranks - 1) / p.nranks;
   const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   const int nctas = gridDim.x * gridDim.y * gridDim.z;
@@ -144,19 +162,60 @@ gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   const int kb0 = blockIdx.z * f.kblocks_per_split;
   const int nkb = min(f.kblocks, kb0 + f.kblocks_per_split) - kb0;
 
+  // The producer thread requests the first ring of WEIGHT tiles (never written by a kernel) before it waits for
+  // the previous kernel of the stream; everything else - activations, the communication state - comes after.
+  if (warp == 0 && lane == 0)
+    pipe.template produce<kEpb>(&map_w, &map_a, blockIdx.x * kBM, blockIdx.y * kBN, kb0, nkb, f.status, [] {
+      ptx::pdl_wait();
+      return true;
+    });
+  ptx::pdl_wait();
+  ptx::pdl_launch_dependents();
+  const uint32_t epoch = ctl->lamport_epoch;
+  const uint64_t dirty_prev = ctl->lamport_dirty[(epoch + 2u) % 3u];
+  const size_t buf_off = p.layout.off_lamport + (size_t)(epoch % 3u) * p.layout.lamport_bytes;
+
   if (warp == 0) {
-    if (lane == 0)
-      pipe.template produce<kElemsPerBlock>(&map_w, &map_a, blockIdx.x * kBM, blockIdx.y * kBN, kb0, nkb, f.status,
-                                            [] { return true; });
   } else if (warp == 1) {
-    if (lane == 0) pipe.template issue<false, false>(nkb, f.idesc, f.status);
+    if (lane == 0) pipe.template issue<kScaled, kScaled>(nkb, f.idesc, f.status);
   } else if (warp < 6) {
-    const bool ok = tc::mbar_wait(&pipe.acc_full[0], 0, gemm_core::kWaitLimit, pipe.abort_flag);
-    tc::fence_after_thread_sync();
+    bool ok = true;
+    float acc[kScaled ? kBN : 1];
+    if constexpr (kScaled) {
+      const int q = warp & 3;
+      const int x = blockIdx.x * kBM + q * 32 + lane;          // weight row (output column) of this thread
+      const uint32_t lane_addr = pipe.tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+      for (int i = 0; i < kBN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int buf = i & 1;
+        ok = tc::mbar_wait(&pipe.acc_full[buf], (i >> 1) & 1, gemm_core::kWaitLimit, pipe.abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
+        const int kb = kb0 + i;
+        const float ws = f.w_scale[(size_t)(x < p.hidden ? x / 128 : 0) * f.scale_kb + kb];
+#pragma unroll
+        for (int c = 0; c < kBN; c += 16) {
+          float v[16];
+          tc::tmem_ld_16(lane_addr + buf * kBN + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = min((int)blockIdx.y * kBN + c + j, p.tokens - 1);
+            acc[c + j] = fmaf(v[j], ws * f.a_scale[(size_t)t * f.scale_kb + kb], acc[c + j]);
+          }
+        }
+        tc::fence_before_thread_sync();
+        tc::mbar_arrive(&pipe.acc_empty[buf]);
+      }
+    } else {
+      ok = tc::mbar_wait(&pipe.acc_full[0], 0, gemm_core::kWaitLimit, pipe.abort_flag);
+      tc::fence_after_thread_sync();
+    }
     if (!ok) pipe.fail(f.status);
     // every MMA has completed, so the operand ring is free: stage the tile there
     if (ok)
-      push_tile_to_owners<kBN>(p, f, pipe.smem, pipe.scratch, pipe.tmem_base, blockIdx.x, blockIdx.y, buf_off, groups);
+      push_tile_to_owners<kBN, kScaled>(p, f, pipe.smem, pipe.scratch, pipe.tmem_base, blockIdx.x, blockIdx.y, buf_off, groups,
+                                        acc);
   }
   __syncthreads();
   clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev, cta, nctas);
@@ -197,18 +256,24 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   pipe.init(smem_raw, kTmemCols, &map_w, &map_g0);
   char* self = static_cast<char*>(a.peer[a.rank]);
   Control* ctl = reinterpret_cast<Control*>(self + a.layout.off_control);
-  const uint32_t epoch = ctl->ag_epoch;
-  const uint32_t target = epoch + 1u;
-  const size_t gbuf_off = a.layout.off_ag + (size_t)(epoch & 1u) * a.layout.ag_buf_bytes;
-  const CUtensorMap* map_g = (epoch & 1u) ? &map_g1 : &map_g0;
   const int cta = blockIdx.x + gridDim.x * blockIdx.y, nctas = gridDim.x * gridDim.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t row_bytes = (size_t)a.k * sizeof(T);
   const int my_rows = (a.tokens - a.rank + a.nranks - 1) / a.nranks;
+  // Only the producer thread runs ahead of the previous kernel of the stream, and only to request weight tiles
+  // (its gate begins with the same wait); the epoch is read after the wait on every path.
+  if (!(warp == 0 && lane == 0)) {
+    ptx::pdl_wait();
+    ptx::pdl_launch_dependents();
+  }
 
   if (warp == 0) {
     if (lane == 0) {
+      uint32_t epoch_p = 0;
       auto gate = [&]() -> bool {
+        ptx::pdl_wait();
+        epoch_p = ctl->ag_epoch;
+        const uint32_t target = epoch_p + 1u;
         // all N shards must have landed in THIS rank's staging buffer
         Waiter w(a.timeout_ns);
         for (int r = 0; r < a.nranks; ++r) {
@@ -225,12 +290,16 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         asm volatile("fence.proxy.async.global;" ::: "memory");
         return true;
       };
-      pipe.template produce<kElemsPerBlock>(&map_w, map_g, blockIdx.x * kBM, blockIdx.y * kBN, 0, a.kblocks, a.status, gate);
+      pipe.template produce_late_y<kElemsPerBlock>(&map_w, &map_g0, &map_g1, &epoch_p, blockIdx.x * kBM, blockIdx.y * kBN, 0,
+                                                   a.kblocks, a.status, gate);
     }
   } else if (warp == 1) {
     if (lane == 0) pipe.template issue<false, false>(a.kblocks, a.idesc, a.status);
   } else {
     // warps 2..7: destination `d` of the all-gather is served by CTA d % nctas
+    const uint32_t epoch = ctl->ag_epoch;
+    const uint32_t target = epoch + 1u;
+    const size_t gbuf_off = a.layout.off_ag + (size_t)(epoch & 1u) * a.layout.ag_buf_bytes;
     const int tp = threadIdx.x - 64;   // 0..191
     for (int d = cta; d < a.nranks; d += nctas) {
       char* dst_base = static_cast<char*>(a.peer[d]) + gbuf_off;
@@ -271,7 +340,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __threadfence();
     const uint32_t done = atomicAdd(&ctl->arrive, 1u);
     if (done == (uint32_t)nctas - 1) {
-      ctl->ag_epoch = target;
+      ctl->ag_epoch = ctl->ag_epoch + 1u;
       ctl->arrive = 0;
       __threadfence();
     }
@@ -292,24 +361,23 @@ int sm_count() {
   return n;
 }
 
-template <int kBN, int kStages, int kVpt, int kOut>
+template <int kBN, int kStages, int kVpt, int kOut, bool kScaled>
 std::string launch_ar(const CUtensorMap& mw, const CUtensorMap& ma, const FusedArgs& f, dim3 grid, cudaStream_t s) {
-  auto kern = gemm_ar_rmsnorm_kernel<kBN, kStages, TDX_FUSED_N, kVpt, kOut>;
+  auto kern = gemm_ar_rmsnorm_kernel<kBN, kStages, TDX_FUSED_N, kVpt, kOut, kScaled>;
   std::string err = reserve_dynamic_smem(kern, SmemLayout<kBN, kStages>::kTotal);
   if (!err.empty()) return err;
-  kern<<<grid, kThreads, SmemLayout<kBN, kStages>::kTotal, s>>>(mw, ma, f);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), SmemLayout<kBN, kStages>::kTotal, s, mw, ma, f);
   return e == cudaSuccess ? "" : std::string("fused GEMM launch failed: ") + cudaGetErrorString(e);
 }
 
-template <int kBN, int kStages>
+template <int kBN, int kStages, bool kScaled>
 std::string launch_ar_vpt(int vpt, int out_mode, const CUtensorMap& mw, const CUtensorMap& ma, const FusedArgs& f, dim3 grid,
                           cudaStream_t s) {
   const bool q = out_mode == kOutFp8Block128;
   switch (vpt) {
-    case 1: return q ? launch_ar<kBN, kStages, 1, kOutFp8Block128>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 1, kOutSame>(mw, ma, f, grid, s);
-    case 2: return q ? launch_ar<kBN, kStages, 2, kOutFp8Block128>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 2, kOutSame>(mw, ma, f, grid, s);
-    case 4: return q ? launch_ar<kBN, kStages, 4, kOutFp8Block128>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 4, kOutSame>(mw, ma, f, grid, s);
+    case 1: return q ? launch_ar<kBN, kStages, 1, kOutFp8Block128, kScaled>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 1, kOutSame, kScaled>(mw, ma, f, grid, s);
+    case 2: return q ? launch_ar<kBN, kStages, 2, kOutFp8Block128, kScaled>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 2, kOutSame, kScaled>(mw, ma, f, grid, s);
+    case 4: return q ? launch_ar<kBN, kStages, 4, kOutFp8Block128, kScaled>(mw, ma, f, grid, s) : launch_ar<kBN, kStages, 4, kOutSame, kScaled>(mw, ma, f, grid, s);
   }
   return "unsupported hidden size for the fused GEMM";
 }
@@ -323,9 +391,12 @@ std::string launch_ar_vpt(int vpt, int out_mode, const CUtensorMap& mw, const CU
 // specialisation (0 = any rank count, runtime loop).
 std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, cudaStream_t stream) {
   const ArParams& p = g.ar;
-  if (p.dtype != kBF16) return "the fused GEMM paths take bfloat16 operands";
+  if (p.dtype != kBF16) return "the fused GEMM paths produce bfloat16 partial sums (bf16 or block-scaled e4m3 operands)";
   if (p.hidden % 128) return "hidden must be a multiple of 128";
-  if (g.k <= 0 || g.k % 64) return "K must be a positive multiple of 64";
+  const bool scaled = g.elem_size == 1;
+  if (scaled && (g.a_scale == nullptr || g.w_scale == nullptr)) return "e4m3 operands need block scales for both of them";
+  const int epb = scaled ? 128 : 64;
+  if (g.k <= 0 || g.k % epb) return "K must be a positive multiple of " + std::to_string(epb);
   if (p.out_mode != kOutSame && p.out_mode != kOutFp8Block128) return "fused GEMM output is bf16 or e4m3 with 1x128 scales";
   if (p.tokens <= 0) return "";
   const int bn = p.tokens <= 16 ? 16 : 64;
@@ -334,7 +405,7 @@ std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, c
   if ((int)(grid.x * grid.y) > sms)
     return "too many tokens for the fused GEMM (all CTAs must be resident): use the GEMM followed by the all-reduce op";
   // split K until the grid covers the SMs (every CTA must stay resident, so never beyond them)
-  const int kblocks = g.k / 64;
+  const int kblocks = g.k / epb;
   int splits = g.splits > 0 ? g.splits : sms / (int)(grid.x * grid.y);
   if (splits > kblocks / 2) splits = kblocks / 2;
   if (splits < 1 || g.ws == nullptr || g.counters == nullptr) splits = 1;
@@ -356,17 +427,23 @@ std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, c
   f.ar = p;
   f.kblocks = kblocks;
   f.kblocks_per_split = per_split;
-  f.idesc = tc::make_idesc(kBM, bn, 1, 1);
+  f.idesc = scaled ? tc::make_idesc(kBM, bn, 0, 0) : tc::make_idesc(kBM, bn, 1, 1);
   f.status = g.status;
   f.ws = g.ws;
   f.counters = g.counters;
+  f.w_scale = g.w_scale;
+  f.a_scale = g.a_scale;
+  f.scale_kb = g.k / 128;
   CUtensorMap mw, ma;
-  std::string err = bf16_map(&mw, g.w, p.hidden, g.k, g.ldw, kBM);
+  std::string err = tma::kmajor_2d(&mw, g.w, p.hidden, g.k, g.ldw, g.elem_size == 1 ? 1 : 2, kBF16, kBM);
   if (!err.empty()) return err;
-  err = bf16_map(&ma, g.a, p.tokens, g.k, g.lda, bn);
+  err = tma::kmajor_2d(&ma, g.a, p.tokens, g.k, g.lda, g.elem_size == 1 ? 1 : 2, kBF16, bn);
   if (!err.empty()) return err;
-  return bn == 16 ? launch_ar_vpt<16, 10>(vpt, p.out_mode, mw, ma, f, grid, stream)
-                  : launch_ar_vpt<64, 8>(vpt, p.out_mode, mw, ma, f, grid, stream);
+  if (scaled)
+    return bn == 16 ? launch_ar_vpt<16, 10, true>(vpt, p.out_mode, mw, ma, f, grid, stream)
+                    : launch_ar_vpt<64, 8, true>(vpt, p.out_mode, mw, ma, f, grid, stream);
+  return bn == 16 ? launch_ar_vpt<16, 10, false>(vpt, p.out_mode, mw, ma, f, grid, stream)
+                  : launch_ar_vpt<64, 8, false>(vpt, p.out_mode, mw, ma, f, grid, stream);
 }
 
 #if TDX_FUSED_N == 0
@@ -408,12 +485,12 @@ std::string ag_gemm(const AgGemmProblem& g, cudaStream_t stream) {
     auto kern = ag_gemm_kernel<16, 10>;
     err = reserve_dynamic_smem(kern, SmemLayout<16, 10>::kTotal);
     if (!err.empty()) return err;
-    kern<<<grid, kThreads, SmemLayout<16, 10>::kTotal, stream>>>(mw, m0, m1, a);
+    launch_chained(kern, grid, dim3(kThreads), SmemLayout<16, 10>::kTotal, stream, mw, m0, m1, a);
   } else {
     auto kern = ag_gemm_kernel<64, 8>;
     err = reserve_dynamic_smem(kern, SmemLayout<64, 8>::kTotal);
     if (!err.empty()) return err;
-    kern<<<grid, kThreads, SmemLayout<64, 8>::kTotal, stream>>>(mw, m0, m1, a);
+    launch_chained(kern, grid, dim3(kThreads), SmemLayout<64, 8>::kTotal, stream, mw, m0, m1, a);
   }
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : std::string("all-gather GEMM launch failed: ") + cudaGetErrorString(e);

@@ -16,7 +16,7 @@
 // Every wait is bounded; a wait that runs out records a status word, raises the CTA's abort flag and
 // all roles fall through to the common exit (copies in flight land, tensor memory is freed).
 //
-// Opt-in (ops/gemm.py: linear(..., persistent=True) or TDX_GEMM_PERSIST=1), bf16 / fp16 / unscaled
+// The default for prefill-sized problems (ops/gemm.py; TDX_GEMM_PERSIST=0 turns it off), bf16 / fp16 / unscaled
 // e4m3 operands, no split-K. The reference (xytpai/torch_dist_ext) has no GEMM.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -26,6 +26,8 @@
 #include "tdx/comm.h"
 #include "tdx/gemm.h"
 #include "tdx/gemm_core.cuh"
+#include "tdx/launch.h"
+#include "tdx/ptx.cuh"
 #include "tdx/tc.cuh"
 #include "tdx/tma_host.h"
 
@@ -96,6 +98,8 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   tc::fence_after_thread_sync();
   const uint32_t tmem_base = *tmem_slot;
+  ptx::pdl_wait();                // prefill shapes: both operands may come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
 
   auto fail = [&]() {
     *abort_flag = 1;
@@ -200,8 +204,7 @@ std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const PersistAr
   auto kern = gemm_persist_kernel<kFp8>;
   const std::string err = reserve_dynamic_smem(kern, kSmemTotal);
   if (!err.empty()) return err;
-  kern<<<grid, kThreads, kSmemTotal, stream>>>(mx, my, a);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_chained(kern, dim3(grid), dim3(kThreads), kSmemTotal, stream, mx, my, a);
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
 }
 

@@ -29,6 +29,8 @@
 #include "tdx/comm.h"
 #include "tdx/gemm.h"
 #include "tdx/gemm_core.cuh"
+#include "tdx/launch.h"
+#include "tdx/ptx.cuh"
 #include "tdx/tc.cuh"
 #include "tdx/tma_host.h"
 
@@ -60,6 +62,8 @@ struct GemmArgs {
   const float* y_scale;
   int x_scale_per_row, y_scale_per_row;
   int scale_kb;            // K blocks per scale row (= total K / 128)
+  int x_static;            // X is never written by a kernel (weights): its first tiles may be requested before the
+                           // previous kernel of the stream has finished
 };
 
 template <int kBN, int kStages, bool kFp8, bool kScaled>
@@ -86,11 +90,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int nkb = kb1 - kb0;
 
   if (warp == 0) {
-    if (lane == 0)
-      pipe.template produce<kElemsPerBlock>(&map_x, &map_y, tile_x * kBM, tile_y * kBN, kb0, nkb, a.status, [] { return true; });
+    if (lane == 0) {
+      // With static X (decode orientation: the weights) the first ring of X tiles is requested before the wait for
+      // the previous kernel of the stream; everything else is read and written after it.
+      if (!a.x_static) ptx::pdl_wait();
+      pipe.template produce<kElemsPerBlock>(&map_x, &map_y, tile_x * kBM, tile_y * kBN, kb0, nkb, a.status, [] {
+        ptx::pdl_wait();
+        return true;
+      });
+      ptx::pdl_launch_dependents();
+    }
   } else if (warp == 1) {
     if (lane == 0) pipe.template issue<kFp8, kScaled>(nkb, a.idesc, a.status);
   } else {
+    ptx::pdl_wait();   // scales, split-K scratch and the output belong to the stream's order
     // ---- epilogue (warps 2..5): TMEM lane quarter = warp % 4 -----------------------------------------
     const int q = warp & 3;
     const int x = tile_x * kBM + q * 32 + lane;
@@ -190,8 +203,7 @@ std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs&
   auto kern = gemm_tn_kernel<kBN, kStages, kFp8, kScaled>;
   const std::string err = reserve_dynamic_smem(kern, L::kTotal);
   if (!err.empty()) return err;
-  kern<<<grid, kThreads, L::kTotal, stream>>>(mx, my, a);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), L::kTotal, stream, mx, my, a);
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
 }
 
@@ -277,6 +289,7 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
   a.x_scale_per_row = g.x_scale_per_row;
   a.y_scale_per_row = g.y_scale_per_row;
   a.scale_kb = a.kblocks;
+  a.x_static = g.x_static;
   CUtensorMap mx, my;
   std::string err = tma::kmajor_2d(&mx, g.x, g.x_rows, g.k, g.ldx, g.elem_size, g.elem_kind, kBM);
   if (!err.empty()) return err;

@@ -29,6 +29,9 @@ struct GemmProblem {
   const float* x_scale;
   const float* y_scale;
   int x_scale_per_row, y_scale_per_row;
+  // X holds data that no kernel writes (weights): with programmatic dependent launch its first tiles are requested
+  // before the previous kernel of the stream has completed.
+  int x_static;
 };
 
 std::string gemm_tn(const GemmProblem& g, cudaStream_t stream);
@@ -46,8 +49,11 @@ std::string gemm_tn_persistent(const GemmProblem& g, cudaStream_t stream);
 // 1x128 scales), scatter_only. `ar.in` is unused: the partial rows come from the GEMM.
 struct FusedGemmProblem {
   ArParams ar;
-  const void* a;      // [tokens, k] bf16, this rank's K shard of the activations
-  const void* w;      // [hidden, k] bf16, this rank's K shard of the weight
+  const void* a;      // [tokens, k] bf16 or e4m3, this rank's K shard of the activations
+  const void* w;      // [hidden, k] bf16 or e4m3, this rank's K shard of the weight
+  int elem_size;      // 2: bf16 operands; 1: e4m3 operands with the block scales below (0 is read as 2)
+  const float* a_scale;   // e4m3: [tokens, k / 128] fp32, one scale per token and 128-wide K block
+  const float* w_scale;   // e4m3: [hidden / 128, k / 128] fp32, one scale per 128 x 128 block
   int k;
   int64_t lda, ldw;
   uint32_t* status;

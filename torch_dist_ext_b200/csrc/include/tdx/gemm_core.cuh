@@ -123,6 +123,21 @@ struct Pipeline {
   template <int kElemsPerBlock, typename Gate>
   __device__ __forceinline__ void produce(const CUtensorMap* mx, const CUtensorMap* my, int x_row0, int y_row0, int kb0,
                                           int nkb, uint32_t* status, Gate gate_y) {
+    produce_pick<kElemsPerBlock>(mx, x_row0, y_row0, kb0, nkb, status, gate_y, [my] { return my; });
+  }
+
+  // The same with the Y tensor map chosen only after the gate has passed (`*parity` odd: my1, else my0), for a Y
+  // operand whose buffer is selected by state that may be read only behind the gate.
+  template <int kElemsPerBlock, typename Gate>
+  __device__ __forceinline__ void produce_late_y(const CUtensorMap* mx, const CUtensorMap* my0, const CUtensorMap* my1,
+                                                 const uint32_t* parity, int x_row0, int y_row0, int kb0, int nkb,
+                                                 uint32_t* status, Gate gate_y) {
+    produce_pick<kElemsPerBlock>(mx, x_row0, y_row0, kb0, nkb, status, gate_y, [=] { return (*parity & 1u) ? my1 : my0; });
+  }
+
+  template <int kElemsPerBlock, typename Gate, typename PickY>
+  __device__ __forceinline__ void produce_pick(const CUtensorMap* mx, int x_row0, int y_row0, int kb0, int nkb,
+                                               uint32_t* status, Gate gate_y, PickY pick_y) {
     using L = SmemLayout<kBN, kStages>;
     const int first = nkb < kStages ? nkb : kStages;
     for (int i = 0; i < first; ++i) {
@@ -133,6 +148,7 @@ struct Pipeline {
       fail(status);
       return;
     }
+    const CUtensorMap* my = pick_y();
     for (int i = 0; i < first; ++i)
       tc::tma_load_2d(smem + i * L::kStageBytes + L::kXBytes, my, &full[i], (kb0 + i) * kElemsPerBlock, y_row0);
     for (int i = first; i < nkb; ++i) {

@@ -35,7 +35,7 @@ std::string attention_decode(const void* q, const void* k_cache, const void* v_c
                              int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,
                              cudaStream_t stream, uint32_t* status = nullptr);
 // The same computation with both products of a chunk on the tensor cores (attention_decode_tc.cu); same
-// arguments and scratch layout (the first 4096 words of `partial` are left untouched).
+// arguments and scratch layout.
 std::string attention_decode_tc(const void* q, const void* k_cache, const void* v_cache, const int32_t* seq_lens,
                                 float* partial, size_t partial_floats, void* out, int B, int Hq, int Hkv, int D, int S_max,
                                 int64_t q_stride_b, int64_t kv_stride_b, int64_t kv_stride_s, int nsplit, float scale,

@@ -156,8 +156,9 @@ static tdx::GemmProblem gemm_problem(const Tensor& x, const Tensor& y, Tensor& o
 void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, int64_t block_n, int64_t splits,
              const c10::optional<Tensor>& ws, const c10::optional<Tensor>& counters, const c10::optional<Tensor>& status,
              const c10::optional<Tensor>& x_scale, const c10::optional<Tensor>& y_scale, bool x_scale_per_row,
-             bool y_scale_per_row) {
+             bool y_scale_per_row, bool x_static) {
   tdx::GemmProblem g = gemm_problem(x, y, out, sx, sy, status);
+  g.x_static = x_static;
   const c10::cuda::CUDAGuard guard(x.device());
   g.block_n = (int)block_n;
   g.splits = (int)splits;
@@ -266,10 +267,13 @@ static tdx::Workspace* workspace_of(const Tensor& table) {
 void gemm_ar_rmsnorm(const Tensor& a, const Tensor& w, const c10::optional<Tensor>& residual_in, const Tensor& gamma,
                      c10::optional<Tensor> residual_out, Tensor norm_out, c10::optional<Tensor> scale_out, double eps,
                      const Tensor& workspace, int64_t out_mode, bool scatter_only, const c10::optional<Tensor>& status,
-                     int64_t splits, const c10::optional<Tensor>& splitk_ws, const c10::optional<Tensor>& splitk_counters) {
+                     int64_t splits, const c10::optional<Tensor>& splitk_ws, const c10::optional<Tensor>& splitk_counters,
+                     const c10::optional<Tensor>& a_scale, const c10::optional<Tensor>& w_scale) {
   tdx::Workspace* ws = workspace_of(workspace);
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1), "gemm_ar_rmsnorm: a [tokens, k], w [hidden, k]");
-  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && gamma.scalar_type() == at::kBFloat16, "gemm_ar_rmsnorm: bfloat16 operands");
+  const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
+  TORCH_CHECK((fp8 || a.scalar_type() == at::kBFloat16) && w.scalar_type() == a.scalar_type() && gamma.scalar_type() == at::kBFloat16,
+              "gemm_ar_rmsnorm: bfloat16 operands, or float8_e4m3fn operands with block scales; bfloat16 gamma");
   TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1 && gamma.is_contiguous() && norm_out.is_contiguous(), "gemm_ar_rmsnorm: K-major operands, contiguous outputs");
   const c10::cuda::CUDAGuard guard(a.device());
   tdx::FusedGemmProblem g{};
@@ -284,6 +288,18 @@ void gemm_ar_rmsnorm(const Tensor& a, const Tensor& w, const c10::optional<Tenso
     TORCH_CHECK(t->is_contiguous() && t->numel() == rows * hidden && t->scalar_type() == at::kBFloat16, name, " must be contiguous bf16 [", rows, ", ", hidden, "]");
     return t->data_ptr();
   };
+  g.elem_size = fp8 ? 1 : 2;
+  if (fp8) {
+    const int64_t kb = a.size(1) / 128;
+    TORCH_CHECK(a.size(1) % 128 == 0 && a_scale.has_value() && w_scale.has_value() && a_scale->defined() && w_scale->defined(),
+                "gemm_ar_rmsnorm: e4m3 operands need K % 128 == 0 and both scale tensors");
+    TORCH_CHECK(a_scale->is_cuda() && w_scale->is_cuda() && a_scale->scalar_type() == at::kFloat && w_scale->scalar_type() == at::kFloat &&
+                    a_scale->is_contiguous() && w_scale->is_contiguous() && a_scale->numel() == tokens * kb &&
+                    w_scale->numel() == ((hidden + 127) / 128) * kb,
+                "gemm_ar_rmsnorm: scales must be contiguous float32 [tokens, K/128] and [hidden/128, K/128]");
+    g.a_scale = a_scale->data_ptr<float>();
+    g.w_scale = w_scale->data_ptr<float>();
+  }
   g.ar.residual_in = opt_ptr(residual_in, "residual_in");
   g.ar.residual_out = opt_ptr(residual_out, "residual_out");
   g.ar.gamma = gamma.data_ptr();
@@ -352,7 +368,7 @@ void ag_gemm(const Tensor& x_shard, const Tensor& w, Tensor out, int64_t tokens,
 void register_extra_ops(torch::Library& m) {
   m.def("gemm_ar_rmsnorm(Tensor a, Tensor w, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
         "Tensor(c!)? scale_out, float eps, Tensor workspace, int out_mode, bool scatter_only, Tensor(d!)? status, "
-        "int splits, Tensor(e!)? splitk_ws, Tensor(f!)? splitk_counters) -> ()",
+        "int splits, Tensor(e!)? splitk_ws, Tensor(f!)? splitk_counters, Tensor? a_scale=None, Tensor? w_scale=None) -> ()",
         &gemm_ar_rmsnorm);
   m.def("attention_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor seq_lens, Tensor(a!) out, Tensor(b!) partial, "
         "int nsplit, float scale, Tensor(c!)? status) -> ()", &attention_decode);
@@ -363,7 +379,7 @@ void register_extra_ops(torch::Library& m) {
   m.def("ag_gemm(Tensor x_shard, Tensor w, Tensor(a!) out, int tokens, Tensor workspace, Tensor(b!)? status) -> ()", &ag_gemm);
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
-        "bool y_scale_per_row) -> ()", &gemm_tn);
+        "bool y_scale_per_row, bool x_static=False) -> ()", &gemm_tn);
   m.def("gemm_tn_pair(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_pair);
   m.def("gemm_tn_persistent(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_persistent);
   m.def("fused_add_rmsnorm(Tensor x, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "

@@ -148,8 +148,11 @@ class TPLlama:
         """a @ W_r^T -> all-reduce (or reduce-scatter) -> + res -> RMSNorm. Returns (x, x_scale, res)."""
         scatter = self.mode == "sp"
         if lin.fp8:
-            y = lin(a, a_scale)
-            x, res, xs = fused_allreduce_rms(y, res, gamma, self.cfg.eps, out_mode=OUT_FP8_BLOCK128, scatter_only=scatter)
+            # block-scaled e4m3 operands go through the same fused kernel; its epilogue quantises the next layer's input
+            if a_scale is None:
+                a, a_scale = quant.quant_fp8(a, block_scaled=True)
+            x, res, xs = fused_gemm.gemm_allreduce_rms(a, lin.w, res, gamma, self.cfg.eps, out_mode=OUT_FP8_BLOCK128,
+                                                       scatter_only=scatter, a_scale=a_scale, w_scale=lin.scale)
             return x, xs, res
         x, res, xs = fused_gemm.gemm_allreduce_rms(a, lin.w, res, gamma, self.cfg.eps, out_mode=OUT_SAME,
                                                    scatter_only=scatter)

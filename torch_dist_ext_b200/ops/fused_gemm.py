@@ -33,29 +33,41 @@ def _fits(tokens: int, rows: int) -> bool:
 def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor], gamma: torch.Tensor,
                        eps: float, *, out_mode: int = OUT_SAME, scatter_only: bool = False,
                        want_residual: bool = True, force_unfused: bool = False, splits: int = 0,
+                       a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
                        ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """``y = all_reduce(a @ w.T); res = y + residual; norm = rmsnorm(res) * gamma``.
 
-    ``a [tokens, K_shard]``, ``w [hidden, K_shard]`` (bf16). Returns ``(norm, res, scales)``; with
-    ``scatter_only`` only the rows ``rank::world`` (and ``residual`` is that row shard).
+    ``a [tokens, K_shard]``, ``w [hidden, K_shard]``: bf16, or e4m3 with ``a_scale [tokens, K/128]`` (one scale per
+    token and 128-wide K block) and ``w_scale [hidden/128, K/128]`` (one per 128 x 128 block), fp32. Residual, gamma
+    and the non-quantised outputs are bf16. Returns ``(norm, res, scales)``; with ``scatter_only`` only the rows
+    ``rank::world`` (and ``residual`` is that row shard).
     """
     c = _comm.get_comm()
     tokens, hidden = a.shape[0], w.shape[0]
+    fp8 = a.dtype == torch.float8_e4m3fn
+    if fp8 and w.shape[0] != gamma.shape[0]:
+        hidden = gamma.shape[0]         # weights padded to a multiple of 128 rows
     if force_unfused or not _fits(tokens, hidden) or hidden % 128 or out_mode not in (OUT_SAME, OUT_FP8_BLOCK128):
-        y = _gemm.linear(a, w)
+        if fp8:
+            y = _gemm.linear_fp8_blockscaled(a, a_scale, w, w_scale)
+            y = y[:, :hidden] if y.shape[1] != hidden else y
+        else:
+            y = _gemm.linear(a, w)
         return fused_allreduce_rms(y, residual, gamma, eps, out_mode=out_mode, scatter_only=scatter_only,
                                    want_residual=want_residual)
     n = c.world_size
     rows = (tokens + n - 1) // n if scatter_only else tokens
-    res_out = torch.empty(rows, hidden, dtype=a.dtype, device=a.device) if want_residual else None
+    act_dtype = torch.bfloat16 if fp8 else a.dtype
+    res_out = torch.empty(rows, hidden, dtype=act_dtype, device=a.device) if want_residual else None
     if out_mode == OUT_SAME:
-        norm, scales = torch.empty(rows, hidden, dtype=a.dtype, device=a.device), None
+        norm, scales = torch.empty(rows, hidden, dtype=act_dtype, device=a.device), None
     else:
         norm = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=a.device)
         scales = torch.empty(rows, hidden // 128, dtype=torch.float32, device=a.device)
     ws, counters, status = _gemm._workspace(a.device)
-    _lib.ops().gemm_ar_rmsnorm(a, w, residual, gamma, res_out, norm, scales, eps, c.get_workspace(a), out_mode,
-                               scatter_only, status, splits, ws, counters)
+    _lib.ops().gemm_ar_rmsnorm(a, w[:hidden] if w.shape[0] != hidden else w, residual, gamma, res_out, norm, scales, eps,
+                               c.get_workspace(a), out_mode, scatter_only, status, splits, ws, counters,
+                               a_scale.contiguous() if fp8 else None, w_scale.contiguous() if fp8 else None)
     return norm, res_out, scales
 
 

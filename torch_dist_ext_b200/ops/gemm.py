@@ -100,7 +100,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         out = torch.empty(m, n, dtype=dt, device=a.device)
     ws, counters, status = _workspace(a.device)
     if swap:
-        _lib.ops().gemm_tn(w, a, out, 1, n, block_n, splits, ws, counters, status, None, None, False, False)
+        # swapped: X is the weight, which no kernel writes, so its first tiles may be fetched ahead of the stream order
+        _lib.ops().gemm_tn(w, a, out, 1, n, block_n, splits, ws, counters, status, None, None, False, False, True)
     else:
         _lib.ops().gemm_tn(a, w, out, n, 1, block_n, splits, ws, counters, status, None, None, False, False)
     return out
@@ -119,7 +120,7 @@ def linear_fp8_blockscaled(a_q: torch.Tensor, a_scale: torch.Tensor, w_q: torch.
         out = torch.empty(m, n, dtype=out_dtype, device=a_q.device)
     ws, counters, status = _workspace(a_q.device)
     _lib.ops().gemm_tn(w_q, a_q, out, 1, n, bn, splits, ws, counters, status, w_scale.contiguous(),
-                       a_scale.contiguous(), False, True)
+                       a_scale.contiguous(), False, True, True)
     return out
 
 
