@@ -208,8 +208,12 @@ def main():
     g = args.group
     if g in ("gemm", "all"):        # decode: weight streaming (Llama-3-8B shapes at TP=1)
         gemm_cases(dev, args.steps, [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)], (1, 16, 64), out)
-    if g in ("gemm_prefill", "all"):
+    if g in ("gemm_prefill", "all"):   # the persistent kernel (the default for these shapes)
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out)
+        gemm_cases(dev, max(5, args.steps // 3), [(8192, 8192), (3584, 8192)], (2048,), out)   # Llama-3-70B shapes at TP=1 / TP=8
+    if g == "gemm_one_tile":           # one 128 x N tile per CTA, no persistence (the decode kernel on prefill shapes)
+        os.environ["TDX_GEMM_PERSIST"] = "0"
+        gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336), (8192, 8192)], (2048,), out, persistent=False)
     if g == "gemm_pair":            # opt-in kernel: 256 x 256 tiles on CTA pairs (not part of "all")
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out, cta_pair=True)
     if g == "gemm_persist":         # opt-in kernel: persistent grid, double-buffered accumulator (not part of "all")

@@ -48,3 +48,17 @@ def test_fp8_world1(block):
     e_y, _, _ = tdx.reference.fused_allreduce_rms_reference([x], r, w, 1e-6, OUT_SAME)
     # e4m3 keeps 3 mantissa bits: relative error <= 2^-4 of the block/token maximum
     assert (y - e_y.float()).abs().max().item() <= e_y.float().abs().max().item() * 2.0 ** -4
+
+
+def test_float64_inputs_give_the_fp32_result_as_doubles():
+    """The reference's dispatch covers double but its arithmetic stays in fp32; so does this path."""
+    x = torch.randn(9, 1024, device="cuda", dtype=torch.float64)
+    r = torch.randn_like(x)
+    w = 1 + 0.1 * torch.randn(1024, device="cuda", dtype=torch.float64)
+    norm, res = tdx.allreduce_rms(0, 1, x, r, w, 1e-6, tdx.get_workspace(x))
+    assert norm.dtype == torch.float64 and res.dtype == torch.float64
+    n32, r32 = tdx.allreduce_rms(0, 1, x.float(), r.float(), w.float(), 1e-6, tdx.get_workspace(x))
+    assert torch.equal(norm, n32.double()) and torch.equal(res, r32.double())
+    want = (x + r)
+    want = want * torch.rsqrt(want.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    assert (norm - want).abs().max().item() <= 1e-4

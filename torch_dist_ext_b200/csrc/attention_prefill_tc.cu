@@ -46,7 +46,9 @@ constexpr int kThreads = kSoftmaxThreads + 32;
 constexpr int kMmaWarp = kSoftmaxThreads / 32;
 constexpr int kHalfBytes = kRows * 128;           // one 64-column half of a 128-row tile
 constexpr int kTileBytes = 2 * kHalfBytes;        // Q, P, one K chunk or one V chunk
-constexpr int kBarrierBytes = 128;                // 13 mbarriers, the TMEM address and the abort flag
+constexpr int kNumBarriers = 2 * kStagesK + 2 * kStagesV + 4 + 3;   // k/v full+free, s full+free [2], q_full, p_full, o_full
+constexpr int kBarrierBytes = 256;                // the mbarriers, the TMEM address and the abort flag
+static_assert(kNumBarriers * 8 + 8 <= kBarrierBytes, "barrier area too small");
 constexpr int kSmem = (kStagesK + kStagesV + 2) * kTileBytes + kBarrierBytes + 2 * 2 * kRows * (int)sizeof(float);
 static_assert(kSmem <= 227 * 1024, "shared memory of one CTA");
 constexpr uint32_t kTmemCols = 512;               // S buffers at columns 0 and 128, O at 256

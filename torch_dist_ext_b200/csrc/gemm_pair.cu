@@ -1,27 +1,33 @@
-// Two-SM tcgen05 GEMM for prefill-sized problems:  D[x, y] = sum_k X[x, k] * Y[y, k], both K-major.
+// Two-SM persistent tcgen05 GEMM for prefill-sized problems:  D[x, y] = sum_k X[x, k] * Y[y, k], both K-major.
 //
-// A cluster of two CTAs (a "pair") computes one 256 x 256 tile with tcgen05.mma.cta_group::2:
+// A cluster of two CTAs (a "pair") computes 256 x 256 tiles with tcgen05.mma.cta_group::2:
 // CTA r of the pair loads rows [128 r, 128 r + 128) of the X tile and rows [128 r, 128 r + 128) of the
 // 256-row Y tile - each CTA fetches only its own half, with ordinary TMA copies - and the leader
 // (r = 0) issues the MMAs, which read both CTAs' shared memory. Compared with two independent
 // 128 x 256 tiles, every SM stages half as much of Y per K block (32 KB instead of 48 KB per stage),
 // so the operand ring is deeper and the shared-memory traffic per FLOP lower. The accumulator is
-// split by rows: rows 0-127 in the leader's tensor memory, rows 128-255 in the peer's; each CTA's
-// epilogue warps read their own half with tcgen05.ld and store it.
+// split by rows: rows 0-127 in the leader's tensor memory, rows 128-255 in the peer's.
+//
+// The grid is persistent: pair p walks the tiles p, p + pairs, ... (the x tile index runs fastest, so pairs that
+// work side by side share the Y tile in L2). The operand ring keeps streaming across tile boundaries and the
+// accumulator is double-buffered in tensor memory (2 x 256 columns in each CTA): while the epilogue warps of both
+// CTAs read tile n back with tcgen05.ld and store it, the leader is already accumulating tile n + 1.
 //
 // Synchronisation (all waits bounded):
-//  * full[s]   leader only: armed by the leader's producer for the bytes of BOTH CTAs; the peer's
-//              copies credit the leader's barrier (address translated with mapa).
-//  * empty[s]  one per CTA: the leader's MMA thread commits to its own and (through the cluster's
-//              shared window) to the peer's.
-//  * acc_full  one per CTA, committed the same way after the last K block.
+//  * full[s]       leader only: armed by the leader's producer for the bytes of BOTH CTAs; the peer's
+//                  copies credit the leader's barrier (address translated with mapa).
+//  * empty[s]      one per CTA: the leader's MMA thread commits to its own and (through the cluster's
+//                  shared window) to the peer's.
+//  * acc_full[b]   one per CTA and accumulator buffer, committed the same way after a tile's last K block.
+//  * acc_empty[b]  leader only: one arrival per epilogue warp of BOTH CTAs (8) once the warp has read its part
+//                  of buffer b; the leader waits for it before it reuses the buffer two tiles later.
 //  * cluster barriers after barrier initialisation (no remote arrival before the target exists)
 //    and before tensor memory is freed (no CTA leaves while its peer may still read its shared
 //    memory or write its barriers).
 // A wait that runs out records a status word, raises the abort flag of both CTAs and falls through
 // to the common exit, where in-flight copies are given time to land and tensor memory is freed.
 //
-// Opt-in (ops/gemm.py: linear(..., cta_pair=True) or TDX_GEMM_PAIR=1) for bf16 / fp16 / unscaled e4m3
+// Selected by ops/gemm.py (linear(..., cta_pair=True) or TDX_GEMM_PAIR=1) for bf16 / fp16 / unscaled e4m3
 // operands. The reference (xytpai/torch_dist_ext) has no GEMM.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -32,6 +38,8 @@
 #include "tdx/comm.h"
 #include "tdx/gemm.h"
 #include "tdx/gemm_core.cuh"
+#include "tdx/launch.h"
+#include "tdx/ptx.cuh"
 #include "tdx/tc.cuh"
 #include "tdx/tma_host.h"
 
@@ -49,11 +57,12 @@ constexpr int kOperandBytes = kRowsPerCta * 128; // 128 rows x one 128-byte swiz
 constexpr int kStageBytes = 2 * kOperandBytes;   // X half + Y half
 constexpr int kBarrierOffset = kStages * kStageBytes;
 constexpr int kSmemTotal = kBarrierOffset + 1024 /* barriers */ + 1024 /* alignment slack */;
-constexpr uint32_t kTmemCols = kTileN;           // fp32 accumulator columns
+constexpr uint32_t kTmemCols = 2 * kTileN;       // two fp32 accumulator buffers
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 struct PairArgs {
   int x_rows, y_rows, kblocks;
+  int tiles_x, tiles_y;
   void* out;
   int64_t sx, sy;
   int out_dtype;
@@ -71,14 +80,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kBarrierOffset);
   uint64_t* empty = full + kStages;
-  uint64_t* acc_full = empty + kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = empty + kStages;      // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2], used in the leader
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = tc::cluster_ctarank();      // 0: leader, 1: peer
   const uint32_t leader = rank & ~1u, other = rank ^ 1u;
-  const int tile_m = blockIdx.x >> 1, tile_n = blockIdx.y;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int ntiles = a.tiles_x * a.tiles_y;
   const int nkb = a.kblocks;
 
   if (threadIdx.x == 0) {
@@ -86,7 +97,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tc::mbar_init(&full[s], 1);
       tc::mbar_init(&empty[s], 1);
     }
-    tc::mbar_init(acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&acc_full[i], 1);
+      tc::mbar_init(&acc_empty[i], 8);         // four epilogue warps in each of the two CTAs
+    }
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_desc(&map_x);
@@ -103,6 +117,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   __syncthreads();
   tc::fence_after_thread_sync();
   const uint32_t tmem_base = *tmem_slot;
+  ptx::pdl_wait();             // prefill shapes: both operands may come from earlier kernels of the stream
+  ptx::pdl_launch_dependents();
 
   // a role that gives up tells the whole pair, so that the other roles stop early too
   auto fail = [&]() {
@@ -115,60 +131,84 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (lane == 0) {
       // ---- producer (both CTAs): own halves of X and Y, bytes credited to the leader's barrier ----
       const uint32_t leader_full = tc::map_to_cta(tc::smem_u32(&full[0]), leader);
-      const int x_row0 = tile_m * kTileM + (int)(rank & 1u) * kRowsPerCta;
-      const int y_row0 = tile_n * kTileN + (int)(rank & 1u) * kRowsPerCta;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % kStages;
-        if (i >= kStages && !tc::mbar_wait(&empty[s], ((i / kStages) - 1) & 1, kWaitLimit, abort_flag)) {
-          fail();
-          break;
+      uint32_t it = 0;                                   // K blocks issued so far by this CTA
+      bool ok = true;
+      for (int t = pair; t < ntiles && ok && !*abort_flag; t += npairs) {
+        const int x_row0 = (t % a.tiles_x) * kTileM + (int)(rank & 1u) * kRowsPerCta;
+        const int y_row0 = (t / a.tiles_x) * kTileN + (int)(rank & 1u) * kRowsPerCta;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          if (it >= (uint32_t)kStages && !tc::mbar_wait(&empty[s], ((it / kStages) - 1) & 1, kWaitLimit, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (rank == leader) tc::mbar_arrive_expect_tx(&full[s], 2 * kStageBytes);
+          const uint32_t dst = tc::smem_u32(smem + s * kStageBytes);
+          const uint32_t bar = leader_full + s * 8u;
+          tc::tma_load_2d_pair(dst, &map_x, bar, kb * kElemsPerBlock, x_row0);
+          tc::tma_load_2d_pair(dst + kOperandBytes, &map_y, bar, kb * kElemsPerBlock, y_row0);
         }
-        if (rank == leader) tc::mbar_arrive_expect_tx(&full[s], 2 * kStageBytes);
-        const uint32_t dst = tc::smem_u32(smem + s * kStageBytes);
-        const uint32_t bar = leader_full + (uint32_t)s * 8u;
-        tc::tma_load_2d_pair(dst, &map_x, bar, i * kElemsPerBlock, x_row0);
-        tc::tma_load_2d_pair(dst + kOperandBytes, &map_y, bar, i * kElemsPerBlock, y_row0);
       }
+      if (!ok) fail();
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == leader) {
       // ---- MMA issue (leader only) ----
+      uint32_t it = 0;
+      int n = 0;                                         // tiles started so far by this pair
       bool ok = true;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % kStages;
-        if (!tc::mbar_wait(&full[s], (i / kStages) & 1, kWaitLimit, abort_flag)) {
-          fail();
+      for (int t = pair; t < ntiles && ok; t += npairs, ++n) {
+        const uint32_t buf = n & 1;
+        if (n >= 2 && !tc::mbar_wait(&acc_empty[buf], ((n >> 1) - 1) & 1, kWaitLimit, abort_flag)) {
           ok = false;
           break;
         }
         tc::fence_after_thread_sync();
-        const uint32_t xa = tc::smem_u32(smem + s * kStageBytes);
-        const uint64_t dx = tc::make_smem_desc_sw128(xa);
-        const uint64_t dy = tc::make_smem_desc_sw128(xa + kOperandBytes);
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          if (!tc::mbar_wait(&full[s], (it / kStages) & 1, kWaitLimit, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc::fence_after_thread_sync();
+          const uint32_t xa = tc::smem_u32(smem + s * kStageBytes);
+          const uint64_t dx = tc::make_smem_desc_sw128(xa);
+          const uint64_t dy = tc::make_smem_desc_sw128(xa + kOperandBytes);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // 32 bytes of K per instruction, stepped inside the swizzle span
-          tc::umma_pair<kFp8>(tmem_base, dx + (uint64_t)(k * 2), dy + (uint64_t)(k * 2), a.idesc, (i > 0 || k > 0) ? 1u : 0u);
-        tc::umma_commit_pair(&empty[s], other);   // the stage is free again in both CTAs
+          for (int k = 0; k < 4; ++k)   // 32 bytes of K per instruction, stepped inside the swizzle span
+            tc::umma_pair<kFp8>(tmem_base + buf * kTileN, dx + (uint64_t)(k * 2), dy + (uint64_t)(k * 2), a.idesc,
+                                (kb > 0 || k > 0) ? 1u : 0u);
+          tc::umma_commit_pair(&empty[s], other);   // the stage is free again in both CTAs
+        }
+        if (ok) tc::umma_commit_pair(&acc_full[buf], other);
       }
-      if (ok) tc::umma_commit_pair(acc_full, other);
+      if (!ok) fail();
     }
   } else {
     // ---- epilogue (warps 2..5 of both CTAs): TMEM lane quarter = warp % 4 ----
     const int q = warp & 3;
-    const int x = tile_m * kTileM + (int)(rank & 1u) * kRowsPerCta + q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    const int y_base = tile_n * kTileN;
-    const bool ok = nkb > 0 && tc::mbar_wait(acc_full, 0, kWaitLimit, abort_flag);
-    tc::fence_after_thread_sync();
-    if (ok) {
+    const uint32_t leader_acc_empty = tc::map_to_cta(tc::smem_u32(&acc_empty[0]), leader);
+    int n = 0;
+    for (int t = pair; t < ntiles; t += npairs, ++n) {
+      const uint32_t buf = n & 1;
+      const int x = (t % a.tiles_x) * kTileM + (int)(rank & 1u) * kRowsPerCta + q * 32 + lane;
+      const int y_base = (t / a.tiles_x) * kTileN;
+      // the warp leaves the loop as a whole (tcgen05.ld is a warp-wide instruction)
+      if (nkb <= 0 || !__all_sync(0xffffffffu, tc::mbar_wait(&acc_full[buf], (n >> 1) & 1, kWaitLimit, abort_flag))) {
+        if (nkb > 0 && lane == 0 && q == 0) fail();
+        break;
+      }
+      tc::fence_after_thread_sync();
 #pragma unroll 4
       for (int c = 0; c < kTileN; c += 16) {
         float v[16];
-        tc::tmem_ld_16(lane_addr + c, v);
+        tc::tmem_ld_16(lane_addr + buf * kTileN + c, v);
         if (y_base + c < a.y_rows) store_chunk(a, x, y_base + c, v);
       }
-    } else if (nkb > 0 && lane == 0 && q == 0) {
-      fail();
+      tc::fence_before_thread_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive_cluster(leader_acc_empty + buf * 8u);   // this warp has read its part of the buffer
     }
   }
 
@@ -191,8 +231,7 @@ std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const PairArgs&
   auto kern = gemm_pair_kernel<kFp8>;
   const std::string err = reserve_dynamic_smem(kern, kSmemTotal);
   if (!err.empty()) return err;
-  kern<<<grid, kThreads, kSmemTotal, stream>>>(mx, my, a);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), kSmemTotal, stream, mx, my, a);
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
 }
 
@@ -220,8 +259,15 @@ std::string gemm_tn_pair(const GemmProblem& g, cudaStream_t stream) {
   if (!err.empty()) return err;
   err = tma::kmajor_2d(&my, g.y, g.y_rows, g.k, g.ldy, g.elem_size, g.elem_kind, kRowsPerCta);
   if (!err.empty()) return err;
-  const dim3 grid(2 * ((g.x_rows + kTileM - 1) / kTileM), (g.y_rows + kTileN - 1) / kTileN, 1);
-  if (grid.y > 65535) return "too many column tiles for one launch";
+  a.tiles_x = (g.x_rows + kTileM - 1) / kTileM;
+  a.tiles_y = (g.y_rows + kTileN - 1) / kTileN;
+  // one pair per two SMs, fewer when there are fewer tiles; pairs that cannot be resident at once simply start later
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long ntiles = (long long)a.tiles_x * a.tiles_y;
+  const int pairs = (int)(ntiles < sms / 2 ? ntiles : sms / 2);
+  const dim3 grid(2 * pairs, 1, 1);
   return fp8 ? launch<true>(mx, my, a, grid, stream) : launch<false>(mx, my, a, grid, stream);
 }
 

@@ -53,6 +53,15 @@ def fused_allreduce_rms(allreduce_in: torch.Tensor, residual_in: Optional[torch.
         if scatter_only and residual_in is not None:
             raise NotImplementedError("scatter_only with a sharded residual is CUDA-only")
         return _cpu_path(allreduce_in, residual_in, rms_gamma, eps, out_mode, scatter_only)
+    if allreduce_in.dtype == torch.float64:
+        # The reference instantiates its kernels for double through its dispatch macro
+        # (src/ops/all_reduce_fusion.cpp:29-33) but still accumulates, adds and normalises in fp32
+        # (src/common/all_reduce_fusion_impl.h:280-298, :316-340), so its float64 results are fp32 values stored
+        # as doubles. The same values come out of the fp32 kernels around two conversions.
+        norm, res, scales = fused_allreduce_rms(
+            allreduce_in.float(), None if residual_in is None else residual_in.float(), rms_gamma.float(), eps, workspace,
+            out_mode=out_mode, algo=algo, scatter_only=scatter_only, want_residual=want_residual)
+        return (norm.double() if out_mode == OUT_SAME else norm), (None if res is None else res.double()), scales
     c = _comm.get_comm()
     if workspace is None:
         workspace = c.get_workspace(allreduce_in)
