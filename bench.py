@@ -184,8 +184,9 @@ def run(args):
     msg = tokens * hidden * 2
     floor_us = 0.0 if world == 1 else 2.0 * (world - 1) / world * msg / 770e9 * 1e6
     out.update({
-        "per_rank_link_floor_us": round(floor_us, 3),
-        "fraction_of_link_floor": round(floor_us / mean_us, 3) if mean_us > 0 else None,
+        "value": round(mean_us, 3), "ms_per_step": round(mean_us / 1e3, 6),
+        "per_rank_link_floor_us": round(floor_us, 3) if world > 1 else None,
+        "fraction_of_link_floor": round(floor_us / mean_us, 3) if world > 1 and mean_us > 0 else None,
         "single_call_after_l2_flush_median_us": round(med_us, 3),
         "e2e": e2e,
         "gpu_launches": K if args.impl == "own" else 0,

@@ -60,7 +60,7 @@ def row(name, us, lib_us, nbytes, flops, hbm, tf, src):
             "TFLOP/s": round(tfl, 1), f"frac_bf16_of_{src}": round(tfl / tf, 3)}
 
 
-def gemm_cases(dev, steps, shapes, ms, out, cta_pair=False, persistent=False):
+def gemm_cases(dev, steps, shapes, ms, out, cta_pair=None, persistent=None):
     from torch_dist_ext_b200.ops import gemm
 
     hbm, tf, src = peaks()
@@ -68,14 +68,16 @@ def gemm_cases(dev, steps, shapes, ms, out, cta_pair=False, persistent=False):
         ws = rotating(lambda: torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02, n * k * 2)
         for m in ms:
             a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
-            if cta_pair or persistent:   # a new kernel: check it before timing it
-                err = (gemm.linear(a, ws[0], cta_pair=cta_pair, persistent=persistent).float() - gemm.linear(a, ws[0]).float()).abs().max().item()
+            if m >= 256:   # the tiled kernels against the one-tile-per-CTA kernel before timing them
+                err = (gemm.linear(a, ws[0], cta_pair=cta_pair, persistent=persistent).float() -
+                       gemm.linear(a, ws[0], cta_pair=False, persistent=False).float()).abs().max().item()
                 if err > 0.05 or gemm.pipeline_status() != 0:
                     raise SystemExit(f"opt-in GEMM disagrees with the default kernel (max err {err}, status {gemm.pipeline_status()})")
             us = time_us(lambda i: gemm.linear(a, ws[i], cta_pair=cta_pair, persistent=persistent), len(ws), steps)
             lib = time_us(lambda i: torch.matmul(a, ws[i].t()), len(ws), steps)
             nbytes = (n * k + m * k + m * n) * 2
-            tag = "gemm bf16 (CTA pairs)" if cta_pair else "gemm bf16 (persistent)" if persistent else "gemm bf16"
+            tag = ("gemm bf16 (CTA pairs)" if cta_pair else "gemm bf16 (persistent)" if persistent else
+                   "gemm bf16 (one tile per CTA)" if persistent is False and cta_pair is False else "gemm bf16")
             out.append(row(f"{tag} m={m} n={n} k={k}", us, lib, nbytes, 2.0 * m * n * k, hbm, tf, src))
             print(out[-1], flush=True)
         del ws
@@ -208,15 +210,16 @@ def main():
     g = args.group
     if g in ("gemm", "all"):        # decode: weight streaming (Llama-3-8B shapes at TP=1)
         gemm_cases(dev, args.steps, [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)], (1, 16, 64), out)
-    if g in ("gemm_prefill", "all"):   # the persistent kernel (the default for these shapes)
+    if g in ("gemm_prefill", "all"):   # the library's default for these shapes: persistent CTA pairs
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out)
         gemm_cases(dev, max(5, args.steps // 3), [(8192, 8192), (3584, 8192)], (2048,), out)   # Llama-3-70B shapes at TP=1 / TP=8
     if g == "gemm_one_tile":           # one 128 x N tile per CTA, no persistence (the decode kernel on prefill shapes)
         os.environ["TDX_GEMM_PERSIST"] = "0"
-        gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336), (8192, 8192)], (2048,), out, persistent=False)
-    if g == "gemm_pair":            # opt-in kernel: 256 x 256 tiles on CTA pairs (not part of "all")
+        gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336), (8192, 8192)], (2048,), out, cta_pair=False,
+                   persistent=False)
+    if g == "gemm_pair":            # 256 x 256 tiles on persistent CTA pairs, named explicitly
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out, cta_pair=True)
-    if g == "gemm_persist":         # opt-in kernel: persistent grid, double-buffered accumulator (not part of "all")
+    if g == "gemm_persist":         # persistent grid of single CTAs, 128 x 256 tiles, double-buffered accumulator
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out, persistent=True)
     if g in ("gemm_fp8", "all"):
         gemm_fp8_cases(dev, args.steps, out)

@@ -22,7 +22,7 @@ _SM_COUNT = 148
 _ws = {}
 
 
-_PAIR_DEFAULT = os.environ.get("TDX_GEMM_PAIR", "0") not in ("0", "", "false", "off")
+_PAIR_DEFAULT = os.environ.get("TDX_GEMM_PAIR", "1") not in ("0", "", "false", "off")
 _PERSIST_DEFAULT = os.environ.get("TDX_GEMM_PERSIST", "1") not in ("0", "", "false", "off")
 
 
@@ -72,19 +72,24 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
     """``a [M, K] @ w [N, K]^T -> [M, N]`` (bf16 / fp16 / e4m3 operands, fp32 accumulation).
 
     ``cta_pair=True`` runs prefill-sized problems (M, N >= 256) on 256 x 256 tiles computed by pairs of
-    CTAs (``tcgen05.mma.cta_group::2``); the default follows ``TDX_GEMM_PAIR`` (off). ``persistent=True`` runs
+    CTAs (``tcgen05.mma.cta_group::2``) that walk the tiles persistently with the accumulator double-buffered in
+    tensor memory; the default follows ``TDX_GEMM_PAIR`` (on: it is the fastest kernel for these shapes). ``persistent=True`` runs
     them on a persistent grid (one CTA per SM, accumulator double-buffered in tensor memory so that the epilogue
     of a tile overlaps the main loop of the next); the default follows ``TDX_GEMM_PERSIST`` (on)."""
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "linear: a [M, K], w [N, K]"
     m, k = a.shape
     n = w.shape[0]
-    if (_PAIR_DEFAULT if cta_pair is None else cta_pair) and m >= 256 and n >= 256 and not swap and splits in (None, 1):
+    # an explicit choice of one kernel is not overridden by the default of the other
+    use_pair = cta_pair if cta_pair is not None else (_PAIR_DEFAULT and persistent is None)
+    use_persistent = persistent if persistent is not None else (_PERSIST_DEFAULT and not use_pair)
+    if use_pair and m >= 256 and n >= 256 and not swap and splits in (None, 1):
         if out is None:
             dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
             out = torch.empty(m, n, dtype=dt, device=a.device)
         _lib.ops().gemm_tn_pair(a, w, out, n, 1, _workspace(a.device)[2])
         return out
-    if (_PERSIST_DEFAULT if persistent is None else persistent) and m > 128 and n >= 256 and not swap and splits in (None, 1):
+    if (use_persistent or (use_pair and persistent is None and _PERSIST_DEFAULT)) and m > 128 and n >= 256 and not swap \
+            and splits in (None, 1):
         if out is None:
             dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
             out = torch.empty(m, n, dtype=dt, device=a.device)
