@@ -8,10 +8,13 @@ models replay the role programs of
 
  * the persistent GEMM (csrc/gemm_persist.cu): operand ring that runs across tile boundaries,
    two accumulator buffers handed between the MMA thread and the epilogue warps;
- * the tensor-core attention kernels (csrc/attention_decode_tc.cu, attention_prefill_tc.cu):
-   K/V ring, double-buffered scores, one probability tile, one P*V buffer;
+ * the tensor-core decode attention kernel (csrc/attention_decode_tc.cu): K/V ring, double-buffered
+   scores, one probability tile, one P*V buffer;
+ * the prompt attention kernel (csrc/attention_prefill_tc.cu): separate K and V rings, double-buffered
+   scores, one probability tile, the output accumulated in tensor memory across all chunks;
  * the CTA-pair GEMM (csrc/gemm_pair.cu): two producers crediting the leader's transaction-counting
-   barriers, stages released in both CTAs by the leader's MMA thread
+   barriers, stages released in both CTAs by the leader's MMA thread, a persistent tile loop with two
+   accumulator buffers that the epilogue warps of BOTH CTAs hand back to the leader
 
 with the same parity expressions, under random schedules in which TMA completions and MMA
 completions (tcgen05.commit arrivals) land late and at arbitrary moments, and check that every
@@ -386,3 +389,214 @@ def pair_gemm(nkb, stages, rng):
 def test_cta_pair_gemm_pipeline(nkb, stages):
     for seed in range(80):
         pair_gemm(nkb, stages, random.Random(seed))
+
+
+# ---- prompt attention (csrc/attention_prefill_tc.cu) ------------------------------------------------------
+# K ring (freed when the scores of the chunk are complete) and V ring (freed when P*V is complete) run apart;
+# O accumulates in tensor memory over all chunks, so before the softmax threads touch the P tile (or rescale O)
+# for chunk i they wait for the P*V product of chunk i - 1, observing every phase of o_full exactly once.
+
+def prefill_attention(nchunks, stages_k, stages_v, rng):
+    k_full = [MBar(1) for _ in range(stages_k)]
+    k_free = [MBar(1) for _ in range(stages_k)]
+    v_full = [MBar(1) for _ in range(stages_v)]
+    v_free = [MBar(1) for _ in range(stages_v)]
+    s_full = [MBar(1) for _ in range(2)]
+    n_sm = 3                                             # stands for the 256 softmax threads
+    s_free = [MBar(n_sm) for _ in range(2)]
+    p_full = MBar(n_sm)
+    o_full = MBar(1)
+    kbuf, vbuf = [None] * stages_k, [None] * stages_v
+    k_reads, v_reads = [0] * stages_k, [0] * stages_v
+    s_buf, s_readers = [None, None], [0, 0]
+    p_tile = {"chunk": None, "reads_pending": 0}
+    o_acc = {"chunks": [], "mma_pending": 0, "rescaling": 0}
+    seen = [[] for _ in range(n_sm)]
+    events = {"tma": [], "mma": []}
+
+    def load_k(c):
+        s = c % stages_k
+        assert k_reads[s] == 0, "K stage overwritten while the score MMAs still read it"
+
+        def land():
+            kbuf[s] = c
+            k_full[s].arrive()
+        events["tma"].append(land)
+
+    def load_v(c):
+        s = c % stages_v
+        assert v_reads[s] == 0, "V stage overwritten while the P*V MMAs still read it"
+
+        def land():
+            vbuf[s] = c
+            v_full[s].arrive()
+        events["tma"].append(land)
+
+    def issue_scores(c):
+        s = c % stages_k
+        assert kbuf[s] == c and s_readers[c & 1] == 0
+        k_reads[s] += 1
+
+        def retire():
+            s_buf[c & 1] = c
+            k_reads[s] -= 1
+            s_full[c & 1].arrive()
+            k_free[s].arrive()
+        events["mma"].append(retire)
+
+    def issue_pv(c):
+        s = c % stages_v
+        assert vbuf[s] == c and p_tile["chunk"] == c, f"P*V of chunk {c}: V holds {vbuf[s]}, P holds {p_tile['chunk']}"
+        assert o_acc["rescaling"] == 0, "P*V issued while a softmax thread rescales O"
+        v_reads[s] += 1
+        p_tile["reads_pending"] += 1
+        o_acc["mma_pending"] += 1
+
+        def retire():
+            o_acc["chunks"].append(c)
+            o_acc["mma_pending"] -= 1
+            v_reads[s] -= 1
+            p_tile["reads_pending"] -= 1
+            o_full.arrive()
+            v_free[s].arrive()
+        events["mma"].append(retire)
+
+    def mma():
+        for c in range(min(nchunks, stages_k)):
+            load_k(c)
+        for c in range(min(nchunks, stages_v)):
+            load_v(c)
+        yield from wait(k_full[0], 0)
+        issue_scores(0)
+        for i in range(nchunks):
+            if i + 1 < nchunks:
+                n = i + 1
+                yield from wait(k_full[n % stages_k], (n // stages_k) & 1)
+                if n >= 2:
+                    yield from wait(s_free[n & 1], ((n >> 1) - 1) & 1)
+                issue_scores(n)
+                yield ("step",)
+            if i + stages_k < nchunks:
+                yield from wait(k_free[i % stages_k], (i // stages_k) & 1)
+                load_k(i + stages_k)
+            if i >= 1 and i - 1 + stages_v < nchunks:
+                yield from wait(v_free[(i - 1) % stages_v], ((i - 1) // stages_v) & 1)
+                load_v(i - 1 + stages_v)
+            yield from wait(p_full, i & 1)
+            yield from wait(v_full[i % stages_v], (i // stages_v) & 1)
+            issue_pv(i)
+            yield ("step",)
+
+    def softmax(who):
+        for i in range(nchunks):
+            buf = i & 1
+            yield from wait(s_full[buf], (i >> 1) & 1)
+            s_readers[buf] += 1
+            yield ("step",)
+            assert s_buf[buf] == i, f"softmax of chunk {i} read scores of {s_buf[buf]}"
+            s_readers[buf] -= 1
+            s_free[buf].arrive()
+            if i > 0:
+                yield from wait(o_full, (i - 1) & 1)
+                assert o_acc["chunks"] == list(range(i)) and o_acc["mma_pending"] == 0, "O not stable at the rescale point"
+                if rng.random() < 0.3:                  # the rare rescale of O in tensor memory
+                    o_acc["rescaling"] += 1
+                    yield ("step",)
+                    o_acc["rescaling"] -= 1
+            assert p_tile["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
+            yield ("step",)
+            p_tile["chunk"] = i
+            seen[who].append(i)
+            p_full.arrive()
+        yield from wait(o_full, (nchunks - 1) & 1)
+        assert o_acc["chunks"] == list(range(nchunks))
+
+    run([mma()] + [softmax(w) for w in range(n_sm)], events, rng)
+    assert all(x == list(range(nchunks)) for x in seen)
+
+
+@pytest.mark.parametrize("nchunks", [1, 2, 3, 4, 5, 7, 16])
+def test_prefill_attention_pipeline(nchunks):
+    for seed in range(60):
+        prefill_attention(nchunks, 2, 3, random.Random(seed))
+
+
+# ---- persistent CTA-pair GEMM: tile loop and accumulator hand-back ------------------------------------------
+
+def pair_gemm_persistent(ntiles, nkb, stages, rng):
+    full = [TxBar(1) for _ in range(stages)]
+    empty = [[MBar(1) for _ in range(stages)] for _ in range(2)]
+    acc_full = [[MBar(1), MBar(1)] for _ in range(2)]               # [cta][buffer]
+    n_warps = 2                                                      # stands for the four epilogue warps of a CTA
+    acc_empty = [MBar(2 * n_warps) for _ in range(2)]                # leader's, arrivals from both CTAs
+    data = [[None] * stages for _ in range(2)]
+    busy = [[False] * stages for _ in range(2)]
+    acc = [None, None]
+    readers = [0, 0]
+    stored = {(r, w): [] for r in range(2) for w in range(n_warps)}
+    events = {"tma0": [], "tma1": [], "mma": []}
+
+    def producer(rank):
+        it = 0
+        for t in range(ntiles):
+            for kb in range(nkb):
+                s = it % stages
+                if it >= stages:
+                    yield from wait(empty[rank][s], ((it // stages) - 1) & 1)
+                assert not busy[rank][s]
+                if rank == 0:
+                    full[s].arrive_expect(2)
+
+                def land(s=s, tag=(t, kb)):
+                    data[rank][s] = tag
+                    full[s].complete_tx(1)
+                events[f"tma{rank}"].append(land)
+                it += 1
+                yield ("step",)
+
+    def mma():
+        it = 0
+        for n in range(ntiles):
+            buf = n & 1
+            if n >= 2:
+                yield from wait(acc_empty[buf], ((n >> 1) - 1) & 1)
+            assert readers[buf] == 0, "accumulator overwritten while an epilogue warp reads it"
+            for kb in range(nkb):
+                s = it % stages
+                yield from wait(full[s], (it // stages) & 1)
+                assert data[0][s] == (n, kb) and data[1][s] == (n, kb)
+                busy[0][s] = busy[1][s] = True
+                acc[buf] = (n, [kb]) if kb == 0 else (acc[buf][0], acc[buf][1] + [kb])
+
+                def retire(s=s):
+                    busy[0][s] = busy[1][s] = False
+                    empty[0][s].arrive()
+                    empty[1][s].arrive()
+                events["mma"].append(retire)
+                it += 1
+                yield ("step",)
+
+            def done(buf=buf):
+                acc_full[0][buf].arrive()
+                acc_full[1][buf].arrive()
+            events["mma"].append(done)
+
+    def epilogue(rank, w):
+        for n in range(ntiles):
+            buf = n & 1
+            yield from wait(acc_full[rank][buf], (n >> 1) & 1)
+            readers[buf] += 1
+            yield ("step",)
+            assert acc[buf] == (n, list(range(nkb))), f"epilogue of tile {n} read {acc[buf]}"
+            readers[buf] -= 1
+            stored[(rank, w)].append(n)
+            acc_empty[buf].arrive()
+
+    run([producer(0), producer(1), mma()] + [epilogue(r, w) for r in range(2) for w in range(n_warps)], events, rng)
+    assert all(v == list(range(ntiles)) for v in stored.values())
+
+
+@pytest.mark.parametrize("ntiles,nkb,stages", [(1, 1, 6), (2, 7, 6), (3, 2, 6), (5, 1, 6), (6, 9, 6), (4, 3, 2)])
+def test_persistent_cta_pair_gemm_pipeline(ntiles, nkb, stages):
+    for seed in range(60):
+        pair_gemm_persistent(ntiles, nkb, stages, random.Random(seed))
