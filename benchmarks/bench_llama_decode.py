@@ -2,7 +2,7 @@
 """Decode throughput of Llama-shaped tensor-parallel models on this library's kernels.
 
     python -m torch.distributed.run --nproc-per-node N benchmarks/bench_llama_decode.py --gpus N
-        --model 8b|70b|tiny [--layers L] [--batch 1,16,64] [--kv 2048] [--steps 128] [--mode ar|sp]
+        --model 8b|70b|tiny|8b-shard8|70b-shard8 [--layers L] [--batch 1,16,64] [--kv 2048] [--steps 128] [--mode ar|sp]
 
 Weights are random (N(0, 0.02)); the KV cache is filled with random bf16 for `--kv` positions per
 sequence (`--prefill` instead runs one real `--kv`-token prompt per sequence through the prefill
@@ -43,7 +43,12 @@ def main():
     from torch_dist_ext_b200.models.llama import LlamaConfig, TPLlama
 
     tdx.setup_env(rank, world, max_size_in_bytes=64 << 20, device=local)
-    cfg = {"8b": LlamaConfig.llama3_8b, "70b": LlamaConfig.llama3_70b, "tiny": LlamaConfig.tiny}[args.model]()
+    if args.model.endswith("-shard8"):
+        # one rank's share of the TP=8 model, run as a single-rank model (kernel shapes of the TP=8 layer on one GPU)
+        full = {"8b": LlamaConfig.llama3_8b, "70b": LlamaConfig.llama3_70b}[args.model[:-7]]()
+        cfg = LlamaConfig.shard_of(full, 8)
+    else:
+        cfg = {"8b": LlamaConfig.llama3_8b, "70b": LlamaConfig.llama3_70b, "tiny": LlamaConfig.tiny}[args.model]()
     if args.layers:
         cfg.n_layers = args.layers
     batches = [int(b) for b in args.batch.split(",")]

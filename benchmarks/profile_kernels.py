@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Runs ONE kernel of the library a few times on a small case, for `ncu` captures.
 
-    python benchmarks/profile_kernels.py --kernel gemm|gemm_fp8|attention|fused_ar|gemm_ar|ag_gemm [--iters 4]
+    python benchmarks/profile_kernels.py --kernel gemm|gemm_fp8|gemm_prefill|attention|attention_prefill|fused_ar|gemm_ar|ag_gemm|ar_oneshot_emu|ar_twoshot_emu [--iters 4]
 
 Cases are sized so that the inputs exceed the 126 MB L2 where the kernel is bandwidth-bound, while
 the process holds well under a few GB, so that a multi-pass `ncu --set full` capture of one to three
@@ -62,6 +62,30 @@ def main():
         x = torch.randn(16, 4096, device=dev, dtype=torch.bfloat16)
         w = torch.randn(28672, 4096, device=dev, dtype=torch.bfloat16)
         fn = lambda: fused_gemm.allgather_gemm(x, w, 16)
+    elif args.kernel == "gemm_prefill":  # the persistent CTA-pair kernel where it is compute-bound: 2048 x 8192 x 8192 bf16
+        a = torch.randn(2048, 8192, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(8192, 8192, device=dev, dtype=torch.bfloat16) * 0.02
+        fn = lambda: gemm.linear(a, w)
+    elif args.kernel == "attention_prefill":   # causal attention over one 2048-token prompt, 8 query heads on 1 KV head
+        qkv = torch.randn(2048, 10 * 128, device=dev, dtype=torch.bfloat16)
+        q, k, v = qkv[:, :1024].view(2048, 8, 128), qkv[:, 1024:1152].view(2048, 1, 128), qkv[:, 1152:].view(2048, 1, 128)
+        fn = lambda: attention.prefill_attention(q, k, v)
+    elif args.kernel in ("ar_oneshot_emu", "ar_twoshot_emu"):
+        # the multi-rank protocols with 8 ranks EMULATED inside one cooperative launch on this GPU (blockIdx.y = rank):
+        # the only safe way to look at their stall reasons with a profiler. 128 x 4096 bf16 per rank; a short wait
+        # budget, so that a replay artefact ends as a status code
+        from torch_dist_ext_b200.utils.config import ALGO_CODES, OUT_SAME
+
+        ws = tdx.local_workspaces(8, size_in_bytes=8 << 20, timeout_ms=200)
+        ins = [torch.randn(128, 4096, device=dev, dtype=torch.bfloat16) for _ in range(8)]
+        rr = torch.randn(128, 4096, device=dev, dtype=torch.bfloat16)
+        g = torch.ones(4096, device=dev, dtype=torch.bfloat16)
+        outs = [torch.empty_like(rr) for _ in range(8)]
+        ress = [torch.empty_like(rr) for _ in range(8)]
+        algo = ALGO_CODES["oneshot" if args.kernel == "ar_oneshot_emu" else "twoshot"]
+
+        def fn():
+            torch.ops.torch_dist_ext.allreduce_rms_emulated(ws, ins, [rr] * 8, g, ress, outs, [], 1e-6, OUT_SAME, algo, False)
     else:
         raise SystemExit(f"unknown kernel {args.kernel}")
     for _ in range(args.iters):
@@ -73,6 +97,10 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     print(f"{args.kernel}: last call {e0.elapsed_time(e1) * 1e3:.1f} us (CUDA events)")
+    if args.kernel.endswith("_emu"):
+        bad = [w.errors_seen() for w in ws]
+        if any(bad):
+            raise SystemExit(f"a device-side wait ran out in the emulated launch: {bad}")
     tdx.teardown_env()
 
 

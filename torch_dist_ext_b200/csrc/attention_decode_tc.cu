@@ -10,11 +10,12 @@
 //
 // so neither K nor V is transposed or touched by a thread: TMA -> shared memory -> tensor core.
 // Per chunk the four softmax warps read S^T from tensor memory (one cache position per thread),
-// do the online-softmax bookkeeping, write the probabilities as a bf16 [heads, keys] tile (128-byte
-// swizzle, the B operand of the second product) and, once that product has completed, add its
-// result to their running output (one head-dimension index per thread, G registers).
-// A fifth warp issues the TMA copies (3-stage ring) and the MMAs; S^T is double-buffered in TMEM so
-// that the scores of chunk i+1 are computed while the softmax warps work on chunk i.
+// do the online-softmax bookkeeping and write the probabilities as a bf16 [heads, keys] tile (128-byte
+// swizzle, the B operand of the second product). O^T accumulates in tensor memory over all chunks of a
+// split; a head's column of it is rescaled there only when its running maximum has to be raised.
+// A fifth warp issues the TMA copies (3-stage ring) and the MMAs; S^T is double-buffered in TMEM and P in
+// shared memory, so that the scores of chunk i+1 and the P*V product of chunk i-1 run while the softmax
+// warps work on chunk i.
 //
 // Every wait is bounded; a wait that runs out records a status word, raises the CTA's abort flag
 // (which ends every other wait early) and all threads still reach the common exit, where copies in
@@ -49,10 +50,11 @@ constexpr int kMaxG = 8;
 constexpr int kHalfBytes = kKeys * 128;           // one 64-column half of a K or V chunk
 constexpr int kStageBytes = 4 * kHalfBytes;       // K lo, K hi, V lo, V hi
 constexpr int kSmallTileBytes = 2 * kNq * 128;    // Q or P: two 64-wide K blocks of 16 rows x 128 bytes
-constexpr int kSmem = kStages * kStageBytes + 2 * kSmallTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+constexpr int kSmem = kStages * kStageBytes + 3 * kSmallTileBytes /*Q, two P tiles*/ + 256 /*barriers*/ + 1024 /*alignment*/;
 constexpr uint32_t kTmemCols = 64;                // S^T buffers at columns 0 and 16, O^T chunk at 32
 constexpr uint32_t kColO = 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr float kRescaleThreshold = 5.f;          // natural-log units
 constexpr int kCounterWords = 4096;               // head of the scratch buffer reserved by the other kernel
 
 struct TcAttnArgs {
@@ -80,17 +82,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ float wred[2][kG][4];
-  __shared__ uint32_t s_last;
+  __shared__ uint32_t s_last, s_stop;
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_tile = ring + kStages * kStageBytes;
   uint8_t* p_tile = q_tile + kSmallTileBytes;
-  uint64_t* kv_full = reinterpret_cast<uint64_t*>(p_tile + kSmallTileBytes);
+  // two P tiles, alternating by chunk: the probabilities of chunk i are written while P*V of chunk i - 1 may still run
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(p_tile + 2 * kSmallTileBytes);
   uint64_t* kv_free = kv_full + kStages;
   uint64_t* s_full = kv_free + kStages;     // [2]
   uint64_t* s_free = s_full + 2;            // [2]
-  uint64_t* p_full = s_free + 2;
-  uint64_t* o_full = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* p_full = s_free + 2;            // [2]: the probabilities of chunk c are in P tile c & 1
+  uint64_t* o_full = p_full + 2;            // [2]: P*V of chunk c completes o_full[c & 1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
@@ -111,15 +114,17 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       tc::mbar_init(&s_full[i], 1);
       tc::mbar_init(&s_free[i], kSoftmaxThreads);
     }
-    tc::mbar_init(p_full, kSoftmaxThreads);
-    tc::mbar_init(o_full, 1);
+    tc::mbar_init(&p_full[0], kSoftmaxThreads);
+    tc::mbar_init(&p_full[1], kSoftmaxThreads);
+    tc::mbar_init(&o_full[0], 1);
+    tc::mbar_init(&o_full[1], 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_desc(&map_k);
     tc::tma_prefetch_desc(&map_v);
   }
   // Q and P tiles: zero everything (rows beyond the G real heads stay zero), then the query rows
-  for (int i = tid; i < 2 * kSmallTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < 3 * kSmallTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(q_tile)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   for (int i = tid; i < kG * kD; i += kThreads) {
     const int g = i / kD, d = i % kD;
@@ -173,14 +178,15 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                             tc::make_smem_desc_sw128(qbase + kb * (kNq * 128)) + (uint64_t)(ks * 2), a.idesc_s, (kb | ks) ? 1u : 0u);
         tc::umma_commit(&s_full[c & 1]);
       };
-      auto issue_pv = [&](int c) {       // O^T chunk = V chunk^T * P^T, 16 cache positions per instruction
+      auto issue_pv = [&](int c) {       // O^T (+)= V chunk^T * P^T, 16 cache positions per instruction
         const uint32_t vbase = tc::smem_u32(ring + (c % kStages) * kStageBytes + 2 * kHalfBytes);
-        const uint32_t pbase = tc::smem_u32(p_tile);
+        const uint32_t pbase = tc::smem_u32(p_tile + (c & 1) * kSmallTileBytes);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           tc::umma<false>(tmem_base + kColO, tc::make_smem_desc_mn_sw128(vbase + j * 2048, kHalfBytes),
-                          tc::make_smem_desc_sw128(pbase + (j >> 2) * (kNq * 128)) + (uint64_t)((j & 3) * 2), a.idesc_pv, j ? 1u : 0u);
-        tc::umma_commit(o_full);
+                          tc::make_smem_desc_sw128(pbase + (j >> 2) * (kNq * 128)) + (uint64_t)((j & 3) * 2), a.idesc_pv,
+                          (c | j) ? 1u : 0u);
+        tc::umma_commit(&o_full[c & 1]);
         tc::umma_commit(&kv_free[c % kStages]);
       };
       bool ok = true;
@@ -199,7 +205,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
           tc::fence_after_thread_sync();
           issue_scores(n);
         }
-        ok = tc::mbar_wait(p_full, i & 1, kWaitLimit, abort_flag);
+        ok = tc::mbar_wait(&p_full[i & 1], (i >> 1) & 1, kWaitLimit, abort_flag);
         if (!ok) break;
         tc::fence_after_thread_sync();
         issue_pv(i);
@@ -213,6 +219,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
   } else {
     // ---- softmax warps: thread t owns cache position t of the chunk and head-dimension index t of the output ----
+    // O^T accumulates in tensor memory over all chunks of the split (the P*V MMAs add to it), so a chunk costs the
+    // softmax warps one read of the scores and one write of the probabilities. A head's running maximum is raised
+    // - and its column of O^T rescaled in tensor memory - only when the new maximum exceeds it by more than
+    // kRescaleThreshold; until then the probabilities are taken against the older maximum (at most e^5, exact in
+    // the final O / l). The maxima are block-wide values, so every thread takes the same decision.
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     for (int i = 0; i < nchunks; ++i) {
       const int buf = i & 1;
@@ -229,7 +240,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int j = 0; j < 16; ++j) sv[j] = 0.f;
       }
       const bool live = s0 + i * kKeys + tid < s1;
-      float s[kG], corr[kG];
+      float s[kG];
 #pragma unroll
       for (int g = 0; g < kG; ++g) {
         s[g] = live ? sv[g] * a.scale : -FLT_MAX;
@@ -237,37 +248,64 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         if (lane == 0) wred[0][g][warp] = v;
       }
       tc::named_barrier_sync(1, kSoftmaxThreads);
+      float cmax[kG];
+      bool grow = false;
 #pragma unroll
       for (int g = 0; g < kG; ++g) {
-        const float cmax = fmaxf(fmaxf(wred[0][g][0], wred[0][g][1]), fmaxf(wred[0][g][2], wred[0][g][3]));
-        const float m_new = fmaxf(m_run[g], cmax);
-        corr[g] = __expf(m_run[g] - m_new);
-        const float p = live ? __expf(s[g] - m_new) : 0.f;
-        *reinterpret_cast<__nv_bfloat16*>(p_tile + small_tile_offset(g, tid)) = __float2bfloat16(p);
+        cmax[g] = fmaxf(fmaxf(wred[0][g][0], wred[0][g][1]), fmaxf(wred[0][g][2], wred[0][g][3]));
+        grow = grow || (cmax[g] - m_run[g] > kRescaleThreshold);
+      }
+      if (i == 0) {
+#pragma unroll
+        for (int g = 0; g < kG; ++g) m_run[g] = cmax[g];
+      } else {
+        // this chunk's P tile was last read by P*V of chunk i - 2
+        if (i >= 2 && !tc::mbar_wait(&o_full[i & 1], ((i - 2) >> 1) & 1, kWaitLimit, abort_flag)) fail();
+        if (grow) {
+          // O^T must be stable while it is rescaled: P*V of chunk i - 1 (and with it every earlier one) is complete
+          if (!tc::mbar_wait(&o_full[(i - 1) & 1], ((i - 1) >> 1) & 1, kWaitLimit, abort_flag)) fail();
+          tc::fence_after_thread_sync();
+          float ov[16];
+          tc::tmem_ld_16(lane_addr + kColO, ov);
+#pragma unroll
+          for (int g = 0; g < kG; ++g) {
+            if (cmax[g] - m_run[g] > kRescaleThreshold) {
+              const float f = __expf(m_run[g] - cmax[g]);
+              ov[g] *= f;
+              l_run[g] *= f;
+              m_run[g] = cmax[g];
+            }
+          }
+          tc::tmem_st_16(lane_addr + kColO, ov);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < kG; ++g) {
+        const float p = live ? __expf(s[g] - m_run[g]) : 0.f;
+        *reinterpret_cast<__nv_bfloat16*>(p_tile + buf * kSmallTileBytes + small_tile_offset(g, tid)) = __float2bfloat16(p);
         const float ps = warp_sum(p);
         if (lane == 0) wred[1][g][warp] = ps;
-        m_run[g] = m_new;
       }
-      tc::fence_proxy_async();        // P was written by threads and is read by the tensor core
-      tc::mbar_arrive(p_full);
+      tc::fence_proxy_async();          // P was written by threads and is read by the tensor core
+      tc::fence_before_thread_sync();   // orders the rescaled O^T (tcgen05.st) before the MMA that the arrival releases
+      tc::mbar_arrive(&p_full[buf]);
+      if (tid == 0) s_stop = *abort_flag;   // one thread samples the flag, so that all threads leave the loop together
       tc::named_barrier_sync(1, kSoftmaxThreads);
 #pragma unroll
-      for (int g = 0; g < kG; ++g)
-        l_run[g] = l_run[g] * corr[g] + (wred[1][g][0] + wred[1][g][1] + wred[1][g][2] + wred[1][g][3]);
+      for (int g = 0; g < kG; ++g) l_run[g] += wred[1][g][0] + wred[1][g][1] + wred[1][g][2] + wred[1][g][3];
+      if (s_stop) break;
+    }
+    if (nchunks > 0) {
       float ov[16];
-      ok = tc::mbar_wait(o_full, i & 1, kWaitLimit, abort_flag);
-      if (ok) {
+      if (!*abort_flag && tc::mbar_wait(&o_full[(nchunks - 1) & 1], ((nchunks - 1) >> 1) & 1, kWaitLimit, abort_flag)) {
         tc::fence_after_thread_sync();
         tc::tmem_ld_16(lane_addr + kColO, ov);
         tc::fence_before_thread_sync();
 #pragma unroll
-        for (int g = 0; g < kG; ++g) o[g] = o[g] * corr[g] + ov[g];
+        for (int g = 0; g < kG; ++g) o[g] = ov[g];
       } else {
         fail();
       }
-      // every flag raised in this iteration is visible after this barrier: all threads leave together
-      tc::named_barrier_sync(1, kSoftmaxThreads);
-      if (*abort_flag) break;
     }
     // ---- result: thread t holds output column t of the G heads ----
 #pragma unroll

@@ -187,23 +187,27 @@ gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
       const uint32_t lane_addr = pipe.tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
       for (int i = 0; i < kBN; ++i) acc[i] = 0.f;
+      // Scales of a K block: the weight scale of this thread's row block, and the kBN (<= 64) token scales held two
+      // per lane and handed round with shuffles; those of block i + 1 are requested before the wait for block i.
+      static_assert(kBN <= 64, "the promoting epilogue keeps the token scales of a K block in two registers per lane");
+      const float* ws_ptr = f.w_scale + (size_t)(x < p.hidden ? x / 128 : 0) * f.scale_kb;
+      const float* as_lo_ptr = f.a_scale + (size_t)min((int)blockIdx.y * kBN + lane, p.tokens - 1) * f.scale_kb;
+      const float* as_hi_ptr = f.a_scale + (size_t)min((int)blockIdx.y * kBN + 32 + lane, p.tokens - 1) * f.scale_kb;
+      float ws_next = nkb > 0 ? ws_ptr[kb0] : 0.f;
+      float lo_next = nkb > 0 ? as_lo_ptr[kb0] : 0.f;
+      float hi_next = (nkb > 0 && kBN > 32) ? as_hi_ptr[kb0] : 0.f;
       for (int i = 0; i < nkb && ok; ++i) {
         const int buf = i & 1;
-        ok = tc::mbar_wait(&pipe.acc_full[buf], (i >> 1) & 1, gemm_core::kWaitLimit, pipe.abort_flag);
+        const float ws = ws_next, as_lo = lo_next, as_hi = hi_next;
+        if (i + 1 < nkb) {
+          ws_next = ws_ptr[kb0 + i + 1];
+          lo_next = as_lo_ptr[kb0 + i + 1];
+          if (kBN > 32) hi_next = as_hi_ptr[kb0 + i + 1];
+        }
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(&pipe.acc_full[buf], (i >> 1) & 1, gemm_core::kWaitLimit, pipe.abort_flag));
         if (!ok) break;
         tc::fence_after_thread_sync();
-        const int kb = kb0 + i;
-        const float ws = f.w_scale[(size_t)(x < p.hidden ? x / 128 : 0) * f.scale_kb + kb];
-#pragma unroll
-        for (int c = 0; c < kBN; c += 16) {
-          float v[16];
-          tc::tmem_ld_16(lane_addr + buf * kBN + c, v);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = min((int)blockIdx.y * kBN + c + j, p.tokens - 1);
-            acc[c + j] = fmaf(v[j], ws * f.a_scale[(size_t)t * f.scale_kb + kb], acc[c + j]);
-          }
-        }
+        gemm_core::promote_block<kBN>(lane_addr + buf * kBN, ws, as_lo, as_hi, acc);
         tc::fence_before_thread_sync();
         tc::mbar_arrive(&pipe.acc_empty[buf]);
       }

@@ -114,24 +114,30 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if constexpr (kScaled) {
 #pragma unroll
       for (int i = 0; i < kBN; ++i) acc[i] = 0.f;
+      // Scales of a K block: one per thread for its X row, and the kBN (<= 64) column scales held two per lane
+      // and handed round with shuffles. Those of block i + 1 are requested before the wait for block i's partial
+      // product, so their latency hides behind the MMAs instead of sitting in front of every multiply-add.
+      static_assert(kBN <= 64, "the promoting epilogue keeps the column scales of a K block in two registers per lane");
+      const float* xs_ptr = a.x_scale + (size_t)(a.x_scale_per_row ? min(x, a.x_rows - 1) : (x < a.x_rows ? x / 128 : 0)) * a.scale_kb;
+      const int y_lo = min(y_base + lane, a.y_rows - 1), y_hi = min(y_base + 32 + lane, a.y_rows - 1);
+      const float* ys_lo_ptr = a.y_scale + (size_t)(a.y_scale_per_row ? y_lo : y_lo / 128) * a.scale_kb;
+      const float* ys_hi_ptr = a.y_scale + (size_t)(a.y_scale_per_row ? y_hi : y_hi / 128) * a.scale_kb;
+      float xs_next = nkb > 0 ? xs_ptr[kb0] : 0.f;
+      float lo_next = nkb > 0 ? ys_lo_ptr[kb0] : 0.f;
+      float hi_next = (nkb > 0 && kBN > 32) ? ys_hi_ptr[kb0] : 0.f;
       for (int i = 0; i < nkb && ok; ++i) {
         const int buf = i & 1;
-        ok = tc::mbar_wait(&acc_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag);
+        const float xs = xs_next, ys_lo = lo_next, ys_hi = hi_next;
+        if (i + 1 < nkb) {
+          xs_next = xs_ptr[kb0 + i + 1];
+          lo_next = ys_lo_ptr[kb0 + i + 1];
+          if (kBN > 32) hi_next = ys_hi_ptr[kb0 + i + 1];
+        }
+        // (the shuffles below are warp-wide: the warp gives up as a whole)
+        ok = __all_sync(0xffffffffu, tc::mbar_wait(&acc_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag));
         if (!ok) break;
         tc::fence_after_thread_sync();
-        const int kb = kb0 + i;
-        const float xs = a.x_scale[(size_t)(a.x_scale_per_row ? min(x, a.x_rows - 1) : (x < a.x_rows ? x / 128 : 0)) * a.scale_kb + kb];
-#pragma unroll
-        for (int c = 0; c < kBN; c += 16) {
-          float v[16];
-          tc::tmem_ld_16(lane_addr + buf * kBN + c, v);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int y = min(y_base + c + j, a.y_rows - 1);
-            const float ys = a.y_scale[(size_t)(a.y_scale_per_row ? y : y / 128) * a.scale_kb + kb];
-            acc[c + j] = fmaf(v[j], xs * ys, acc[c + j]);
-          }
-        }
+        gemm_core::promote_block<kBN>(lane_addr + buf * kBN, xs, ys_lo, ys_hi, acc);
         tc::fence_before_thread_sync();
         tc::mbar_arrive(&acc_empty[buf]);
       }

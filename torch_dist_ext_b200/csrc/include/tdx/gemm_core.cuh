@@ -55,6 +55,31 @@ __device__ __forceinline__ void store_chunk(const Args& a, int x, int y0, const 
   }
 }
 
+// Block-scale promotion of one K block: acc[j] += partial[j] * xs * ys[j] for the kBN (<= 64) columns of this
+// thread's row. The partial products are fetched from tensor memory with ONE load (one round trip per K block);
+// the column scales sit two per lane (`ys_lo`: columns 0-31, `ys_hi`: 32-63) and are handed round by shuffles.
+// Warp-wide: every lane of the warp calls it.
+template <int kBN>
+__device__ __forceinline__ void promote_block(uint32_t taddr, float xs, float ys_lo, float ys_hi, float (&acc)[kBN]) {
+  static_assert(kBN == 16 || kBN == 32 || kBN == 64, "promotion handles 16, 32 or 64 columns");
+  uint32_t v[kBN];
+  if constexpr (kBN == 64) {
+    tc::tmem_ld_x64(taddr, v);
+  } else if constexpr (kBN == 32) {
+    tc::tmem_ld_x32(taddr, v);
+  } else {
+    float f[16];
+    tc::tmem_ld_16(taddr, f);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(f[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < kBN; ++j) {
+    const float ys = __shfl_sync(0xffffffffu, j < 32 ? ys_lo : ys_hi, j & 31);
+    acc[j] = fmaf(__uint_as_float(v[j]), xs * ys, acc[j]);
+  }
+}
+
 template <int kBN, int kStages>
 struct SmemLayout {
   static constexpr int kXBytes = kBM * kSwizzleBytes;

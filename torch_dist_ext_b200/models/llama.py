@@ -64,6 +64,18 @@ class LlamaConfig:
         return LlamaConfig(**base)
 
     @staticmethod
+    def shard_of(cfg: "LlamaConfig", tp: int, **kw) -> "LlamaConfig":
+        """What ONE rank of a ``tp``-way tensor-parallel ``cfg`` computes, as a single-rank model: the same GEMM,
+        attention and elementwise shapes per layer (heads and FFN divided by ``tp``, at least one KV head), with
+        the collectives reduced to their local tail. For single-GPU launch lists and kernel timing of the
+        tensor-parallel layer."""
+        base = dict(hidden=cfg.hidden, n_heads=cfg.n_heads // tp, n_kv_heads=max(1, cfg.n_kv_heads // tp), ffn=cfg.ffn // tp,
+                    n_layers=cfg.n_layers, vocab=cfg.vocab // tp, rope_theta=cfg.rope_theta, eps=cfg.eps,
+                    head_dim=cfg.head_dim, fp8=cfg.fp8)
+        base.update(kw)
+        return LlamaConfig(**base)
+
+    @staticmethod
     def tiny(**kw) -> "LlamaConfig":
         base = dict(hidden=512, n_heads=8, n_kv_heads=8, ffn=1024, n_layers=2, vocab=1024)
         base.update(kw)
