@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Single-GPU roofline table of the library's kernels (no communication).
 
-    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_pair|gemm_persist|gemm_fp8|attention|attention_tc|attention_prefill_tc|elementwise|all] [--steps 30]
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_one_tile|gemm_pair|gemm_persist|gemm_fp8|attention|attention_simt|attention_prefill_tc|elementwise|all] [--steps 30]
 
 Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
 over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
@@ -104,7 +104,7 @@ def gemm_fp8_cases(dev, steps, out):
         torch.cuda.empty_cache()
 
 
-def attention_cases(dev, steps, out, tensor_cores=False):
+def attention_cases(dev, steps, out, tensor_cores=True):
     from torch_dist_ext_b200.ops import attention
 
     hbm, tf, src = peaks()
@@ -138,7 +138,7 @@ def attention_cases(dev, steps, out, tensor_cores=False):
 
 
 def prefill_attention_cases(dev, steps, out):
-    """Causal attention over one prompt: this library's tcgen05 kernel against PyTorch's SDPA (opt-in kernel)."""
+    """Causal attention over one prompt: this library's tcgen05 kernel against PyTorch's SDPA."""
     from torch_dist_ext_b200.ops import attention
 
     hbm, tf, src = peaks()
@@ -223,11 +223,11 @@ def main():
         gemm_cases(dev, max(5, args.steps // 3), [(28672, 4096), (4096, 14336)], (2048, 8192), out, persistent=True)
     if g in ("gemm_fp8", "all"):
         gemm_fp8_cases(dev, args.steps, out)
-    if g in ("attention", "all"):
-        attention_cases(dev, args.steps, out)
-    if g == "attention_tc":         # opt-in kernel (not part of "all")
+    if g in ("attention", "attention_tc", "all"):   # the tcgen05 decode kernel (the library's default)
         attention_cases(dev, args.steps, out, tensor_cores=True)
-    if g == "attention_prefill_tc":  # opt-in kernel (not part of "all")
+    if g == "attention_simt":       # the SIMT decode kernel (TDX_ATTN_TC=0), for comparison
+        attention_cases(dev, args.steps, out, tensor_cores=False)
+    if g in ("attention_prefill_tc", "all"):
         prefill_attention_cases(dev, max(5, args.steps // 3), out)
     if g in ("elementwise", "all"):
         elementwise_cases(dev, args.steps, out)

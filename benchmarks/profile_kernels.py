@@ -58,9 +58,9 @@ def main():
         r = torch.randn(16, 4096, device=dev, dtype=torch.bfloat16)
         g = torch.ones(4096, device=dev, dtype=torch.bfloat16)
         fn = lambda: fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6)
-    elif args.kernel == "ag_gemm":       # gate_up-shaped: 16 tokens, [28672, 4096]
+    elif args.kernel == "ag_gemm":       # 16 tokens, [14336, 4096] (117 MB; 112 tiles, all resident as the kernel needs)
         x = torch.randn(16, 4096, device=dev, dtype=torch.bfloat16)
-        w = torch.randn(28672, 4096, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(14336, 4096, device=dev, dtype=torch.bfloat16)
         fn = lambda: fused_gemm.allgather_gemm(x, w, 16)
     elif args.kernel == "gemm_prefill":  # the persistent CTA-pair kernel where it is compute-bound: 2048 x 8192 x 8192 bf16
         a = torch.randn(2048, 8192, device=dev, dtype=torch.bfloat16)

@@ -36,3 +36,21 @@ def test_pair_gemm_fp8_unscaled():
     assert gemm.pipeline_status() == 0
     ref = a.float() @ w.float().t()
     assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(2304, 2560, 512), (2304, 2560, 2048), (2100, 2500, 1024), (2048, 3584, 1024)])
+def test_partly_filled_last_round_is_split_along_k(m, n, k):
+    """More tiles than CTA pairs with a remainder: the tail tiles are cut along K, summed in the fp32 scratch and
+    finished by the last arriver. Two calls in a row: the second finds scratch and counters as the first left them."""
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    for _ in range(2):
+        out = gemm.linear(a, w, cta_pair=True)
+        torch.cuda.synchronize()
+        assert gemm.pipeline_status() == 0
+        err = (out.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 1e-2, err
+    ws, counters, _ = gemm._workspace(a.device)
+    assert int(counters.abs().sum()) == 0 and float(ws.abs().max()) == 0.0

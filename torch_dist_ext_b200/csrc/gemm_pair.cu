@@ -9,7 +9,9 @@
 // split by rows: rows 0-127 in the leader's tensor memory, rows 128-255 in the peer's.
 //
 // The grid is persistent: pair p walks the tiles p, p + pairs, ... (the x tile index runs fastest, so pairs that
-// work side by side share the Y tile in L2). The operand ring keeps streaming across tile boundaries and the
+// work side by side share the Y tile in L2). When the last round would be partly filled, its tiles are cut along K
+// into 2-4 pieces, one piece per pair, summed in an fp32 scratch tile with red.global.add and finished by the CTA
+// that arrives last at its half of the tile - the idle pairs of the last round then share its work. The operand ring keeps streaming across tile boundaries and the
 // accumulator is double-buffered in tensor memory (2 x 256 columns in each CTA): while the epilogue warps of both
 // CTAs read tile n back with tcgen05.ld and store it, the leader is already accumulating tile n + 1.
 //
@@ -63,12 +65,41 @@ constexpr uint32_t kWaitLimit = 1u << 22;
 struct PairArgs {
   int x_rows, y_rows, kblocks;
   int tiles_x, tiles_y;
+  // Tail split: the tiles of the last, partly filled round (tail_first ...) are cut along K into tail_parts pieces of
+  // tail_kb K blocks each, one piece per pair, and summed through an fp32 scratch tile (0 parts: no split).
+  int tail_first, tail_parts, tail_kb;
+  float* ws;               // [tail tiles][256 columns][256 rows] fp32, zero on entry and on exit
+  uint32_t* counters;      // [tail tiles][2 CTAs of the pair], zero on entry and on exit
   void* out;
   int64_t sx, sy;
   int out_dtype;
   uint32_t idesc;
   uint32_t* status;
 };
+
+// The n-th piece of work of pair `pair`: a whole tile (full rounds: tiles pair, pair + pairs, ...) or, in the split
+// tail, one K range of a tail tile. Every role of both CTAs walks the same sequence.
+struct WorkItem {
+  int tile, kb0, kb1;
+  bool partial;
+};
+__device__ __forceinline__ bool work_item(const PairArgs& a, int pair, int npairs, int n, WorkItem* w) {
+  const int ntiles = a.tiles_x * a.tiles_y;
+  const int full_rounds = a.tail_parts > 1 ? a.tail_first / npairs : 0x7fffffff;   // tail_first is a multiple of npairs
+  if (n < full_rounds) {
+    const int t = pair + n * npairs;
+    if (t >= ntiles) return false;
+    *w = WorkItem{t, 0, a.kblocks, false};
+    return true;
+  }
+  // split tail: unit u covers part u % parts of tail tile u / parts; a pair may get several units
+  const int u = pair + (n - full_rounds) * npairs;
+  const int tile = a.tail_first + u / a.tail_parts, part = u % a.tail_parts;
+  if (tile >= ntiles) return false;
+  const int kb0 = part * a.tail_kb, kb1 = min(a.kblocks, kb0 + a.tail_kb);
+  *w = WorkItem{tile, kb0, kb1, true};
+  return true;
+}
 
 template <bool kFp8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -84,12 +115,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   uint64_t* acc_empty = acc_full + 2;        // [2], used in the leader
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint32_t* last_flag = tmem_slot + 2;       // tail split: "this CTA arrived last at its half of the tile"
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = tc::cluster_ctarank();      // 0: leader, 1: peer
   const uint32_t leader = rank & ~1u, other = rank ^ 1u;
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int ntiles = a.tiles_x * a.tiles_y;
   const int nkb = a.kblocks;
 
   if (threadIdx.x == 0) {
@@ -133,10 +164,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint32_t leader_full = tc::map_to_cta(tc::smem_u32(&full[0]), leader);
       uint32_t it = 0;                                   // K blocks issued so far by this CTA
       bool ok = true;
-      for (int t = pair; t < ntiles && ok && !*abort_flag; t += npairs) {
+      WorkItem w;
+      for (int n = 0; work_item(a, pair, npairs, n, &w) && ok && !*abort_flag; ++n) {
+        const int t = w.tile;
         const int x_row0 = (t % a.tiles_x) * kTileM + (int)(rank & 1u) * kRowsPerCta;
         const int y_row0 = (t / a.tiles_x) * kTileN + (int)(rank & 1u) * kRowsPerCta;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t s = it % kStages;
           if (it >= (uint32_t)kStages && !tc::mbar_wait(&empty[s], ((it / kStages) - 1) & 1, kWaitLimit, abort_flag)) {
             ok = false;
@@ -157,14 +190,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       uint32_t it = 0;
       int n = 0;                                         // tiles started so far by this pair
       bool ok = true;
-      for (int t = pair; t < ntiles && ok; t += npairs, ++n) {
+      WorkItem w;
+      for (; work_item(a, pair, npairs, n, &w) && ok; ++n) {
         const uint32_t buf = n & 1;
         if (n >= 2 && !tc::mbar_wait(&acc_empty[buf], ((n >> 1) - 1) & 1, kWaitLimit, abort_flag)) {
           ok = false;
           break;
         }
         tc::fence_after_thread_sync();
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t s = it % kStages;
           if (!tc::mbar_wait(&full[s], (it / kStages) & 1, kWaitLimit, abort_flag)) {
             ok = false;
@@ -177,7 +211,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
           for (int k = 0; k < 4; ++k)   // 32 bytes of K per instruction, stepped inside the swizzle span
             tc::umma_pair<kFp8>(tmem_base + buf * kTileN, dx + (uint64_t)(k * 2), dy + (uint64_t)(k * 2), a.idesc,
-                                (kb > 0 || k > 0) ? 1u : 0u);
+                                (kb > w.kb0 || k > 0) ? 1u : 0u);
           tc::umma_commit_pair(&empty[s], other);   // the stage is free again in both CTAs
         }
         if (ok) tc::umma_commit_pair(&acc_full[buf], other);
@@ -190,7 +224,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const uint32_t leader_acc_empty = tc::map_to_cta(tc::smem_u32(&acc_empty[0]), leader);
     int n = 0;
-    for (int t = pair; t < ntiles; t += npairs, ++n) {
+    WorkItem w;
+    for (; work_item(a, pair, npairs, n, &w); ++n) {
+      const int t = w.tile;
       const uint32_t buf = n & 1;
       const int x = (t % a.tiles_x) * kTileM + (int)(rank & 1u) * kRowsPerCta + q * 32 + lane;
       const int y_base = (t / a.tiles_x) * kTileN;
@@ -200,15 +236,54 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         break;
       }
       tc::fence_after_thread_sync();
+      if (!w.partial) {
 #pragma unroll 4
-      for (int c = 0; c < kTileN; c += 16) {
-        float v[16];
-        tc::tmem_ld_16(lane_addr + buf * kTileN + c, v);
-        if (y_base + c < a.y_rows) store_chunk(a, x, y_base + c, v);
+        for (int c = 0; c < kTileN; c += 16) {
+          float v[16];
+          tc::tmem_ld_16(lane_addr + buf * kTileN + c, v);
+          if (y_base + c < a.y_rows) store_chunk(a, x, y_base + c, v);
+        }
+        tc::fence_before_thread_sync();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive_cluster(leader_acc_empty + buf * 8u);   // this warp has read its part of the buffer
+      } else {
+        // A K range of a tail tile: add this CTA's 128 x 256 partial sums to the tile's fp32 scratch (column-major,
+        // so that a warp's lanes add to 32 consecutive floats), then the CTA that arrives last at its half of the
+        // tile turns the sums into the output and leaves scratch and counter zeroed for the next call.
+        const int rem = t - a.tail_first, half = (int)(rank & 1u);
+        float* tile_ws = a.ws + (size_t)rem * (kTileM * kTileN) + half * kRowsPerCta + q * 32 + lane;
+#pragma unroll 4
+        for (int c = 0; c < kTileN; c += 16) {
+          float v[16];
+          tc::tmem_ld_16(lane_addr + buf * kTileN + c, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) atomicAdd(tile_ws + (size_t)(c + j) * kTileM, v[j]);
+        }
+        tc::fence_before_thread_sync();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive_cluster(leader_acc_empty + buf * 8u);
+        __threadfence();
+        tc::named_barrier_sync(1, 128);
+        if (threadIdx.x == 64) {
+          const uint32_t prev = atomicAdd(&a.counters[rem * 2 + half], 1u);
+          *last_flag = (prev == (uint32_t)a.tail_parts - 1u) ? 1u : 0u;        // every piece is non-empty (host)
+        }
+        tc::named_barrier_sync(1, 128);
+        if (*last_flag) {
+          __threadfence();
+#pragma unroll 2
+          for (int c = 0; c < kTileN; c += 16) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              v[j] = __ldcg(tile_ws + (size_t)(c + j) * kTileM);
+              __stcg(tile_ws + (size_t)(c + j) * kTileM, 0.f);
+            }
+            if (y_base + c < a.y_rows) store_chunk(a, x, y_base + c, v);
+          }
+          if (threadIdx.x == 64) a.counters[rem * 2 + half] = 0;
+        }
       }
-      tc::fence_before_thread_sync();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive_cluster(leader_acc_empty + buf * 8u);   // this warp has read its part of the buffer
     }
   }
 
@@ -268,6 +343,33 @@ std::string gemm_tn_pair(const GemmProblem& g, cudaStream_t stream) {
   const long long ntiles = (long long)a.tiles_x * a.tiles_y;
   const int pairs = (int)(ntiles < sms / 2 ? ntiles : sms / 2);
   const dim3 grid(2 * pairs, 1, 1);
+  // Tail split: when the last round is partly filled, its tiles are cut along K into `parts` pieces so that the idle
+  // pairs share the work; the pieces meet in an fp32 scratch tile. parts minimises ceil(tail * parts / pairs) / parts
+  // (the time of the tail in tile-times) with a small charge per extra piece for the scratch traffic.
+  a.tail_first = (int)ntiles;
+  a.tail_parts = 0;
+  const int tail = (int)(ntiles % pairs);
+  if (tail > 0 && ntiles > pairs && g.ws != nullptr && g.counters != nullptr &&
+      (size_t)tail * kTileM * kTileN * sizeof(float) <= g.ws_bytes && (size_t)tail * 2 <= g.counter_count) {
+    int best = 1;
+    double best_cost = 1.0;
+    for (int parts = 2; parts <= 4 && a.kblocks / parts >= 4; ++parts) {
+      const double cost = (double)((tail * parts + pairs - 1) / pairs) / parts + 0.04 * (parts - 1);
+      if (cost < best_cost - 1e-9) {
+        best_cost = cost;
+        best = parts;
+      }
+    }
+    if (best > 1) {
+      a.tail_kb = (a.kblocks + best - 1) / best;
+      if ((best - 1) * a.tail_kb < a.kblocks) {      // every piece non-empty
+        a.tail_first = (int)(ntiles - tail);
+        a.tail_parts = best;
+        a.ws = g.ws;
+        a.counters = g.counters;
+      }
+    }
+  }
   return fp8 ? launch<true>(mx, my, a, grid, stream) : launch<false>(mx, my, a, grid, stream);
 }
 

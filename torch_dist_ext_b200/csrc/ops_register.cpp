@@ -185,8 +185,17 @@ void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t s
 }
 
 // The same product on 256 x 256 tiles computed by CTA pairs (tcgen05.mma.cta_group::2).
-void gemm_tn_pair(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, const c10::optional<Tensor>& status) {
+void gemm_tn_pair(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t sy, const c10::optional<Tensor>& status,
+                  const c10::optional<Tensor>& ws, const c10::optional<Tensor>& counters) {
   tdx::GemmProblem g = gemm_problem(x, y, out, sx, sy, status);
+  if (ws.has_value() && ws->defined() && counters.has_value() && counters->defined()) {
+    TORCH_CHECK(ws->scalar_type() == at::kFloat && counters->scalar_type() == at::kInt && ws->is_cuda() && counters->is_cuda(),
+                "gemm_tn_pair: scratch must be float32 / int32 CUDA tensors");
+    g.ws = ws->data_ptr<float>();
+    g.ws_bytes = (size_t)ws->numel() * 4;
+    g.counters = reinterpret_cast<uint32_t*>(counters->data_ptr<int>());
+    g.counter_count = (size_t)counters->numel();
+  }
   const c10::cuda::CUDAGuard guard(x.device());
   const std::string err = tdx::gemm_tn_pair(g, cur_stream());
   TORCH_CHECK(err.empty(), "gemm_tn_pair: ", err);
@@ -380,7 +389,8 @@ void register_extra_ops(torch::Library& m) {
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
         "bool y_scale_per_row, bool x_static=False) -> ()", &gemm_tn);
-  m.def("gemm_tn_pair(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_pair);
+  m.def("gemm_tn_pair(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status, Tensor(c!)? ws=None, "
+        "Tensor(d!)? counters=None) -> ()", &gemm_tn_pair);
   m.def("gemm_tn_persistent(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_persistent);
   m.def("fused_add_rmsnorm(Tensor x, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
         "Tensor(c!)? scale_out, float eps, int out_mode) -> int", &fused_add_rmsnorm);

@@ -86,7 +86,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         if out is None:
             dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
             out = torch.empty(m, n, dtype=dt, device=a.device)
-        _lib.ops().gemm_tn_pair(a, w, out, n, 1, _workspace(a.device)[2])
+        ws, counters, status = _workspace(a.device)
+        _lib.ops().gemm_tn_pair(a, w, out, n, 1, status, ws, counters)   # scratch: K-split of a partly filled last round
         return out
     if (use_persistent or (use_pair and persistent is None and _PERSIST_DEFAULT)) and m > 128 and n >= 256 and not swap \
             and splits in (None, 1):
