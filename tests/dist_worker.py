@@ -86,6 +86,19 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
                 torch.cuda.synchronize()
                 tdx.check_status()
                 assert torch.equal(p_res, res.cpu()) and torch.equal(p_norm, norm.cpu()), f"case {i}: pinned-memory path differs on rank {rank}"
+        # greedy sampling over a sharded vocabulary: the candidates are gathered by the fused all-reduce itself
+        from torch_dist_ext_b200.ops import sampling
+        g = torch.Generator().manual_seed(4242)
+        full = torch.randn(33, world * 1000, generator=g)
+        full[5, 17] = full[5, world * 1000 - 3] = 9.0          # equal logits in the first and the last shard: the lower index wins
+        want = full.argmax(dim=-1)
+        want[5] = 17
+        mine = full[:, rank * 1000:(rank + 1) * 1000].contiguous().to(dev)
+        got = sampling.greedy_sample_sharded(mine, rank, world, rank * 1000)
+        if cuda:
+            torch.cuda.synchronize()
+            tdx.check_status()
+        assert torch.equal(got.cpu(), want), f"sharded greedy sampling differs on rank {rank}"
         st = tdx.stats()
         if cuda:
             assert st["error_count"] == 0

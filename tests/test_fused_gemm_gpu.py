@@ -96,11 +96,46 @@ def test_allgather_gemm_world1(tokens, n_out, k):
     assert gemm.pipeline_status() == 0
 
 
-def test_large_token_counts_take_the_unfused_route():
-    a = torch.randn(4096, 256, device="cuda", dtype=torch.bfloat16)
-    w = (torch.randn(1024, 256, device="cuda") * 0.05).to(torch.bfloat16)
-    r = torch.randn(4096, 1024, device="cuda", dtype=torch.bfloat16)
-    g = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
-    norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6)
+def _standalone_allreduce_calls():
+    from torch_dist_ext_b200.parallel import comm
+    return sum(comm.get_comm().algo_counts.values())
+
+
+@pytest.mark.parametrize("tokens,hidden,k", [(2048, 4096, 512), (4096, 1024, 256), (1000, 4096, 1792), (300, 8192, 1024),
+                                             (2049, 2048, 64)])
+@pytest.mark.parametrize("out_mode", [OUT_SAME, OUT_FP8_BLOCK128])
+def test_prompt_sized_token_counts_stay_fused(tokens, hidden, k, out_mode):
+    """More tiles than SMs: the persistent kernel walks them and still ends in the reduce / normalise tail; no
+    standalone all-reduce launch is involved."""
+    a = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(hidden, k, device="cuda") * 0.05).to(torch.bfloat16)
+    r = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(hidden, device="cuda")).to(torch.bfloat16)
+    before = _standalone_allreduce_calls()
+    for _ in range(3):   # repeated calls walk through the three Lamport buffers
+        norm, res, scales = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6, out_mode=out_mode)
+    assert _standalone_allreduce_calls() == before, "the call fell back to GEMM + all-reduce"
     e_norm, e_res, _ = oracle(a, w, r, g, 1e-6)
+    assert (res.float() - e_res.float()).abs().max().item() <= 0.07
+    if out_mode == OUT_SAME:
+        assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07
+    else:
+        back = ref.dequantize_fp8(norm, scales)
+        assert (back - e_norm.float()).abs().max().item() <= e_norm.float().abs().max().item() * 2.0 ** -3
+    tdx.check_status()
+    assert gemm.pipeline_status() == 0
+    # a decode-sized call afterwards finds the communication state intact
+    n2, r2, _ = fused_gemm.gemm_allreduce_rms(a[:16], w, r[:16], g, 1e-6)
+    assert (r2.float() - e_res[:16].float()).abs().max().item() <= 0.07
+
+
+def test_messages_beyond_the_lamport_buffers_take_the_unfused_route():
+    tokens, hidden, k = 8192, 4096, 64                                    # 64 MiB of partial sums
+    a = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(hidden, k, device="cuda") * 0.05).to(torch.bfloat16)
+    g = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
+    before = _standalone_allreduce_calls()
+    norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, None, g, 1e-6)
+    assert _standalone_allreduce_calls() == before + 1
+    e_norm, e_res, _ = oracle(a, w, None, g, 1e-6)
     assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07

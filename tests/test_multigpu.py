@@ -52,5 +52,6 @@ def test_gemm_fused_with_collectives_across_processes(world):
     from dist_worker_gemm import worker as gemm_worker
 
     cases = [(1, 4096, 4096, False), (16, 4096, 4096, False), (64, 8192, 8192, False), (33, 2048, 1024, False),
-             (16, 4096, 4096, True), (61, 2048, 2048, True)]
+             (16, 4096, 4096, True), (61, 2048, 2048, True),
+             (600, 2048, 1024, False), (601, 2048, 1024, True)]      # more tiles than SMs: the persistent fused kernel
     run_world(world, "nccl", cases, target=gemm_worker)

@@ -522,10 +522,11 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
     assert all(x == list(range(nchunks)) for x in seen)
 
 
-@pytest.mark.parametrize("nchunks", [1, 2, 3, 4, 5, 7, 16])
-def test_prefill_attention_pipeline(nchunks):
-    for seed in range(60):
-        prefill_attention(nchunks, 2, 3, random.Random(seed))
+@pytest.mark.parametrize("stages_v", [2, 3])
+@pytest.mark.parametrize("nchunks", [1, 2, 3, 4, 5, 7, 16, 32])
+def test_prefill_attention_pipeline(nchunks, stages_v):
+    for seed in range(40):
+        prefill_attention(nchunks, 2, stages_v, random.Random(seed))
 
 
 # ---- persistent CTA-pair GEMM: tile loop and accumulator hand-back ------------------------------------------

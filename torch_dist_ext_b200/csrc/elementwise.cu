@@ -212,6 +212,85 @@ int grid_for(size_t work_items, int threads, int max_blocks = 148 * 8) {
     default: return "unsupported dtype";                                  \
   }
 
+// Greedy sampling over a vocabulary that is sharded across ranks. One block per token: the largest logit of this
+// rank's slice and its index in the whole vocabulary go into slot `rank` of the token's row of `pack`
+// [tokens, 4 * nranks] fp32 as {value, index, 0, 0}; the other ranks' slots of the row are set to zero, so that the
+// SUM of `pack` over the ranks (one call of the fused all-reduce) is the gather of every rank's candidate. Indices
+// stay exact in fp32 up to 2^24. Of equal logits the lowest index wins; a NaN never wins.
+__global__ void __launch_bounds__(256) argmax_pack_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
+                                                          int index_base, int rank, int nranks, float* __restrict__ pack) {
+  ptx::pdl_wait();
+  ptx::pdl_launch_dependents();
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+  const int t = blockIdx.x;
+  const float* row = logits + (int64_t)t * ld;
+  float best = -INFINITY;
+  int at = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) { best = v; at = i; }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, at, off);
+    if (ov > best || (ov == best && oi < at)) { best = ov; at = oi; }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { s_val[warp] = best; s_idx[warp] = at; }
+  __syncthreads();
+  if (threadIdx.x < 4 * nranks) {
+    float out = 0.f;
+    const int slot = threadIdx.x >> 2, word = threadIdx.x & 3;
+    if (slot == rank && word < 2) {
+      best = s_val[0];
+      at = s_idx[0];
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+        if (s_val[w] > best || (s_val[w] == best && s_idx[w] < at)) { best = s_val[w]; at = s_idx[w]; }
+      if (at == 0x7fffffff) at = 0;   // a row of NaN or -inf: a valid index all the same
+      out = word == 0 ? best : float(index_base + at);
+    }
+    pack[(int64_t)t * 4 * nranks + threadIdx.x] = out;
+  }
+}
+
+// The winner among the ranks' candidates: gathered [tokens, 4 * nranks] fp32 -> token ids int64 [tokens].
+__global__ void __launch_bounds__(128) select_token_kernel(const float* __restrict__ gathered, int tokens, int nranks,
+                                                           int64_t* __restrict__ out) {
+  ptx::pdl_wait();
+  ptx::pdl_launch_dependents();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  const float4* row = reinterpret_cast<const float4*>(gathered) + (int64_t)t * nranks;
+  float best = row[0].x;
+  float at = row[0].y;
+  for (int r = 1; r < nranks; ++r) {
+    const float4 c = row[r];
+    if (c.x > best || (c.x == best && c.y < at)) { best = c.x; at = c.y; }
+  }
+  out[t] = (int64_t)at;
+}
+
+std::string argmax_pack(const float* logits, int64_t ld, int tokens, int vocab, int index_base, int rank, int nranks,
+                        float* pack, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxRanks || rank < 0 || rank >= nranks) return "rank / nranks out of range";
+  if (vocab < 1 || (int64_t)index_base + vocab > (1 << 24)) return "vocabulary indices must stay below 2^24";
+  if (tokens == 0) return "";
+  launch_chained(argmax_pack_kernel, dim3(tokens), dim3(256), 0, stream, logits, ld, vocab, index_base, rank, nranks, pack);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : cudaGetErrorString(e);
+}
+
+std::string select_token(const float* gathered, int tokens, int nranks, int64_t* out, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxRanks) return "nranks out of range";
+  if (reinterpret_cast<uintptr_t>(gathered) & 15u) return "candidates must be 16-byte aligned";
+  if (tokens == 0) return "";
+  launch_chained(select_token_kernel, dim3((tokens + 127) / 128), dim3(128), 0, stream, gathered, tokens, nranks, out);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? "" : cudaGetErrorString(e);
+}
+
 std::string quant_fp8(const void* x, void* q, float* scales, int rows, int cols, int dtype, bool block128,
                       cudaStream_t stream) {
   const int vec = dtype == kF32 ? 4 : 8;

@@ -16,7 +16,8 @@
 //                    ever reads a peer's memory, and none uses cluster multicast.
 //
 // Both need all CTAs of the grid to be resident at once (CTAs wait for data produced by others), so
-// the host refuses grids larger than the SM count.
+// the host refuses grids larger than the SM count; for gemm_ar_rmsnorm with bf16 operands the persistent kernel
+// of gemm_fused_persist.cu takes over there.
 //
 // The reference has neither (its only kernel is the standalone all-reduce+RMSNorm,
 // src/common/all_reduce_fusion_impl.h:342-474); these are the two paths that a tensor-parallel
@@ -501,6 +502,10 @@ std::string ag_gemm(const AgGemmProblem& g, cudaStream_t stream) {
 }
 
 std::string gemm_ar_rmsnorm(const FusedGemmProblem& g, cudaStream_t stream) {
+  // one CTA per tile only while all of them are resident; beyond that the persistent kernel walks the tiles
+  const int bn = g.ar.tokens <= 16 ? 16 : 64;
+  if (g.elem_size == 2 && (long long)(g.ar.hidden / 128) * ((g.ar.tokens + bn - 1) / bn) > sm_count())
+    return gemm_ar_rmsnorm_persist(g, stream);
   switch (g.ar.nranks) {
     case 2: return gemm_ar_rmsnorm_n2(g, stream);
     case 4: return gemm_ar_rmsnorm_n4(g, stream);

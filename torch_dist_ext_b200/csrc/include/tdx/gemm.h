@@ -68,6 +68,10 @@ std::string gemm_ar_rmsnorm_n0(const FusedGemmProblem& g, cudaStream_t stream);
 std::string gemm_ar_rmsnorm_n2(const FusedGemmProblem& g, cudaStream_t stream);
 std::string gemm_ar_rmsnorm_n4(const FusedGemmProblem& g, cudaStream_t stream);
 std::string gemm_ar_rmsnorm_n8(const FusedGemmProblem& g, cudaStream_t stream);
+// The same step for token counts whose tiles outnumber the SMs (gemm_fused_persist.cu): one CTA per SM walks the
+// tiles and joins the reduce / normalise tail after its last one; bf16 operands. gemm_ar_rmsnorm hands over to it
+// by itself.
+std::string gemm_ar_rmsnorm_persist(const FusedGemmProblem& g, cudaStream_t stream);
 
 // All-gather of sequence-parallel activations fused with a column-parallel linear (gemm_fused.cu).
 struct AgGemmProblem {

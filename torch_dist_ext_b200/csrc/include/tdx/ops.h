@@ -26,6 +26,15 @@ std::string rope_inplace(void* q, void* k, const int64_t* positions, const float
                          cudaStream_t stream, const void* v = nullptr, int64_t v_stride = 0, void* k_cache = nullptr,
                          void* v_cache = nullptr, int64_t cache_stride_b = 0, int64_t cache_stride_s = 0);
 
+// Greedy sampling over a vocabulary sharded across ranks, in two launches around one fused all-reduce:
+// argmax_pack writes {largest logit, its index + index_base, 0, 0} of every row of logits [tokens, vocab] fp32 (rows
+// `ld` elements apart) into slot `rank` of pack [tokens, 4 * nranks] fp32 and zeroes the other slots, so that the
+// sum of `pack` over the ranks holds every rank's candidate; select_token picks the winner per row (the lowest
+// index among equal logits) into out [tokens] int64.
+std::string argmax_pack(const float* logits, int64_t ld, int tokens, int vocab, int index_base, int rank, int nranks,
+                        float* pack, cudaStream_t stream);
+std::string select_token(const float* gathered, int tokens, int nranks, int64_t* out, cudaStream_t stream);
+
 // Decode attention over a contiguous bf16 KV cache [B, S_max, Hkv, 128] for one new token per
 // sequence: q [B, Hq, 128] -> out [B, Hq, 128]. `partial` is scratch of at least
 // 4096 + B * Hq * nsplit * 130 floats whose first 4096 words must be ZERO on entry (arrival counters;

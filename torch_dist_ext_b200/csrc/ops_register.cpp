@@ -79,6 +79,28 @@ void silu_mul(const Tensor& gate_up, Tensor out, c10::optional<Tensor> scales) {
   TORCH_CHECK(err.empty(), "silu_mul: ", err);
 }
 
+void argmax_pack(const Tensor& logits, int64_t index_base, int64_t rank, int64_t nranks, Tensor pack) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kFloat && logits.stride(1) == 1,
+              "logits must be a CUDA fp32 [tokens, vocab] tensor with unit stride along the vocabulary");
+  TORCH_CHECK(pack.is_cuda() && pack.device() == logits.device() && pack.scalar_type() == at::kFloat && pack.is_contiguous() &&
+              pack.numel() == logits.size(0) * 4 * nranks, "pack must be a contiguous fp32 [tokens, 4 * nranks] tensor");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const std::string err = tdx::argmax_pack(logits.data_ptr<float>(), logits.stride(0), (int)logits.size(0), (int)logits.size(1),
+                                           (int)index_base, (int)rank, (int)nranks, pack.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(err.empty(), "argmax_pack: ", err);
+}
+
+void select_token(const Tensor& gathered, int64_t nranks, Tensor out) {
+  TORCH_CHECK(gathered.is_cuda() && gathered.scalar_type() == at::kFloat && gathered.is_contiguous() && gathered.dim() == 2 &&
+              gathered.size(1) == 4 * nranks, "candidates must be a contiguous fp32 [tokens, 4 * nranks] tensor");
+  TORCH_CHECK(out.is_cuda() && out.device() == gathered.device() && out.scalar_type() == at::kLong && out.is_contiguous() &&
+              out.numel() == gathered.size(0), "out must be a contiguous int64 [tokens] tensor");
+  const c10::cuda::CUDAGuard guard(gathered.device());
+  const std::string err = tdx::select_token(gathered.data_ptr<float>(), (int)gathered.size(0), (int)nranks,
+                                            out.data_ptr<int64_t>(), cur_stream());
+  TORCH_CHECK(err.empty(), "select_token: ", err);
+}
+
 void rope_impl(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_sin_cache, const c10::optional<Tensor>& v,
                c10::optional<Tensor> k_cache, c10::optional<Tensor> v_cache);
 
@@ -396,6 +418,8 @@ void register_extra_ops(torch::Library& m) {
         "Tensor(c!)? scale_out, float eps, int out_mode) -> int", &fused_add_rmsnorm);
   m.def("quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) scales, bool block128) -> ()", &quant_fp8);
   m.def("silu_mul(Tensor gate_up, Tensor(a!) out, Tensor(b!)? scales) -> ()", &silu_mul);
+  m.def("argmax_pack(Tensor logits, int index_base, int rank, int nranks, Tensor(a!) pack) -> ()", &argmax_pack);
+  m.def("select_token(Tensor gathered, int nranks, Tensor(a!) out) -> ()", &select_token);
   m.def("rope_(Tensor(a!) q, Tensor(b!) k, Tensor positions, Tensor cos_sin_cache) -> ()", &rope_);
   m.def("rope_append_kv_(Tensor(a!) q, Tensor(b!) k, Tensor v, Tensor positions, Tensor cos_sin_cache, Tensor(c!) k_cache, "
         "Tensor(d!) v_cache) -> ()", &rope_append_kv_);

@@ -30,7 +30,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from ..ops import activation, attention, fused_gemm, gemm, norm, quant, rope
+from ..ops import activation, attention, fused_gemm, gemm, norm, quant, rope, sampling
 from ..ops.fused_allreduce import fused_allreduce_rms
 from ..parallel import comm as _comm
 from ..utils.config import OUT_FP8_BLOCK128, OUT_SAME
@@ -204,16 +204,7 @@ class TPLlama:
         if x.dtype == torch.float8_e4m3fn:
             raise RuntimeError("final norm output must be bf16")
         logits = gemm.linear(x, self.lm_head, out_dtype=torch.float32)          # [tokens, vocab_r]
-        val, idx = logits.max(dim=-1)
-        idx = idx + self.rank * self.vocab_r
-        if self.world > 1:
-            packed = torch.stack([val, idx.float()], dim=-1).contiguous()
-            allp = [torch.empty_like(packed) for _ in range(self.world)]
-            dist.all_gather(allp, packed, group=self.group)
-            allp = torch.stack(allp)                                           # [world, tokens, 2]
-            best = allp[..., 0].argmax(dim=0)
-            idx = allp[best, torch.arange(tokens, device=x.device), 1].long()
-        return idx
+        return sampling.greedy_sample_sharded(logits, self.rank, self.world, self.rank * self.vocab_r)
 
     def _gather_rows(self, x_shard: torch.Tensor, tokens: int) -> torch.Tensor:
         n = self.world

@@ -5,8 +5,10 @@
 ``allgather_gemm``      all-gather of sequence-parallel rows + column-parallel linear:
                         the qkv / gate-up step that follows a reduce-scattered norm.
 
-Both are decode-sized paths (all CTAs must be resident at once); for more tokens the functions
-fall back to the tcgen05 GEMM followed / preceded by the fused all-reduce op.
+``allgather_gemm`` and the e4m3 form of ``gemm_allreduce_rms`` are decode-sized paths (one CTA per tile, all CTAs
+resident at once); for more tokens they fall back to the tcgen05 GEMM followed / preceded by the fused all-reduce
+op. With bf16 operands ``gemm_allreduce_rms`` stays fused at any token count that fits the Lamport buffers: a
+persistent kernel (one CTA per SM) walks the tiles.
 """
 from __future__ import annotations
 
@@ -47,7 +49,15 @@ def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torc
     fp8 = a.dtype == torch.float8_e4m3fn
     if fp8 and w.shape[0] != gamma.shape[0]:
         hidden = gamma.shape[0]         # weights padded to a multiple of 128 rows
-    if force_unfused or not _fits(tokens, hidden) or hidden % 128 or out_mode not in (OUT_SAME, OUT_FP8_BLOCK128):
+    n = c.world_size
+    if not _fits(tokens, hidden):
+        # beyond one CTA per tile: the persistent kernel, bf16 operands, gather slots + result rows in one Lamport buffer
+        groups = (tokens + n - 1) // n
+        need = n * groups * hidden * 2 + (0 if scatter_only else tokens * (hidden * 2 + 16))
+        fused = not fp8 and a.dtype == torch.bfloat16 and need <= c.lamport_bytes
+    else:
+        fused = True
+    if force_unfused or not fused or hidden % 128 or out_mode not in (OUT_SAME, OUT_FP8_BLOCK128):
         if fp8:
             y = _gemm.linear_fp8_blockscaled(a, a_scale, w, w_scale)
             y = y[:, :hidden] if y.shape[1] != hidden else y
@@ -55,7 +65,6 @@ def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torc
             y = _gemm.linear(a, w)
         return fused_allreduce_rms(y, residual, gamma, eps, out_mode=out_mode, scatter_only=scatter_only,
                                    want_residual=want_residual)
-    n = c.world_size
     rows = (tokens + n - 1) // n if scatter_only else tokens
     act_dtype = torch.bfloat16 if fp8 else a.dtype
     res_out = torch.empty(rows, hidden, dtype=act_dtype, device=a.device) if want_residual else None

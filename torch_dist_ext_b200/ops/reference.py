@@ -98,3 +98,18 @@ def fused_allreduce_rms_distributed(allreduce_in: torch.Tensor, residual: Option
 def scatter_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     """Rows owned by ``rank`` in the round-robin layout of the reduce-scatter variant."""
     return t[rank::world].contiguous()
+
+
+def greedy_sample_sharded(logits: torch.Tensor, rank: int, world: int, index_base: int,
+                          group: Optional["dist.ProcessGroup"] = None) -> torch.Tensor:
+    """Arg-max over a vocabulary sharded across ranks, in plain PyTorch: the oracle of ops.sampling."""
+    val, idx = logits.float().max(dim=-1)
+    idx = idx + index_base
+    if world == 1:
+        return idx
+    packed = torch.stack([val, idx.float()], dim=-1).contiguous()
+    parts = [torch.empty_like(packed) for _ in range(world)]
+    dist.all_gather(parts, packed, group=group)
+    allp = torch.stack(parts)                                                  # [world, tokens, 2]
+    best = allp[..., 0].argmax(dim=0)
+    return allp[best, torch.arange(logits.shape[0], device=logits.device), 1].long()

@@ -35,6 +35,7 @@ class CommProcess:
         self.size_in_bytes = size_in_bytes
         self.is_cuda = torch.cuda.is_available()
         self.algo_counts = {}
+        self.lamport_bytes = config.lamport_mb << 20
         if not self.is_cuda:
             # CPU ranks (gloo): no device buffers; the op runs the PyTorch statement of itself.
             self.comm = None

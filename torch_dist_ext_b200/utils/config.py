@@ -12,7 +12,7 @@ environment:
 ``TDX_PDL``            ``0`` launches the fused all-reduce kernels without programmatic stream
                        serialisation (read by the native launcher)
 ``TDX_TIMEOUT_MS``     budget of every device-side wait (default 5000)
-``TDX_LAMPORT_MB``     capacity of each of the three Lamport buffers (default 32)
+``TDX_LAMPORT_MB``     capacity of each of the three Lamport buffers (default 72: a 32 MiB message with its result rows)
 ``TDX_NVLS``           ``0`` disables the NVSwitch-multicast mapping and kernels
 ``TDX_WAVES``          pipeline depth (1..4) of the flag-synchronised two-shot paths (default 1)
 ``TDX_NVLS_BATCH``     NVLS two-shot: rows whose switch-side sums are requested together (1..4, default 1)
@@ -50,7 +50,7 @@ OUT_SAME, OUT_FP8_TOKEN, OUT_FP8_BLOCK128 = 0, 1, 2
 class Config:
     algo: str = "auto"
     timeout_ms: int = 5000
-    lamport_mb: int = 32
+    lamport_mb: int = 72
     nvls: bool = True
     # nranks -> (oneshot_max_bytes, lamport_max_bytes, mc_oneshot, mc_twoshot, nvls_min_bytes), -1 = keep the
     # built-in value; empty = built-in defaults
