@@ -82,6 +82,18 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
             del model
         diff = (hidden_states["ar"] - hidden_states["sp"]).abs().max().item()
         assert diff <= 0.08, f"replicated and sequence-parallel modes differ by {diff}"
+        # the same pair of modes with e4m3 weights: the scattered rows travel as e4m3 with their 1x128 scales
+        hs = {}
+        for mode in ("ar", "sp"):
+            model = TPLlama(LlamaConfig.tiny(fp8=True), max_batch=nb, max_seq=64, mode=mode, seed=3)
+            model.fill_cache_random(nb, 12, seed=5)
+            model.decode_step(tokens, positions, max_len=13)
+            torch.cuda.synchronize()
+            tdx.check_status()
+            hs[mode] = model._gather_rows(model.last_hidden, nb).float() if mode == "sp" else model.last_hidden.float()
+            del model
+        diff = (hs["ar"] - hs["sp"]).abs().max().item()
+        assert diff <= 0.15, f"e4m3 weights: replicated and sequence-parallel modes differ by {diff}"
         assert gemm.pipeline_status() == 0
         dist.barrier()
         tdx.teardown_env()

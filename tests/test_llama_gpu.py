@@ -101,3 +101,22 @@ def test_prefill_then_decode_runs():
     nxt = model.decode_step(first, torch.tensor([48], device="cuda"), max_len=49)
     torch.cuda.synchronize()
     assert bool(torch.isfinite(model.last_hidden.float()).all()) and nxt.shape == (1,)
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_sequence_parallel_mode_equals_replicated_mode(fp8):
+    """One rank: every row is this rank's row, so the scattered flow (reduce-scatter + norm, gathered input of the
+    column-parallel GEMMs; with e4m3 weights the rows travel as e4m3 with their 1x128 scales) must reproduce the
+    replicated one, next tokens included."""
+    cfg = LlamaConfig.tiny(fp8=fp8)
+    tokens = torch.arange(5, device="cuda") * 11 % cfg.vocab
+    positions = torch.full((5,), 9, device="cuda", dtype=torch.long)
+    hidden, nxt = {}, {}
+    for mode in ("ar", "sp"):
+        model = TPLlama(cfg, max_batch=8, max_seq=32, mode=mode, seed=4)
+        model.fill_cache_random(5, 9, seed=2)
+        nxt[mode] = model.decode_step(tokens, positions, max_len=10)
+        hidden[mode] = model.last_hidden.float().clone()
+        del model
+    assert (hidden["ar"] - hidden["sp"]).abs().max().item() <= (0.12 if fp8 else 0.05)
+    assert torch.equal(nxt["ar"], nxt["sp"]) or not fp8

@@ -608,3 +608,50 @@ def pair_gemm_persistent(ntiles, nkb, stages, rng):
 def test_persistent_cta_pair_gemm_pipeline(ntiles, nkb, stages):
     for seed in range(60):
         pair_gemm_persistent(ntiles, nkb, stages, random.Random(seed))
+
+
+# ---- push epilogue of the persistent fused GEMM (csrc/gemm_fused_persist.cu) --------------------------------
+# The four epilogue warps transpose 16 tokens at a time through one of TWO shared-memory buffers with ONE named
+# barrier per step: write buffer (step & 1), barrier, read it. A thread can write the buffer of step k + 2 only after
+# it passed the barrier of step k + 1, which every thread reaches only after its reads of step k.
+
+def push_epilogue(nthreads, nsteps, nbuffers, rng):
+    bar = MBar(nthreads)
+    cells = [[None] * nthreads for _ in range(nbuffers)]          # cells[buffer][writer] = step it holds
+    unread = [[0] * nthreads for _ in range(nbuffers)]            # reads still owed on the cell's current content
+    seen = [[] for _ in range(nthreads)]
+
+    def thread(me):
+        for k in range(nsteps):
+            b = k % nbuffers
+            assert unread[b][me] == 0, f"step {k}: buffer {b} overwritten while {unread[b][me]} readers still owe a read"
+            cells[b][me] = k
+            unread[b][me] = nthreads
+            yield ("step",)
+            bar.arrive()
+            yield from wait(bar, k & 1)
+            for w in rng.sample(range(nthreads), nthreads):
+                assert cells[b][w] == k, f"step {k}: thread {me} read step {cells[b][w]} of writer {w}"
+                unread[b][w] -= 1
+                yield ("step",)
+            seen[me].append(k)
+
+    run([thread(i) for i in range(nthreads)], {}, rng)
+    assert all(s == list(range(nsteps)) for s in seen)
+
+
+@pytest.mark.parametrize("nsteps", [1, 2, 3, 8, 17])
+def test_push_epilogue_two_buffers_one_barrier(nsteps):
+    for seed in range(40):
+        push_epilogue(4, nsteps, 2, random.Random(seed))
+
+
+def test_push_epilogue_one_buffer_would_race():
+    """The model does see the race that a single buffer with one barrier per step has."""
+    hits = 0
+    for seed in range(40):
+        try:
+            push_epilogue(4, 6, 1, random.Random(seed))
+        except AssertionError:
+            hits += 1
+    assert hits > 0

@@ -11,7 +11,8 @@ Per layer and decode step::
     x,res = (act @ Wd_r^T --all-reduce-->) + res -> RMSNorm        gather back
 
 ``mode="sp"`` keeps the normalised rows scattered (rank r owns rows r::world) and feeds them to the
-next column-parallel GEMM through the fused all-gather->GEMM kernel instead.
+next column-parallel GEMM through the fused all-gather->GEMM kernel instead (bf16 weights; with e4m3
+weights the e4m3 rows and their scales are gathered by the process group and the block-scaled GEMM follows).
 
 With ``fp8=True`` the four projection weights are e4m3 with 128x128 fp32 block scales; the
 activations that feed them are quantised to e4m3 with 1x128 scales by the producing kernel
@@ -174,7 +175,10 @@ class TPLlama:
         if self.mode == "sp" and not lin.fp8:
             return fused_gemm.allgather_gemm(x, lin.w, tokens)
         if self.mode == "sp":
-            raise NotImplementedError("sequence-parallel mode is implemented for bf16 weights")
+            # e4m3 rows and their 1x128 scales are gathered as they are (half the bytes of bf16 rows), then the
+            # block-scaled GEMM runs on the full batch; the fused all-gather GEMM takes bf16 rows only
+            full = self._gather_rows(x.view(torch.uint8), tokens).view(torch.float8_e4m3fn)
+            return lin(full, self._gather_rows(x_scale, tokens))
         return lin(x, x_scale)
 
     def _layer(self, i: int, x, x_scale, res, positions, tokens: int, max_len: int, bf16_tail: bool = False):
@@ -193,7 +197,7 @@ class TPLlama:
         act, act_scale = activation.silu_mul(gu, quant_block128=cfg.fp8)
         if bf16_tail:
             y = L["wd"](act, act_scale)
-            x, res, _ = fused_allreduce_rms(y, res, self.final_norm, cfg.eps, out_mode=OUT_SAME)
+            x, res, _ = fused_allreduce_rms(y, res, self.final_norm, cfg.eps, out_mode=OUT_SAME, scatter_only=self.mode == "sp")
             return x, None, res
         next_gamma = self.layers[i + 1]["ln1"] if i + 1 < cfg.n_layers else self.final_norm
         return self._row_parallel(act, L["wd"], res, next_gamma, act_scale)
