@@ -17,6 +17,9 @@ import sys
 import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+# a profiler that replays a launch saves and restores the process's device memory: keep the communication buffers
+# small (the library reads this when it is imported)
+os.environ.setdefault("TDX_LAMPORT_MB", "32")
 
 
 def main():

@@ -257,6 +257,11 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                const __grid_constant__ CUtensorMap map_g1, const AgArgs a) {
   constexpr uint32_t kTmemCols = kBN < 32 ? 32 : kBN;
   extern __shared__ uint8_t smem_raw[];
+  // 0 while the producer still waits for the peers' rows, then 1 (arrived) or 2 (gave up). The MMA thread and the
+  // epilogue warps watch it with the workspace's TIME budget before they start their poll-counted pipeline waits,
+  // so a peer that is late but within budget cannot make them give up first.
+  __shared__ volatile uint32_t gate_state;
+  if (threadIdx.x == 0) gate_state = 0;
   gemm_core::Pipeline<kBN, kStages> pipe;
   pipe.init(smem_raw, kTmemCols, &map_w, &map_g0);
   char* self = static_cast<char*>(a.peer[a.rank]);
@@ -271,6 +276,16 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     ptx::pdl_wait();
     ptx::pdl_launch_dependents();
   }
+
+  auto gate_passed = [&]() -> bool {
+    Waiter w(a.timeout_ns * (uint64_t)(a.nranks + 1));   // the producer waits for the ranks one after the other
+    w.begin();
+    while (gate_state == 0) {
+      if (!w.keep_waiting()) return false;
+      __nanosleep(64);
+    }
+    return true;   // on 2 the producer has raised the abort flag already: the pipeline waits return at once
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -287,19 +302,24 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           while ((int32_t)(ptx::ld_acquire_sys(fl) - target) < 0) {
             if (!w.keep_waiting()) {
               report_error(ctl, a.host_status, kTimeoutTileFlag, a.rank, r, 1, -1);
+              gate_state = 2;
               return false;
             }
           }
         }
         // the rows were written through the generic proxy (peer stores); TMA reads through the async proxy
         asm volatile("fence.proxy.async.global;" ::: "memory");
+        gate_state = 1;
         return true;
       };
       pipe.template produce_late_y<kElemsPerBlock>(&map_w, &map_g0, &map_g1, &epoch_p, blockIdx.x * kBM, blockIdx.y * kBN, 0,
                                                    a.kblocks, a.status, gate);
     }
   } else if (warp == 1) {
-    if (lane == 0) pipe.template issue<false, false>(a.kblocks, a.idesc, a.status);
+    if (lane == 0) {
+      if (gate_passed()) pipe.template issue<false, false>(a.kblocks, a.idesc, a.status);
+      else pipe.fail(a.status);
+    }
   } else {
     // warps 2..7: destination `d` of the all-gather is served by CTA d % nctas
     const uint32_t epoch = ctl->ag_epoch;
@@ -321,7 +341,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp < 6) {
       // epilogue: D[x = weight row, y = token] -> out[token, weight row]
       const int q = warp & 3;
-      const bool ok = tc::mbar_wait(&pipe.acc_full[0], 0, gemm_core::kWaitLimit, pipe.abort_flag);
+      const bool ok = gate_passed() && tc::mbar_wait(&pipe.acc_full[0], 0, gemm_core::kWaitLimit, pipe.abort_flag);
       tc::fence_after_thread_sync();
       if (!ok) pipe.fail(a.status);
       const int x = blockIdx.x * kBM + q * 32 + lane;
