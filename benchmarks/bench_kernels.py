@@ -69,9 +69,10 @@ def gemm_cases(dev, steps, shapes, ms, out, cta_pair=None, persistent=None):
         for m in ms:
             a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
             if m >= 256:   # the tiled kernels against the one-tile-per-CTA kernel before timing them
-                err = (gemm.linear(a, ws[0], cta_pair=cta_pair, persistent=persistent).float() -
-                       gemm.linear(a, ws[0], cta_pair=False, persistent=False).float()).abs().max().item()
-                if err > 0.05 or gemm.pipeline_status() != 0:
+                want = gemm.linear(a, ws[0], cta_pair=False, persistent=False).float()
+                err = (gemm.linear(a, ws[0], cta_pair=cta_pair, persistent=persistent).float() - want).abs().max().item()
+                # one bf16 rounding step of the largest output: the kernels add the K blocks in different orders
+                if err > 2.0 ** -7 * max(1.0, want.abs().max().item()) or gemm.pipeline_status() != 0:
                     raise SystemExit(f"opt-in GEMM disagrees with the default kernel (max err {err}, status {gemm.pipeline_status()})")
             us = time_us(lambda i: gemm.linear(a, ws[i], cta_pair=cta_pair, persistent=persistent), len(ws), steps)
             lib = time_us(lambda i: torch.matmul(a, ws[i].t()), len(ws), steps)
@@ -195,6 +196,19 @@ def elementwise_cases(dev, steps, out):
 
     out.append(row("silu(gate)*up 8192x(2x4096)", us, time_us(torch_silu, len(xs), steps), nb + nb // 2, 0, hbm, tf, src))
     print(out[-1], flush=True)
+    del xs
+    torch.cuda.empty_cache()
+    # greedy sampling: arg-max over fp32 logits (decode batch x the vocabulary shard of a rank, and the whole vocabulary)
+    from torch_dist_ext_b200.ops import sampling
+
+    for tokens, vocab in [(16, 16032), (64, 16032), (64, 128256)]:
+        lb = tokens * vocab * 4
+        ls = rotating(lambda: torch.randn(tokens, vocab, device=dev), lb)
+        us = time_us(lambda i: sampling.greedy_sample_sharded(ls[i], 0, 1, 0), len(ls), steps)
+        out.append(row(f"arg-max over logits {tokens}x{vocab} fp32", us, time_us(lambda i: ls[i].argmax(dim=-1), len(ls), steps), lb, 0,
+                       hbm, tf, src))
+        print(out[-1], flush=True)
+        del ls
 
 
 def main():

@@ -11,7 +11,7 @@ models replay the role programs of
  * the tensor-core decode attention kernel (csrc/attention_decode_tc.cu): K/V ring, double-buffered
    scores, one probability tile, one P*V buffer;
  * the prompt attention kernel (csrc/attention_prefill_tc.cu): separate K and V rings, double-buffered
-   scores, one probability tile, the output accumulated in tensor memory across all chunks;
+   scores, two probability tiles, the output accumulated in tensor memory across all chunks;
  * the CTA-pair GEMM (csrc/gemm_pair.cu): two producers crediting the leader's transaction-counting
    barriers, stages released in both CTAs by the leader's MMA thread, a persistent tile loop with two
    accumulator buffers that the epilogue warps of BOTH CTAs hand back to the leader
@@ -400,8 +400,9 @@ def test_cta_pair_gemm_pipeline(nkb, stages):
 
 # ---- prompt attention (csrc/attention_prefill_tc.cu) ------------------------------------------------------
 # K ring (freed when the scores of the chunk are complete) and V ring (freed when P*V is complete) run apart;
-# O accumulates in tensor memory over all chunks, so before the softmax threads touch the P tile (or rescale O)
-# for chunk i they wait for the P*V product of chunk i - 1, observing every phase of o_full exactly once.
+# O accumulates in tensor memory over all chunks. The probabilities of chunk i go through tile i & 1, so the softmax
+# threads wait for the P*V product of chunk i - 2 before they write (barrier pv_done[i & 1]), never for the one of
+# chunk i - 1 - except before the rare rescale of O, which needs every product issued so far to have completed.
 
 def prefill_attention(nchunks, stages_k, stages_v, rng):
     k_full = [MBar(1) for _ in range(stages_k)]
@@ -409,14 +410,14 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
     v_full = [MBar(1) for _ in range(stages_v)]
     v_free = [MBar(1) for _ in range(stages_v)]
     s_full = [MBar(1) for _ in range(2)]
-    n_sm = 3                                             # stands for the 256 softmax threads
+    n_sm = 3                                             # stands for the 128 softmax threads
     s_free = [MBar(n_sm) for _ in range(2)]
-    p_full = MBar(n_sm)
-    o_full = MBar(1)
+    p_full = [MBar(n_sm) for _ in range(2)]
+    pv_done = [MBar(1) for _ in range(2)]
     kbuf, vbuf = [None] * stages_k, [None] * stages_v
     k_reads, v_reads = [0] * stages_k, [0] * stages_v
     s_buf, s_readers = [None, None], [0, 0]
-    p_tile = {"chunk": None, "reads_pending": 0}
+    p_tile = [{"rows": [None] * n_sm, "reads_pending": 0} for _ in range(2)]
     o_acc = {"chunks": [], "mma_pending": 0, "rescaling": 0}
     seen = [[] for _ in range(n_sm)]
     events = {"tma": [], "mma": []}
@@ -453,18 +454,19 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
 
     def issue_pv(c):
         s = c % stages_v
-        assert vbuf[s] == c and p_tile["chunk"] == c, f"P*V of chunk {c}: V holds {vbuf[s]}, P holds {p_tile['chunk']}"
+        t = p_tile[c & 1]
+        assert vbuf[s] == c and t["rows"] == [c] * n_sm, f"P*V of chunk {c}: V holds {vbuf[s]}, P holds {t['rows']}"
         assert o_acc["rescaling"] == 0, "P*V issued while a softmax thread rescales O"
         v_reads[s] += 1
-        p_tile["reads_pending"] += 1
+        t["reads_pending"] += 1
         o_acc["mma_pending"] += 1
 
         def retire():
             o_acc["chunks"].append(c)
             o_acc["mma_pending"] -= 1
             v_reads[s] -= 1
-            p_tile["reads_pending"] -= 1
-            o_full.arrive()
+            t["reads_pending"] -= 1
+            pv_done[c & 1].arrive()
             v_free[s].arrive()
         events["mma"].append(retire)
 
@@ -489,7 +491,7 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
             if i >= 1 and i - 1 + stages_v < nchunks:
                 yield from wait(v_free[(i - 1) % stages_v], ((i - 1) // stages_v) & 1)
                 load_v(i - 1 + stages_v)
-            yield from wait(p_full, i & 1)
+            yield from wait(p_full[i & 1], (i >> 1) & 1)
             yield from wait(v_full[i % stages_v], (i // stages_v) & 1)
             issue_pv(i)
             yield ("step",)
@@ -503,30 +505,31 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
             assert s_buf[buf] == i, f"softmax of chunk {i} read scores of {s_buf[buf]}"
             s_readers[buf] -= 1
             s_free[buf].arrive()
-            if i > 0:
-                yield from wait(o_full, (i - 1) & 1)
+            if i > 0 and rng.random() < 0.3:            # the rare rescale of O in tensor memory
+                yield from wait(pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1)
                 assert o_acc["chunks"] == list(range(i)) and o_acc["mma_pending"] == 0, "O not stable at the rescale point"
-                if rng.random() < 0.3:                  # the rare rescale of O in tensor memory
-                    o_acc["rescaling"] += 1
-                    yield ("step",)
-                    o_acc["rescaling"] -= 1
-            assert p_tile["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
+                o_acc["rescaling"] += 1
+                yield ("step",)
+                o_acc["rescaling"] -= 1
+            if i >= 2:
+                yield from wait(pv_done[buf], ((i >> 1) - 1) & 1)
+            assert p_tile[buf]["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
             yield ("step",)
-            p_tile["chunk"] = i
+            p_tile[buf]["rows"][who] = i
             seen[who].append(i)
-            p_full.arrive()
-        yield from wait(o_full, (nchunks - 1) & 1)
+            p_full[buf].arrive()
+        yield from wait(pv_done[(nchunks - 1) & 1], ((nchunks - 1) >> 1) & 1)
         assert o_acc["chunks"] == list(range(nchunks))
 
     run([mma()] + [softmax(w) for w in range(n_sm)], events, rng)
     assert all(x == list(range(nchunks)) for x in seen)
 
 
-@pytest.mark.parametrize("stages_v", [2, 3])
+@pytest.mark.parametrize("stages", [(2, 2), (2, 3), (3, 3)])
 @pytest.mark.parametrize("nchunks", [1, 2, 3, 4, 5, 7, 16, 32])
-def test_prefill_attention_pipeline(nchunks, stages_v):
+def test_prefill_attention_pipeline(nchunks, stages):
     for seed in range(40):
-        prefill_attention(nchunks, 2, stages_v, random.Random(seed))
+        prefill_attention(nchunks, stages[0], stages[1], random.Random(seed))
 
 
 # ---- persistent CTA-pair GEMM: tile loop and accumulator hand-back ------------------------------------------

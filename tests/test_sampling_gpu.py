@@ -25,10 +25,12 @@ def test_single_rank_matches_argmax(tokens, vocab):
     assert got.dtype == torch.int64 and torch.equal(got.cpu(), logits.cpu().argmax(dim=-1))
 
 
-def test_rows_of_a_wider_matrix_and_an_index_base():
+@pytest.mark.parametrize("first,last", [(1000, 3000), (1001, 3000), (1002, 2999), (0, 20481)])
+def test_rows_of_a_wider_matrix_and_an_index_base(first, last):
+    """Row stride 32768, unit column stride; rows that start off a 16-byte boundary take the element-wise loads."""
     g = torch.Generator().manual_seed(3)
-    wide = torch.randn(16, 4096, generator=g).cuda()
-    view = wide[:, 1000:3000]                                   # row stride 4096, unit column stride
+    wide = torch.randn(16, 32768, generator=g).cuda()
+    view = wide[:, first:last]
     got = sampling.greedy_sample_sharded(view, 0, 1, 50000)
     assert torch.equal(got.cpu(), view.cpu().argmax(dim=-1) + 50000)
 

@@ -15,8 +15,10 @@ from torch_dist_ext_b200.utils.config import ALGO_CODES, OUT_SAME
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("algo,code", [("oneshot", 1), ("twoshot", 1), ("twoshot_barrier", 3)])
-def test_missing_peer_times_out_and_reports(algo, code):
+# two-shot: the blocks that own a row wait for the peer's partial sums (1), the others for the rows that the peer owns
+# (2); both budgets run out together and the first report wins
+@pytest.mark.parametrize("algo,codes", [("oneshot", (1,)), ("twoshot", (1, 2)), ("twoshot_barrier", (3,))])
+def test_missing_peer_times_out_and_reports(algo, codes):
     ws = tdx.local_workspaces(2, size_in_bytes=4 << 20, timeout_ms=200)
     ins, residual, gamma = make_inputs(2, 8, 1024, torch.bfloat16, "cuda")
     table0 = ws[0].get_workspace(ins[0])
@@ -30,7 +32,8 @@ def test_missing_peer_times_out_and_reports(algo, code):
     end.record()
     torch.cuda.synchronize()  # returns: the kernel exits by itself
     assert 150 <= start.elapsed_time(end) <= 3000
-    assert ws[0].errors_seen() == code
+    code = ws[0].errors_seen()
+    assert code in codes
     st = ws[0].stats()
     assert st[3] >= 1           # error_count
     assert st[7] == code        # status[0] = code

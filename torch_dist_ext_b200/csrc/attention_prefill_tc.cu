@@ -6,17 +6,18 @@
 //   O[q 128, d 128]  += P[q, keys] * V[keys, d]         P written by the softmax warps (K-major over keys),
 //                                                       V read MN-major (d contiguous) straight from its TMA tile
 //
-// Two CTAs share an SM (112 KB of shared memory and 256 tensor-memory columns each): while one of them
-// is in its softmax the other one's MMAs run, which is what keeps the tensor core and the exp2 unit
-// busy - a single CTA per SM spends most of its time in the latency of its own per-chunk chain.
 // Four softmax warps, one query row per thread: a thread fetches its 64 scores of a chunk with ONE
 // tcgen05.ld and gives the score buffer back at once (S is double-buffered, so the scores of chunk c+1
-// are computed while chunk c is in the softmax). O stays in tensor memory and is accumulated there by
+// are computed while chunk c is in the softmax). The probabilities go through TWO shared-memory tiles, so
+// the softmax of chunk c+1 never waits for the P*V product of chunk c: the softmax warps run back to back
+// and the tensor core trails them (a softmax that waited for its own P*V spent more than half of every
+// chunk in the latency of that round trip). O stays in tensor memory and is accumulated there by
 // the P*V products of all chunks. A row's running maximum is only raised - and its row of O rescaled in
-// tensor memory - when the new maximum exceeds it by more than 2^8 (a warp-uniform decision); until
-// then the probabilities are taken against the older maximum, which changes neither O / l nor the
-// accuracy of bf16 probabilities below 256. A fifth warp issues the TMA copies (two-stage rings for K,
-// freed as soon as the scores are computed, and for V, freed after P*V) and all MMAs.
+// tensor memory, after the products issued so far have completed - when the new maximum exceeds it by
+// more than 2^8 (a warp-uniform decision); until then the probabilities are taken against the older
+// maximum, which changes neither O / l nor the accuracy of bf16 probabilities below 256. A fifth warp
+// issues the TMA copies (three-stage rings for K, freed as soon as the scores are computed, and for V,
+// freed after P*V) and all MMAs.
 //
 // Every wait is bounded; a wait that runs out records a status word and raises the CTA's abort flag,
 // and all threads still reach the common exit. Not part of the reference (it has no attention).
@@ -40,8 +41,8 @@ namespace {
 constexpr int kD = 128;
 constexpr int kRows = 128;                        // query rows per CTA
 constexpr int kKeys = 64;                         // key positions per chunk
-constexpr int kStagesK = 2;
-constexpr int kStagesV = 2;
+constexpr int kStagesK = 3;
+constexpr int kStagesV = 3;
 constexpr int kSoftmaxThreads = 128;
 constexpr int kThreads = kSoftmaxThreads + 32;
 constexpr int kMmaWarp = kSoftmaxThreads / 32;
@@ -50,11 +51,11 @@ constexpr int kQBytes = 2 * kQHalfBytes;
 constexpr int kKVHalfBytes = kKeys * 128;         // 64 head-dimension columns of the 64 positions of a chunk
 constexpr int kKVBytes = 2 * kKVHalfBytes;        // one K chunk or one V chunk
 constexpr int kPBytes = kRows * kKeys * 2;        // probabilities of a chunk: one 64-key K block of 128 rows
-constexpr int kNumBarriers = 2 * kStagesK + 2 * kStagesV + 4 + 3;   // k/v full+free, s full+free [2], q_full, p_full, o_full
+constexpr int kNumBarriers = 2 * kStagesK + 2 * kStagesV + 4 + 5;   // k/v full+free, s full+free [2], q_full, p_full [2], pv_done [2]
 constexpr int kBarrierBytes = 256;                // the mbarriers, the TMEM address and the abort flag
 static_assert(kNumBarriers * 8 + 8 <= kBarrierBytes, "barrier area too small");
-constexpr int kSmem = kQBytes + kPBytes + (kStagesK + kStagesV) * kKVBytes + kBarrierBytes;
-static_assert(2 * (kSmem + 1024) <= 228 * 1024, "two CTAs must fit the shared memory of one SM");
+constexpr int kSmem = kQBytes + 2 * kPBytes + (kStagesK + kStagesV) * kKVBytes + kBarrierBytes;
+static_assert(kSmem <= 227 * 1024, "shared memory of one CTA");
 constexpr uint32_t kTmemCols = 256;               // S buffers at columns 0 and 64, O at 128
 constexpr uint32_t kColO = 128;
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -68,12 +69,18 @@ struct PrefillArgs {
   uint32_t* status;
 };
 
-__global__ void __launch_bounds__(kThreads, 2)
+// exp2 of a non-positive (or slightly positive) argument, flushing what underflows to zero
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillArgs a) {
-  // The tiles need 1024-byte alignment (128-byte swizzle) and two CTAs fill the shared memory of the SM, so
-  // there is no room for alignment slack: the dynamic region is declared aligned, and a kernel that finds it
-  // otherwise reports that instead of running.
+  // The tiles need 1024-byte alignment (128-byte swizzle): the dynamic region is declared aligned, and a kernel
+  // that finds it otherwise reports that instead of running.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   if ((tc::smem_u32(smem_raw) & 1023u) != 0) {
     if (threadIdx.x == 0 && a.status) atomicExch(a.status, (uint32_t)kTimeoutGemmPipeline);
@@ -81,7 +88,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
   uint8_t* q_tile = smem_raw;
   uint8_t* p_tile = q_tile + kQBytes;
-  uint8_t* k_ring = p_tile + kPBytes;
+  uint8_t* k_ring = p_tile + 2 * kPBytes;
   uint8_t* v_ring = k_ring + kStagesK * kKVBytes;
   uint64_t* k_full = reinterpret_cast<uint64_t*>(v_ring + kStagesV * kKVBytes);
   uint64_t* k_free = k_full + kStagesK;
@@ -90,14 +97,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* s_full = v_free + kStagesV;     // [2]
   uint64_t* s_free = s_full + 2;            // [2]
   uint64_t* q_full = s_free + 2;
-  uint64_t* p_full = q_full + 1;
-  uint64_t* o_full = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* p_full = q_full + 1;            // [2]: probabilities of chunk c are in tile c & 1
+  uint64_t* pv_done = p_full + 2;           // [2]: the P*V product that read tile c & 1 has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
-  // the blocks with the most key chunks start first
-  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y;
+  // The blocks with the most key chunks start first, for all heads (blockIdx.x runs fastest): the short blocks of
+  // the causal triangle fill the tail of the grid. Neighbouring blocks are the query heads of one KV head and
+  // read the same K / V tiles out of L2.
+  const int qb = (int)gridDim.y - 1 - (int)blockIdx.y;
+  const int h = blockIdx.x;
   const int hkv = h / (a.Hq / a.Hkv);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int q0 = qb * kRows;
@@ -117,8 +126,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc::mbar_init(&s_free[i], kSoftmaxThreads);
     }
     tc::mbar_init(q_full, 1);
-    tc::mbar_init(p_full, kSoftmaxThreads);
-    tc::mbar_init(o_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&p_full[i], kSoftmaxThreads);
+      tc::mbar_init(&pv_done[i], 1);
+    }
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_desc(&map_q);
@@ -170,12 +181,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       };
       auto issue_pv = [&](int c) {       // O (+)= P * V chunk, 16 key positions per instruction
         const uint32_t vbase = tc::smem_u32(v_ring + (c % kStagesV) * kKVBytes);
-        const uint32_t pbase = tc::smem_u32(p_tile);
+        const uint32_t pbase = tc::smem_u32(p_tile + (c & 1) * kPBytes);
 #pragma unroll
         for (int j = 0; j < kKeys / 16; ++j)
           tc::umma<false>(tmem_base + kColO, tc::make_smem_desc_sw128(pbase) + (uint64_t)(j * 2),
                           tc::make_smem_desc_mn_sw128(vbase + j * 2048, kKVHalfBytes), a.idesc_pv, (c | j) ? 1u : 0u);
-        tc::umma_commit(o_full);
+        tc::umma_commit(&pv_done[c & 1]);
         tc::umma_commit(&v_free[c % kStagesV]);
       };
       tc::mbar_arrive_expect_tx(q_full, kQBytes);
@@ -210,7 +221,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (!ok) break;
           load_v(i - 1 + kStagesV);
         }
-        ok = tc::mbar_wait(p_full, i & 1, kWaitLimit, abort_flag) &&
+        ok = tc::mbar_wait(&p_full[i & 1], (i >> 1) & 1, kWaitLimit, abort_flag) &&
              tc::mbar_wait(&v_full[i % kStagesV], (i / kStagesV) & 1, kWaitLimit, abort_flag);
         if (!ok) break;
         tc::fence_after_thread_sync();
@@ -239,27 +250,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc::mbar_arrive(&s_free[buf]);            // the scores are in registers: the buffer can take chunk i + 2
       const int key0 = i * kKeys;
       const bool diagonal = key0 + kKeys - 1 > q0;   // the last two chunks cross the causal boundary of some row
-      // scores in units of log2 (multiplied by scale * log2 e), masked where the key lies after the query; row maximum
+      // row maximum of the raw scores, masked where the key lies after the query; the softmax scale (times log2 e)
+      // is positive, so it commutes with the maximum and is folded into the exponent's multiply-add below
       float cmax = -FLT_MAX;
 #pragma unroll
       for (int j = 0; j < kKeys; ++j) {
-        float x = __uint_as_float(sv[j]) * a.scale_log2;
-        if (diagonal && key0 + j > q_pos) x = -FLT_MAX;
-        sv[j] = __float_as_uint(x);
+        float x = __uint_as_float(sv[j]);
+        if (diagonal && key0 + j > q_pos) {
+          x = -FLT_MAX;
+          sv[j] = __float_as_uint(x);
+        }
         cmax = fmaxf(cmax, x);
       }
+      cmax *= a.scale_log2;                     // in units of log2 from here on
       if (i == 0) {
         m_run = cmax;                           // key 0 is live for every row, so this is finite
       } else {
-        // P*V of the previous chunk is complete: the P tile may be overwritten and O is stable
-        if (!tc::mbar_wait(o_full, (i - 1) & 1, kWaitLimit, abort_flag) && ok) {
-          ok = false;
-          fail();
-        }
-        tc::fence_after_thread_sync();
         const bool grow = cmax - m_run > kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
-          const float f = grow ? exp2f(m_run - cmax) : 1.f;
+          // O may only be touched when every P*V product issued so far has completed: the latest one read the
+          // other probability tile (products complete in issue order)
+          if (!tc::mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, kWaitLimit, abort_flag) && ok) {
+            ok = false;
+            fail();
+          }
+          tc::fence_after_thread_sync();
+          const float f = grow ? ex2(m_run - cmax) : 1.f;
           if (grow) {
             m_run = cmax;
             l_run *= f;
@@ -274,17 +290,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       }
+      // this chunk's probability tile was last read by the P*V product of chunk i - 2
+      if (i >= 2 && !tc::mbar_wait(&pv_done[buf], ((i >> 1) - 1) & 1, kWaitLimit, abort_flag) && ok) {
+        ok = false;
+        fail();
+      }
       // probabilities against m_run, row sum, this row of the P tile (bf16, K-major over the 64 key positions,
-      // 128-byte swizzle). A row that the mask removes from a whole chunk contributes zeros.
+      // 128-byte swizzle). A masked score is -FLT_MAX and comes out as zero.
       float psum = 0.f;
-      uint8_t* row = p_tile + tid * 128;
+      uint8_t* row = p_tile + buf * kPBytes + tid * 128;
+      const float neg_m = -m_run;
 #pragma unroll
       for (int cc = 0; cc < kKeys / 8; ++cc) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float p0 = exp2f(__uint_as_float(sv[cc * 8 + 2 * j]) - m_run);
-          const float p1 = exp2f(__uint_as_float(sv[cc * 8 + 2 * j + 1]) - m_run);
+          const float p0 = ex2(fmaf(__uint_as_float(sv[cc * 8 + 2 * j]), a.scale_log2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[cc * 8 + 2 * j + 1]), a.scale_log2, neg_m));
           psum += p0 + p1;
           __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           w[j] = *reinterpret_cast<uint32_t*>(&hh);
@@ -294,9 +316,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       l_run += psum;
       tc::fence_proxy_async();          // P was written by threads and is read by the tensor core
       tc::fence_before_thread_sync();   // orders the rescaled O (tcgen05.st) before the MMA that the arrival releases
-      tc::mbar_arrive(p_full);
+      tc::mbar_arrive(&p_full[buf]);
     }
-    if (!tc::mbar_wait(o_full, (nchunks - 1) & 1, kWaitLimit, abort_flag) && ok) {
+    // the last product completes after all the others
+    if (!tc::mbar_wait(&pv_done[(nchunks - 1) & 1], ((nchunks - 1) >> 1) & 1, kWaitLimit, abort_flag) && ok) {
       ok = false;
       fail();
     }
@@ -359,9 +382,7 @@ std::string attention_prefill_tc(const void* q, const void* k, const void* v, vo
   auto kern = attn_prefill_tc_kernel;
   const std::string smem_err = reserve_dynamic_smem(kern, kSmem);
   if (!smem_err.empty()) return smem_err;
-  // two CTAs per SM need (nearly) all of the SM's shared memory: ask for the largest carve-out
-  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  const dim3 grid((S + kRows - 1) / kRows, Hq, 1);
+  const dim3 grid(Hq, (S + kRows - 1) / kRows, 1);
   const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), kSmem, stream, mq, mk, mv, a);
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }

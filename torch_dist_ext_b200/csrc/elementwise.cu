@@ -217,20 +217,45 @@ int grid_for(size_t work_items, int threads, int max_blocks = 148 * 8) {
 // [tokens, 4 * nranks] fp32 as {value, index, 0, 0}; the other ranks' slots of the row are set to zero, so that the
 // SUM of `pack` over the ranks (one call of the fused all-reduce) is the gather of every rank's candidate. Indices
 // stay exact in fp32 up to 2^24. Of equal logits the lowest index wins; a NaN never wins.
-__global__ void __launch_bounds__(256) argmax_pack_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
-                                                          int index_base, int rank, int nranks, float* __restrict__ pack) {
+__global__ void __launch_bounds__(1024) argmax_pack_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
+                                                           int index_base, int rank, int nranks, float* __restrict__ pack) {
   ptx::pdl_wait();
   ptx::pdl_launch_dependents();
-  __shared__ float s_val[8];
-  __shared__ int s_idx[8];
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
   const int t = blockIdx.x;
   const float* row = logits + (int64_t)t * ld;
   float best = -INFINITY;
   int at = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best) { best = v; at = i; }
+  auto take = [&](float v, int i) {
+    if (v > best) { best = v; at = i; }      // a thread walks its indices upwards, so the first of equal values stays
+  };
+  // 16-byte loads, four of them in flight per thread, when the row allows it; single elements otherwise and at the end
+  const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0);
+  const int nvec = vec ? vocab / 4 : 0;
+  const float4* row4 = reinterpret_cast<const float4*>(row);
+  int i = threadIdx.x;
+  for (; i + 3 * (int)blockDim.x < nvec; i += 4 * blockDim.x) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcs(row4 + i + u * blockDim.x);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = 4 * (i + u * (int)blockDim.x);
+      take(v[u].x, e);
+      take(v[u].y, e + 1);
+      take(v[u].z, e + 2);
+      take(v[u].w, e + 3);
+    }
   }
+  for (; i < nvec; i += blockDim.x) {
+    const float4 v = __ldcs(row4 + i);
+    take(v.x, 4 * i);
+    take(v.y, 4 * i + 1);
+    take(v.z, 4 * i + 2);
+    take(v.w, 4 * i + 3);
+  }
+  for (int e = 4 * nvec + threadIdx.x; e < vocab; e += blockDim.x) take(row[e], e);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, off);
@@ -277,7 +302,7 @@ std::string argmax_pack(const float* logits, int64_t ld, int tokens, int vocab, 
   if (nranks < 1 || nranks > kMaxRanks || rank < 0 || rank >= nranks) return "rank / nranks out of range";
   if (vocab < 1 || (int64_t)index_base + vocab > (1 << 24)) return "vocabulary indices must stay below 2^24";
   if (tokens == 0) return "";
-  launch_chained(argmax_pack_kernel, dim3(tokens), dim3(256), 0, stream, logits, ld, vocab, index_base, rank, nranks, pack);
+  launch_chained(argmax_pack_kernel, dim3(tokens), dim3(vocab >= 8192 ? 1024 : 256), 0, stream, logits, ld, vocab, index_base, rank, nranks, pack);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }
