@@ -38,19 +38,25 @@ def test_pair_gemm_fp8_unscaled():
     assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
 
 
-@pytest.mark.parametrize("m,n,k", [(2304, 2560, 512), (2304, 2560, 2048), (2100, 2500, 1024), (2048, 3584, 1024)])
+@pytest.mark.parametrize("m,n,k", [(2304, 2560, 512), (2304, 2560, 2048), (2100, 2500, 4096), (2048, 3584, 8192),
+                                   (2048, 4096, 14336)])
 def test_partly_filled_last_round_is_split_along_k(m, n, k):
-    """More tiles than CTA pairs with a remainder: the tail tiles are cut along K, summed in the fp32 scratch and
-    finished by the last arriver. Two calls in a row: the second finds scratch and counters as the first left them."""
+    """More tiles than CTA pairs with a remainder: where K is long enough to pay for it the tail tiles are cut along
+    K, every piece stores its partial tile in a scratch slice and the last arriver adds them up. The scratch may hold
+    anything beforehand (NaN here); two calls in a row: the second finds the counters as the first left them."""
     g = torch.Generator(device="cuda").manual_seed(m + n + k)
     a = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
     w = (torch.randn(n, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
     ref = a.float() @ w.float().t()
+    gemm._pair_scratch(a.device).fill_(float("nan"))
+    outs = []
     for _ in range(2):
         out = gemm.linear(a, w, cta_pair=True)
         torch.cuda.synchronize()
         assert gemm.pipeline_status() == 0
         err = (out.float() - ref).abs().max().item()
         assert err <= 2e-2 * ref.abs().max().item() + 1e-2, err
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]), "the sum must not depend on which piece arrives last"
     ws, counters, _ = gemm._workspace(a.device)
     assert int(counters.abs().sum()) == 0 and float(ws.abs().max()) == 0.0

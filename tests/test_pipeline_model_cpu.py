@@ -10,8 +10,8 @@ models replay the role programs of
    two accumulator buffers handed between the MMA thread and the epilogue warps;
  * the tensor-core decode attention kernel (csrc/attention_decode_tc.cu): K/V ring, double-buffered
    scores, one probability tile, one P*V buffer;
- * the prompt attention kernel (csrc/attention_prefill_tc.cu): separate K and V rings, double-buffered
-   scores, two probability tiles, the output accumulated in tensor memory across all chunks;
+ * the prompt attention kernel (csrc/attention_prefill_tc.cu): separate K and V rings, two softmax groups on
+   alternate chunks, each with its score buffer, probability tile and accumulator in tensor memory;
  * the CTA-pair GEMM (csrc/gemm_pair.cu): two producers crediting the leader's transaction-counting
    barriers, stages released in both CTAs by the leader's MMA thread, a persistent tile loop with two
    accumulator buffers that the epilogue warps of BOTH CTAs hand back to the leader
@@ -399,10 +399,11 @@ def test_cta_pair_gemm_pipeline(nkb, stages):
 
 
 # ---- prompt attention (csrc/attention_prefill_tc.cu) ------------------------------------------------------
-# K ring (freed when the scores of the chunk are complete) and V ring (freed when P*V is complete) run apart;
-# O accumulates in tensor memory over all chunks. The probabilities of chunk i go through tile i & 1, so the softmax
-# threads wait for the P*V product of chunk i - 2 before they write (barrier pv_done[i & 1]), never for the one of
-# chunk i - 1 - except before the rare rescale of O, which needs every product issued so far to have completed.
+# K ring (freed when the scores of the chunk are complete) and V ring (freed when P*V is complete) run apart.
+# Two softmax groups: group g takes the chunks g, g + 2, ... with score buffer g, probability tile g and its own
+# accumulator O_g; before it rescales O_g or overwrites its probability tile for chunk i it waits for the P*V product
+# of chunk i - 2 (barrier pv_done[g], every phase observed exactly once). One more barrier, armed after the last
+# product, tells both groups that both accumulators are final.
 
 def prefill_attention(nchunks, stages_k, stages_v, rng):
     k_full = [MBar(1) for _ in range(stages_k)]
@@ -410,16 +411,17 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
     v_full = [MBar(1) for _ in range(stages_v)]
     v_free = [MBar(1) for _ in range(stages_v)]
     s_full = [MBar(1) for _ in range(2)]
-    n_sm = 3                                             # stands for the 128 softmax threads
+    n_sm = 2                                             # stands for the 128 softmax threads of a group
     s_free = [MBar(n_sm) for _ in range(2)]
     p_full = [MBar(n_sm) for _ in range(2)]
     pv_done = [MBar(1) for _ in range(2)]
+    o_final = MBar(1)
     kbuf, vbuf = [None] * stages_k, [None] * stages_v
     k_reads, v_reads = [0] * stages_k, [0] * stages_v
     s_buf, s_readers = [None, None], [0, 0]
     p_tile = [{"rows": [None] * n_sm, "reads_pending": 0} for _ in range(2)]
-    o_acc = {"chunks": [], "mma_pending": 0, "rescaling": 0}
-    seen = [[] for _ in range(n_sm)]
+    o_acc = [{"chunks": [], "mma_pending": 0, "rescaling": 0} for _ in range(2)]
+    seen = [[[] for _ in range(n_sm)] for _ in range(2)]
     events = {"tma": [], "mma": []}
 
     def load_k(c):
@@ -454,20 +456,22 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
 
     def issue_pv(c):
         s = c % stages_v
-        t = p_tile[c & 1]
+        t, o = p_tile[c & 1], o_acc[c & 1]
         assert vbuf[s] == c and t["rows"] == [c] * n_sm, f"P*V of chunk {c}: V holds {vbuf[s]}, P holds {t['rows']}"
-        assert o_acc["rescaling"] == 0, "P*V issued while a softmax thread rescales O"
+        assert o["rescaling"] == 0, "P*V issued while a softmax thread rescales its accumulator"
         v_reads[s] += 1
         t["reads_pending"] += 1
-        o_acc["mma_pending"] += 1
+        o["mma_pending"] += 1
 
         def retire():
-            o_acc["chunks"].append(c)
-            o_acc["mma_pending"] -= 1
+            o["chunks"].append(c)
+            o["mma_pending"] -= 1
             v_reads[s] -= 1
             t["reads_pending"] -= 1
             pv_done[c & 1].arrive()
             v_free[s].arrive()
+            if c + 1 == nchunks:
+                o_final.arrive()
         events["mma"].append(retire)
 
     def mma():
@@ -496,37 +500,38 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
             issue_pv(i)
             yield ("step",)
 
-    def softmax(who):
-        for i in range(nchunks):
-            buf = i & 1
-            yield from wait(s_full[buf], (i >> 1) & 1)
-            s_readers[buf] += 1
+    def softmax(g, who):
+        mine = list(range(g, nchunks, 2))
+        for i in mine:
+            yield from wait(s_full[g], (i >> 1) & 1)
+            s_readers[g] += 1
             yield ("step",)
-            assert s_buf[buf] == i, f"softmax of chunk {i} read scores of {s_buf[buf]}"
-            s_readers[buf] -= 1
-            s_free[buf].arrive()
-            if i > 0 and rng.random() < 0.3:            # the rare rescale of O in tensor memory
-                yield from wait(pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1)
-                assert o_acc["chunks"] == list(range(i)) and o_acc["mma_pending"] == 0, "O not stable at the rescale point"
-                o_acc["rescaling"] += 1
-                yield ("step",)
-                o_acc["rescaling"] -= 1
+            assert s_buf[g] == i, f"softmax of chunk {i} read scores of {s_buf[g]}"
+            s_readers[g] -= 1
+            s_free[g].arrive()
             if i >= 2:
-                yield from wait(pv_done[buf], ((i >> 1) - 1) & 1)
-            assert p_tile[buf]["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
+                yield from wait(pv_done[g], ((i >> 1) - 1) & 1)
+                if rng.random() < 0.3:                  # the rare rescale of O_g in tensor memory
+                    assert o_acc[g]["chunks"] == list(range(g, i, 2)) and o_acc[g]["mma_pending"] == 0, "O_g not stable"
+                    o_acc[g]["rescaling"] += 1
+                    yield ("step",)
+                    o_acc[g]["rescaling"] -= 1
+            assert p_tile[g]["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
             yield ("step",)
-            p_tile[buf]["rows"][who] = i
-            seen[who].append(i)
-            p_full[buf].arrive()
-        yield from wait(pv_done[(nchunks - 1) & 1], ((nchunks - 1) >> 1) & 1)
-        assert o_acc["chunks"] == list(range(nchunks))
+            p_tile[g]["rows"][who] = i
+            seen[g][who].append(i)
+            p_full[g].arrive()
+        yield from wait(o_final, 0)
+        assert o_acc[0]["chunks"] == list(range(0, nchunks, 2)) and o_acc[1]["chunks"] == list(range(1, nchunks, 2))
+        assert o_acc[0]["mma_pending"] == 0 and o_acc[1]["mma_pending"] == 0
 
-    run([mma()] + [softmax(w) for w in range(n_sm)], events, rng)
-    assert all(x == list(range(nchunks)) for x in seen)
+    run([mma()] + [softmax(g, w) for g in range(2) for w in range(n_sm)], events, rng)
+    for g in range(2):
+        assert all(x == list(range(g, nchunks, 2)) for x in seen[g])
 
 
 @pytest.mark.parametrize("stages", [(2, 2), (2, 3), (3, 3)])
-@pytest.mark.parametrize("nchunks", [1, 2, 3, 4, 5, 7, 16, 32])
+@pytest.mark.parametrize("nchunks", [2, 4, 6, 8, 16, 32])
 def test_prefill_attention_pipeline(nchunks, stages):
     for seed in range(40):
         prefill_attention(nchunks, stages[0], stages[1], random.Random(seed))

@@ -46,8 +46,9 @@ Policy& policy() {
     Policy q{};
     for (int n = 0; n <= kMaxRanks; ++n) {
       // Egress of the one-shot push grows with (n-1) x message, so its range shrinks with n.
-      // measured on 8 x B200 (benchmarks/bench_fused_allreduce.py); 4 ranks interpolated
-      q.oneshot_max_bytes[n] = n <= 2 ? (4u << 20) : n <= 4 ? (1u << 20) : (512u << 10);
+      // measured on 8 x B200 (benchmarks/bench_fused_allreduce.py) at 2 and 8 ranks; at 4 ranks the two-shot was
+      // already ahead at 1 MiB (15.1 against 15.3 us) before its result hop went through multimem.st
+      q.oneshot_max_bytes[n] = n <= 2 ? (4u << 20) : (512u << 10);
       q.lamport_max_bytes[n] = 12u << 20;
       // in-switch reduction pays off once N-1 peers' worth of traffic is saved: never at 2 ranks
       q.nvls_min_bytes[n] = n <= 2 ? ~0ull : n <= 4 ? (32ull << 20) : (12ull << 20);

@@ -6,18 +6,21 @@
 //   O[q 128, d 128]  += P[q, keys] * V[keys, d]         P written by the softmax warps (K-major over keys),
 //                                                       V read MN-major (d contiguous) straight from its TMA tile
 //
-// Four softmax warps, one query row per thread: a thread fetches its 64 scores of a chunk with ONE
-// tcgen05.ld and gives the score buffer back at once (S is double-buffered, so the scores of chunk c+1
-// are computed while chunk c is in the softmax). The probabilities go through TWO shared-memory tiles, so
-// the softmax of chunk c+1 never waits for the P*V product of chunk c: the softmax warps run back to back
-// and the tensor core trails them (a softmax that waited for its own P*V spent more than half of every
-// chunk in the latency of that round trip). O stays in tensor memory and is accumulated there by
-// the P*V products of all chunks. A row's running maximum is only raised - and its row of O rescaled in
-// tensor memory, after the products issued so far have completed - when the new maximum exceeds it by
-// more than 2^8 (a warp-uniform decision); until then the probabilities are taken against the older
-// maximum, which changes neither O / l nor the accuracy of bf16 probabilities below 256. A fifth warp
-// issues the TMA copies (three-stage rings for K, freed as soon as the scores are computed, and for V,
-// freed after P*V) and all MMAs.
+// Two softmax warpgroups of four warps, one query row per thread in each: group g takes the chunks
+// c = g, g + 2, ... - score buffer g, probability tile g and its OWN output accumulator O_g in tensor
+// memory, with its own running maximum and sum - so two chunks are in the softmax at any time and every
+// scheduler has two warps to choose from (one warp per scheduler issued an instruction in one cycle out of
+// five: the softmax is a latency chain, not a throughput limit). At the end both groups combine
+// O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)), each writing one half of
+// the head dimension. A thread fetches its 64 scores of a chunk with ONE tcgen05.ld and gives the score
+// buffer back at once. A group waits for the tensor core only where it must: before it overwrites its
+// probability tile (and before it rescales O_g) the P*V product of ITS previous chunk must have
+// completed, which by then it long has. A row's running maximum is only raised - and its row of O_g
+// rescaled in tensor memory - when the new maximum exceeds it by more than 2^8 (a warp-uniform
+// decision); until then the probabilities are taken against the older maximum, which changes neither
+// O / l nor the accuracy of bf16 probabilities below 256. A ninth warp issues the TMA copies
+// (three-stage rings for K, freed as soon as the scores are computed, and for V, freed after P*V) and all
+// MMAs.
 //
 // Every wait is bounded; a wait that runs out records a status word and raises the CTA's abort flag,
 // and all threads still reach the common exit. Not part of the reference (it has no attention).
@@ -43,20 +46,20 @@ constexpr int kRows = 128;                        // query rows per CTA
 constexpr int kKeys = 64;                         // key positions per chunk
 constexpr int kStagesK = 3;
 constexpr int kStagesV = 3;
-constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = kSoftmaxThreads + 32;
-constexpr int kMmaWarp = kSoftmaxThreads / 32;
+constexpr int kSoftmaxThreads = 128;              // per warpgroup; two groups
+constexpr int kThreads = 2 * kSoftmaxThreads + 32;
+constexpr int kMmaWarp = 2 * kSoftmaxThreads / 32;
 constexpr int kQHalfBytes = kRows * 128;          // 64 head-dimension columns of the 128 query rows
 constexpr int kQBytes = 2 * kQHalfBytes;
 constexpr int kKVHalfBytes = kKeys * 128;         // 64 head-dimension columns of the 64 positions of a chunk
 constexpr int kKVBytes = 2 * kKVHalfBytes;        // one K chunk or one V chunk
 constexpr int kPBytes = kRows * kKeys * 2;        // probabilities of a chunk: one 64-key K block of 128 rows
-constexpr int kNumBarriers = 2 * kStagesK + 2 * kStagesV + 4 + 5;   // k/v full+free, s full+free [2], q_full, p_full [2], pv_done [2]
+constexpr int kNumBarriers = 2 * kStagesK + 2 * kStagesV + 4 + 6;   // k/v full+free, s full+free [2], q_full, p_full [2], pv_done [2], o_final
 constexpr int kBarrierBytes = 256;                // the mbarriers, the TMEM address and the abort flag
 static_assert(kNumBarriers * 8 + 8 <= kBarrierBytes, "barrier area too small");
 constexpr int kSmem = kQBytes + 2 * kPBytes + (kStagesK + kStagesV) * kKVBytes + kBarrierBytes;
 static_assert(kSmem <= 227 * 1024, "shared memory of one CTA");
-constexpr uint32_t kTmemCols = 256;               // S buffers at columns 0 and 64, O at 128
+constexpr uint32_t kTmemCols = 512;               // S buffers at columns 0 and 64, O_0 at 128, O_1 at 256
 constexpr uint32_t kColO = 128;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr float kRescaleThreshold = 8.f;          // log2 units
@@ -99,7 +102,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* q_full = s_free + 2;
   uint64_t* p_full = q_full + 1;            // [2]: probabilities of chunk c are in tile c & 1
   uint64_t* pv_done = p_full + 2;           // [2]: the P*V product that read tile c & 1 has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* o_final = pv_done + 2;          // every product has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_final + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   // The blocks with the most key chunks start first, for all heads (blockIdx.x runs fastest): the short blocks of
@@ -130,6 +134,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc::mbar_init(&p_full[i], kSoftmaxThreads);
       tc::mbar_init(&pv_done[i], 1);
     }
+    tc::mbar_init(o_final, 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
     tc::tma_prefetch_desc(&map_q);
@@ -179,15 +184,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc::umma_commit(&s_full[c & 1]);
         tc::umma_commit(&k_free[c % kStagesK]);
       };
-      auto issue_pv = [&](int c) {       // O (+)= P * V chunk, 16 key positions per instruction
+      auto issue_pv = [&](int c) {       // O_(c & 1) (+)= P * V chunk, 16 key positions per instruction
         const uint32_t vbase = tc::smem_u32(v_ring + (c % kStagesV) * kKVBytes);
         const uint32_t pbase = tc::smem_u32(p_tile + (c & 1) * kPBytes);
 #pragma unroll
         for (int j = 0; j < kKeys / 16; ++j)
-          tc::umma<false>(tmem_base + kColO, tc::make_smem_desc_sw128(pbase) + (uint64_t)(j * 2),
-                          tc::make_smem_desc_mn_sw128(vbase + j * 2048, kKVHalfBytes), a.idesc_pv, (c | j) ? 1u : 0u);
+          tc::umma<false>(tmem_base + kColO + (uint32_t)(c & 1) * kD, tc::make_smem_desc_sw128(pbase) + (uint64_t)(j * 2),
+                          tc::make_smem_desc_mn_sw128(vbase + j * 2048, kKVHalfBytes), a.idesc_pv, (c >= 2 || j > 0) ? 1u : 0u);
         tc::umma_commit(&pv_done[c & 1]);
         tc::umma_commit(&v_free[c % kStagesV]);
+        if (c + 1 == nchunks) tc::umma_commit(o_final);
       };
       tc::mbar_arrive_expect_tx(q_full, kQBytes);
       tc::tma_load_3d(q_tile, &map_q, q_full, 0, h, q0);
@@ -230,50 +236,54 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!ok) fail();
     }
   } else {
-    // ---- softmax warps: thread t owns query row q0 + t ----
+    // ---- softmax warps: group g = warp / 4 takes the chunks g, g + 2, ...; its thread t owns query row q0 + t ----
     // A thread whose wait ran out keeps walking the loop (its waits return at once because the abort flag is up),
-    // so that the warp-wide tensor-memory instructions below are always executed by whole warps.
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const int q_pos = q0 + tid;
-    float m_run = -FLT_MAX, l_run = 0.f;
+    // so that the warp-wide tensor-memory instructions and the named barrier below are always executed by all.
+    const int g = warp >> 2;
+    const int t = tid & (kSoftmaxThreads - 1);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t o_addr = lane_addr + kColO + (uint32_t)g * kD;
+    const int q_pos = q0 + t;
+    float m_run = -1e30f, l_run = 0.f;
     bool ok = true;
-    for (int i = 0; i < nchunks; ++i) {
-      const int buf = i & 1;
-      if (!tc::mbar_wait(&s_full[buf], (i >> 1) & 1, kWaitLimit, abort_flag) && ok) {
+    for (int i = g; i < nchunks; i += 2) {
+      if (!tc::mbar_wait(&s_full[g], (i >> 1) & 1, kWaitLimit, abort_flag) && ok) {
         ok = false;
         fail();
       }
       tc::fence_after_thread_sync();
       uint32_t sv[kKeys];
-      tc::tmem_ld_x64(lane_addr + (uint32_t)buf * kKeys, sv);
+      tc::tmem_ld_x64(lane_addr + (uint32_t)g * kKeys, sv);
       tc::fence_before_thread_sync();
-      tc::mbar_arrive(&s_free[buf]);            // the scores are in registers: the buffer can take chunk i + 2
+      tc::mbar_arrive(&s_free[g]);              // the scores are in registers: the buffer can take chunk i + 2
       const int key0 = i * kKeys;
       const bool diagonal = key0 + kKeys - 1 > q0;   // the last two chunks cross the causal boundary of some row
       // row maximum of the raw scores, masked where the key lies after the query; the softmax scale (times log2 e)
       // is positive, so it commutes with the maximum and is folded into the exponent's multiply-add below
-      float cmax = -FLT_MAX;
+      if (diagonal) {
 #pragma unroll
-      for (int j = 0; j < kKeys; ++j) {
-        float x = __uint_as_float(sv[j]);
-        if (diagonal && key0 + j > q_pos) {
-          x = -FLT_MAX;
-          sv[j] = __float_as_uint(x);
-        }
-        cmax = fmaxf(cmax, x);
+        for (int j = 0; j < kKeys; ++j)
+          if (key0 + j > q_pos) sv[j] = __float_as_uint(-FLT_MAX);
       }
-      cmax *= a.scale_log2;                     // in units of log2 from here on
-      if (i == 0) {
-        m_run = cmax;                           // key 0 is live for every row, so this is finite
+      float cm[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};   // four chains instead of one of 64 dependent maxima
+#pragma unroll
+      for (int j = 0; j < kKeys; j += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cm[u] = fmaxf(cm[u], __uint_as_float(sv[j + u]));
+      }
+      // in units of log2 from here on; a chunk that the mask removes entirely for this row (the group of the odd
+      // chunks, first rows of the prompt) must not become the reference: keep the maximum above -1e30
+      const float cmax = fmaxf(fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3])) * a.scale_log2, -1e30f);
+      // this group's probability tile and O_g were last used by the P*V product of chunk i - 2
+      if (i >= 2 && !tc::mbar_wait(&pv_done[g], ((i >> 1) - 1) & 1, kWaitLimit, abort_flag) && ok) {
+        ok = false;
+        fail();
+      }
+      if (i < 2) {
+        m_run = cmax;
       } else {
         const bool grow = cmax - m_run > kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
-          // O may only be touched when every P*V product issued so far has completed: the latest one read the
-          // other probability tile (products complete in issue order)
-          if (!tc::mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, kWaitLimit, abort_flag) && ok) {
-            ok = false;
-            fail();
-          }
           tc::fence_after_thread_sync();
           const float f = grow ? ex2(m_run - cmax) : 1.f;
           if (grow) {
@@ -283,22 +293,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll 1
           for (int c = 0; c < kD; c += 32) {
             uint32_t ov[32];
-            tc::tmem_ld_x32(lane_addr + kColO + c, ov);
+            tc::tmem_ld_x32(o_addr + c, ov);
 #pragma unroll
             for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * f);
-            tc::tmem_st_x32(lane_addr + kColO + c, ov);
+            tc::tmem_st_x32(o_addr + c, ov);
           }
         }
       }
-      // this chunk's probability tile was last read by the P*V product of chunk i - 2
-      if (i >= 2 && !tc::mbar_wait(&pv_done[buf], ((i >> 1) - 1) & 1, kWaitLimit, abort_flag) && ok) {
-        ok = false;
-        fail();
-      }
       // probabilities against m_run, row sum, this row of the P tile (bf16, K-major over the 64 key positions,
       // 128-byte swizzle). A masked score is -FLT_MAX and comes out as zero.
-      float psum = 0.f;
-      uint8_t* row = p_tile + buf * kPBytes + tid * 128;
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+      uint8_t* row = p_tile + g * kPBytes + t * 128;
       const float neg_m = -m_run;
 #pragma unroll
       for (int cc = 0; cc < kKeys / 8; ++cc) {
@@ -307,39 +312,52 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int j = 0; j < 4; ++j) {
           const float p0 = ex2(fmaf(__uint_as_float(sv[cc * 8 + 2 * j]), a.scale_log2, neg_m));
           const float p1 = ex2(fmaf(__uint_as_float(sv[cc * 8 + 2 * j + 1]), a.scale_log2, neg_m));
-          psum += p0 + p1;
+          ps[j] += p0 + p1;
           __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           w[j] = *reinterpret_cast<uint32_t*>(&hh);
         }
-        *reinterpret_cast<uint4*>(row + ((cc ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(row + ((cc ^ (t & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l_run += psum;
+      l_run += (ps[0] + ps[1]) + (ps[2] + ps[3]);
       tc::fence_proxy_async();          // P was written by threads and is read by the tensor core
       tc::fence_before_thread_sync();   // orders the rescaled O (tcgen05.st) before the MMA that the arrival releases
-      tc::mbar_arrive(&p_full[buf]);
+      tc::mbar_arrive(&p_full[g]);
     }
-    // the last product completes after all the others
-    if (!tc::mbar_wait(&pv_done[(nchunks - 1) & 1], ((nchunks - 1) >> 1) & 1, kWaitLimit, abort_flag) && ok) {
+    // every product has completed: both accumulators are final and the probability tiles are free
+    if (!tc::mbar_wait(o_final, 0, kWaitLimit, abort_flag) && ok) {
       ok = false;
       fail();
     }
     tc::fence_after_thread_sync();
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    uint4* dst = reinterpret_cast<uint4*>(a.out + ((int64_t)q_pos * a.Hq + h) * kD);
+    // the two groups tell each other maximum and sum of their rows (through the first probability tile)
+    float2* ml = reinterpret_cast<float2*>(p_tile);
+    ml[g * kSoftmaxThreads + t] = make_float2(m_run, l_run);
+    tc::named_barrier_sync(1, 2 * kSoftmaxThreads);
+    const float2 other = ml[(g ^ 1) * kSoftmaxThreads + t];
+    const float m = fmaxf(m_run, other.x);
+    const float w_own = ex2(m_run - m), w_other = ex2(other.x - m);
+    const float l = l_run * w_own + other.y * w_other;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float w0 = (g == 0 ? w_own : w_other) * inv, w1 = (g == 0 ? w_other : w_own) * inv;
+    // group g writes the head-dimension columns 64 g .. 64 g + 63 of its rows
+    uint4* dst = reinterpret_cast<uint4*>(a.out + ((int64_t)q_pos * a.Hq + h) * kD + g * 64);
 #pragma unroll 1
-    for (int c = 0; c < kD; c += 32) {
-      uint32_t ov[32];
-      tc::tmem_ld_x32(lane_addr + kColO + c, ov);   // every lane of the warp takes part, rows beyond S included
+    for (int c = 0; c < 64; c += 32) {
+      uint32_t o0[32], o1[32];
+      tc::tmem_ld_x32(lane_addr + kColO + (uint32_t)(g * 64 + c), o0);        // every lane of the warp takes part,
+      tc::tmem_ld_x32(lane_addr + kColO + kD + (uint32_t)(g * 64 + c), o1);   // rows beyond S included
       if (ok && q_pos < a.S) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
+        for (int gg = 0; gg < 4; ++gg) {
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(ov[g * 8 + 2 * j]) * inv, __uint_as_float(ov[g * 8 + 2 * j + 1]) * inv);
+            const int e = gg * 8 + 2 * j;
+            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o0[e]) * w0 + __uint_as_float(o1[e]) * w1,
+                                                      __uint_as_float(o0[e + 1]) * w0 + __uint_as_float(o1[e + 1]) * w1);
             w[j] = *reinterpret_cast<uint32_t*>(&hh);
           }
-          dst[c / 8 + g] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[c / 8 + gg] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }

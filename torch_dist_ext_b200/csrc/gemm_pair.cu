@@ -10,8 +10,9 @@
 //
 // The grid is persistent: pair p walks the tiles p, p + pairs, ... (the x tile index runs fastest, so pairs that
 // work side by side share the Y tile in L2). When the last round would be partly filled, its tiles are cut along K
-// into 2-4 pieces, one piece per pair, summed in an fp32 scratch tile with red.global.add and finished by the CTA
-// that arrives last at its half of the tile - the idle pairs of the last round then share its work. The operand ring keeps streaming across tile boundaries and the
+// into 2-4 pieces, one piece per pair; every piece stores its fp32 partial tile in a scratch slice of its own and the
+// CTA that arrives last at its half of the tile adds the slices up - the idle pairs of the last round then share its
+// work. The operand ring keeps streaming across tile boundaries and the
 // accumulator is double-buffered in tensor memory (2 x 256 columns in each CTA): while the epilogue warps of both
 // CTAs read tile n back with tcgen05.ld and store it, the leader is already accumulating tile n + 1.
 //
@@ -66,9 +67,10 @@ struct PairArgs {
   int x_rows, y_rows, kblocks;
   int tiles_x, tiles_y;
   // Tail split: the tiles of the last, partly filled round (tail_first ...) are cut along K into tail_parts pieces of
-  // tail_kb K blocks each, one piece per pair, and summed through an fp32 scratch tile (0 parts: no split).
+  // tail_kb K blocks each, one piece per pair; every piece leaves its fp32 partial tile in its own slice of a scratch
+  // buffer and the piece that arrives last adds them up (0 parts: no split).
   int tail_first, tail_parts, tail_kb;
-  float* ws;               // [tail tiles][256 columns][256 rows] fp32, zero on entry and on exit
+  float* ws;               // [tail tiles][parts][256 columns][256 rows] fp32; contents undefined before and after
   uint32_t* counters;      // [tail tiles][2 CTAs of the pair], zero on entry and on exit
   void* out;
   int64_t sx, sy;
@@ -82,6 +84,7 @@ struct PairArgs {
 struct WorkItem {
   int tile, kb0, kb1;
   bool partial;
+  int part;
 };
 __device__ __forceinline__ bool work_item(const PairArgs& a, int pair, int npairs, int n, WorkItem* w) {
   const int ntiles = a.tiles_x * a.tiles_y;
@@ -89,7 +92,7 @@ __device__ __forceinline__ bool work_item(const PairArgs& a, int pair, int npair
   if (n < full_rounds) {
     const int t = pair + n * npairs;
     if (t >= ntiles) return false;
-    *w = WorkItem{t, 0, a.kblocks, false};
+    *w = WorkItem{t, 0, a.kblocks, false, 0};
     return true;
   }
   // split tail: unit u covers part u % parts of tail tile u / parts; a pair may get several units
@@ -97,7 +100,7 @@ __device__ __forceinline__ bool work_item(const PairArgs& a, int pair, int npair
   const int tile = a.tail_first + u / a.tail_parts, part = u % a.tail_parts;
   if (tile >= ntiles) return false;
   const int kb0 = part * a.tail_kb, kb1 = min(a.kblocks, kb0 + a.tail_kb);
-  *w = WorkItem{tile, kb0, kb1, true};
+  *w = WorkItem{tile, kb0, kb1, true, part};
   return true;
 }
 
@@ -247,17 +250,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         __syncwarp();
         if (lane == 0) tc::mbar_arrive_cluster(leader_acc_empty + buf * 8u);   // this warp has read its part of the buffer
       } else {
-        // A K range of a tail tile: add this CTA's 128 x 256 partial sums to the tile's fp32 scratch (column-major,
-        // so that a warp's lanes add to 32 consecutive floats), then the CTA that arrives last at its half of the
-        // tile turns the sums into the output and leaves scratch and counter zeroed for the next call.
+        // A K range of a tail tile: this CTA's 128 x 256 partial sums go to the piece's own slice of the scratch
+        // (column-major, so that a warp's lanes write 32 consecutive floats; plain stores - fp32 atomics on a
+        // shared tile cost several times the tile's own MMA time). The CTA that arrives last at its half of the
+        // tile adds the slices up, writes the output and re-zeroes the counter.
         const int rem = t - a.tail_first, half = (int)(rank & 1u);
-        float* tile_ws = a.ws + (size_t)rem * (kTileM * kTileN) + half * kRowsPerCta + q * 32 + lane;
+        const size_t slice = (size_t)kTileM * kTileN;
+        float* tile_ws = a.ws + (size_t)rem * a.tail_parts * slice + half * kRowsPerCta + q * 32 + lane;
+        float* mine = tile_ws + (size_t)w.part * slice;
 #pragma unroll 4
         for (int c = 0; c < kTileN; c += 16) {
           float v[16];
           tc::tmem_ld_16(lane_addr + buf * kTileN + c, v);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) atomicAdd(tile_ws + (size_t)(c + j) * kTileM, v[j]);
+          for (int j = 0; j < 16; ++j) __stcg(mine + (size_t)(c + j) * kTileM, v[j]);
         }
         tc::fence_before_thread_sync();
         __syncwarp();
@@ -271,13 +277,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tc::named_barrier_sync(1, 128);
         if (*last_flag) {
           __threadfence();
-#pragma unroll 2
+#pragma unroll 1
           for (int c = 0; c < kTileN; c += 16) {
             float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              v[j] = __ldcg(tile_ws + (size_t)(c + j) * kTileM);
-              __stcg(tile_ws + (size_t)(c + j) * kTileM, 0.f);
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int pp = 0; pp < a.tail_parts; ++pp) {     // in the order of the pieces: the sum does not depend on who is last
+              const float* src = tile_ws + (size_t)pp * slice;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (size_t)(c + j) * kTileM);
             }
             if (y_base + c < a.y_rows) store_chunk(a, x, y_base + c, v);
           }
@@ -344,17 +352,19 @@ std::string gemm_tn_pair(const GemmProblem& g, cudaStream_t stream) {
   const int pairs = (int)(ntiles < sms / 2 ? ntiles : sms / 2);
   const dim3 grid(2 * pairs, 1, 1);
   // Tail split: when the last round is partly filled, its tiles are cut along K into `parts` pieces so that the idle
-  // pairs share the work; the pieces meet in an fp32 scratch tile. parts minimises ceil(tail * parts / pairs) / parts
-  // (the time of the tail in tile-times) with a small charge per extra piece for the scratch traffic.
+  // pairs share the work; the pieces meet in fp32 scratch slices. parts minimises the time of the tail in tile-times,
+  // ceil(tail * parts / pairs) / parts, plus what a piece pays for the scratch (128 KB written per CTA, parts x 128 KB
+  // read by the one that adds up: about 2 + 1.5 x parts microseconds against 8.6 ns of tile time per unit of K).
   a.tail_first = (int)ntiles;
   a.tail_parts = 0;
   const int tail = (int)(ntiles % pairs);
-  if (tail > 0 && ntiles > pairs && g.ws != nullptr && g.counters != nullptr &&
-      (size_t)tail * kTileM * kTileN * sizeof(float) <= g.ws_bytes && (size_t)tail * 2 <= g.counter_count) {
+  if (tail > 0 && ntiles > pairs && g.ws != nullptr && g.counters != nullptr && (size_t)tail * 2 <= g.counter_count) {
+    const double tile_us = 8.6e-3 * (double)g.k;
     int best = 1;
-    double best_cost = 1.0;
+    double best_cost = 0.97;      // the unsplit tail costs one tile time; a split has to win by a margin
     for (int parts = 2; parts <= 4 && a.kblocks / parts >= 4; ++parts) {
-      const double cost = (double)((tail * parts + pairs - 1) / pairs) / parts + 0.04 * (parts - 1);
+      if ((size_t)tail * parts * kTileM * kTileN * sizeof(float) > g.ws_bytes) break;
+      const double cost = (double)((tail * parts + pairs - 1) / pairs) / parts + (2.0 + 1.5 * parts) / tile_us;
       if (cost < best_cost - 1e-9) {
         best_cost = cost;
         best = parts;

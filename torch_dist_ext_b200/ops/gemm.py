@@ -36,6 +36,18 @@ def _workspace(device: torch.device):
     return _ws[key]
 
 
+_pair_ws = {}
+
+
+def _pair_scratch(device: torch.device) -> torch.Tensor:
+    """Scratch of the CTA-pair kernel's tail split: fp32 partial tiles, contents undefined between calls (unlike the
+    split-K scratch above, which every kernel leaves zeroed)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _pair_ws:
+        _pair_ws[key] = torch.empty(20 << 20, dtype=torch.float32, device=device)      # 80 MiB: 73 tiles x 4 pieces
+    return _pair_ws[key]
+
+
 def pipeline_status(device=None) -> int:
     """Non-zero if a GEMM pipeline wait ever ran out on this device (reads the device word)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -86,8 +98,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
         if out is None:
             dt = out_dtype or (torch.bfloat16 if a.element_size() == 1 else a.dtype)
             out = torch.empty(m, n, dtype=dt, device=a.device)
-        ws, counters, status = _workspace(a.device)
-        _lib.ops().gemm_tn_pair(a, w, out, n, 1, status, ws, counters)   # scratch: K-split of a partly filled last round
+        _, counters, status = _workspace(a.device)
+        _lib.ops().gemm_tn_pair(a, w, out, n, 1, status, _pair_scratch(a.device), counters)   # K-split of a partly filled last round
         return out
     if (use_persistent or (use_pair and persistent is None and _PERSIST_DEFAULT)) and m > 128 and n >= 256 and not swap \
             and splits in (None, 1):
