@@ -400,10 +400,12 @@ def test_cta_pair_gemm_pipeline(nkb, stages):
 
 # ---- prompt attention (csrc/attention_prefill_tc.cu) ------------------------------------------------------
 # K ring (freed when the scores of the chunk are complete) and V ring (freed when P*V is complete) run apart.
-# Two softmax groups: group g takes the chunks g, g + 2, ... with score buffer g, probability tile g and its own
-# accumulator O_g; before it rescales O_g or overwrites its probability tile for chunk i it waits for the P*V product
-# of chunk i - 2 (barrier pv_done[g], every phase observed exactly once). One more barrier, armed after the last
-# product, tells both groups that both accumulators are final.
+# Two softmax groups: group g takes the chunks g, g + 2, ... with score buffer g, its own accumulator O_g and TWO
+# probability tiles (chunk i uses tile i % 4): before it overwrites the tile for chunk i it waits for the P*V product
+# of chunk i - 4, and before the rare rescale of O_g for the product of chunk i - 2 (barriers pv_done[0..3], no phase
+# skipped by any waiter). One more barrier, armed by both P*V issuers after their last product, tells both groups
+# that both accumulators are final. Copies, the score MMAs of the even and of the odd chunks, and the P*V
+# MMAs into each accumulator are issued by five threads with a chain of waits each.
 
 def prefill_attention(nchunks, stages_k, stages_v, rng):
     k_full = [MBar(1) for _ in range(stages_k)]
@@ -413,16 +415,18 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
     s_full = [MBar(1) for _ in range(2)]
     n_sm = 2                                             # stands for the 128 softmax threads of a group
     s_free = [MBar(n_sm) for _ in range(2)]
-    p_full = [MBar(n_sm) for _ in range(2)]
-    pv_done = [MBar(1) for _ in range(2)]
-    o_final = MBar(1)
+    p_full = [MBar(n_sm) for _ in range(4)]             # chunk c uses probability tile c % 4: two tiles per group
+    pv_done = [MBar(1) for _ in range(4)]
+    o_final = MBar(2)                                   # one arrival per P*V issuer
+    turn = [MBar(2 * n_sm) for _ in range(2)]           # named barriers: group g's turn at the exponentials
+    in_exp = [0, 0]
     kbuf, vbuf = [None] * stages_k, [None] * stages_v
     k_reads, v_reads = [0] * stages_k, [0] * stages_v
     s_buf, s_readers = [None, None], [0, 0]
-    p_tile = [{"rows": [None] * n_sm, "reads_pending": 0} for _ in range(2)]
+    p_tile = [{"rows": [None] * n_sm, "reads_pending": 0} for _ in range(4)]
     o_acc = [{"chunks": [], "mma_pending": 0, "rescaling": 0} for _ in range(2)]
     seen = [[[] for _ in range(n_sm)] for _ in range(2)]
-    events = {"tma": [], "mma": []}
+    events = {"tma": [], "mma_s0": [], "mma_s1": [], "mma_pv0": [], "mma_pv1": []}   # an issuer's MMAs complete in its issue order
 
     def load_k(c):
         s = c % stages_k
@@ -452,11 +456,11 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
             k_reads[s] -= 1
             s_full[c & 1].arrive()
             k_free[s].arrive()
-        events["mma"].append(retire)
+        events["mma_s%d" % (c & 1)].append(retire)
 
     def issue_pv(c):
         s = c % stages_v
-        t, o = p_tile[c & 1], o_acc[c & 1]
+        t, o = p_tile[c & 3], o_acc[c & 1]
         assert vbuf[s] == c and t["rows"] == [c] * n_sm, f"P*V of chunk {c}: V holds {vbuf[s]}, P holds {t['rows']}"
         assert o["rescaling"] == 0, "P*V issued while a softmax thread rescales its accumulator"
         v_reads[s] += 1
@@ -468,69 +472,83 @@ def prefill_attention(nchunks, stages_k, stages_v, rng):
             o["mma_pending"] -= 1
             v_reads[s] -= 1
             t["reads_pending"] -= 1
-            pv_done[c & 1].arrive()
+            pv_done[c & 3].arrive()
             v_free[s].arrive()
-            if c + 1 == nchunks:
+            if c + 2 >= nchunks:
                 o_final.arrive()
-        events["mma"].append(retire)
+        events["mma_pv%d" % (c & 1)].append(retire)
 
-    def mma():
+    def loader():
         for c in range(min(nchunks, stages_k)):
             load_k(c)
         for c in range(min(nchunks, stages_v)):
             load_v(c)
-        yield from wait(k_full[0], 0)
-        issue_scores(0)
-        for i in range(nchunks):
-            if i + 1 < nchunks:
-                n = i + 1
-                yield from wait(k_full[n % stages_k], (n // stages_k) & 1)
-                if n >= 2:
-                    yield from wait(s_free[n & 1], ((n >> 1) - 1) & 1)
-                issue_scores(n)
-                yield ("step",)
-            if i + stages_k < nchunks:
-                yield from wait(k_free[i % stages_k], (i // stages_k) & 1)
-                load_k(i + stages_k)
-            if i >= 1 and i - 1 + stages_v < nchunks:
-                yield from wait(v_free[(i - 1) % stages_v], ((i - 1) // stages_v) & 1)
-                load_v(i - 1 + stages_v)
-            yield from wait(p_full[i & 1], (i >> 1) & 1)
-            yield from wait(v_full[i % stages_v], (i // stages_v) & 1)
-            issue_pv(i)
+        for j in range(nchunks + 2):
+            if j + stages_k < nchunks:
+                yield from wait(k_free[j % stages_k], (j // stages_k) & 1)
+                load_k(j + stages_k)
+            i = j - 2
+            if i >= 0 and i + stages_v < nchunks:
+                yield from wait(v_free[i % stages_v], (i // stages_v) & 1)
+                load_v(i + stages_v)
+            yield ("step",)
+
+    def score_issuer(first):
+        for c in range(first, nchunks, 2):
+            yield from wait(k_full[c % stages_k], (c // stages_k) & 1)
+            if c >= 2:
+                yield from wait(s_free[c & 1], ((c >> 1) - 1) & 1)
+            issue_scores(c)
+            yield ("step",)
+
+    def pv_issuer(first):
+        for c in range(first, nchunks, 2):
+            yield from wait(p_full[c & 3], (c >> 2) & 1)
+            yield from wait(v_full[c % stages_v], (c // stages_v) & 1)
+            issue_pv(c)
             yield ("step",)
 
     def softmax(g, who):
         mine = list(range(g, nchunks, 2))
-        for i in mine:
+        if g == 1:
+            turn[0].arrive()                            # group 0 has the first turn
+        for it, i in enumerate(mine):
             yield from wait(s_full[g], (i >> 1) & 1)
             s_readers[g] += 1
             yield ("step",)
             assert s_buf[g] == i, f"softmax of chunk {i} read scores of {s_buf[g]}"
             s_readers[g] -= 1
             s_free[g].arrive()
-            if i >= 2:
-                yield from wait(pv_done[g], ((i >> 1) - 1) & 1)
-                if rng.random() < 0.3:                  # the rare rescale of O_g in tensor memory
-                    assert o_acc[g]["chunks"] == list(range(g, i, 2)) and o_acc[g]["mma_pending"] == 0, "O_g not stable"
-                    o_acc[g]["rescaling"] += 1
-                    yield ("step",)
-                    o_acc[g]["rescaling"] -= 1
-            assert p_tile[g]["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
+            if i >= 2 and rng.random() < 0.3:           # the rare rescale of O_g: the group's latest product must be done
+                yield from wait(pv_done[(i - 2) & 3], ((i - 2) >> 2) & 1)
+                assert o_acc[g]["chunks"] == list(range(g, i, 2)) and o_acc[g]["mma_pending"] == 0, "O_g not stable"
+                o_acc[g]["rescaling"] += 1
+                yield ("step",)
+                o_acc[g]["rescaling"] -= 1
+            if i >= 4:
+                yield from wait(pv_done[i & 3], ((i >> 2) - 1) & 1)
+            turn[g].arrive()                            # bar.sync: arrive and wait for the phase
+            yield from wait(turn[g], it & 1)
+            assert in_exp[g ^ 1] == 0, "both groups in their exponential phase"
+            in_exp[g] += 1
+            assert p_tile[i & 3]["reads_pending"] == 0, "P tile overwritten while an MMA reads it"
             yield ("step",)
-            p_tile[g]["rows"][who] = i
+            p_tile[i & 3]["rows"][who] = i
             seen[g][who].append(i)
-            p_full[g].arrive()
+            in_exp[g] -= 1
+            if g == 0 or i + 2 < nchunks:
+                turn[g ^ 1].arrive()                    # bar.arrive: the other group's turn
+            p_full[i & 3].arrive()
         yield from wait(o_final, 0)
         assert o_acc[0]["chunks"] == list(range(0, nchunks, 2)) and o_acc[1]["chunks"] == list(range(1, nchunks, 2))
         assert o_acc[0]["mma_pending"] == 0 and o_acc[1]["mma_pending"] == 0
 
-    run([mma()] + [softmax(g, w) for g in range(2) for w in range(n_sm)], events, rng)
+    run([loader(), score_issuer(0), score_issuer(1), pv_issuer(0), pv_issuer(1)] + [softmax(g, w) for g in range(2) for w in range(n_sm)], events, rng)
     for g in range(2):
         assert all(x == list(range(g, nchunks, 2)) for x in seen[g])
 
 
-@pytest.mark.parametrize("stages", [(2, 2), (2, 3), (3, 3)])
+@pytest.mark.parametrize("stages", [(2, 2), (2, 3), (4, 4)])
 @pytest.mark.parametrize("nchunks", [2, 4, 6, 8, 16, 32])
 def test_prefill_attention_pipeline(nchunks, stages):
     for seed in range(40):

@@ -140,7 +140,9 @@ def write_ninja() -> Path:
     for flavour, (define, lib_path) in FLAVOURS.items():
         flavour_objs = []
         # the tracing flavour instruments the real launches only; the single-GPU emulation is shared
-        own_unit = (lambda stem: stem.startswith("ar_inst_") and not (flavour == "trace" and stem.endswith("_emu")))
+        # (and, in the tracing flavour, the prompt attention kernel with its per-role clock stamps)
+        own_unit = (lambda stem: (stem.startswith("ar_inst_") and not (flavour == "trace" and stem.endswith("_emu")))
+                    or (flavour == "trace" and stem == "attention_prefill_tc"))
         for obj in objs:
             if own_unit(obj[:-2]):
                 flavour_objs.append(obj.replace(".o", f".{flavour}.o", 1))

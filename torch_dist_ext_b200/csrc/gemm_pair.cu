@@ -277,17 +277,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tc::named_barrier_sync(1, 128);
         if (*last_flag) {
           __threadfence();
+          // 64 columns at a time: all loads of a piece are issued before the first add waits for one, and before the
+          // stores of the group (which the compiler must assume to alias the scratch) - the pass is bound by how many
+          // loads are in flight, not by bytes
 #pragma unroll 1
-          for (int c = 0; c < kTileN; c += 16) {
-            float v[16];
+          for (int c = 0; c < kTileN; c += 64) {
+            float v[64];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int j = 0; j < 64; ++j) v[j] = 0.f;
             for (int pp = 0; pp < a.tail_parts; ++pp) {     // in the order of the pieces: the sum does not depend on who is last
-              const float* src = tile_ws + (size_t)pp * slice;
+              const float* src = tile_ws + (size_t)pp * slice + (size_t)c * kTileM;
+              float in[64];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] += __ldcg(src + (size_t)(c + j) * kTileM);
+              for (int j = 0; j < 64; ++j) in[j] = __ldcg(src + (size_t)j * kTileM);
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] += in[j];
             }
-            if (y_base + c < a.y_rows) store_chunk(a, x, y_base + c, v);
+#pragma unroll
+            for (int cc = 0; cc < 64; cc += 16) {
+              float o[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) o[j] = v[cc + j];
+              if (y_base + c + cc < a.y_rows) store_chunk(a, x, y_base + c + cc, o);
+            }
           }
           if (threadIdx.x == 64) a.counters[rem * 2 + half] = 0;
         }
@@ -353,18 +365,19 @@ std::string gemm_tn_pair(const GemmProblem& g, cudaStream_t stream) {
   const dim3 grid(2 * pairs, 1, 1);
   // Tail split: when the last round is partly filled, its tiles are cut along K into `parts` pieces so that the idle
   // pairs share the work; the pieces meet in fp32 scratch slices. parts minimises the time of the tail in tile-times,
-  // ceil(tail * parts / pairs) / parts, plus what a piece pays for the scratch (128 KB written per CTA, parts x 128 KB
-  // read by the one that adds up: about 2 + 1.5 x parts microseconds against 8.6 ns of tile time per unit of K).
+  // ceil(tail * parts / pairs) / parts, plus what the pieces pay for meeting in the scratch (128 KB written per CTA,
+  // a memory fence and a counter per piece, parts x 128 KB read by the one that adds up: measured about
+  // 6 + 3 x parts microseconds, against 8.6 ns of tile time per unit of K).
   a.tail_first = (int)ntiles;
   a.tail_parts = 0;
   const int tail = (int)(ntiles % pairs);
   if (tail > 0 && ntiles > pairs && g.ws != nullptr && g.counters != nullptr && (size_t)tail * 2 <= g.counter_count) {
     const double tile_us = 8.6e-3 * (double)g.k;
     int best = 1;
-    double best_cost = 0.97;      // the unsplit tail costs one tile time; a split has to win by a margin
+    double best_cost = 0.95;      // the unsplit tail costs one tile time; a split has to win by a margin
     for (int parts = 2; parts <= 4 && a.kblocks / parts >= 4; ++parts) {
       if ((size_t)tail * parts * kTileM * kTileN * sizeof(float) > g.ws_bytes) break;
-      const double cost = (double)((tail * parts + pairs - 1) / pairs) / parts + (2.0 + 1.5 * parts) / tile_us;
+      const double cost = (double)((tail * parts + pairs - 1) / pairs) / parts + (6.0 + 3.0 * parts) / tile_us;
       if (cost < best_cost - 1e-9) {
         best_cost = cost;
         best = parts;

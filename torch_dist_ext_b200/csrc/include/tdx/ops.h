@@ -58,4 +58,8 @@ std::string attention_prefill_tc(const void* q, const void* k, const void* v, vo
                                  int64_t q_stride_s, int64_t k_stride_s, int64_t v_stride_s, float scale, cudaStream_t stream,
                                  uint32_t* status = nullptr);
 
+// Clock stamps of the last prompt attention launch (tracing flavour only): 3 roles x 64 chunks x 8 slots, see
+// attention_prefill_tc.cu.
+std::string attention_prefill_probe(unsigned long long* dst, size_t count);
+
 }  // namespace tdx

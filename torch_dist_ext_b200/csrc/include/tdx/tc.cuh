@@ -223,6 +223,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Arrive on a named barrier without waiting (the other half of a producer / consumer pair: `nthreads` counts the
+// arriving and the waiting threads together).
+__device__ __forceinline__ void named_barrier_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 // ---- CTA pairs (cta_group::2) ---------------------------------------------------------------------------
 // Two CTAs of one cluster (ranks 2k and 2k+1; the even one leads) compute one 256-row tile: each

@@ -79,6 +79,13 @@ void silu_mul(const Tensor& gate_up, Tensor out, c10::optional<Tensor> scales) {
   TORCH_CHECK(err.empty(), "silu_mul: ", err);
 }
 
+Tensor attention_prefill_probe() {
+  Tensor out = at::zeros({3, 64, 8}, at::TensorOptions().dtype(at::kLong));
+  const std::string err = tdx::attention_prefill_probe(reinterpret_cast<unsigned long long*>(out.data_ptr<int64_t>()), 3 * 64 * 8);
+  TORCH_CHECK(err.empty(), "attention_prefill_probe: ", err);
+  return out;
+}
+
 void argmax_pack(const Tensor& logits, int64_t index_base, int64_t rank, int64_t nranks, Tensor pack) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kFloat && logits.stride(1) == 1,
               "logits must be a CUDA fp32 [tokens, vocab] tensor with unit stride along the vocabulary");
@@ -418,6 +425,7 @@ void register_extra_ops(torch::Library& m) {
         "Tensor(c!)? scale_out, float eps, int out_mode) -> int", &fused_add_rmsnorm);
   m.def("quant_fp8(Tensor x, Tensor(a!) q, Tensor(b!) scales, bool block128) -> ()", &quant_fp8);
   m.def("silu_mul(Tensor gate_up, Tensor(a!) out, Tensor(b!)? scales) -> ()", &silu_mul);
+  m.def("attention_prefill_probe() -> Tensor", &attention_prefill_probe);
   m.def("argmax_pack(Tensor logits, int index_base, int rank, int nranks, Tensor(a!) pack) -> ()", &argmax_pack);
   m.def("select_token(Tensor gathered, int nranks, Tensor(a!) out) -> ()", &select_token);
   m.def("rope_(Tensor(a!) q, Tensor(b!) k, Tensor positions, Tensor cos_sin_cache) -> ()", &rope_);
