@@ -38,7 +38,7 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
             if (nvls or (isinstance(algo, str) and algo.endswith("_mc"))) and not has_mc:
                 continue
             # the automatic choice moves large messages onto the NVLS path when there is one
-            nvls_min = {2: 1 << 62, 4: 32 << 20}.get(world, 12 << 20)
+            nvls_min = {2: 1 << 62, 4: 1 << 62}.get(world, 12 << 20)
             nvls = nvls or (algo is None and has_mc and tokens * hidden * torch.finfo(dtype).bits // 8 >= nvls_min)
             ins, residual, gamma = make_case(world, tokens, hidden, dtype, seed=i)
             exp_norm, exp_res, exp_scale = tdx.reference.fused_allreduce_rms_reference(ins, residual, gamma, 1e-6, out_mode)

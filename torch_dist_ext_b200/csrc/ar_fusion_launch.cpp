@@ -46,12 +46,14 @@ Policy& policy() {
     Policy q{};
     for (int n = 0; n <= kMaxRanks; ++n) {
       // Egress of the one-shot push grows with (n-1) x message, so its range shrinks with n.
-      // measured on 8 x B200 (benchmarks/bench_fused_allreduce.py) at 2 and 8 ranks; at 4 ranks the two-shot was
-      // already ahead at 1 MiB (15.1 against 15.3 us) before its result hop went through multimem.st
-      q.oneshot_max_bytes[n] = n <= 2 ? (4u << 20) : (512u << 10);
-      q.lamport_max_bytes[n] = 12u << 20;
-      // in-switch reduction pays off once N-1 peers' worth of traffic is saved: never at 2 ranks
-      q.nvls_min_bytes[n] = n <= 2 ? ~0ull : n <= 4 ? (32ull << 20) : (12ull << 20);
+      // Measured on 8 x B200 at 2, 4 and 8 ranks (benchmarks/bench_fused_allreduce.py). 2 ranks: one-shot wins up to
+      // 16 MiB (49 against 52 us). 4 ranks: one-shot up to 512 KiB (1 MiB: 14.2 against 13.7 us), two-shot Lamport up
+      // to 16 MiB (55 against 64 us for the flag-synchronised flow; equal at 32 MiB).
+      q.oneshot_max_bytes[n] = n <= 2 ? (16u << 20) : (512u << 10);
+      q.lamport_max_bytes[n] = n <= 2 ? (32u << 20) : n <= 4 ? (16u << 20) : (12u << 20);
+      // In-switch reduction pays off once N-1 peers' worth of traffic is saved: never at 2 ranks, and at 4 ranks the
+      // flag-synchronised peer-to-peer flow measured faster at every size (186 against 219 us at 64 MiB).
+      q.nvls_min_bytes[n] = n <= 4 ? ~0ull : (12ull << 20);
       // one multimem.st instead of n - 1 stores pays off from three peers on
       q.mc_oneshot[n] = n >= 4;
       q.mc_twoshot[n] = n >= 4;
@@ -165,7 +167,9 @@ std::string plan_allreduce(const ArParams& p, int emu_ranks, LaunchPlan* plan) {
       else if (!p.scatter_only && msg_bytes <= pol.oneshot_max_bytes[n] && need_oneshot <= p.layout.lamport_bytes)
         algo = (mc_ok && pol.mc_oneshot[n]) ? kAlgoOneShotMc : kAlgoOneShotLamport;
       else if (msg_bytes <= pol.lamport_max_bytes[n] && need_ts_lamport <= p.layout.lamport_bytes)
-        algo = (mc_ok && pol.mc_twoshot[n] && !p.scatter_only) ? kAlgoTwoShotMc : kAlgoTwoShotLamport;
+        // the multicast result hop wins at every size at 8 ranks, at fewer ranks only up to 2 MiB
+        algo = (mc_ok && pol.mc_twoshot[n] && !p.scatter_only && (n >= 8 || msg_bytes <= (2u << 20))) ? kAlgoTwoShotMc
+                                                                                                      : kAlgoTwoShotLamport;
       else
         algo = kAlgoTwoShotBarrier;
     }
