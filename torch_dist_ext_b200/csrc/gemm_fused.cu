@@ -25,7 +25,6 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
-#include <map>
 #include <mutex>
 #include <set>
 #include <utility>
@@ -55,7 +54,7 @@ struct FusedArgs {
   int kblocks_per_split;
   uint32_t idesc;
   uint32_t* status;
-  float* ws;          // unused (the K splits of a tile add up inside their cluster); kept for the op's signature
+  float* ws;          // split-K scratch, zero on entry and on exit
   uint32_t* counters;
   // e4m3 operands with block scales (kScaled kernels): weights one scale per 128 x 128 block, activations one per
   // token and 128-wide K block; fp32, row length scale_kb = K / 128
@@ -64,74 +63,76 @@ struct FusedArgs {
   int scale_kb;
 };
 
-// D tile -> bf16 rows in shared memory -> 16-byte pushes into the owners' gather slots, in two steps around a
-// cluster barrier when K is split over gridDim.z (the splits of a tile are one thread-block cluster):
-//   stage_tile   without a split: the tile as bf16 rows [token][128 columns] in `stage`.
-//                With a split: this CTA's fp32 partial tile, column-major ([token][128 rows of the instruction]),
-//                at the start of the operand ring, for the cluster to read.
-//   push_rows    without a split: all rows. With a split: this CTA adds up ITS share of the tokens from every CTA of
-//                the cluster through distributed shared memory, converts them and pushes them - no global scratch and
-//                no atomics (fp32 atomics of several CTAs on one tile cost more than the tile's own MMAs).
+// D tile (TMEM) -> bf16 rows in shared memory -> 16-byte pushes into the owners' gather slots.
+// With K split over gridDim.z the partial tiles are first summed in an fp32 scratch tile with
+// red.global.add; the CTA that arrives last at the tile converts and pushes it (and leaves the
+// scratch tile and its counter zeroed for the next call).
 // kFromRegs: the tile's values come from `acc` (this thread's row of the tile, promoted block by block from the
-// scaled fp8 partial products) instead of tensor memory. `live`: the pipeline of this CTA completed and had K blocks.
+// scaled fp8 partial products) instead of tensor memory.
 template <int kBN, bool kFromRegs>
-__device__ __forceinline__ void stage_tile(uint8_t* ring, uint32_t tmem_base, const float* acc, bool live) {
+__device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const FusedArgs& f, uint8_t* stage,
+                                                    uint32_t* shared_flag, uint32_t tmem_base, int tile_x, int tile_y,
+                                                    size_t buf_off, int groups, const float* acc) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = warp & 3;
+  const int te = threadIdx.x - 64;                 // 0..127 among the epilogue threads
   const int xl = q * 32 + lane;                    // column of this thread inside the tile
   const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-  const bool split = gridDim.z > 1;
-  float* part = reinterpret_cast<float*>(ring);
-  __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(ring);
+  __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
+  bool push = true;
+  if (gridDim.z > 1) {
+    // column-major scratch tile: a warp's 32 lanes add to one 128-byte line per instruction
+    float* tile = f.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + xl;
 #pragma unroll
-  for (int c = 0; c < kBN; c += 16) {
-    float v[16];
-    if (live) {
+    for (int c = 0; c < kBN; c += 16) {
+      float v[16];
       if constexpr (kFromRegs) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
       } else {
         tc::tmem_ld_16(lane_addr + c, v);
       }
-    } else {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[j] = 0.f;
+      for (int j = 0; j < 16; ++j) atomicAdd(tile + (size_t)(c + j) * kBM, v[j]);
     }
+    __threadfence();
+    tc::named_barrier_sync(1, 128);
+    if (te == 0) {
+      const uint32_t prev = atomicAdd(&f.counters[tile_y * gridDim.x + tile_x], 1u);
+      *shared_flag = (prev == gridDim.z - 1) ? 1u : 0u;
+    }
+    tc::named_barrier_sync(1, 128);
+    push = *shared_flag != 0;
+    if (push) {
+      __threadfence();
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if (split) part[(c + j) * kBM + xl] = v[j];
-      else st[(c + j) * kBM + xl] = __float2bfloat16(v[j]);
+      for (int c = 0; c < kBN; ++c) {
+        st[c * kBM + xl] = __float2bfloat16(__ldcg(tile + (size_t)c * kBM));
+        __stcg(tile + (size_t)c * kBM, 0.f);
+      }
+      if (te == 0) f.counters[tile_y * gridDim.x + tile_x] = 0;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < kBN; c += 16) {
+      float v[16];
+      if constexpr (kFromRegs) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
+      } else {
+        tc::tmem_ld_16(lane_addr + c, v);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) st[(c + j) * kBM + xl] = __float2bfloat16(v[j]);
     }
   }
-}
-
-template <int kBN>
-__device__ __forceinline__ void push_rows(const ArParams& p, uint8_t* ring, int tile_x, int tile_y, size_t buf_off, int groups) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int te = threadIdx.x - 64;                 // 0..127 among the epilogue threads
-  const int xl = (warp & 3) * 32 + lane;
-  int t_begin = 0, t_end = kBN;
-  uint8_t* stage = ring;
-  if (gridDim.z > 1) {
-    const int cz = (int)gridDim.z, rank = (int)tc::cluster_ctarank();
-    const int per = (kBN + cz - 1) / cz;
-    t_begin = min(kBN, rank * per);
-    t_end = min(kBN, t_begin + per);
-    stage = ring + kBN * kBM * 4;                  // behind the fp32 partial tile that the cluster still reads
-    __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
-    const uint32_t part0 = tc::smem_u32(ring) + (uint32_t)xl * 4u;
-    for (int c = t_begin; c < t_end; ++c) {
-      float sum = 0.f;
-      for (int r = 0; r < cz; ++r) sum += tc::ld_shared_cluster_f32(tc::map_to_cta(part0 + (uint32_t)c * (kBM * 4u), (uint32_t)r));
-      st[c * kBM + xl] = __float2bfloat16(sum);
-    }
-  }
+  if (!push) return;
   tc::named_barrier_sync(1, 128);
   const int y_base = tile_y * kBN;
-  t_end = min(t_end, p.tokens - y_base);
+  const int valid = min(kBN, p.tokens - y_base);
   const size_t row_bytes = (size_t)p.hidden * sizeof(T);
-  for (int i = te; i < (t_end - t_begin) * 16; i += 128) {
-    const int tl = t_begin + (i >> 4), part = i & 15;
+  for (int i = te; i < valid * 16; i += 128) {
+    const int tl = i >> 4, part = i & 15;
     const int t = y_base + tl;
     const int owner = t % p.nranks, j = t / p.nranks;
     const uint4 val = scrub(*reinterpret_cast<const uint4*>(stage + (size_t)tl * (kBM * 2) + part * 16));
@@ -217,16 +218,9 @@ gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     }
     if (!ok) pipe.fail(f.status);
     // every MMA has completed, so the operand ring is free: stage the tile there
-    stage_tile<kBN, kScaled>(pipe.smem, pipe.tmem_base, acc, ok && nkb > 0);
-  }
-  if (gridDim.z > 1) {      // the splits of this tile: every thread of the cluster takes part
-    tc::cluster_arrive();
-    tc::cluster_wait();
-  }
-  if (warp >= 2 && warp < 6) push_rows<kBN>(p, pipe.smem, blockIdx.x, blockIdx.y, buf_off, groups);
-  if (gridDim.z > 1) {      // no CTA reuses or gives away shared memory that another one may still read
-    tc::cluster_arrive();
-    tc::cluster_wait();
+    if (ok)
+      push_tile_to_owners<kBN, kScaled>(p, f, pipe.smem, pipe.scratch, pipe.tmem_base, blockIdx.x, blockIdx.y, buf_off, groups,
+                                        acc);
   }
   __syncthreads();
   clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev, cta, nctas);
@@ -392,52 +386,12 @@ int sm_count() {
   return n;
 }
 
-// How many clusters of `cluster_z` CTAs of `kern` the device can hold at once (they must sit inside one GPC each, so
-// this is less than SMs / cluster_z); cached per kernel and cluster size.
-template <typename Kernel>
-int resident_clusters(Kernel kern, int smem, int cluster_z) {
-  static std::mutex mu;
-  static std::map<std::pair<const void*, int>, int> cache;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const auto key = std::make_pair(reinterpret_cast<const void*>(kern), dev * 16 + cluster_z);
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(key);
-  if (it != cache.end()) return it->second;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(1, 1, cluster_z * 64);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = cluster_z;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
-    cudaGetLastError();
-    n = 0;
-  }
-  cache[key] = n;
-  return n;
-}
-
 template <int kBN, int kStages, int kVpt, int kOut, bool kScaled>
-std::string launch_ar(const CUtensorMap& mw, const CUtensorMap& ma, FusedArgs f, dim3 grid, cudaStream_t s) {
+std::string launch_ar(const CUtensorMap& mw, const CUtensorMap& ma, const FusedArgs& f, dim3 grid, cudaStream_t s) {
   auto kern = gemm_ar_rmsnorm_kernel<kBN, kStages, TDX_FUSED_N, kVpt, kOut, kScaled>;
-  constexpr int kSmemBytes = SmemLayout<kBN, kStages>::kTotal;
-  std::string err = reserve_dynamic_smem(kern, kSmemBytes);
+  std::string err = reserve_dynamic_smem(kern, SmemLayout<kBN, kStages>::kTotal);
   if (!err.empty()) return err;
-  // The K splits of a tile (gridDim.z of them) are one thread-block cluster, and every CTA of the grid has to be
-  // resident at once: fewer, longer splits until all clusters fit.
-  while (grid.z > 1 && resident_clusters(kern, kSmemBytes, (int)grid.z) < (int)(grid.x * grid.y)) {
-    const int splits = (int)grid.z - 1;
-    f.kblocks_per_split = (f.kblocks + splits - 1) / splits;
-    grid.z = (f.kblocks + f.kblocks_per_split - 1) / f.kblocks_per_split;
-  }
-  const cudaError_t e = launch_chained_cluster_z(kern, grid, dim3(kThreads), kSmemBytes, s, grid.z, mw, ma, f);
+  const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), SmemLayout<kBN, kStages>::kTotal, s, mw, ma, f);
   return e == cudaSuccess ? "" : std::string("fused GEMM launch failed: ") + cudaGetErrorString(e);
 }
 
@@ -475,16 +429,16 @@ std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, c
   const int sms = sm_count();
   if ((int)(grid.x * grid.y) > sms)
     return "too many tokens for the fused GEMM (all CTAs must be resident): use the GEMM followed by the all-reduce op";
-  // split K until the grid covers the SMs (every CTA must stay resident, so never beyond them); the splits of a tile
-  // are one thread-block cluster and add up through distributed shared memory, so at most eight of them
+  // split K until the grid covers the SMs (every CTA must stay resident, so never beyond them)
   const int kblocks = g.k / epb;
   int splits = g.splits > 0 ? g.splits : sms / (int)(grid.x * grid.y);
   if (splits > kblocks / 2) splits = kblocks / 2;
-  if (splits > 8) splits = 8;
-  if (splits < 1) splits = 1;
+  if (splits < 1 || g.ws == nullptr || g.counters == nullptr) splits = 1;
   while (splits > 1 && (int)(grid.x * grid.y) * splits > sms) --splits;
   int per_split = (kblocks + splits - 1) / splits;
   splits = (kblocks + per_split - 1) / per_split;
+  if (splits > 1 && ((size_t)grid.x * grid.y * kBM * bn * sizeof(float) > g.ws_bytes || (size_t)grid.x * grid.y > g.counter_count))
+    return "split-K workspace is too small";
   grid.z = splits;
   const int nvec = p.hidden / 8;
   const int vpt = nvec <= kThreads ? 1 : nvec <= 2 * kThreads ? 2 : nvec <= 4 * kThreads ? 4 : 0;

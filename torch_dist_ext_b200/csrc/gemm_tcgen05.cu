@@ -7,13 +7,8 @@
 // out[M, N] = a[M, K] * w[N, K]^T runs either as (X = a, Y = w) for large M, or as (X = w, Y = a)
 // for decode-sized M, so that the weights fill the 128-row dimension of the instruction and the
 // few tokens sit on the narrow N side; the output strides (sx, sy) place D either way round.
-// K can be split over gridDim.z. The splits of a tile form thread-block clusters of up to eight CTAs: every CTA
-// leaves its fp32 partial tile in its own shared memory (the operand ring is free by then), and after a cluster
-// barrier each CTA adds up ITS share of the tile's columns from all of them through distributed shared memory and
-// writes that share of the output - no global scratch, no atomics. With more than eight splits the clusters' sums
-// still meet in an fp32 workspace with red.global.add, finished by whichever CTA arrives last at the tile, but
-// there are eight times fewer adds on the same addresses (fp32 atomics of many CTAs on ONE tile were the largest
-// single cost of the decode GEMMs at 64 tokens).
+// K can be split over gridDim.z; partial tiles are then reduced in an fp32 workspace with
+// red.global.add and finished by whichever CTA arrives last at the tile.
 //
 // fp8 (e4m3) operands use kind::f8f6f4. With block scales (1x128 on one operand, 128x128 on the
 // other, fp32) each 128-wide K block is multiplied into its own TMEM buffer and promoted by the
@@ -43,7 +38,6 @@ namespace tdx {
 namespace {
 
 using gemm_core::store_chunk;
-using gemm_core::store_out;
 
 using gemm_core::kBM;
 using gemm_core::kSwizzleBytes;
@@ -59,8 +53,7 @@ struct GemmArgs {
   int64_t sx, sy;          // D[x, y] -> out[x * sx + y * sy]
   int out_dtype;           // kF32 / kF16 / kBF16
   uint32_t idesc;
-  int cluster_z;           // splits of a tile that reduce through shared memory (cluster size along z; 1: none)
-  float* ws;               // more clusters than one per tile: fp32 tiles [tile][column][128 rows], zero on entry and on exit
+  float* ws;               // split-K: fp32 tiles [tile][column][128 rows], zero on entry and on exit
   int ws_ld;
   uint32_t* counters;      // split-K: one per output tile, zero on entry and on exit
   uint32_t* status;        // device word: non-zero after a wait ran out
@@ -157,99 +150,52 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (a.status) atomicExch(a.status, kTimeoutGemmPipeline);
     }
     const bool split = gridDim.z > 1;
-    if (!split) {
-      if (ok && nkb > 0) {
-#pragma unroll
-        for (int c = 0; c < kBN; c += 16) {
-          float v[16];
-          if constexpr (kScaled) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
-          } else {
-            tc::tmem_ld_16(lane_addr + c, v);
-          }
-          store_chunk(a, x, y_base + c, v);
-        }
-      }
-    } else {
-      // This CTA's partial tile goes to its own shared memory, column-major ([column][128 rows] fp32, at the start
-      // of the operand ring: every MMA that read the ring has completed). A CTA without K blocks, or one whose
-      // pipeline gave up, leaves zeros.
-      float* part = reinterpret_cast<float*>(pipe.smem) + q * 32 + lane;
+    if (ok && nkb > 0) {
 #pragma unroll
       for (int c = 0; c < kBN; c += 16) {
         float v[16];
-        if (ok && nkb > 0) {
-          if constexpr (kScaled) {
+        if constexpr (kScaled) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
-          } else {
-            tc::tmem_ld_16(lane_addr + c, v);
-          }
+          for (int j = 0; j < 16; ++j) v[j] = acc[c + j];
         } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          tc::tmem_ld_16(lane_addr + c, v);
         }
+        if (!split) {
+          store_chunk(a, x, y_base + c, v);
+        } else {
+          // scratch tile is column-major ([column][128 rows]): the lanes of a warp add to 32
+          // consecutive floats, one 128-byte line per instruction
+          float* dst = a.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + (size_t)c * kBM + q * 32 + lane;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) part[(c + j) * kBM] = v[j];
+          for (int j = 0; j < 16; ++j) atomicAdd(dst + j * kBM, v[j]);
+        }
       }
     }
-  }
-
-  if (gridDim.z > 1) {
-    // ---- split K: the cluster adds its partial tiles up through distributed shared memory ----
-    // (every thread of every CTA of the cluster takes part in the two barriers)
-    tc::cluster_arrive();
-    tc::cluster_wait();
-    if (warp >= 2) {
-      const int q = warp & 3;
-      const int xl = q * 32 + lane;
-      const int x = tile_x * kBM + xl;
-      const int y_base = tile_y * kBN;
-      const int cz = a.cluster_z;
-      const int rank = (int)tc::cluster_ctarank();
-      const int cols_per = (kBN + cz - 1) / cz;
-      const int c_begin = rank * cols_per, c_end = min(kBN, c_begin + cols_per);
-      const uint32_t part0 = tc::smem_u32(pipe.smem) + (uint32_t)xl * 4u;
-      const bool one_cluster = (int)gridDim.z == cz;
-      float* tile_ws = one_cluster ? nullptr : a.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + xl;
-      for (int c = c_begin; c < c_end; ++c) {
-        float sum = 0.f;
-        for (int p = 0; p < cz; ++p) sum += tc::ld_shared_cluster_f32(tc::map_to_cta(part0 + (uint32_t)c * (kBM * 4u), (uint32_t)p));
-        if (one_cluster) {
-          if (x < a.x_rows && y_base + c < a.y_rows) store_out(a, (int64_t)x * a.sx + (int64_t)(y_base + c) * a.sy, sum);
-        } else {
-          atomicAdd(tile_ws + (size_t)c * kBM, sum);   // lanes of a warp: 32 consecutive floats, one 128-byte line
-        }
+    if (split) {
+      // the CTA that arrives last at this tile turns the fp32 sums into the output and re-zeroes them
+      __threadfence();
+      tc::named_barrier_sync(1, 128);
+      if (threadIdx.x == 64) {
+        const uint32_t prev = atomicAdd(&a.counters[tile_y * gridDim.x + tile_x], 1u);
+        *last_flag = (prev == gridDim.z - 1) ? 1u : 0u;
       }
-      if (!one_cluster) {
-        // the CTA that arrives last at this tile turns the fp32 sums into the output and re-zeroes them
+      tc::named_barrier_sync(1, 128);
+      if (*last_flag) {
         __threadfence();
-        tc::named_barrier_sync(1, 128);
-        if (threadIdx.x == 64) {
-          const uint32_t prev = atomicAdd(&a.counters[tile_y * gridDim.x + tile_x], 1u);
-          *last_flag = (prev == gridDim.z - 1) ? 1u : 0u;
-        }
-        tc::named_barrier_sync(1, 128);
-        if (*last_flag) {
-          __threadfence();
+        float* src = a.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + q * 32 + lane;
 #pragma unroll
-          for (int c = 0; c < kBN; c += 16) {
-            float v[16];
+        for (int c = 0; c < kBN; c += 16) {
+          float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              v[j] = __ldcg(tile_ws + (size_t)(c + j) * kBM);
-              __stcg(tile_ws + (size_t)(c + j) * kBM, 0.f);
-            }
-            store_chunk(a, x, y_base + c, v);
+          for (int j = 0; j < 16; ++j) {
+            v[j] = __ldcg(src + (size_t)(c + j) * kBM);
+            __stcg(src + (size_t)(c + j) * kBM, 0.f);
           }
-          if (threadIdx.x == 64) a.counters[tile_y * gridDim.x + tile_x] = 0;
+          store_chunk(a, x, y_base + c, v);
         }
+        if (threadIdx.x == 64) a.counters[tile_y * gridDim.x + tile_x] = 0;
       }
     }
-    // no CTA leaves (and gives its shared memory away) while another one may still read it
-    tc::cluster_arrive();
-    tc::cluster_wait();
   }
 
   pipe.finish(kTmemCols);
@@ -263,7 +209,7 @@ std::string launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmArgs&
   auto kern = gemm_tn_kernel<kBN, kStages, kFp8, kScaled>;
   const std::string err = reserve_dynamic_smem(kern, L::kTotal);
   if (!err.empty()) return err;
-  const cudaError_t e = launch_chained_cluster_z(kern, grid, dim3(kThreads), L::kTotal, stream, (unsigned)a.cluster_z, mx, my, a);
+  const cudaError_t e = launch_chained(kern, grid, dim3(kThreads), L::kTotal, stream, mx, my, a);
   return e == cudaSuccess ? "" : std::string("GEMM launch failed: ") + cudaGetErrorString(e);
 }
 
@@ -329,16 +275,6 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
   if (splits > a.kblocks) splits = a.kblocks;
   a.kblocks_per_split = (a.kblocks + splits - 1) / splits;
   splits = (a.kblocks + a.kblocks_per_split - 1) / a.kblocks_per_split;
-  // The splits of a tile reduce inside thread-block clusters of up to eight CTAs along z: as few clusters per tile
-  // as that allows, all of the same size. Rounding the grid up to whole clusters can add CTAs without K blocks;
-  // they contribute zeros.
-  a.cluster_z = 1;
-  if (splits > 1) {
-    const int clusters = (splits + 7) / 8;
-    a.cluster_z = (splits + clusters - 1) / clusters;
-    splits = clusters * a.cluster_z;
-    a.kblocks_per_split = (a.kblocks + splits - 1) / splits;
-  }
   a.out = g.out;
   a.sx = g.sx;
   a.sy = g.sy;
@@ -346,8 +282,8 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
   a.idesc = fp8 ? tc::make_idesc(kBM, bn, 0, 0) : tc::make_idesc(kBM, bn, g.elem_kind == kBF16 ? 1 : 0, g.elem_kind == kBF16 ? 1 : 0);
   a.status = g.status;
   const dim3 grid((g.x_rows + kBM - 1) / kBM, (g.y_rows + bn - 1) / bn, splits);
-  if (splits > a.cluster_z) {
-    if (!g.ws || !g.counters) return "split-K over more than eight CTAs per tile needs a workspace";
+  if (splits > 1) {
+    if (!g.ws || !g.counters) return "split-K needs a workspace";
     a.ws_ld = grid.y * bn;
     if ((size_t)grid.x * grid.y * kBM * bn * sizeof(float) > g.ws_bytes || (size_t)grid.x * grid.y > g.counter_count)
       return "split-K workspace is too small for this problem";

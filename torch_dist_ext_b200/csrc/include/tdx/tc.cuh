@@ -252,12 +252,6 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
 // Cluster-wide barrier; every thread of every CTA of the cluster executes both halves.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// One fp32 from the shared memory of any CTA of the cluster; `addr` comes from map_to_cta.
-__device__ __forceinline__ float ld_shared_cluster_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
-}
 
 // Arrive on an mbarrier of another CTA of the cluster (address from map_to_cta).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
