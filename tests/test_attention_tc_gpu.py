@@ -29,6 +29,28 @@ def test_decode_attention_tc(b, hq, hkv, smax):
         assert (got.float() - simt.float()).abs().max().item() <= 3e-2, nsplit
 
 
+def test_prefill_attention_tc_rescales_and_masked_groups():
+    """Scores with a large spread make a row's running maximum jump by more than the lazy threshold between chunks
+    (the accumulators are rescaled in tensor memory); prompts shorter than 64 tokens leave the softmax group of the
+    odd chunks with nothing but masked scores."""
+    g = torch.Generator(device="cuda").manual_seed(7)
+    for s, hq, hkv, gain in [(1024, 4, 1, 8.0), (640, 2, 2, 16.0), (40, 4, 1, 1.0), (64, 2, 1, 4.0), (100, 2, 1, 1.0)]:
+        qkv = torch.randn(s, (hq + 2 * hkv) * 128, device="cuda", dtype=torch.bfloat16, generator=g)
+        qkv[:, : hq * 128] *= gain
+        # keys that grow along the sequence: later chunks keep raising the row maxima
+        ramp = torch.linspace(0.2, 1.5, s, device="cuda").view(s, 1).to(torch.bfloat16)
+        qkv[:, hq * 128: (hq + hkv) * 128] *= ramp
+        q = qkv[:, : hq * 128].view(s, hq, 128)
+        k = qkv[:, hq * 128: (hq + hkv) * 128].view(s, hkv, 128)
+        v = qkv[:, (hq + hkv) * 128:].view(s, hkv, 128)
+        got = attention.prefill_attention(q, k, v)
+        torch.cuda.synchronize()
+        assert gemm.pipeline_status() == 0
+        want = attention.prefill_attention_reference(q, k, v)
+        assert bool(torch.isfinite(got.float()).all())
+        assert (got.float() - want.float()).abs().max().item() <= 4e-2, (s, hq, hkv, gain)
+
+
 @pytest.mark.parametrize("s,hq,hkv", [(128, 1, 1), (256, 4, 1), (300, 4, 2), (1000, 8, 8), (2048, 4, 1)])
 def test_prefill_attention_tc(s, hq, hkv):
     g = torch.Generator(device="cuda").manual_seed(s + hq)
