@@ -39,6 +39,9 @@ from ..utils.tracing import nvtx_range, traced
 
 # prompt-phase attention: this library's tcgen05 kernel; "sdpa" selects PyTorch's kernel for comparisons
 _PREFILL_ATTN_TC = os.environ.get("TDX_PREFILL_ATTN", "tc").lower() != "sdpa"
+# TDX_FUSED_FP8=0: row-parallel projections with e4m3 weights run as block-scaled GEMM + the all-reduce op (two
+# launches) instead of the fused kernel, for comparisons
+_FUSED_FP8 = os.environ.get("TDX_FUSED_FP8", "1") != "0"
 
 
 @dataclass
@@ -165,7 +168,8 @@ class TPLlama:
             if a_scale is None:
                 a, a_scale = quant.quant_fp8(a, block_scaled=True)
             x, res, xs = fused_gemm.gemm_allreduce_rms(a, lin.w, res, gamma, self.cfg.eps, out_mode=OUT_FP8_BLOCK128,
-                                                       scatter_only=scatter, a_scale=a_scale, w_scale=lin.scale)
+                                                       scatter_only=scatter, a_scale=a_scale, w_scale=lin.scale,
+                                                       force_unfused=not _FUSED_FP8)
             return x, xs, res
         x, res, xs = fused_gemm.gemm_allreduce_rms(a, lin.w, res, gamma, self.cfg.eps, out_mode=OUT_SAME,
                                                    scatter_only=scatter)
