@@ -84,7 +84,9 @@ def run(args):
         ref, why = common.load_reference()
         if ref is None:
             return {"impl": "reference", "unavailable": why}
+        _progress("process group")
         ref.setup_env(rank, world)
+        _progress("setup_env")
         api = ref
     else:
         import torch_dist_ext_b200 as tdx
@@ -97,7 +99,8 @@ def run(args):
     host_x, host_r, gamma, xs, rs = make_step_inputs(tokens, hidden, rank, n_sets=n_sets)
     ws = api.get_workspace(xs[0])
     # The reference re-initialises its buffers inside get_workspace when the dtype changes, with
-    # no synchronisation of its own; its test puts a barrier here, and so does this loop.
+    # no synchronisation of its own; its test puts a device synchronisation and a barrier here, and so does this loop.
+    torch.cuda.synchronize()
     common.barrier(world)
     timing = common.timing_utils()
     flusher = timing.L2Flusher()
@@ -109,8 +112,10 @@ def run(args):
         state["out"] = api.allreduce_rms(rank, world, xs[i], rs[i], gamma, EPS, ws)
 
     # correctness of what is being timed (also catches a launch that silently did nothing)
+    _progress("get_workspace")
     step()
     torch.cuda.synchronize()
+    _progress("first call")
     ok, err = _verify(state["out"], host_x, host_r, gamma, world, rank)
     ok = bool(common.min_over_ranks(1.0 if ok else 0.0, world))
     if not ok:
@@ -124,8 +129,10 @@ def run(args):
         common.barrier(world)
         region_us = common.region_time_us(step, K, W, align)
         common.barrier(world)
+        _progress("timed region")
         times = common.device_times_us(step, min(K, 100), 3, flusher, align)
         common.barrier(world)
+        _progress("single calls")
         # a sustained burst of the same step so that the clock samples are taken under this load
         t_end = common.now() + 0.6
         while common.now() < t_end:
@@ -353,10 +360,49 @@ def _reexec_with_reference_on_library_path():
     os.execve(sys.executable, [sys.executable] + sys.argv, os.environ)
 
 
+class _ReferenceWatchdog:
+    """The reference's device-side waits have no limit: a race in its buffer initialisation (its ranks fill each
+    other's flag and Lamport buffers without a common point of synchronisation) can leave a kernel spinning for ever.
+    This thread turns such a hang into the arm's ``unavailable`` line: when the arm makes no progress for `limit_s`
+    seconds every rank leaves the process (which ends the spinning kernel with its context), rank 0 after printing."""
+
+    def __init__(self, limit_s: float = 75.0):
+        import threading
+        import time
+
+        self.limit_s, self._time, self._last, self.where = limit_s, time, time.monotonic(), "start"
+        self._thread = threading.Thread(target=self._watch, daemon=True)
+        self._thread.start()
+
+    def progress(self, where: str) -> None:
+        self._last, self.where = self._time.monotonic(), where
+
+    def _watch(self) -> None:
+        while True:
+            self._time.sleep(1.0)
+            if self._time.monotonic() - self._last > self.limit_s:
+                if int(os.environ.get("RANK", "0")) == 0:
+                    print(json.dumps({"impl": "reference", "unavailable":
+                                      f"the reference did not return within {self.limit_s:.0f} s after '{self.where}' "
+                                      "(its kernels wait without a limit); the process was ended"}), flush=True)
+                os._exit(0)
+
+
+_watchdog = None
+
+
+def _progress(where: str) -> None:
+    if _watchdog is not None:
+        _watchdog.progress(where)
+
+
 def main():
+    global _watchdog
     args = parse()
     if args.impl == "reference" and os.path.isdir(common.REF_DIR):
         _reexec_with_reference_on_library_path()
+    if args.impl == "reference":
+        _watchdog = _ReferenceWatchdog()
     result = run(args)
     if result is not None and int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(result), flush=True)
