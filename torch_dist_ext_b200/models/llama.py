@@ -6,9 +6,9 @@ Per layer and decode step::
     qkv   = x @ Wqkv_r^T                                  tcgen05 GEMM (column-parallel, no comm)
     q, k  = rope(q, k)  ;  cache[pos] = k, v
     attn  = split-KV decode attention over the local heads
-    x,res = (attn @ Wo_r^T  --all-reduce-->) + res -> RMSNorm      ONE kernel: GEMM -> reduce-scatter
-    gu    = x @ Wgu_r^T ;  act = silu(gate) * up                   (push to the row owners) -> norm ->
-    x,res = (act @ Wd_r^T --all-reduce-->) + res -> RMSNorm        gather back
+    x,res = (attn @ Wo_r^T  --all-reduce-->) + res -> RMSNorm      tcgen05 GEMM, then ONE kernel for all-reduce +
+    gu    = x @ Wgu_r^T ;  act = silu(gate) * up                   residual + norm (+ e4m3 quantisation); or both in
+    x,res = (act @ Wd_r^T --all-reduce-->) + res -> RMSNorm        one kernel (GEMM -> reduce-scatter -> norm -> gather)
 
 ``mode="sp"`` keeps the normalised rows scattered (rank r owns rows r::world) and feeds them to the
 next column-parallel GEMM through the fused all-gather->GEMM kernel instead (bf16 weights; with e4m3
@@ -39,11 +39,14 @@ from ..utils.tracing import nvtx_range, traced
 
 # prompt-phase attention: this library's tcgen05 kernel; "sdpa" selects PyTorch's kernel for comparisons
 _PREFILL_ATTN_TC = os.environ.get("TDX_PREFILL_ATTN", "tc").lower() != "sdpa"
-# Row-parallel projections with e4m3 weights run as block-scaled GEMM + the fused all-reduce op (two launches):
-# measured on two B200 at the Llama-3-70B shapes, batch 64, that is 262 us per layer against 301 us through the fused
-# GEMM + all-reduce kernel, whose promotion of every 128-wide K block sits in front of its reduce-scatter.
-# TDX_FUSED_FP8=1 selects the fused kernel (bf16 weights always use theirs, which measured faster).
+# Row-parallel projections (o_proj, down_proj) run as GEMM + the fused all-reduce op (two launches) by default: with
+# dependent launch and the one-shot all-reduce at decode sizes that measured faster than the fused GEMM + all-reduce
+# kernel, whose tail is a two-hop reduce-scatter + gather - Llama-3-8B shapes, 8 layers, batch 1 / 16 / 64: 99 / 109 /
+# 161 against 112 / 122 / 191 us per layer on two B200, 80 / 83 / 117 against 94 / 97 / 148 on four; Llama-3-70B shapes
+# with e4m3 weights, batch 64: 262 against 301 (two) and 171 against 213 (four).
+# TDX_FUSED_BF16=1 / TDX_FUSED_FP8=1 select the fused kernel for bf16 / e4m3 weights.
 _FUSED_FP8 = os.environ.get("TDX_FUSED_FP8", "0") != "0"
+_FUSED_BF16 = os.environ.get("TDX_FUSED_BF16", "0") != "0"
 
 
 @dataclass
@@ -175,7 +178,7 @@ class TPLlama:
                                                        force_unfused=not _FUSED_FP8)
             return x, xs, res
         x, res, xs = fused_gemm.gemm_allreduce_rms(a, lin.w, res, gamma, self.cfg.eps, out_mode=OUT_SAME,
-                                                   scatter_only=scatter)
+                                                   scatter_only=scatter, force_unfused=not _FUSED_BF16)
         return x, xs, res
 
     def _col_parallel(self, x: torch.Tensor, lin: _Linear, tokens: int, x_scale=None) -> torch.Tensor:
