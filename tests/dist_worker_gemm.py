@@ -41,8 +41,15 @@ def worker(rank: int, world: int, port: int, backend: str, cases, result_queue=N
                 res_in = res_in.to(dev)
             else:
                 res_in = residual.to(dev)
-            for _ in range(3):
-                norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, res_in, gamma.to(dev), 1e-6, scatter_only=scatter)
+            # replicated output: both tails of the fused kernel (one hop / two hops), then the op's own choice
+            for hop in ((True, False, None) if not scatter else (None,)):
+                for _ in range(3):
+                    norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, res_in, gamma.to(dev), 1e-6, scatter_only=scatter, one_hop=hop)
+                torch.cuda.synchronize()
+                tdx.check_status()
+                kk0 = (e_norm[rank::world] if scatter else e_norm).shape[0]
+                want0 = e_res[rank::world] if scatter else e_res
+                assert (res[:kk0].cpu().float() - want0.float()).abs().max().item() <= 0.13, f"case {i} (one_hop={hop}): residual"
             torch.cuda.synchronize()
             tdx.check_status()
             want_n = e_norm[rank::world] if scatter else e_norm

@@ -19,22 +19,30 @@ def env():
     tdx.teardown_env()
 
 
+def tol(expected):
+    """Two bf16 roundings (the GEMM output, then the sum with the residual) at the magnitude of the largest value."""
+    return 0.03 + 2.0 ** -7 * expected.float().abs().max().item()
+
+
 def oracle(a, w, residual, gamma, eps, out_mode=OUT_SAME):
     y = (a.float() @ w.float().t()).to(torch.bfloat16)       # each rank's GEMM output is rounded to bf16
     return ref.residual_rmsnorm_reference(y.float(), residual, gamma, eps, out_mode)
 
 
+@pytest.mark.parametrize("one_hop", [None, True, False])
 @pytest.mark.parametrize("tokens,hidden,k", [(1, 4096, 512), (16, 4096, 1792), (64, 8192, 1024), (33, 1024, 256), (100, 2048, 128)])
-def test_gemm_allreduce_rms_world1(tokens, hidden, k):
+def test_gemm_allreduce_rms_world1(tokens, hidden, k, one_hop):
+    """Both tails of the fused kernel: one hop (tiles pushed to every rank, each rank reduces all rows) and two hops
+    (reduce-scatter to the owners, gather back); None lets the op choose by message size."""
     a = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
     w = (torch.randn(hidden, k, device="cuda") * 0.05).to(torch.bfloat16)
     r = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
     g = (1 + 0.1 * torch.randn(hidden, device="cuda")).to(torch.bfloat16)
     for _ in range(3):   # repeated calls walk through the three Lamport buffers
-        norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6)
+        norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6, one_hop=one_hop)
     e_norm, e_res, _ = oracle(a, w, r, g, 1e-6)
-    assert (res.float() - e_res.float()).abs().max().item() <= 0.07
-    assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07
+    assert (res.float() - e_res.float()).abs().max().item() <= tol(e_res)
+    assert (norm.float() - e_norm.float()).abs().max().item() <= tol(e_norm)
     tdx.check_status()
     assert gemm.pipeline_status() == 0
 
@@ -64,15 +72,16 @@ def test_gemm_allreduce_rms_block_scaled_fp8_operands_world1(tokens, hidden, k, 
     g = (1 + 0.1 * torch.randn(hidden, device="cuda")).to(torch.bfloat16)
     aq, ascale = quant.quant_fp8(a, block_scaled=True)
     wq, wscale = gemm.quantize_weight_block128(w)
-    for _ in range(3):
-        norm, res, scales = fused_gemm.gemm_allreduce_rms(aq, wq, r, g, 1e-6, out_mode=out_mode, a_scale=ascale, w_scale=wscale)
+    for hop in (True, False, None):
+        norm, res, scales = fused_gemm.gemm_allreduce_rms(aq, wq, r, g, 1e-6, out_mode=out_mode, a_scale=ascale, w_scale=wscale,
+                                                          one_hop=hop)
     a_deq = (aq.float().view(tokens, k // 128, 128) * ascale.view(tokens, k // 128, 1)).view(tokens, k)
     w_deq = (wq.float().view(hidden // 128, 128, k // 128, 128) * wscale.view(hidden // 128, 1, k // 128, 1)).view(hidden, k)
     y = (a_deq @ w_deq.t()).to(torch.bfloat16)
     e_norm, e_res, _ = ref.residual_rmsnorm_reference(y.float(), r, g, 1e-6, OUT_SAME)
-    assert (res.float() - e_res.float()).abs().max().item() <= 0.07
+    assert (res.float() - e_res.float()).abs().max().item() <= tol(e_res)
     if out_mode == OUT_SAME:
-        assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07
+        assert (norm.float() - e_norm.float()).abs().max().item() <= tol(e_norm)
     else:
         back = ref.dequantize_fp8(norm, scales)
         assert (back - e_norm.float()).abs().max().item() <= e_norm.float().abs().max().item() * 2.0 ** -3
@@ -116,9 +125,9 @@ def test_prompt_sized_token_counts_stay_fused(tokens, hidden, k, out_mode):
         norm, res, scales = fused_gemm.gemm_allreduce_rms(a, w, r, g, 1e-6, out_mode=out_mode)
     assert _standalone_allreduce_calls() == before, "the call fell back to GEMM + all-reduce"
     e_norm, e_res, _ = oracle(a, w, r, g, 1e-6)
-    assert (res.float() - e_res.float()).abs().max().item() <= 0.07
+    assert (res.float() - e_res.float()).abs().max().item() <= tol(e_res)
     if out_mode == OUT_SAME:
-        assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07
+        assert (norm.float() - e_norm.float()).abs().max().item() <= tol(e_norm)
     else:
         back = ref.dequantize_fp8(norm, scales)
         assert (back - e_norm.float()).abs().max().item() <= e_norm.float().abs().max().item() * 2.0 ** -3
@@ -126,7 +135,7 @@ def test_prompt_sized_token_counts_stay_fused(tokens, hidden, k, out_mode):
     assert gemm.pipeline_status() == 0
     # a decode-sized call afterwards finds the communication state intact
     n2, r2, _ = fused_gemm.gemm_allreduce_rms(a[:16], w, r[:16], g, 1e-6)
-    assert (r2.float() - e_res[:16].float()).abs().max().item() <= 0.07
+    assert (r2.float() - e_res[:16].float()).abs().max().item() <= tol(e_res)
 
 
 def test_messages_beyond_the_lamport_buffers_take_the_unfused_route():
@@ -138,4 +147,4 @@ def test_messages_beyond_the_lamport_buffers_take_the_unfused_route():
     norm, res, _ = fused_gemm.gemm_allreduce_rms(a, w, None, g, 1e-6)
     assert _standalone_allreduce_calls() == before + 1
     e_norm, e_res, _ = oracle(a, w, None, g, 1e-6)
-    assert (norm.float() - e_norm.float()).abs().max().item() <= 0.07
+    assert (norm.float() - e_norm.float()).abs().max().item() <= tol(e_norm)

@@ -61,9 +61,12 @@ struct FusedArgs {
   const float* w_scale;
   const float* a_scale;
   int scale_kb;
+  int one_hop;        // replicated output at decode sizes: tiles go to EVERY rank and each rank reduces all rows itself
 };
 
-// D tile (TMEM) -> bf16 rows in shared memory -> 16-byte pushes into the owners' gather slots.
+// D tile (TMEM) -> bf16 rows in shared memory -> 16-byte pushes into the owners' gather slots, or (one_hop) into this
+// rank's slot of EVERY rank's buffer - one multimem.st per vector where NVSwitch multicast is mapped, else one peer
+// store per rank - for the one-hop tail below.
 // With K split over gridDim.z the partial tiles are first summed in an fp32 scratch tile with
 // red.global.add; the CTA that arrives last at the tile converts and pushes it (and leaves the
 // scratch tile and its counter zeroed for the next call).
@@ -72,7 +75,7 @@ struct FusedArgs {
 template <int kBN, bool kFromRegs>
 __device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const FusedArgs& f, uint8_t* stage,
                                                     uint32_t* shared_flag, uint32_t tmem_base, int tile_x, int tile_y,
-                                                    size_t buf_off, int groups, const float* acc) {
+                                                    size_t buf_off, int groups, const float* acc, bool one_hop) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = warp & 3;
   const int te = threadIdx.x - 64;                 // 0..127 among the epilogue threads
@@ -136,10 +139,80 @@ __device__ __forceinline__ void push_tile_to_owners(const ArParams& p, const Fus
     const int t = y_base + tl;
     const int owner = t % p.nranks, j = t / p.nranks;
     const uint4 val = scrub(*reinterpret_cast<const uint4*>(stage + (size_t)tl * (kBM * 2) + part * 16));
-    char* dst = static_cast<char*>(p.peer[owner]) + buf_off + ((size_t)p.rank * groups + j) * row_bytes +
-                ((size_t)tile_x * kBM + part * 8) * sizeof(T);
-    ptx::st_v4(dst, val);
+    if (one_hop) {
+      // slot `rank` of the one-shot layout [source rank][token][hidden], the same offset in every rank's buffer
+      const size_t off = buf_off + ((size_t)p.rank * p.tokens + t) * row_bytes + ((size_t)tile_x * kBM + part * 8) * sizeof(T);
+      if (p.mc_base != nullptr) {
+        ptx::multimem_st_v4(symm_mc(p, off), val);
+      } else {
+        for (int r = 0; r < p.nranks; ++r) ptx::st_v4(static_cast<char*>(p.peer[r]) + off, val);
+      }
+    } else {
+      char* dst = static_cast<char*>(p.peer[owner]) + buf_off + ((size_t)p.rank * groups + j) * row_bytes +
+                  ((size_t)tile_x * kBM + part * 8) * sizeof(T);
+      ptx::st_v4(dst, val);
+    }
   }
+}
+
+// One-hop tail: every rank holds every rank's partial rows (slot r of the current Lamport buffer, this rank's own
+// included), so each CTA takes rows cta, cta + nctas, ..., waits for the N vectors of a row, adds them and the
+// residual, normalises and writes the outputs - the all-reduce is complete after ONE trip through NVSwitch. The
+// reduction is done N times over (once per rank), which at decode sizes costs less than the second hop of the
+// reduce-scatter + gather flow. Returns the bytes of the buffer that were written.
+template <int kN, int kVpt, int kOut>
+__device__ __forceinline__ uint64_t onehop_tail(const ArParams& p, int cta, int nctas, uint32_t epoch, float (*red)[32]) {
+  constexpr int kVec = VecTraits<T>::kVec;
+  const int nranks = kN > 0 ? kN : p.nranks;
+  const RowView<T, kVpt> rv(p.hidden);
+  char* self = static_cast<char*>(p.peer[p.rank]);
+  Control* ctl = reinterpret_cast<Control*>(self + p.layout.off_control);
+  const size_t msg_bytes = rv.row_bytes * p.tokens;
+  const char* mine = lamport_buf(self, p.layout, epoch % 3u);
+  uint4 gamma[kVpt];
+  load_gamma<T, kVpt>(p, rv, gamma);
+  Waiter w(p.timeout_ns);
+  int parity = 0;
+  for (int row = cta; row < p.tokens; row += nctas, parity ^= 1) {
+    float x[kVpt][kVec];
+    uint4 res[kVpt];
+    request_residual<T, kVpt>(p, rv, row, res);
+#pragma unroll
+    for (int v = 0; v < kVpt; ++v) {
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) x[v][i] = 0.f;
+      if (!rv.active(v)) continue;
+      const size_t off = (size_t)row * rv.row_bytes + (size_t)rv.vec_index(v) * 16;
+      if constexpr (kN > 0) {
+        uint4 vals[kN];
+#pragma unroll
+        for (int r = 0; r < kN; ++r) vals[r] = ptx::ld_volatile_v4(mine + (size_t)r * msg_bytes + off);   // all polls in flight together
+#pragma unroll
+        for (int r = 0; r < kN; ++r)
+          if (!all_arrived(vals[r])) vals[r] = poll_vec(mine + (size_t)r * msg_bytes + off, w, p, ctl, kTimeoutLamportGather, r, 1, row);
+#pragma unroll
+        for (int r = 0; r < kN; ++r) {
+          float f[kVec];
+          unpack<T>(vals[r], f);
+#pragma unroll
+          for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
+        }
+      } else {
+        for (int r = 0; r < nranks; ++r) {
+          const uint4 val = poll_vec(mine + (size_t)r * msg_bytes + off, w, p, ctl, kTimeoutLamportGather, r, 1, row);
+          float f[kVec];
+          unpack<T>(val, f);
+#pragma unroll
+          for (int i = 0; i < kVec; ++i) x[v][i] += f[i];
+        }
+      }
+      add_residual_loaded<T>(x[v], p.residual_in != nullptr, res[v]);
+      if (p.residual_out) ptx::st_stream_v4(static_cast<char*>(p.residual_out) + off, pack<T>(x[v]));
+    }
+    float rstd, sc;
+    finish_row<T, kVpt, kOut>(p, rv, row, x, gamma, red, parity, rstd, sc);
+  }
+  return (uint64_t)nranks * msg_bytes;
 }
 
 template <int kBN, int kStages, int kN, int kVpt, int kOut, bool kScaled>
@@ -220,11 +293,12 @@ gemm_ar_rmsnorm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     // every MMA has completed, so the operand ring is free: stage the tile there
     if (ok)
       push_tile_to_owners<kBN, kScaled>(p, f, pipe.smem, pipe.scratch, pipe.tmem_base, blockIdx.x, blockIdx.y, buf_off, groups,
-                                        acc);
+                                        acc, f.one_hop != 0);
   }
   __syncthreads();
   clear_previous(lamport_buf(self, p.layout, (epoch + 2u) % 3u), dirty_prev, cta, nctas);
-  const uint64_t dirty = twoshot_lamport_tail<T, kN, kVpt, kOut, true>(p, cta, nctas, epoch, red);
+  const uint64_t dirty = f.one_hop ? onehop_tail<kN, kVpt, kOut>(p, cta, nctas, epoch, red)
+                                   : twoshot_lamport_tail<T, kN, kVpt, kOut, true>(p, cta, nctas, epoch, red);
   finish_launch(ctl, true, epoch, dirty, 0, nctas);
   pipe.finish(kTmemCols);
 }
@@ -444,12 +518,15 @@ std::string TDX_CAT(gemm_ar_rmsnorm_n, TDX_FUSED_N)(const FusedGemmProblem& g, c
   const int vpt = nvec <= kThreads ? 1 : nvec <= 2 * kThreads ? 2 : nvec <= 4 * kThreads ? 4 : 0;
   const uint64_t row_bytes = (uint64_t)p.hidden * 2;
   const uint64_t groups = ((uint64_t)p.tokens + p.nranks - 1) / p.nranks;
-  const uint64_t need = (uint64_t)p.nranks * groups * row_bytes + (p.scatter_only ? 0 : (uint64_t)p.tokens * (row_bytes + 16));
+  if (g.one_hop && p.scatter_only) return "the one-hop tail produces replicated output";
+  const uint64_t need = g.one_hop ? (uint64_t)p.nranks * p.tokens * row_bytes
+                                  : (uint64_t)p.nranks * groups * row_bytes + (p.scatter_only ? 0 : (uint64_t)p.tokens * (row_bytes + 16));
   if (need > p.layout.lamport_bytes) return "message exceeds the Lamport buffer capacity";
   for (int r = 0; r < p.nranks; ++r)
     if (p.peer[r] == nullptr) return "workspace is not registered with all peers";
   FusedArgs f{};
   f.ar = p;
+  f.one_hop = g.one_hop ? 1 : 0;
   f.kblocks = kblocks;
   f.kblocks_per_split = per_split;
   f.idesc = scaled ? tc::make_idesc(kBM, bn, 0, 0) : tc::make_idesc(kBM, bn, 1, 1);

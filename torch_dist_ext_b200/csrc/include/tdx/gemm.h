@@ -62,6 +62,7 @@ struct FusedGemmProblem {
   size_t ws_bytes;
   uint32_t* counters;  // zero-initialised, one per output tile
   size_t counter_count;
+  bool one_hop = false;   // replicated output: tiles pushed to every rank, each rank reduces all rows (one NVSwitch hop)
 };
 std::string gemm_ar_rmsnorm(const FusedGemmProblem& g, cudaStream_t stream);
 std::string gemm_ar_rmsnorm_n0(const FusedGemmProblem& g, cudaStream_t stream);

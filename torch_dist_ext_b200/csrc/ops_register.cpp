@@ -306,7 +306,7 @@ void gemm_ar_rmsnorm(const Tensor& a, const Tensor& w, const c10::optional<Tenso
                      c10::optional<Tensor> residual_out, Tensor norm_out, c10::optional<Tensor> scale_out, double eps,
                      const Tensor& workspace, int64_t out_mode, bool scatter_only, const c10::optional<Tensor>& status,
                      int64_t splits, const c10::optional<Tensor>& splitk_ws, const c10::optional<Tensor>& splitk_counters,
-                     const c10::optional<Tensor>& a_scale, const c10::optional<Tensor>& w_scale) {
+                     const c10::optional<Tensor>& a_scale, const c10::optional<Tensor>& w_scale, bool one_hop) {
   tdx::Workspace* ws = workspace_of(workspace);
   TORCH_CHECK(a.is_cuda() && w.is_cuda() && a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1), "gemm_ar_rmsnorm: a [tokens, k], w [hidden, k]");
   const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
@@ -341,6 +341,7 @@ void gemm_ar_rmsnorm(const Tensor& a, const Tensor& w, const c10::optional<Tenso
   g.ar.residual_in = opt_ptr(residual_in, "residual_in");
   g.ar.residual_out = opt_ptr(residual_out, "residual_out");
   g.ar.gamma = gamma.data_ptr();
+  g.one_hop = one_hop;
   TORCH_CHECK(gamma.numel() == hidden && norm_out.numel() == rows * hidden, "gemm_ar_rmsnorm: gamma / norm_out sizes");
   g.ar.norm_out = norm_out.data_ptr();
   g.ar.scale_out = nullptr;
@@ -406,7 +407,8 @@ void ag_gemm(const Tensor& x_shard, const Tensor& w, Tensor out, int64_t tokens,
 void register_extra_ops(torch::Library& m) {
   m.def("gemm_ar_rmsnorm(Tensor a, Tensor w, Tensor? residual_in, Tensor gamma, Tensor(a!)? residual_out, Tensor(b!) norm_out, "
         "Tensor(c!)? scale_out, float eps, Tensor workspace, int out_mode, bool scatter_only, Tensor(d!)? status, "
-        "int splits, Tensor(e!)? splitk_ws, Tensor(f!)? splitk_counters, Tensor? a_scale=None, Tensor? w_scale=None) -> ()",
+        "int splits, Tensor(e!)? splitk_ws, Tensor(f!)? splitk_counters, Tensor? a_scale=None, Tensor? w_scale=None, "
+        "bool one_hop=False) -> ()",
         &gemm_ar_rmsnorm);
   m.def("attention_decode(Tensor q, Tensor k_cache, Tensor v_cache, Tensor seq_lens, Tensor(a!) out, Tensor(b!) partial, "
         "int nsplit, float scale, Tensor(c!)? status) -> ()", &attention_decode);

@@ -26,6 +26,14 @@ from .fused_allreduce import fused_allreduce_rms
 _SM_COUNT = 148
 
 
+def _oneshot_limit(world: int) -> int:
+    """Message bytes up to which the all-reduce op takes its one-shot route at this rank count (the measured table)."""
+    try:
+        return int(_lib.ops().get_policy(world)[0])
+    except Exception:
+        return 512 << 10
+
+
 def _fits(tokens: int, rows: int) -> bool:
     bn = 16 if tokens <= 16 else 64
     return ((rows + 127) // 128) * ((tokens + bn - 1) // bn) <= _SM_COUNT
@@ -36,6 +44,7 @@ def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torc
                        eps: float, *, out_mode: int = OUT_SAME, scatter_only: bool = False,
                        want_residual: bool = True, force_unfused: bool = False, splits: int = 0,
                        a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
+                       one_hop: Optional[bool] = None,
                        ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """``y = all_reduce(a @ w.T); res = y + residual; norm = rmsnorm(res) * gamma``.
 
@@ -43,6 +52,12 @@ def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torc
     token and 128-wide K block) and ``w_scale [hidden/128, K/128]`` (one per 128 x 128 block), fp32. Residual, gamma
     and the non-quantised outputs are bf16. Returns ``(norm, res, scales)``; with ``scatter_only`` only the rows
     ``rank::world`` (and ``residual`` is that row shard).
+
+    ``one_hop``: the tail of the fused kernel. True: every finished tile is pushed into EVERY rank's buffer (one
+    ``multimem.st`` per vector where NVSwitch multicast is mapped) and each rank reduces all rows itself - one trip
+    through NVSwitch, the choice for decode sizes; False: reduce-scatter to the rows' owners, reduce once, gather
+    back - two trips, N times fewer bytes to reduce. None: one hop up to the message size at which the all-reduce
+    op leaves its one-shot algorithm (the same measured limit), replicated output only.
     """
     c = _comm.get_comm()
     tokens, hidden = a.shape[0], w.shape[0]
@@ -74,9 +89,12 @@ def gemm_allreduce_rms(a: torch.Tensor, w: torch.Tensor, residual: Optional[torc
         norm = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=a.device)
         scales = torch.empty(rows, hidden // 128, dtype=torch.float32, device=a.device)
     ws, counters, status = _gemm._workspace(a.device)
+    if one_hop is None:
+        one_hop = (not scatter_only) and _fits(tokens, hidden) and tokens * hidden * 2 <= _oneshot_limit(n)
+    one_hop = bool(one_hop) and not scatter_only and _fits(tokens, hidden) and n * tokens * hidden * 2 <= c.lamport_bytes
     _lib.ops().gemm_ar_rmsnorm(a, w[:hidden] if w.shape[0] != hidden else w, residual, gamma, res_out, norm, scales, eps,
                                c.get_workspace(a), out_mode, scatter_only, status, splits, ws, counters,
-                               a_scale.contiguous() if fp8 else None, w_scale.contiguous() if fp8 else None)
+                               a_scale.contiguous() if fp8 else None, w_scale.contiguous() if fp8 else None, one_hop)
     return norm, res_out, scales
 
 
