@@ -176,7 +176,7 @@ def attention(nchunks, stages, rng):
     p_tile = [{"chunk": None, "reads_pending": 0} for _ in range(2)]
     o_acc = {"chunks": [], "mma_pending": 0, "rescaling": 0}
     outputs = [[] for _ in range(n_sm)]
-    events = {"tma": [], "mma": []}
+    events = {"tma": [], "mma_s": [], "mma_pv": []}      # each issuer's MMAs complete in its issue order
 
     def copy(c):
         s = c % stages
@@ -197,7 +197,7 @@ def attention(nchunks, stages, rng):
             s_buf[c & 1] = c
             kv_reads_pending[s] -= 1
             s_full[c & 1].arrive()
-        events["mma"].append(retire)
+        events["mma_s"].append(retire)
 
     def issue_pv(c):
         s = c % stages
@@ -214,27 +214,32 @@ def attention(nchunks, stages, rng):
             p_tile[c & 1]["reads_pending"] -= 1
             o_full[c & 1].arrive()
             kv_free[s].arrive()
-        events["mma"].append(retire)
+        events["mma_pv"].append(retire)
 
-    def mma():
+    # three issuing threads: copies, score MMAs, P*V MMAs - each with its own chain of waits
+    def loader():
         for c in range(min(nchunks, stages)):
             copy(c)
-        yield from wait(kv_full[0], 0)
-        issue_scores(0)
         for i in range(nchunks):
-            if i + 1 < nchunks:
-                n = i + 1
-                yield from wait(kv_full[n % stages], (n // stages) & 1)
-                if n >= 2:
-                    yield from wait(s_free[n & 1], ((n >> 1) - 1) & 1)
-                issue_scores(n)
-                yield ("step",)
-            yield from wait(p_full[i & 1], (i >> 1) & 1)
-            issue_pv(i)
-            yield ("step",)
             if i + stages < nchunks:
                 yield from wait(kv_free[i % stages], (i // stages) & 1)
                 copy(i + stages)
+            yield ("step",)
+
+    def score_issuer():
+        for c in range(nchunks):
+            yield from wait(kv_full[c % stages], (c // stages) & 1)
+            if c >= 2:
+                yield from wait(s_free[c & 1], ((c >> 1) - 1) & 1)
+            issue_scores(c)
+            yield ("step",)
+
+    def pv_issuer():
+        for c in range(nchunks):
+            yield from wait(p_full[c & 1], (c >> 1) & 1)
+            yield from wait(kv_full[c % stages], (c // stages) & 1)
+            issue_pv(c)
+            yield ("step",)
 
     def softmax(who):
         for i in range(nchunks):
@@ -261,7 +266,7 @@ def attention(nchunks, stages, rng):
         yield from wait(o_full[(nchunks - 1) & 1], ((nchunks - 1) >> 1) & 1)
         assert o_acc["chunks"] == list(range(nchunks)), f"final read saw {o_acc['chunks']}"
 
-    run([mma()] + [softmax(w) for w in range(n_sm)], events, rng)
+    run([loader(), score_issuer(), pv_issuer()] + [softmax(w) for w in range(n_sm)], events, rng)
     assert all(o == list(range(nchunks)) for o in outputs)
 
 

@@ -13,8 +13,9 @@
 // do the online-softmax bookkeeping and write the probabilities as a bf16 [heads, keys] tile (128-byte
 // swizzle, the B operand of the second product). O^T accumulates in tensor memory over all chunks of a
 // split; a head's column of it is rescaled there only when its running maximum has to be raised.
-// A fifth warp issues the TMA copies (3-stage ring) and the MMAs; S^T is double-buffered in TMEM and P in
-// shared memory, so that the scores of chunk i+1 and the P*V product of chunk i-1 run while the softmax
+// Three more warps hold one single-thread role each - the TMA copies (3-stage ring), the score MMAs, the P*V MMAs -
+// so that none of them queues behind the others' asynchronous instructions; S^T is double-buffered in TMEM and P
+// in shared memory, so that the scores of chunk i+1 and the P*V product of chunk i-1 run while the softmax
 // warps work on chunk i.
 //
 // Every wait is bounded; a wait that runs out records a status word, raises the CTA's abort flag
@@ -45,7 +46,7 @@ constexpr int kKeys = 128;                        // cache positions per chunk =
 constexpr int kNq = 16;                           // MMA N: query heads of one KV head, padded
 constexpr int kStages = 3;
 constexpr int kSoftmaxThreads = 128;
-constexpr int kThreads = kSoftmaxThreads + 32;    // + the copy / MMA warp
+constexpr int kThreads = kSoftmaxThreads + 3 * 32;   // + three single-thread roles: copies (warp 4), score MMAs (5), P*V MMAs (6)
 constexpr int kMaxG = 8;
 constexpr int kHalfBytes = kKeys * 128;           // one 64-column half of a K or V chunk
 constexpr int kStageBytes = 4 * kHalfBytes;       // K lo, K hi, V lo, V hi
@@ -154,9 +155,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     o[g] = 0.f;
   }
 
+  // Three single-thread roles, each with its own chain of waits: one thread needs 70-90 cycles per asynchronous
+  // instruction (four copies, eight score MMAs, eight P*V MMAs and three commits per chunk), which done one after the
+  // other took as long as HBM needs to deliver the chunk.
   if (warp == 4) {
     if (lane == 0 && nchunks > 0) {
-      // ---- copies and MMAs ----
+      // ---- copies: a stage is refilled when the P*V product that read its V tile has completed ----
       auto issue_copy = [&](int c) {
         const int st = c % kStages;
         uint8_t* base = ring + st * kStageBytes;
@@ -167,9 +171,25 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         tc::tma_load_4d(base + 2 * kHalfBytes, &map_v, &kv_full[st], 0, hkv, pos0, b);
         tc::tma_load_4d(base + 3 * kHalfBytes, &map_v, &kv_full[st], 64, hkv, pos0, b);
       };
-      auto issue_scores = [&](int c) {   // S^T[buf c & 1] = K chunk * Q^T
+      bool ok = true;
+      for (int c = 0; c < nchunks && c < kStages; ++c) issue_copy(c);
+      for (int i = 0; i + kStages < nchunks && ok; ++i) {
+        ok = tc::mbar_wait(&kv_free[i % kStages], (i / kStages) & 1, kWaitLimit, abort_flag);
+        if (ok) issue_copy(i + kStages);
+      }
+      if (!ok) fail();
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && nchunks > 0) {
+      // ---- scores: S^T[buf c & 1] = K chunk * Q^T, as soon as the chunk has landed and the buffer is free ----
+      const uint32_t qbase = tc::smem_u32(q_tile);
+      bool ok = true;
+      for (int c = 0; c < nchunks && ok; ++c) {
+        ok = tc::mbar_wait(&kv_full[c % kStages], (c / kStages) & 1, kWaitLimit, abort_flag) &&
+             (c < 2 || tc::mbar_wait(&s_free[c & 1], ((c >> 1) - 1) & 1, kWaitLimit, abort_flag));
+        if (!ok) break;
+        tc::fence_after_thread_sync();
         const uint32_t kbase = tc::smem_u32(ring + (c % kStages) * kStageBytes);
-        const uint32_t qbase = tc::smem_u32(q_tile);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
@@ -177,8 +197,18 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             tc::umma<false>(tmem_base + (uint32_t)(c & 1) * kNq, tc::make_smem_desc_sw128(kbase + kb * kHalfBytes) + (uint64_t)(ks * 2),
                             tc::make_smem_desc_sw128(qbase + kb * (kNq * 128)) + (uint64_t)(ks * 2), a.idesc_s, (kb | ks) ? 1u : 0u);
         tc::umma_commit(&s_full[c & 1]);
-      };
-      auto issue_pv = [&](int c) {       // O^T (+)= V chunk^T * P^T, 16 cache positions per instruction
+      }
+      if (!ok) fail();
+    }
+  } else if (warp == 6) {
+    if (lane == 0 && nchunks > 0) {
+      // ---- O^T (+)= V chunk^T * P^T, 16 cache positions per instruction, once the probabilities are written ----
+      bool ok = true;
+      for (int c = 0; c < nchunks && ok; ++c) {
+        ok = tc::mbar_wait(&p_full[c & 1], (c >> 1) & 1, kWaitLimit, abort_flag) &&
+             tc::mbar_wait(&kv_full[c % kStages], (c / kStages) & 1, kWaitLimit, abort_flag);
+        if (!ok) break;
+        tc::fence_after_thread_sync();
         const uint32_t vbase = tc::smem_u32(ring + (c % kStages) * kStageBytes + 2 * kHalfBytes);
         const uint32_t pbase = tc::smem_u32(p_tile + (c & 1) * kSmallTileBytes);
 #pragma unroll
@@ -188,32 +218,6 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                           (c | j) ? 1u : 0u);
         tc::umma_commit(&o_full[c & 1]);
         tc::umma_commit(&kv_free[c % kStages]);
-      };
-      bool ok = true;
-      for (int c = 0; c < nchunks && c < kStages; ++c) issue_copy(c);
-      ok = tc::mbar_wait(&kv_full[0], 0, kWaitLimit, abort_flag);
-      if (ok) {
-        tc::fence_after_thread_sync();
-        issue_scores(0);
-      }
-      for (int i = 0; i < nchunks && ok; ++i) {
-        if (i + 1 < nchunks) {
-          const int n = i + 1;
-          ok = tc::mbar_wait(&kv_full[n % kStages], (n / kStages) & 1, kWaitLimit, abort_flag) &&
-               (n < 2 || tc::mbar_wait(&s_free[n & 1], ((n >> 1) - 1) & 1, kWaitLimit, abort_flag));
-          if (!ok) break;
-          tc::fence_after_thread_sync();
-          issue_scores(n);
-        }
-        ok = tc::mbar_wait(&p_full[i & 1], (i >> 1) & 1, kWaitLimit, abort_flag);
-        if (!ok) break;
-        tc::fence_after_thread_sync();
-        issue_pv(i);
-        if (i + kStages < nchunks) {
-          ok = tc::mbar_wait(&kv_free[i % kStages], (i / kStages) & 1, kWaitLimit, abort_flag);
-          if (!ok) break;
-          issue_copy(i + kStages);
-        }
       }
       if (!ok) fail();
     }
