@@ -377,6 +377,9 @@ class _ReferenceWatchdog:
     def progress(self, where: str) -> None:
         self._last, self.where = self._time.monotonic(), where
 
+    def stop(self) -> None:
+        self.limit_s = float("inf")
+
     def _watch(self) -> None:
         while True:
             self._time.sleep(1.0)
@@ -404,6 +407,8 @@ def main():
     if args.impl == "reference":
         _watchdog = _ReferenceWatchdog()
     result = run(args)
+    if _watchdog is not None:
+        _watchdog.stop()          # the arm has its result: nothing after this point may print a second line
     if result is not None and int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(result), flush=True)
     if torch.distributed.is_available() and torch.distributed.is_initialized():
