@@ -44,3 +44,16 @@ def test_attention_splits_fit_one_wave_and_keep_128_positions(batch, kv_heads, m
     assert s >= 1
     assert s <= max(1, -(-max_len // 128))                       # at least 128 positions per split
     assert s == 1 or batch * kv_heads * s <= 2 * SMS             # two CTAs per SM, one wave
+    t = attention.pick_splits(batch, kv_heads, max_len, ctas_per_sm=1)
+    assert 1 <= t <= max(1, -(-max_len // 128))
+    assert t == 1 or batch * kv_heads * t <= SMS                 # the tensor-core kernel holds one CTA per SM
+
+
+def test_tensor_core_attention_splits_follow_the_measured_costs():
+    pick = lambda b, h, n: attention.pick_splits(b, h, n, ctas_per_sm=1)
+    assert pick(1, 1, 2048) == 8                                 # 16 chunks: 8 x 2, not 16 x 1 (merge grows with the splits)
+    assert pick(16, 1, 2048) == 4                                # not 9: 9 splits leave 2 chunks to most CTAs, like 8
+    assert pick(64, 1, 2048) == 1                                # a third of the SMs already busy: the merge costs more
+    assert pick(16, 8, 2048) == 1
+    assert pick(1, 1, 128) == 1
+    assert pick(3, 2, 100000) > 8                                # long contexts still spread over the SMs

@@ -338,16 +338,46 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       tc::named_barrier_sync(1, kSoftmaxThreads);
       if (s_last) {
         __threadfence();
+        // Loads first, arithmetic after: a load whose value is needed by the next instruction costs a round trip to
+        // L2 each, and written naively the merge is two dependent chains of nsplit loads per head. Eight splits at a
+        // time: all their maxima (of every head) in one round trip, then per head their sums and partial outputs.
+        const float* src0 = a.partial + ((int64_t)b * a.Hq + hkv * kG) * a.nsplit * (kD + 2);
+        const int64_t head_stride = (int64_t)a.nsplit * (kD + 2);
+        float m[kG];
+#pragma unroll
+        for (int g = 0; g < kG; ++g) m[g] = -FLT_MAX;
+        for (int sp0 = 0; sp0 < a.nsplit; sp0 += 8) {
+          float mv[kG][8];
+#pragma unroll
+          for (int g = 0; g < kG; ++g)
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              mv[g][u] = sp0 + u < a.nsplit ? __ldcg(src0 + g * head_stride + (sp0 + u) * (kD + 2) + kD) : -FLT_MAX;
+#pragma unroll
+          for (int g = 0; g < kG; ++g)
+#pragma unroll
+            for (int u = 0; u < 8; ++u) m[g] = fmaxf(m[g], mv[g][u]);
+        }
 #pragma unroll
         for (int g = 0; g < kG; ++g) {
-          const float* src = a.partial + ((int64_t)b * a.Hq + hkv * kG + g) * a.nsplit * (kD + 2);
-          float m = -FLT_MAX;
-          for (int sp = 0; sp < a.nsplit; ++sp) m = fmaxf(m, __ldcg(src + sp * (kD + 2) + kD));
+          const float* src = src0 + g * head_stride;
           float num = 0.f, den = 0.f;
-          for (int sp = 0; sp < a.nsplit; ++sp) {
-            const float wgt = __expf(__ldcg(src + sp * (kD + 2) + kD) - m);
-            num = fmaf(wgt, __ldcg(src + sp * (kD + 2) + tid), num);
-            den = fmaf(wgt, __ldcg(src + sp * (kD + 2) + kD + 1), den);
+          for (int sp0 = 0; sp0 < a.nsplit; sp0 += 8) {
+            float mm[8], ll[8], vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const bool on = sp0 + u < a.nsplit;
+              const float* row = src + (sp0 + u) * (kD + 2);
+              mm[u] = on ? __ldcg(row + kD) : -FLT_MAX;
+              ll[u] = on ? __ldcg(row + kD + 1) : 0.f;
+              vv[u] = on ? __ldcg(row + tid) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const float wgt = sp0 + u < a.nsplit ? __expf(mm[u] - m[g]) : 0.f;
+              num = fmaf(wgt, vv[u], num);
+              den = fmaf(wgt, ll[u], den);
+            }
           }
           a.out[((int64_t)b * a.Hq + hkv * kG + g) * kD + tid] = __float2bfloat16(den > 0.f ? num / den : 0.f);
         }

@@ -24,13 +24,34 @@ def _partial(device, floats: int) -> torch.Tensor:
     return _scratch[key]
 
 
+# Measured on a B200 for the tensor-core kernel (2048 positions, 1 to 64 sequences, 1 and 8 KV heads): a CTA takes
+# about 1.0 us per 128-position chunk while the grid is small and 13.1 ns x (CTAs in flight) once the grid saturates
+# HBM; an unsplit launch costs about 2.6 us besides, a split one 9 us plus 0.4 us per split (partial results through
+# L2, the arrival counter and the merge by the last CTA of each group).
+_CHUNK_US, _CHUNK_US_PER_CTA, _UNSPLIT_US, _SPLIT_US, _PER_SPLIT_US = 1.0, 0.0131, 2.6, 9.0, 0.4
+
+
+def _split_cost_us(pairs: int, chunks: int, nsplit: int) -> float:
+    ctas = pairs * nsplit
+    per_chunk = max(_CHUNK_US, _CHUNK_US_PER_CTA * ctas)
+    return -(-chunks // nsplit) * per_chunk + (_UNSPLIT_US if nsplit == 1 else _SPLIT_US + _PER_SPLIT_US * nsplit)
+
+
 def pick_splits(batch: int, kv_heads: int, max_len: int, sms: int = 148, ctas_per_sm: int = 2) -> int:
-    """KV splits such that the grid fits ONE wave of the CTAs that the SMs hold at a time (two per SM
-    for the SIMT kernel, one for the tensor-core kernel; a second, partly filled wave costs more
-    than shorter splits save), with at least 128 positions per split."""
+    """KV splits of at least 128 positions each, such that the grid fits ONE wave of the CTAs that the SMs hold at a
+    time (two per SM for the SIMT kernel, one for the tensor-core kernel; a second, partly filled wave costs more than
+    shorter splits save).
+
+    The SIMT kernel takes the most splits that fit. The tensor-core kernel (``ctas_per_sm=1``) takes the split count
+    with the least estimated time: a split that leaves some CTAs one chunk more than others (16 chunks over 9 splits)
+    is no faster than the next count that divides evenly (8), and once the unsplit grid already covers a third of
+    the SMs (64 sequences on one KV head) the merge costs more than the shorter loops save."""
     pairs = batch * kv_heads
-    want = max(1, (ctas_per_sm * sms) // pairs)
-    return max(1, min(want, (max_len + 127) // 128))
+    chunks = max(1, (max_len + 127) // 128)
+    most = max(1, min((ctas_per_sm * sms) // pairs, chunks))
+    if ctas_per_sm != 1:
+        return most
+    return min(range(1, most + 1), key=lambda n: (_split_cost_us(pairs, chunks, n), n))
 
 
 @traced("tdx.decode_attention")
