@@ -120,3 +120,28 @@ def test_sequence_parallel_mode_equals_replicated_mode(fp8):
         del model
     assert (hidden["ar"] - hidden["sp"]).abs().max().item() <= (0.12 if fp8 else 0.05)
     assert torch.equal(nxt["ar"], nxt["sp"]) or not fp8
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_fused_gemm_epilogues_equal_the_separate_kernels(fp8, monkeypatch):
+    """Rotary embedding + KV append inside the qkv GEMM and silu(gate) * up inside the gate/up GEMM (the default) against
+    the same step with the separate kernels: hidden state, appended cache rows and next tokens."""
+    from torch_dist_ext_b200.models import llama
+
+    cfg = LlamaConfig.tiny(fp8=fp8)
+    tokens = torch.arange(6, device="cuda") * 13 % cfg.vocab
+    positions = torch.tensor([3, 9, 9, 0, 17, 11], device="cuda")
+    hidden, nxt, caches = {}, {}, {}
+    for fused in (True, False):
+        monkeypatch.setattr(llama, "_FUSED_EPILOGUES", fused)
+        model = TPLlama(cfg, max_batch=8, max_seq=32, seed=5)
+        model.fill_cache_random(6, 18, seed=3)
+        nxt[fused] = model.decode_step(tokens, positions, max_len=19)
+        hidden[fused] = model.last_hidden.float().clone()
+        caches[fused] = (torch.stack(model.k_cache).float(), torch.stack(model.v_cache).float())
+        del model
+    assert (hidden[True] - hidden[False]).abs().max().item() <= (0.12 if fp8 else 0.05)
+    for a, b in zip(caches[True], caches[False]):
+        assert (a - b).abs().max().item() <= 0.05 * max(1.0, float(b.abs().max()))
+    assert torch.equal(nxt[True], nxt[False]) or fp8
+    tdx.check_status()

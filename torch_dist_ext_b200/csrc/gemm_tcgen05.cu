@@ -8,7 +8,11 @@
 // for decode-sized M, so that the weights fill the 128-row dimension of the instruction and the
 // few tokens sit on the narrow N side; the output strides (sx, sy) place D either way round.
 // K can be split over gridDim.z; partial tiles are then reduced in an fp32 workspace with
-// red.global.add and finished by whichever CTA arrives last at the tile.
+// red.global.add and finished by whichever CTA arrives last at the tile. That finalizer can do more than
+// store: with the weights on the 128-row side it holds 128 output features of up to kBN tokens, enough to
+// rotate a head of a fused qkv projection and append it to the KV cache (rotate-half pairs element i with
+// i + 64), or to form silu(gate) * up when the tile was loaded as 64 gate rows and the 64 up rows of the
+// same features. Either saves a kernel of the decode layer's latency chain.
 //
 // fp8 (e4m3) operands use kind::f8f6f4. With block scales (1x128 on one operand, 128x128 on the
 // other, fp32) each 128-wide K block is multiplied into its own TMEM buffer and promoted by the
@@ -64,7 +68,92 @@ struct GemmArgs {
   int scale_kb;            // K blocks per scale row (= total K / 128)
   int x_static;            // X is never written by a kernel (weights): its first tiles may be requested before the
                            // previous kernel of the stream has finished
+  PairEpilogue epi;        // what the split-K finalizer does with rows r and r + 64 of a tile (kEpiNone: plain store)
 };
+
+// ---- pair epilogues ---------------------------------------------------------------------------------------
+// The finalizer of a tile whose rows r and r + 64 belong together. The 128 epilogue threads split the work as 64 row
+// pairs x 2 column halves; a thread walks its half in steps of kPairW columns. Everything a step needs is requested
+// before anything is used - the two sums per column from the split-K scratch, the angles of the columns' positions -
+// and the positions themselves are fetched one step ahead (those of the first step before the CTA even knows whether
+// it is the finalizer), so that a step costs one round trip to L2, not three dependent ones.
+template <int kBN>
+struct PairShape {
+  static constexpr int kHalf = kBN / 2;                  // columns per thread
+  static constexpr int kW = kHalf < 16 ? kHalf : 16;     // columns per step
+  static constexpr int kSteps = kHalf / kW;
+};
+
+template <int kW>
+__device__ __forceinline__ void pair_positions(const GemmArgs& a, int y0, int (&pos)[kW]) {
+#pragma unroll
+  for (int j = 0; j < kW; ++j) pos[j] = y0 + j < a.y_rows ? (int)__ldg(a.epi.positions + y0 + j) : 0;
+}
+
+// `tile_ws`: this tile's fp32 sums, [column][128 rows]; `pos`: positions of the first step's columns (rope only).
+template <int kBN>
+__device__ __forceinline__ void pair_finalize(const GemmArgs& a, int tile_x, float* tile_ws, int r, int half, int y_base,
+                                              int (&pos)[PairShape<kBN>::kW]) {
+  using S = PairShape<kBN>;
+  constexpr int kW = S::kW;
+  const PairEpilogue& e = a.epi;
+  const bool rope = e.kind == kEpiRopeKv;
+  // rope: tile_x is the head (queries, then keys, then values)
+  const bool is_q = tile_x < e.q_heads;
+  const bool is_v = tile_x >= e.q_heads + e.kv_heads;
+  const bool rotate = rope && !is_v;
+  __nv_bfloat16* cache = (!rope || is_q) ? nullptr : static_cast<__nv_bfloat16*>(is_v ? e.v_cache : e.k_cache);
+  const int kv_head = tile_x - e.q_heads - (is_v ? e.kv_heads : 0);
+  const int64_t x_lo = rope ? (int64_t)tile_x * kBM + r : (int64_t)tile_x * 64 + r;
+  float* src = tile_ws + r;
+#pragma unroll 1
+  for (int s = 0; s < S::kSteps; ++s) {
+    const int c = half * S::kHalf + s * kW;
+    float lo[kW], hi[kW], cs[kW], sn[kW];
+    int cur[kW];
+#pragma unroll
+    for (int j = 0; j < kW; ++j) {
+      lo[j] = __ldcg(src + (size_t)(c + j) * kBM);
+      hi[j] = __ldcg(src + (size_t)(c + j) * kBM + 64);
+      cur[j] = pos[j];
+    }
+    if (rotate) {
+#pragma unroll
+      for (int j = 0; j < kW; ++j) {
+        const int p = cur[j] < 0 ? 0 : (cur[j] >= e.max_pos ? e.max_pos - 1 : cur[j]);
+        cs[j] = __ldg(e.cos_sin + (int64_t)p * 128 + r);
+        sn[j] = __ldg(e.cos_sin + (int64_t)p * 128 + 64 + r);
+      }
+    }
+    if (rope && s + 1 < S::kSteps) pair_positions<kW>(a, y_base + c + kW, pos);
+#pragma unroll
+    for (int j = 0; j < kW; ++j) {
+      __stcg(src + (size_t)(c + j) * kBM, 0.f);
+      __stcg(src + (size_t)(c + j) * kBM + 64, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kW; ++j) {
+      const int y = y_base + c + j;
+      if (y >= a.y_rows) continue;
+      if (!rope) {   // silu(gate) * up
+        gemm_core::store_out(a, x_lo * a.sx + (int64_t)y * a.sy, lo[j] / (1.f + __expf(-lo[j])) * hi[j]);
+        continue;
+      }
+      float o_lo = lo[j], o_hi = hi[j];
+      if (rotate) {
+        o_lo = lo[j] * cs[j] - hi[j] * sn[j];
+        o_hi = hi[j] * cs[j] + lo[j] * sn[j];
+      }
+      gemm_core::store_out(a, x_lo * a.sx + (int64_t)y * a.sy, o_lo);
+      gemm_core::store_out(a, (x_lo + 64) * a.sx + (int64_t)y * a.sy, o_hi);
+      if (cache != nullptr && cur[j] >= 0 && cur[j] < e.cache_seq) {
+        __nv_bfloat16* dst = cache + (int64_t)y * e.cache_batch_stride + (int64_t)cur[j] * e.cache_pos_stride + kv_head * 128 + r;
+        dst[0] = __float2bfloat16(o_lo);
+        dst[64] = __float2bfloat16(o_hi);
+      }
+    }
+  }
+}
 
 template <int kBN, int kStages, bool kFp8, bool kScaled>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -94,10 +183,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       // With static X (decode orientation: the weights) the first ring of X tiles is requested before the wait for
       // the previous kernel of the stream; everything else is read and written after it.
       if (!a.x_static) ptx::pdl_wait();
-      pipe.template produce<kElemsPerBlock>(&map_x, &map_y, tile_x * kBM, tile_y * kBN, kb0, nkb, a.status, [] {
+      // silu(gate) * up: 64 gate rows and the 64 up rows of the same features make one 128-row tile
+      const bool halves = a.epi.kind == kEpiSiluMul;
+      pipe.template produce<kElemsPerBlock>(&map_x, &map_y, halves ? tile_x * 64 : tile_x * kBM, tile_y * kBN, kb0, nkb, a.status, [] {
         ptx::pdl_wait();
         return true;
-      });
+      }, halves ? a.epi.ffn + tile_x * 64 : -1);
       ptx::pdl_launch_dependents();
     }
   } else if (warp == 1) {
@@ -171,6 +262,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
     }
+    int pair_pos[PairShape<kBN>::kW] = {};
+    if (split && a.epi.kind == kEpiRopeKv) pair_positions<PairShape<kBN>::kW>(a, y_base + (q >> 1) * PairShape<kBN>::kHalf, pair_pos);
     if (split) {
       // the CTA that arrives last at this tile turns the fp32 sums into the output and re-zeroes them
       __threadfence();
@@ -183,15 +276,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (*last_flag) {
         __threadfence();
         float* src = a.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN) + q * 32 + lane;
+        if (a.epi.kind == kEpiNone) {
 #pragma unroll
-        for (int c = 0; c < kBN; c += 16) {
-          float v[16];
+          for (int c = 0; c < kBN; c += 16) {
+            float v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            v[j] = __ldcg(src + (size_t)(c + j) * kBM);
-            __stcg(src + (size_t)(c + j) * kBM, 0.f);
+            for (int j = 0; j < 16; ++j) {
+              v[j] = __ldcg(src + (size_t)(c + j) * kBM);
+              __stcg(src + (size_t)(c + j) * kBM, 0.f);
+            }
+            store_chunk(a, x, y_base + c, v);
           }
-          store_chunk(a, x, y_base + c, v);
+        } else {
+          pair_finalize<kBN>(a, tile_x, a.ws + (size_t)(tile_y * gridDim.x + tile_x) * (kBM * kBN), (q & 1) * 32 + lane, q >> 1,
+                             y_base, pair_pos);
         }
         if (threadIdx.x == 64) a.counters[tile_y * gridDim.x + tile_x] = 0;
       }
@@ -272,6 +370,23 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
   a.y_rows = g.y_rows;
   a.kblocks = g.k / epb;
   int splits = g.splits < 1 ? 1 : g.splits;
+  const int epi = g.epi.kind;
+  if (epi != kEpiNone) {
+    // the pair epilogues live in the split-K finalizer
+    if (a.kblocks < 2) return "a pair epilogue needs K of at least two 128-byte blocks";
+    if (splits < 2) splits = 2;
+    if (epi == kEpiRopeKv) {
+      if (g.epi.q_heads < 0 || g.epi.kv_heads < 1 || g.x_rows != (g.epi.q_heads + 2 * g.epi.kv_heads) * kBM)
+        return "rope epilogue: X must hold (q_heads + 2 kv_heads) heads of 128 rows";
+      if (!g.epi.positions || !g.epi.cos_sin || !g.epi.k_cache || !g.epi.v_cache || g.epi.max_pos < 1 || g.epi.cache_seq < 1)
+        return "rope epilogue: positions, angle table and caches are required";
+    } else if (epi == kEpiSiluMul) {
+      if (scaled) return "silu epilogue: block-scaled operands are not supported";
+      if (g.epi.ffn < 64 || g.epi.ffn % 64 || g.x_rows != 2 * g.epi.ffn) return "silu epilogue: X must be [2 ffn, k] with ffn a multiple of 64";
+    } else {
+      return "unknown pair epilogue";
+    }
+  }
   if (splits > a.kblocks) splits = a.kblocks;
   a.kblocks_per_split = (a.kblocks + splits - 1) / splits;
   splits = (a.kblocks + a.kblocks_per_split - 1) / a.kblocks_per_split;
@@ -281,7 +396,9 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
   a.out_dtype = g.out_dtype;
   a.idesc = fp8 ? tc::make_idesc(kBM, bn, 0, 0) : tc::make_idesc(kBM, bn, g.elem_kind == kBF16 ? 1 : 0, g.elem_kind == kBF16 ? 1 : 0);
   a.status = g.status;
-  const dim3 grid((g.x_rows + kBM - 1) / kBM, (g.y_rows + bn - 1) / bn, splits);
+  const dim3 grid(epi == kEpiSiluMul ? g.epi.ffn / 64 : (g.x_rows + kBM - 1) / kBM, (g.y_rows + bn - 1) / bn, splits);
+  if (epi != kEpiNone && splits < 2) return "a pair epilogue needs at least two K splits";
+  a.epi = g.epi;
   if (splits > 1) {
     if (!g.ws || !g.counters) return "split-K needs a workspace";
     a.ws_ld = grid.y * bn;
@@ -297,7 +414,8 @@ std::string gemm_tn(const GemmProblem& g, cudaStream_t stream) {
   a.scale_kb = a.kblocks;
   a.x_static = g.x_static;
   CUtensorMap mx, my;
-  std::string err = tma::kmajor_2d(&mx, g.x, g.x_rows, g.k, g.ldx, g.elem_size, g.elem_kind, kBM);
+  // silu epilogue: the X tile arrives as two boxes of 64 rows (gate rows, then the up rows of the same features)
+  std::string err = tma::kmajor_2d(&mx, g.x, g.x_rows, g.k, g.ldx, g.elem_size, g.elem_kind, epi == kEpiSiluMul ? 64 : kBM);
   if (!err.empty()) return err;
   err = tma::kmajor_2d(&my, g.y, g.y_rows, g.k, g.ldy, g.elem_size, g.elem_kind, bn);
   if (!err.empty()) return err;

@@ -8,6 +8,29 @@
 namespace tdx {
 
 // D[x, y] = sum_k X[x, k] * Y[y, k];  D[x, y] is written to out[x * sx + y * sy].
+// What the split-K finalizer of gemm_tn does with the summed tile instead of a plain store. Both kinds combine row r
+// of a 128-row tile with row r + 64, so they need X on the 128-row side (the weights: decode orientation), at least
+// two K splits (the finalizer is the CTA that arrives last at a tile) and a 16-bit or fp32 output.
+enum PairEpilogueKind { kEpiNone = 0, kEpiRopeKv = 1, kEpiSiluMul = 2 };
+struct PairEpilogue {
+  int kind;
+  // kEpiRopeKv: X rows are [q_heads | kv_heads keys | kv_heads values] x 128 (a fused qkv projection), y = token.
+  // Query and key heads are rotated (rotate-half: element i pairs with i + 64) by the angle of positions[y] and written
+  // to `out`; key and value heads are also written to k_cache / v_cache [batch, cache_seq, kv_heads, 128] (bf16) at
+  // [y, positions[y]].
+  int q_heads, kv_heads;
+  const int64_t* positions;   // [y_rows]
+  const float* cos_sin;       // [max_pos, 128]: the 64 cosines, then the 64 sines
+  int max_pos, cache_seq;
+  void* k_cache;
+  void* v_cache;
+  int64_t cache_batch_stride, cache_pos_stride;   // elements
+  // kEpiSiluMul: X is [2 * ffn, k], gate rows then up rows (ffn a multiple of 64). Tile t holds gate rows
+  // [64 t, 64 t + 64) in its rows 0-63 and the up rows of the same features in rows 64-127;
+  // out[y * sy + (64 t + r) * sx] = silu(gate) * up.
+  int ffn;
+};
+
 struct GemmProblem {
   const void* x;       // [x_rows, k], row pitch ldx elements; fills the 128-row side of the tile
   const void* y;       // [y_rows, k], row pitch ldy elements; the tile's narrow side (16..256)
@@ -32,6 +55,7 @@ struct GemmProblem {
   // X holds data that no kernel writes (weights): with programmatic dependent launch its first tiles are requested
   // before the previous kernel of the stream has completed.
   int x_static;
+  PairEpilogue epi;    // kind == kEpiNone: plain store
 };
 
 std::string gemm_tn(const GemmProblem& g, cudaStream_t stream);

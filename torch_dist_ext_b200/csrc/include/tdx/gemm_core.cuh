@@ -145,10 +145,13 @@ struct Pipeline {
   // One thread. Streams `nkb` K blocks starting at block `kb0`. `gate_y` is called once, before the
   // first Y (narrow-side) tile is requested; X tiles of the first ring pass are requested before it,
   // so that a wait inside the gate overlaps the fetch of the wide operand.
+  // `x_row1 >= 0`: the X tile is two runs of 64 rows, starting at x_row0 and x_row1, fetched by two copies through a
+  // tensor map whose box is 64 rows (the second run lands 8 KB into the stage, where a 128-row box would have put
+  // its rows 64-127: the swizzle pattern repeats every 1 KB, so the MMA sees one 128-row tile).
   template <int kElemsPerBlock, typename Gate>
   __device__ __forceinline__ void produce(const CUtensorMap* mx, const CUtensorMap* my, int x_row0, int y_row0, int kb0,
-                                          int nkb, uint32_t* status, Gate gate_y) {
-    produce_pick<kElemsPerBlock>(mx, x_row0, y_row0, kb0, nkb, status, gate_y, [my] { return my; });
+                                          int nkb, uint32_t* status, Gate gate_y, int x_row1 = -1) {
+    produce_pick<kElemsPerBlock>(mx, x_row0, y_row0, kb0, nkb, status, gate_y, [my] { return my; }, x_row1);
   }
 
   // The same with the Y tensor map chosen only after the gate has passed (`*parity` odd: my1, else my0), for a Y
@@ -162,12 +165,13 @@ struct Pipeline {
 
   template <int kElemsPerBlock, typename Gate, typename PickY>
   __device__ __forceinline__ void produce_pick(const CUtensorMap* mx, int x_row0, int y_row0, int kb0, int nkb,
-                                               uint32_t* status, Gate gate_y, PickY pick_y) {
+                                               uint32_t* status, Gate gate_y, PickY pick_y, int x_row1 = -1) {
     using L = SmemLayout<kBN, kStages>;
     const int first = nkb < kStages ? nkb : kStages;
     for (int i = 0; i < first; ++i) {
       tc::mbar_arrive_expect_tx(&full[i], L::kStageBytes);
       tc::tma_load_2d(smem + i * L::kStageBytes, mx, &full[i], (kb0 + i) * kElemsPerBlock, x_row0);
+      if (x_row1 >= 0) tc::tma_load_2d(smem + i * L::kStageBytes + L::kXBytes / 2, mx, &full[i], (kb0 + i) * kElemsPerBlock, x_row1);
     }
     if (!gate_y()) {
       fail(status);
@@ -185,6 +189,7 @@ struct Pipeline {
       uint8_t* sx = smem + s * L::kStageBytes;
       tc::mbar_arrive_expect_tx(&full[s], L::kStageBytes);
       tc::tma_load_2d(sx, mx, &full[s], (kb0 + i) * kElemsPerBlock, x_row0);
+      if (x_row1 >= 0) tc::tma_load_2d(sx + L::kXBytes / 2, mx, &full[s], (kb0 + i) * kElemsPerBlock, x_row1);
       tc::tma_load_2d(sx + L::kXBytes, my, &full[s], (kb0 + i) * kElemsPerBlock, y_row0);
     }
   }

@@ -155,8 +155,9 @@ void rope_impl(Tensor q, Tensor k, const Tensor& positions, const Tensor& cos_si
 }
 
 // D[x, y] = sum_k X[x, k] * Y[y, k] written to out.flatten()[x * sx + y * sy] (tcgen05 GEMM).
+// `out_x_rows`: how many x rows the output holds when that is not X's row count (the silu epilogue halves it).
 static tdx::GemmProblem gemm_problem(const Tensor& x, const Tensor& y, Tensor& out, int64_t sx, int64_t sy,
-                                     const c10::optional<Tensor>& status) {
+                                     const c10::optional<Tensor>& status, int64_t out_x_rows = -1) {
   TORCH_CHECK(x.is_cuda() && y.is_cuda() && out.is_cuda() && x.dim() == 2 && y.dim() == 2, "gemm_tn: 2-D CUDA operands expected");
   TORCH_CHECK(x.stride(1) == 1 && y.stride(1) == 1, "gemm_tn: operands must be K-major (unit stride along K)");
   TORCH_CHECK(x.size(1) == y.size(1) && x.scalar_type() == y.scalar_type(), "gemm_tn: operands disagree in K or dtype");
@@ -176,7 +177,7 @@ static tdx::GemmProblem gemm_problem(const Tensor& x, const Tensor& y, Tensor& o
   g.sx = sx;
   g.sy = sy;
   g.out_dtype = dtype_code(out);
-  const int64_t max_idx = (g.x_rows - 1) * sx + (g.y_rows - 1) * sy;
+  const int64_t max_idx = ((out_x_rows >= 0 ? out_x_rows : g.x_rows) - 1) * sx + (g.y_rows - 1) * sy;
   TORCH_CHECK(g.x_rows == 0 || g.y_rows == 0 || (max_idx < out.numel() && sx >= 1 && sy >= 1), "gemm_tn: output strides exceed the output tensor");
   if (status.has_value() && status->defined()) g.status = reinterpret_cast<uint32_t*>(status->data_ptr<int>());
   return g;
@@ -211,6 +212,85 @@ void gemm_tn(const Tensor& x, const Tensor& y, Tensor out, int64_t sx, int64_t s
   }
   const std::string err = tdx::gemm_tn(g, cur_stream());
   TORCH_CHECK(err.empty(), "gemm_tn: ", err);
+}
+
+static void gemm_scratch(tdx::GemmProblem& g, const Tensor& ws, const Tensor& counters, const char* who) {
+  TORCH_CHECK(ws.is_cuda() && counters.is_cuda() && ws.scalar_type() == at::kFloat && counters.scalar_type() == at::kInt, who,
+              ": the split-K scratch must be float32 / int32 CUDA tensors");
+  g.ws = ws.data_ptr<float>();
+  g.ws_bytes = (size_t)ws.numel() * 4;
+  g.counters = reinterpret_cast<uint32_t*>(counters.data_ptr<int>());
+  g.counter_count = (size_t)counters.numel();
+}
+
+// Fused qkv projection of a decode step whose split-K finalizer rotates the query and key heads and appends keys and
+// values to the caches: out[t, :] = rope(a[t] @ w^T), k_cache[t, positions[t]] / v_cache[t, positions[t]] = the new rows.
+// w [(q_heads + 2 kv_heads) * 128, K] (bf16 / fp16, or e4m3 with 128 x 128 scales and 1 x 128 scales on a).
+void gemm_tn_rope_kv(const Tensor& w, const Tensor& a, Tensor out, int64_t block_n, int64_t splits, const Tensor& ws,
+                     const Tensor& counters, const c10::optional<Tensor>& status, const c10::optional<Tensor>& w_scale,
+                     const c10::optional<Tensor>& a_scale, const Tensor& positions, const Tensor& cos_sin, Tensor k_cache,
+                     Tensor v_cache, int64_t q_heads, int64_t kv_heads) {
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(0) == a.size(0) && out.size(1) == w.size(0),
+              "gemm_tn_rope_kv: out must be [tokens, (q_heads + 2 kv_heads) * 128] with unit stride along the features");
+  tdx::GemmProblem g = gemm_problem(w, a, out, 1, out.stride(0), status);
+  const c10::cuda::CUDAGuard guard(w.device());
+  g.x_static = 1;
+  g.block_n = (int)block_n;
+  g.splits = (int)splits;
+  gemm_scratch(g, ws, counters, "gemm_tn_rope_kv");
+  if (w_scale.has_value() && w_scale->defined()) {
+    TORCH_CHECK(a_scale.has_value() && a_scale->defined(), "gemm_tn_rope_kv: both operands need scales");
+    TORCH_CHECK(w_scale->scalar_type() == at::kFloat && a_scale->scalar_type() == at::kFloat && w_scale->is_contiguous() && a_scale->is_contiguous(),
+                "gemm_tn_rope_kv: scales must be contiguous float32");
+    const int64_t kb = g.k / 128;
+    TORCH_CHECK(w_scale->numel() == (g.x_rows + 127) / 128 * kb && a_scale->numel() == (int64_t)g.y_rows * kb, "gemm_tn_rope_kv: scales have the wrong size");
+    g.x_scale = w_scale->data_ptr<float>();
+    g.y_scale = a_scale->data_ptr<float>();
+    g.x_scale_per_row = 0;
+    g.y_scale_per_row = 1;
+  }
+  TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.numel() >= a.size(0),
+              "gemm_tn_rope_kv: positions must be a contiguous int64 CUDA tensor with one entry per token");
+  TORCH_CHECK(cos_sin.is_cuda() && cos_sin.scalar_type() == at::kFloat && cos_sin.is_contiguous() && cos_sin.dim() == 2 && cos_sin.size(1) == 128,
+              "gemm_tn_rope_kv: the angle table must be contiguous float32 [max_pos, 128]");
+  for (const Tensor* c : {&k_cache, &v_cache})
+    TORCH_CHECK(c->is_cuda() && c->scalar_type() == at::kBFloat16 && c->dim() == 4 && c->size(0) >= a.size(0) && c->size(2) == kv_heads &&
+                    c->size(3) == 128 && c->stride(3) == 1 && c->stride(2) == 128,
+                "gemm_tn_rope_kv: caches must be bfloat16 [batch >= tokens, seq, kv_heads, 128] with contiguous heads");
+  TORCH_CHECK(k_cache.sizes() == v_cache.sizes() && k_cache.strides() == v_cache.strides(), "gemm_tn_rope_kv: the caches must agree in shape");
+  g.epi.kind = tdx::kEpiRopeKv;
+  g.epi.q_heads = (int)q_heads;
+  g.epi.kv_heads = (int)kv_heads;
+  g.epi.positions = positions.data_ptr<int64_t>();
+  g.epi.cos_sin = cos_sin.data_ptr<float>();
+  g.epi.max_pos = (int)cos_sin.size(0);
+  g.epi.cache_seq = (int)k_cache.size(1);
+  g.epi.k_cache = k_cache.data_ptr();
+  g.epi.v_cache = v_cache.data_ptr();
+  g.epi.cache_batch_stride = k_cache.stride(0);
+  g.epi.cache_pos_stride = k_cache.stride(1);
+  const std::string err = tdx::gemm_tn(g, cur_stream());
+  TORCH_CHECK(err.empty(), "gemm_tn_rope_kv: ", err);
+}
+
+// Gate/up projection of a decode step whose split-K finalizer applies the activation:
+// out[t, f] = silu(a[t] . w[f]) * (a[t] . w[ffn + f]) for w [2 ffn, K] (bf16 / fp16).
+void gemm_tn_silu_mul(const Tensor& w, const Tensor& a, Tensor out, int64_t block_n, int64_t splits, const Tensor& ws,
+                      const Tensor& counters, const c10::optional<Tensor>& status) {
+  TORCH_CHECK(w.dim() == 2 && w.size(0) % 2 == 0, "gemm_tn_silu_mul: w must be [2 ffn, K]");
+  const int64_t ffn = w.size(0) / 2;
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.stride(1) == 1 && out.size(0) == a.size(0) && out.size(1) == ffn,
+              "gemm_tn_silu_mul: out must be [tokens, ffn] with unit stride along the features");
+  tdx::GemmProblem g = gemm_problem(w, a, out, 1, out.stride(0), status, ffn);
+  const c10::cuda::CUDAGuard guard(w.device());
+  g.x_static = 1;
+  g.block_n = (int)block_n;
+  g.splits = (int)splits;
+  gemm_scratch(g, ws, counters, "gemm_tn_silu_mul");
+  g.epi.kind = tdx::kEpiSiluMul;
+  g.epi.ffn = (int)ffn;
+  const std::string err = tdx::gemm_tn(g, cur_stream());
+  TORCH_CHECK(err.empty(), "gemm_tn_silu_mul: ", err);
 }
 
 // The same product on 256 x 256 tiles computed by CTA pairs (tcgen05.mma.cta_group::2).
@@ -420,6 +500,11 @@ void register_extra_ops(torch::Library& m) {
   m.def("gemm_tn(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, int block_n, int splits, Tensor(b!)? ws, "
         "Tensor(c!)? counters, Tensor(d!)? status, Tensor? x_scale, Tensor? y_scale, bool x_scale_per_row, "
         "bool y_scale_per_row, bool x_static=False) -> ()", &gemm_tn);
+  m.def("gemm_tn_rope_kv(Tensor w, Tensor a, Tensor(a!) out, int block_n, int splits, Tensor(b!) ws, Tensor(c!) counters, "
+        "Tensor(d!)? status, Tensor? w_scale, Tensor? a_scale, Tensor positions, Tensor cos_sin, Tensor(e!) k_cache, "
+        "Tensor(f!) v_cache, int q_heads, int kv_heads) -> ()", &gemm_tn_rope_kv);
+  m.def("gemm_tn_silu_mul(Tensor w, Tensor a, Tensor(a!) out, int block_n, int splits, Tensor(b!) ws, Tensor(c!) counters, "
+        "Tensor(d!)? status) -> ()", &gemm_tn_silu_mul);
   m.def("gemm_tn_pair(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status, Tensor(c!)? ws=None, "
         "Tensor(d!)? counters=None) -> ()", &gemm_tn_pair);
   m.def("gemm_tn_persistent(Tensor x, Tensor y, Tensor(a!) out, int sx, int sy, Tensor(b!)? status) -> ()", &gemm_tn_persistent);

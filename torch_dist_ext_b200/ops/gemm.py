@@ -142,6 +142,56 @@ def linear_fp8_blockscaled(a_q: torch.Tensor, a_scale: torch.Tensor, w_q: torch.
     return out
 
 
+def fused_epilogue_fits(tokens: int, k: int, elem_size: int = 2, scaled: bool = False) -> bool:
+    """Whether ``linear_rope_kv`` / ``linear_silu_mul`` can take the problem: the weights must sit on the 128-row side of
+    the tile (decode-sized token counts; always for block-scaled operands) and K must span at least two 128-byte blocks
+    (the fused epilogues live in the split-K finalizer)."""
+    return plan(tokens, 256, k, elem_size, scaled)[0] and k // (128 // elem_size) >= 2
+
+
+@traced("tdx.linear_rope_kv")
+def linear_rope_kv(a: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, cos_sin_cache: torch.Tensor,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor, q_heads: int, kv_heads: int, *,
+                   a_scale: Optional[torch.Tensor] = None, w_scale: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused qkv projection of a decode step with the rotary embedding and the KV append in the GEMM's own epilogue:
+    ``qkv = a [T, K] @ w [(q_heads + 2 kv_heads) * 128, K]^T``, query and key heads rotated (rotate-half) by the angle of
+    ``positions[t]``, the rotated key row and the value row of token ``t`` written to ``k_cache`` / ``v_cache``
+    ``[B, S, kv_heads, 128]`` at ``[t, positions[t]]``. Returns the rotated ``[T, (q_heads + 2 kv_heads) * 128]`` bf16 rows.
+    One kernel where ``linear`` + ``rope_append_kv_`` are two. e4m3 operands take ``a_scale [T, K/128]`` and
+    ``w_scale [N/128, K/128]``."""
+    m, k = a.shape
+    n = w.shape[0]
+    scaled = w_scale is not None
+    assert n == (q_heads + 2 * kv_heads) * 128, "linear_rope_kv: w must hold (q_heads + 2 kv_heads) heads of 128 rows"
+    assert fused_epilogue_fits(m, k, a.element_size(), scaled), "linear_rope_kv: decode-sized token counts only"
+    _, bn, splits = plan(m, n, k, a.element_size(), scaled)
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16 if a.element_size() == 1 else a.dtype, device=a.device)
+    ws, counters, status = _workspace(a.device)
+    _lib.ops().gemm_tn_rope_kv(w, a, out, bn, max(2, splits), ws, counters, status,
+                               w_scale.contiguous() if scaled else None, a_scale.contiguous() if scaled else None,
+                               positions, cos_sin_cache, k_cache, v_cache, q_heads, kv_heads)
+    return out
+
+
+@traced("tdx.linear_silu_mul")
+def linear_silu_mul(a: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(a @ w_gate^T) * (a @ w_up^T)`` for ``w_gate_up [2 ffn, K]`` (gate rows, then up rows; bf16 / fp16; ffn a
+    multiple of 64) in ONE kernel: every tile of the GEMM is loaded as 64 gate rows plus the 64 up rows of the same
+    features, and the split-K finalizer applies the activation. Decode-sized token counts."""
+    m, k = a.shape
+    ffn = w_gate_up.shape[0] // 2
+    assert w_gate_up.shape[0] == 2 * ffn and ffn % 64 == 0, "linear_silu_mul: w must be [2 ffn, K] with ffn a multiple of 64"
+    assert a.element_size() == 2 and fused_epilogue_fits(m, k), "linear_silu_mul: 16-bit operands, decode-sized token counts"
+    _, bn, splits = plan(m, 2 * ffn, k, 2)
+    if out is None:
+        out = torch.empty(m, ffn, dtype=a.dtype, device=a.device)
+    ws, counters, status = _workspace(a.device)
+    _lib.ops().gemm_tn_silu_mul(w_gate_up, a, out, bn, max(2, splits), ws, counters, status)
+    return out
+
+
 def quantize_weight_block128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """e4m3 weights with one fp32 scale per 128x128 block (PyTorch; done once at load time)."""
     n, k = w.shape
