@@ -57,3 +57,32 @@ def test_tensor_core_attention_splits_follow_the_measured_costs():
     assert pick(16, 8, 2048) == 1
     assert pick(1, 1, 128) == 1
     assert pick(3, 2, 100000) > 8                                # long contexts still spread over the SMs
+
+
+def test_fused_decode_epilogues_need_the_weights_on_the_wide_side_and_a_split():
+    assert gemm.fused_epilogue_fits(1, 4096) and gemm.fused_epilogue_fits(128, 4096)
+    assert not gemm.fused_epilogue_fits(129, 4096)                 # the tokens take the 128-row side
+    assert gemm.fused_epilogue_fits(2048, 8192, 1, scaled=True)    # block-scaled operands always run weights-wide
+    assert not gemm.fused_epilogue_fits(16, 64)                    # one 128-byte K block: no split, no finalizer
+    assert gemm.fused_epilogue_fits(16, 128) and not gemm.fused_epilogue_fits(16, 128, 1, scaled=True)
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+def test_pair_finalizer_threads_cover_every_row_pair_and_column_once(bn):
+    """The finalizer's work split (gemm_tcgen05.cu: PairShape, pair_finalize): epilogue warp w has TMEM quarter
+    q = w % 4; row pair r = (q % 2) * 32 + lane, column half = q // 2, walked in steps of min(16, bn / 2) columns."""
+    half_cols = bn // 2
+    width = min(16, half_cols)
+    steps = half_cols // width
+    seen = {}
+    for warp in range(2, 6):
+        q = warp % 4
+        for lane in range(32):
+            r, half = (q % 2) * 32 + lane, q // 2
+            for s in range(steps):
+                for j in range(width):
+                    c = half * half_cols + s * width + j
+                    for row in (r, r + 64):
+                        assert (row, c) not in seen
+                        seen[(row, c)] = (warp, lane)
+    assert len(seen) == 128 * bn
