@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Single-GPU roofline table of the library's kernels (no communication).
 
-    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_one_tile|gemm_pair|gemm_persist|gemm_fp8|attention|attention_simt|attention_prefill_tc|elementwise|all] [--steps 30]
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_one_tile|gemm_pair|gemm_persist|gemm_fp8|attention|attention_simt|attention_prefill_tc|elementwise|decode_epilogues|all] [--steps 30]
 
 Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
 over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
@@ -211,6 +211,47 @@ def elementwise_cases(dev, steps, out):
         del ls
 
 
+def decode_epilogue_cases(dev, steps, out):
+    """The decode GEMMs whose split-K finalizer does the next kernel's work, against the two-kernel form (column
+    `library_us` here: this library's GEMM followed by its own RoPE + KV-append / SiLU kernel). Per-rank shapes of TP=8."""
+    from torch_dist_ext_b200.ops import activation, gemm, rope
+
+    hbm, tf, src = peaks()
+    seq = 2304
+    cos_sin = rope.build_cos_sin_cache(seq, 128, 5e5, dev)
+    for name, hidden, q_heads, kv_heads, ffn in [("8B/8", 4096, 4, 1, 1792), ("70B/8", 8192, 8, 1, 3584)]:
+        n_qkv = (q_heads + 2 * kv_heads) * 128
+        wq = rotating(lambda: torch.randn(n_qkv, hidden, device=dev, dtype=torch.bfloat16) * 0.02, n_qkv * hidden * 2)
+        wg = rotating(lambda: torch.randn(2 * ffn, hidden, device=dev, dtype=torch.bfloat16) * 0.02, 2 * ffn * hidden * 2)
+        for m in (1, 16, 64):
+            a = torch.randn(m, hidden, device=dev, dtype=torch.bfloat16)
+            positions = torch.randint(2048, seq, (m,), device=dev)
+            k_cache = torch.zeros(m, seq, kv_heads, 128, device=dev, dtype=torch.bfloat16)
+            v_cache = torch.zeros_like(k_cache)
+
+            def separate_qkv(i):
+                qkv = gemm.linear(a, wq[i])
+                q = qkv[:, : q_heads * 128].view(m, q_heads, 128)
+                k = qkv[:, q_heads * 128: (q_heads + kv_heads) * 128].view(m, kv_heads, 128)
+                v = qkv[:, (q_heads + kv_heads) * 128:].view(m, kv_heads, 128)
+                rope.rope_append_kv_(q, k, v, positions, cos_sin, k_cache, v_cache)
+
+            us = time_us(lambda i: gemm.linear_rope_kv(a, wq[i], positions, cos_sin, k_cache, v_cache, q_heads, kv_heads), len(wq), steps)
+            out.append(row(f"qkv + rope + KV append, one kernel ({name}) m={m}", us, time_us(separate_qkv, len(wq), steps),
+                           (n_qkv * hidden + m * hidden + m * n_qkv) * 2, 2.0 * m * n_qkv * hidden, hbm, tf, src))
+            print(out[-1], flush=True)
+
+            def separate_gate_up(i):
+                activation.silu_mul(gemm.linear(a, wg[i]))
+
+            us = time_us(lambda i: gemm.linear_silu_mul(a, wg[i]), len(wg), steps)
+            out.append(row(f"gate/up + silu*mul, one kernel ({name}) m={m}", us, time_us(separate_gate_up, len(wg), steps),
+                           (2 * ffn * hidden + m * hidden + m * ffn) * 2, 4.0 * m * ffn * hidden, hbm, tf, src))
+            print(out[-1], flush=True)
+        del wq, wg
+        torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--group", default="all")
@@ -245,6 +286,8 @@ def main():
         prefill_attention_cases(dev, max(5, args.steps // 3), out)
     if g in ("elementwise", "all"):
         elementwise_cases(dev, args.steps, out)
+    if g == "decode_epilogues":     # rotary + KV append / silu inside the GEMM's finalizer against the two-kernel form
+        decode_epilogue_cases(dev, args.steps, out)
     path = os.path.join(common.out_dir(), f"kernels_{g}.json")
     with open(path, "w") as f:
         json.dump(out, f, indent=1)
