@@ -258,6 +258,8 @@ void gemm_tn_rope_kv(const Tensor& w, const Tensor& a, Tensor out, int64_t block
                     c->size(3) == 128 && c->stride(3) == 1 && c->stride(2) == 128,
                 "gemm_tn_rope_kv: caches must be bfloat16 [batch >= tokens, seq, kv_heads, 128] with contiguous heads");
   TORCH_CHECK(k_cache.sizes() == v_cache.sizes() && k_cache.strides() == v_cache.strides(), "gemm_tn_rope_kv: the caches must agree in shape");
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&a, &out, &ws, &counters, &positions, &cos_sin, &k_cache, &v_cache})
+    TORCH_CHECK(t->device() == w.device(), "gemm_tn_rope_kv: every tensor must live on the weights' device");
   g.epi.kind = tdx::kEpiRopeKv;
   g.epi.q_heads = (int)q_heads;
   g.epi.kv_heads = (int)kv_heads;
@@ -287,6 +289,8 @@ void gemm_tn_silu_mul(const Tensor& w, const Tensor& a, Tensor out, int64_t bloc
   g.block_n = (int)block_n;
   g.splits = (int)splits;
   gemm_scratch(g, ws, counters, "gemm_tn_silu_mul");
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&a, &out, &ws, &counters})
+    TORCH_CHECK(t->device() == w.device(), "gemm_tn_silu_mul: every tensor must live on the weights' device");
   g.epi.kind = tdx::kEpiSiluMul;
   g.epi.ffn = (int)ffn;
   const std::string err = tdx::gemm_tn(g, cur_stream());
