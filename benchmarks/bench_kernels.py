@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Single-GPU roofline table of the library's kernels (no communication).
 
-    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_one_tile|gemm_pair|gemm_persist|gemm_fp8|attention|attention_simt|attention_prefill_tc|elementwise|decode_epilogues|all] [--steps 30]
+    python benchmarks/bench_kernels.py [--group gemm|gemm_prefill|gemm_one_tile|gemm_pair|gemm_persist|gemm_fp8|attention|attention_simt|attention_prefill_tc|elementwise|decode_epilogues|attention_splits|all] [--steps 30]
 
 Every case is timed as one region of back-to-back calls between two CUDA events; the calls rotate
 over enough copies of the large operand that no call finds it in the 126 MB L2. Each row reports
@@ -211,6 +211,29 @@ def elementwise_cases(dev, steps, out):
         del ls
 
 
+def attention_split_cases(dev, steps, out):
+    """Decode attention over the KV split count at 2048 positions (the data behind `ops/attention.py: pick_splits`)."""
+    from torch_dist_ext_b200.ops import attention
+
+    length = 2048
+    for (b, hq, hkv) in [(1, 4, 1), (16, 4, 1), (64, 4, 1), (64, 8, 1), (16, 32, 8)]:
+        per_set = 2 * b * length * hkv * 128 * 2
+        sets = [(torch.randn(b, length, hkv, 128, device=dev, dtype=torch.bfloat16),
+                 torch.randn(b, length, hkv, 128, device=dev, dtype=torch.bfloat16))
+                for _ in range(max(2, min(16, (300 << 20) // per_set)))]
+        q = torch.randn(b, hq, 128, device=dev, dtype=torch.bfloat16)
+        lens = torch.full((b,), length, device=dev, dtype=torch.int32)
+        res = {"case": f"decode attention {b} sequences x {hq} heads on {hkv} KV heads x {length}",
+               "picked": attention.pick_splits(b, hkv, length, ctas_per_sm=1)}
+        for ns in (None, 1, 2, 3, 4, 6, 8, 9, 12, 16):
+            us = time_us(lambda i: attention.decode_attention(q, sets[i][0], sets[i][1], lens, length, nsplit=ns), len(sets), steps)
+            res["auto_us" if ns is None else f"splits_{ns}_us"] = round(us, 2)
+        out.append(res)
+        print(res, flush=True)
+        del sets
+        torch.cuda.empty_cache()
+
+
 def decode_epilogue_cases(dev, steps, out):
     """The decode GEMMs whose split-K finalizer does the next kernel's work, against the two-kernel form (column
     `library_us` here: this library's GEMM followed by its own RoPE + KV-append / SiLU kernel). Per-rank shapes of TP=8."""
@@ -286,6 +309,8 @@ def main():
         prefill_attention_cases(dev, max(5, args.steps // 3), out)
     if g in ("elementwise", "all"):
         elementwise_cases(dev, args.steps, out)
+    if g == "attention_splits":     # decode attention over the KV split count
+        attention_split_cases(dev, args.steps, out)
     if g == "decode_epilogues":     # rotary + KV append / silu inside the GEMM's finalizer against the two-kernel form
         decode_epilogue_cases(dev, args.steps, out)
     path = os.path.join(common.out_dir(), f"kernels_{g}.json")
