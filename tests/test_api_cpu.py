@@ -172,3 +172,15 @@ def test_drop_in_module_keeps_the_reference_globals():
     ref_name.setup_env(0, 1)
     assert type(ref_name.comm).__name__ == "CommProcess" and ref_name.world_size_ == 1
     assert ref_name.allreduce_rms is tdx.allreduce_rms
+
+
+def test_cmake_project_lists_every_native_source():
+    """The ninja build globs the sources, the CMake project names them: a new file must be added there too, or the
+    CMake-built library fails to load with an undefined symbol."""
+    import pathlib
+
+    root = pathlib.Path(__file__).resolve().parent.parent
+    cmake = (root / "CMakeLists.txt").read_text()
+    csrc = root / "torch_dist_ext_b200" / "csrc"
+    missing = [p.name for p in sorted(csrc.glob("*.cu")) + sorted(csrc.glob("*.cpp")) if f"/{p.name}" not in cmake]
+    assert not missing, missing
