@@ -41,3 +41,23 @@ def test_other_ranks_leave_silently():
 def test_progress_keeps_the_arm_alive():
     r = run_child("for _ in range(8):\n    time.sleep(0.3)\n    bench._progress('step')", "0")
     assert r.returncode == 0 and "finished" in r.stdout and "unavailable" not in r.stdout
+
+
+def test_the_arm_declines_by_default_after_the_recorded_hang(monkeypatch):
+    """One run of the arm at 2 ranks never returned: by default the arm says so instead of launching that code again."""
+    import argparse
+
+    sys.path.insert(0, ROOT)
+    import bench
+    from benchmarks import common
+
+    monkeypatch.delenv("TDX_BENCH_REFERENCE_RUN", raising=False)
+    for world in (2, 4, 8):
+        monkeypatch.setattr(common, "init_dist", lambda gpus, w=world: (0, w, 0))
+        args = argparse.Namespace(gpus=world, steps=5, warmup=3, impl="reference", tokens=128, hidden=4096, no_extras=True,
+                                  no_pinned_io=True)
+        msg = bench.run(args)
+        assert msg["impl"] == "reference" and "hung" in msg["unavailable"] and "TDX_BENCH_REFERENCE_RUN" in msg["unavailable"]
+    monkeypatch.setattr(common, "init_dist", lambda gpus: (0, 1, 0))
+    args.gpus = 1
+    assert "2, 4 or 8 ranks" in bench.run(args)["unavailable"]
