@@ -159,7 +159,7 @@ def linear_rope_kv(a: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, co
     ``positions[t]``, the rotated key row and the value row of token ``t`` written to ``k_cache`` / ``v_cache``
     ``[B, S, kv_heads, 128]`` at ``[t, positions[t]]``. Returns the rotated ``[T, (q_heads + 2 kv_heads) * 128]`` bf16 rows.
     One kernel where ``linear`` + ``rope_append_kv_`` are two. e4m3 operands take ``a_scale [T, K/128]`` and
-    ``w_scale [N/128, K/128]``."""
+    ``w_scale [N/128, K/128]``. PyTorch statement: ``ops.reference.linear_rope_kv_reference``."""
     m, k = a.shape
     n = w.shape[0]
     scaled = w_scale is not None
@@ -179,7 +179,8 @@ def linear_rope_kv(a: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, co
 def linear_silu_mul(a: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``silu(a @ w_gate^T) * (a @ w_up^T)`` for ``w_gate_up [2 ffn, K]`` (gate rows, then up rows; bf16 / fp16; ffn a
     multiple of 64) in ONE kernel: every tile of the GEMM is loaded as 64 gate rows plus the 64 up rows of the same
-    features, and the split-K finalizer applies the activation. Decode-sized token counts."""
+    features, and the split-K finalizer applies the activation. Decode-sized token counts. PyTorch statement:
+    ``ops.reference.linear_silu_mul_reference``."""
     m, k = a.shape
     ffn = w_gate_up.shape[0] // 2
     assert w_gate_up.shape[0] == 2 * ffn and ffn % 64 == 0, "linear_silu_mul: w must be [2 ffn, K] with ffn a multiple of 64"

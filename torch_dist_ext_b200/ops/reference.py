@@ -113,3 +113,37 @@ def greedy_sample_sharded(logits: torch.Tensor, rank: int, world: int, index_bas
     allp = torch.stack(parts)                                                  # [world, tokens, 2]
     best = allp[..., 0].argmax(dim=0)
     return allp[best, torch.arange(logits.shape[0], device=logits.device), 1].long()
+
+
+def linear_rope_kv_reference(a: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, cos_sin_cache: torch.Tensor,
+                             k_cache: torch.Tensor, v_cache: torch.Tensor, q_heads: int, kv_heads: int) -> torch.Tensor:
+    """PyTorch statement of ``ops.gemm.linear_rope_kv`` in fp32: the fused qkv projection ``a @ w^T`` with query and key
+    heads rotated (rotate-half, head dimension 128) by the angle of ``positions[t]``; the rotated key row and the value row
+    of token ``t`` are written into ``k_cache`` / ``v_cache`` ``[B, S, kv_heads, 128]`` at ``[t, positions[t]]``. Returns
+    the rotated ``[T, (q_heads + 2 kv_heads) * 128]`` rows in fp32. (The reference library has no counterpart: its only
+    op is the fused all-reduce, src/ops/all_reduce_fusion.cpp:120-173.)"""
+    t = a.shape[0]
+    qkv = a.float() @ w.float().t()
+    q = qkv[:, : q_heads * 128].view(t, q_heads, 128)
+    k = qkv[:, q_heads * 128: (q_heads + kv_heads) * 128].view(t, kv_heads, 128)
+    v = qkv[:, (q_heads + kv_heads) * 128:].view(t, kv_heads, 128)
+    cs = cos_sin_cache[positions].float()
+    cos, sin = cs[:, None, :64], cs[:, None, 64:]
+
+    def rotate(x):
+        lo, hi = x[..., :64], x[..., 64:]
+        return torch.cat([lo * cos - hi * sin, hi * cos + lo * sin], dim=-1)
+
+    q, k = rotate(q), rotate(k)
+    rows = torch.arange(t, device=a.device)
+    k_cache[rows, positions] = k.to(k_cache.dtype)
+    v_cache[rows, positions] = v.to(v_cache.dtype)
+    return torch.cat([q.reshape(t, -1), k.reshape(t, -1), v.reshape(t, -1)], dim=1)
+
+
+def linear_silu_mul_reference(a: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """PyTorch statement of ``ops.gemm.linear_silu_mul`` in fp32: ``silu(a @ w_gate^T) * (a @ w_up^T)`` for
+    ``w_gate_up [2 ffn, K]`` with the gate rows first."""
+    ffn = w_gate_up.shape[0] // 2
+    gu = a.float() @ w_gate_up.float().t()
+    return torch.nn.functional.silu(gu[:, :ffn]) * gu[:, ffn:]
